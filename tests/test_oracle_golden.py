@@ -1,0 +1,81 @@
+"""The CPU oracle against fixtures produced by the reference's own PyTorch code
+(tests/golden/make_golden.py).  Runs without a GPU."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import loglinear_oracle as orc
+
+
+def load(golden_dir, name):
+    z = np.load(os.path.join(golden_dir, name))
+    return {k: (torch.from_numpy(z[k]) if z[k].ndim > 0 else z[k].item()) for k in z.files}
+
+
+def test_levels_closed_form_matches_reference_table(golden_dir):
+    z = np.load(os.path.join(golden_dir, "levels.npz"))
+    assert np.array_equal(orc.levels_matrix(256), z["levels256"])
+    for n, want in zip(z["lengths"], z["num_levels"]):
+        assert orc.get_num_levels(int(n)) == int(want)
+
+
+def test_levels_closed_form_matches_recursive_definition():
+    for t in range(1, 300):
+        for s in range(t):
+            assert orc.level_index(t, s) == orc.level_index_recursive(t, s)
+    assert orc.level_index(5, 5) == 0
+
+
+@pytest.mark.parametrize("name", ["mamba2_c1.npz", "mamba2_c64.npz"])
+def test_mamba2_forward_forms_match_reference(golden_dir, name):
+    d = load(golden_dir, name)
+    q, k, v, g, l = (d[x] for x in "qkvgl")
+    o_mat = orc.mamba2_materialized(q, k, v, g, l)
+    o_chk = orc.mamba2_chunkwise(q, k, v, g, l, chunk=int(d["chunk"]))
+    for ref in ("o_chunk", "o_recurrent", "o_materialized"):
+        assert torch.allclose(o_mat, d[ref], rtol=1e-4, atol=2e-6), ref
+        assert torch.allclose(o_chk, d[ref], rtol=1e-4, atol=2e-6), ref
+
+
+def test_mamba2_recurrence_matches_reference(golden_dir):
+    d = load(golden_dir, "mamba2_c1.npz")
+    q, k, v, g, l = (d[x] for x in "qkvgl")
+    o, st = orc.recurrent(q, k, v, g, l)
+    assert torch.allclose(o, d["o_recurrent"], rtol=1e-4, atol=2e-6)
+    assert st.counts == [int(c) for c in d["counts"]]
+
+
+@pytest.mark.parametrize("name", ["mamba2_c1.npz", "mamba2_c64.npz"])
+def test_mamba2_gradients_match_reference_autograd(golden_dir, name):
+    d = load(golden_dir, name)
+    q, k, v, g, l = (d[x] for x in "qkvgl")
+    _, grads = orc.mamba2_grads(q, k, v, g, l, d["do"])
+    for got, key in zip(grads, ("dq", "dk", "dv", "dg", "dl")):
+        want = d[key].double()
+        assert torch.allclose(got, want, rtol=1e-3, atol=1e-5 * max(1.0, want.abs().max().item())), key
+
+
+@pytest.mark.parametrize("name", ["gdn_c1.npz", "gdn_c64.npz"])
+def test_gdn_recurrence_and_gradients_match_reference(golden_dir, name):
+    d = load(golden_dir, name)
+    q, k, v, b, g, l = (d[x] for x in "qkvbgl")
+    scale = float(d["scale"])
+    o, grads = orc.gdn_grads(q, k, v, b, g, l / scale, d["do"], scale)
+    # d l: the fixture differentiates w.r.t. the unscaled lambda
+    grads = list(grads)
+    grads[5] = grads[5] / scale
+    assert torch.allclose(o.float(), d["o_chunk"], rtol=1e-4, atol=5e-6)
+    assert torch.allclose(o.float(), d["o_recurrent"], rtol=1e-4, atol=5e-6)
+    for got, key in zip(grads, ("dq", "dk", "dv", "db", "dg", "dl")):
+        want = d[key].double()
+        assert torch.allclose(got, want, rtol=2e-3, atol=2e-5 * max(1.0, want.abs().max().item())), key
+
+
+def test_gdn_materialized_matches_recurrence():
+    q, k, v, b, g, l = orc.make_gdn_inputs(1, 48, 2, 8, 8, 7, seed=3, dtype=torch.float64)
+    qn, kn = orc.gdn_layer_inputs(q, k, 8 ** -0.5)
+    o1 = orc.gdn_materialized(qn, kn, v, b, g.double(), l)
+    o2, _ = orc.recurrent(qn, kn, v, g.double(), l, b=b)
+    assert torch.allclose(o1, o2, rtol=1e-9, atol=1e-11)
