@@ -1,0 +1,133 @@
+// extern "C" entry points of libllattn.so: argument checks, workspace carving, launches.
+#include <stdint.h>
+
+#include "llattn_mamba2.h"
+
+namespace {
+
+inline size_t align_up(size_t x) { return (x + 255) & ~(size_t)255; }
+
+struct Carver {
+    unsigned char* base;
+    size_t off;
+    explicit Carver(void* p) : base(reinterpret_cast<unsigned char*>(p)), off(0) {}
+    template <typename T>
+    T* take(size_t count) {
+        T* r = base ? reinterpret_cast<T*>(base + off) : nullptr;
+        off += align_up(count * sizeof(T));
+        return r;
+    }
+};
+
+int ceil_log2i(int x) {
+    int l = 0;
+    while ((1 << l) < x) ++l;
+    return l;
+}
+
+int check_shape(int B, int T, int H, int G, int K, int V, int L) {
+    if (B <= 0 || T <= 0 || H <= 0 || G <= 0) return LLATTN_ERR_UNSUPPORTED_SHAPE;
+    if (T % llattn_chunk() != 0) return LLATTN_ERR_BAD_LENGTH;
+    if (H % G != 0) return LLATTN_ERR_BAD_GROUPS;
+    if (!((K == 64 || K == 128) && V == 64)) return LLATTN_ERR_UNSUPPORTED_SHAPE;
+    if (L > 32) return LLATTN_ERR_UNSUPPORTED_SHAPE;
+    if (L < 7 + ceil_log2i(T / 64)) return LLATTN_ERR_TOO_FEW_LEVELS;
+    return 0;
+}
+
+// fills the size-dependent fields and carves the scratch buffers (base may be NULL to size only)
+size_t setup(llattn::Mamba2Params& p, void* ws, bool backward) {
+    const int SEG = 1 << llattn::M2_MLOW;
+    p.NT = p.T / 64;
+    p.NS = (p.NT + SEG - 1) / SEG;
+    p.LH = ceil_log2i(p.NS);
+    p.o_has_high = p.NS > 1;
+    const size_t KV = (size_t)p.K * p.V, BH = (size_t)p.B * p.H;
+    Carver c(ws);
+    if (p.NS > 1) {
+        p.seg_F = c.take<float>(BH * p.NS * KV);
+        p.seg_D = c.take<float>(BH * p.NS);
+        p.seg_H0 = c.take<__nv_bfloat16>(BH * p.NS * p.LH * KV);
+    }
+    if (backward) {
+        p.g = c.take<float>((size_t)p.B * p.T * p.H);
+        p.dq_acc = c.take<float>((size_t)p.B * p.T * p.G * p.K);
+        p.dk_acc = c.take<float>((size_t)p.B * p.T * p.G * p.K);
+        p.wq = c.take<float>((size_t)p.B * p.T * p.H);
+        if (p.NS > 1) {
+            p.seg_dF = c.take<float>(BH * p.NS * p.LH * KV);
+            p.seg_dHf = c.take<float>(BH * p.NS * KV);
+        }
+    }
+    return c.off;
+}
+
+}  // namespace
+
+extern "C" {
+
+int llattn_version(void) { return 1; }
+int llattn_chunk(void) { return 64; }
+
+size_t llattn_mamba2_fwd_workspace_bytes(int B, int T, int H, int G, int K, int V, int L) {
+    if (check_shape(B, T, H, G, K, V, L) != 0) return 0;
+    llattn::Mamba2Params p = {};
+    p.B = B; p.T = T; p.H = H; p.G = G; p.K = K; p.V = V; p.L = L;
+    return setup(p, nullptr, false);
+}
+
+int llattn_mamba2_fwd(const void* q, const void* k, const void* v, const float* g, const void* lambda,
+                      void* o, float* g_cum, void* workspace, size_t workspace_bytes,
+                      int B, int T, int H, int G, int K, int V, int L, void* stream) {
+    int rc = check_shape(B, T, H, G, K, V, L);
+    if (rc != 0) return rc;
+    if (!q || !k || !v || !g || !lambda || !o || !g_cum) return LLATTN_ERR_NULL;
+    llattn::Mamba2Params p = {};
+    p.B = B; p.T = T; p.H = H; p.G = G; p.K = K; p.V = V; p.L = L;
+    const size_t need = setup(p, nullptr, false);
+    if (need > 0 && (!workspace || workspace_bytes < need || ((uintptr_t)workspace & 255))) return LLATTN_ERR_WORKSPACE;
+    setup(p, workspace, false);
+    p.q = (const __nv_bfloat16*)q; p.k = (const __nv_bfloat16*)k; p.v = (const __nv_bfloat16*)v;
+    p.g = g; p.l = (const __nv_bfloat16*)lambda;
+    p.o = (__nv_bfloat16*)o; p.g_cum = g_cum;
+    return llattn::mamba2_fwd_dispatch(p, (cudaStream_t)stream);
+}
+
+size_t llattn_mamba2_bwd_workspace_bytes(int B, int T, int H, int G, int K, int V, int L) {
+    if (check_shape(B, T, H, G, K, V, L) != 0) return 0;
+    llattn::Mamba2Params p = {};
+    p.B = B; p.T = T; p.H = H; p.G = G; p.K = K; p.V = V; p.L = L;
+    return setup(p, nullptr, true);
+}
+
+int llattn_mamba2_bwd(const void* q, const void* k, const void* v, const float* g_cum, const void* lambda,
+                      const void* d_o, void* dq, void* dk, void* dv, float* dg, float* dlambda,
+                      void* workspace, size_t workspace_bytes,
+                      int B, int T, int H, int G, int K, int V, int L, void* stream) {
+    int rc = check_shape(B, T, H, G, K, V, L);
+    if (rc != 0) return rc;
+    if (!q || !k || !v || !g_cum || !lambda || !d_o || !dq || !dk || !dv || !dg || !dlambda) return LLATTN_ERR_NULL;
+    llattn::Mamba2Params p = {};
+    p.B = B; p.T = T; p.H = H; p.G = G; p.K = K; p.V = V; p.L = L;
+    const size_t need = setup(p, nullptr, true);
+    if (!workspace || workspace_bytes < need || ((uintptr_t)workspace & 255)) return LLATTN_ERR_WORKSPACE;
+    setup(p, workspace, true);
+    cudaStream_t st = (cudaStream_t)stream;
+    p.q = (const __nv_bfloat16*)q; p.k = (const __nv_bfloat16*)k; p.v = (const __nv_bfloat16*)v;
+    p.l = (const __nv_bfloat16*)lambda; p.d_o = (const __nv_bfloat16*)d_o;
+    p.dv = (__nv_bfloat16*)dv; p.dl = dlambda;
+    const size_t nqk = (size_t)B * T * G * K, nbth = (size_t)B * T * H;
+    cudaError_t e;
+    // dq_acc, dk_acc and wq are adjacent in the workspace: one clear covers the three
+    if ((e = cudaMemsetAsync(p.dq_acc, 0, (size_t)((unsigned char*)p.wq - (unsigned char*)p.dq_acc) + nbth * sizeof(float), st)) != cudaSuccess) return (int)e;
+    if ((e = cudaMemsetAsync(dlambda, 0, nbth * L * sizeof(float), st)) != cudaSuccess) return (int)e;
+    llattn::mamba2_uncumsum(g_cum, const_cast<float*>(p.g), (long)B * T, H, st);
+    rc = llattn::mamba2_bwd_dispatch(p, st);
+    if (rc != 0) return rc;
+    llattn::mamba2_dg(p.wq, dg, B, T, H, st);
+    llattn::cast_f32_to_bf16(p.dq_acc, dq, (long)nqk, st);
+    llattn::cast_f32_to_bf16(p.dk_acc, dk, (long)nqk, st);
+    return (int)cudaGetLastError();
+}
+
+}  // extern "C"

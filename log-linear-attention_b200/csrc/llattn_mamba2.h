@@ -1,0 +1,47 @@
+// Internal launch parameters shared by the log-linear Mamba-2 kernels.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include "../../include/llattn.h"
+
+namespace llattn {
+
+constexpr int M2_MLOW = 3;   // a segment is 2^M2_MLOW chunks (512 tokens)
+
+struct Mamba2Params {
+    // inputs
+    const __nv_bfloat16* q;      // (B,T,G,K)
+    const __nv_bfloat16* k;      // (B,T,G,K)
+    const __nv_bfloat16* v;      // (B,T,H,V)
+    const float* g;              // (B,T,H) raw log decay
+    const __nv_bfloat16* l;      // (B,T,H,L)
+    const __nv_bfloat16* d_o;    // (B,T,H,V) upstream gradient (backward only)
+    // outputs
+    __nv_bfloat16* o;            // (B,T,H,V)
+    float* g_cum;                // (B,T,H) in-chunk inclusive cumsum of g
+    float* dq_acc;               // (B,T,G,K) fp32 accumulators (backward)
+    float* dk_acc;               // (B,T,G,K)
+    __nv_bfloat16* dv;           // (B,T,H,V)
+    float* dl;                   // (B,T,H,L)
+    float* wq;                   // (B,T,H)  accumulates q.dq - k.dk per token and head (backward)
+    // segment-level scratch
+    float* seg_F;                // (B,H,NS,K,V)
+    float* seg_D;                // (B,H,NS)
+    __nv_bfloat16* seg_H0;       // (B,H,NS,LH,K,V)
+    float* seg_dF;               // (B,H,NS,LH,K,V) reader summaries (backward)
+    float* seg_dHf;              // (B,H,NS,K,V) gradient w.r.t. the segment summaries (backward)
+    int B, T, H, G, K, V, L;
+    int NT, NS, LH;
+    int o_has_high;
+};
+
+int mamba2_fwd_dispatch(Mamba2Params p, cudaStream_t stream);
+int mamba2_bwd_dispatch(Mamba2Params p, cudaStream_t stream);
+// segment summaries and the per-level scan over segments only (needs NS > 1)
+int mamba2_fwd_states_dispatch(Mamba2Params p, cudaStream_t stream);
+void mamba2_uncumsum(const float* gc, float* g, long BT, int H, cudaStream_t stream);
+void mamba2_dg(const float* w, float* dg, int B, int T, int H, cudaStream_t stream);
+void cast_f32_to_bf16(const float* src, void* dst, long n, cudaStream_t stream);
+
+}  // namespace llattn

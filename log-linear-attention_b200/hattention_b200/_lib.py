@@ -1,0 +1,51 @@
+"""ctypes binding of libllattn.so (declared in include/llattn.h)."""
+import ctypes
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB_PATH = os.path.join(_HERE, "libllattn.so")
+_lib = None
+
+ERRORS = {
+    -1: "unsupported shape (K must be 64 or 128, V must be 64, L <= 32)",
+    -2: "sequence length is not a multiple of the 64-token chunk",
+    -3: "too few lambda levels for this sequence length",
+    -4: "number of heads is not a multiple of the number of q/k groups",
+    -5: "workspace missing, misaligned or too small",
+    -6: "null pointer",
+}
+
+_SHAPE = [ctypes.c_int] * 7
+_P = ctypes.c_void_p
+
+
+def lib():
+    """Load the shared library once.  Raises if it has not been built: there is no fallback."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(_LIB_PATH):
+        raise RuntimeError(
+            f"{_LIB_PATH} not found: build it with `make -C log-linear-attention_b200/csrc` "
+            "(or __graft_entry__.build()); this package has no CPU or Triton fallback")
+    L = ctypes.CDLL(_LIB_PATH)
+    L.llattn_version.restype = ctypes.c_int
+    L.llattn_chunk.restype = ctypes.c_int
+    L.llattn_mamba2_fwd_workspace_bytes.restype = ctypes.c_size_t
+    L.llattn_mamba2_fwd_workspace_bytes.argtypes = _SHAPE
+    L.llattn_mamba2_bwd_workspace_bytes.restype = ctypes.c_size_t
+    L.llattn_mamba2_bwd_workspace_bytes.argtypes = _SHAPE
+    L.llattn_mamba2_fwd.restype = ctypes.c_int
+    L.llattn_mamba2_fwd.argtypes = [_P] * 7 + [_P, ctypes.c_size_t] + _SHAPE + [_P]
+    L.llattn_mamba2_bwd.restype = ctypes.c_int
+    L.llattn_mamba2_bwd.argtypes = [_P] * 11 + [_P, ctypes.c_size_t] + _SHAPE + [_P]
+    _lib = L
+    return L
+
+
+def check(rc: int, what: str):
+    if rc == 0:
+        return
+    if rc < 0:
+        raise ValueError(f"{what}: {ERRORS.get(rc, rc)}")
+    raise RuntimeError(f"{what}: CUDA error {rc}")

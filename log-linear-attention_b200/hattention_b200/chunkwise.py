@@ -1,0 +1,120 @@
+"""Host drivers of the log-linear Mamba-2 chunkwise path, with the signatures of the
+reference's `hattention/chunkwise.py` (`chunkwise_fwd` :1118-1129, `chunkwise_bwd` :1286-1299).
+
+The work is done by libllattn.so; these functions validate arguments the way the reference
+does, allocate outputs and scratch with torch, and launch on the current CUDA stream.
+"""
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+from .base import HType, ceil_log, get_num_levels
+
+CHUNK = 64
+
+
+def _check(q, k, v, g, l, head_first, level_base, htype, chunk_size):
+    if head_first:
+        raise NotImplementedError("head_first=True is not supported")
+    if level_base != 2:
+        raise NotImplementedError("level_base must be 2")
+    if htype != HType.WEAK:
+        raise NotImplementedError("only HType.WEAK is supported")
+    if chunk_size != CHUNK:
+        raise NotImplementedError("chunk_size must be 64")
+    if not (q.is_cuda and k.is_cuda and v.is_cuda and g.is_cuda and l.is_cuda):
+        raise RuntimeError("log-linear attention kernels need CUDA tensors (there is no CPU path)")
+    B, T, G, K = k.shape
+    _, _, H, V = v.shape
+    L = l.shape[-1]
+    if q.shape != k.shape or v.shape[:2] != (B, T) or g.shape != (B, T, H) or l.shape[:3] != (B, T, H):
+        raise ValueError("inconsistent shapes")
+    if H % G != 0:
+        raise ValueError(f"H={H} is not a multiple of G={G}")
+    if T % CHUNK != 0:
+        raise ValueError(f"T={T} and BT={CHUNK}")
+    for opt in (32, 64):
+        if K % opt != 0:
+            raise ValueError(f"K={K} and BK could be {opt}")
+        if V % opt != 0:
+            raise ValueError(f"V={V} and BV could be {opt}")
+    if get_num_levels(CHUNK, 2) + ceil_log(T // CHUNK, 2) > L:
+        raise ValueError("not enough lambda levels for this length")
+    return B, T, H, G, K, V, L
+
+
+def _as(x, dtype):
+    return x.to(dtype).contiguous()
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _workspace(nbytes, device):
+    return torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=device)
+
+
+def chunkwise_fwd(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    g: torch.Tensor,
+    l: torch.Tensor,
+    head_first: bool,
+    level_base: int,
+    htype: HType,
+    chunk_size: int,
+    output_final_state: bool,
+) -> Tuple[torch.Tensor, torch.Tensor, Optional[torch.Tensor]]:
+    """Returns (o, in-chunk cumulative g, None) like the reference driver
+    (chunkwise.py:1118-1275)."""
+    if output_final_state:
+        raise NotImplementedError("output_final_state=True (prefill hand-off) is not implemented")
+    B, T, H, G, K, V, L = _check(q, k, v, g, l, head_first, level_base, htype, chunk_size)
+    lib = _lib.lib()
+    with torch.cuda.device(q.device):
+        q_, k_, v_, l_ = (_as(x, torch.bfloat16) for x in (q, k, v, l))
+        g_ = _as(g, torch.float32)
+        o = torch.empty_like(v_)
+        g_cum = torch.empty_like(g_)
+        ws = _workspace(lib.llattn_mamba2_fwd_workspace_bytes(B, T, H, G, K, V, L), q.device)
+        rc = lib.llattn_mamba2_fwd(q_.data_ptr(), k_.data_ptr(), v_.data_ptr(), g_.data_ptr(), l_.data_ptr(),
+                                   o.data_ptr(), g_cum.data_ptr(), ws.data_ptr(), ws.numel(),
+                                   B, T, H, G, K, V, L, _stream())
+        _lib.check(rc, "llattn_mamba2_fwd")
+    return o, g_cum, None
+
+
+def chunkwise_bwd(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    g: torch.Tensor,
+    l: torch.Tensor,
+    do: torch.Tensor,
+    head_first: bool,
+    level_base: int,
+    htype: HType,
+    chunk_size: int,
+):
+    """`g` is the in-chunk cumulative sum returned by chunkwise_fwd (what the reference's
+    autograd function saves, kernel.py:86,125).  Returns (dq, dk, dv, dg, dl) with dq, dk summed
+    over the heads of each group and dg taken w.r.t. the raw g (chunkwise.py:1583-1597)."""
+    B, T, H, G, K, V, L = _check(q, k, v, g, l, head_first, level_base, htype, chunk_size)
+    lib = _lib.lib()
+    with torch.cuda.device(q.device):
+        q_, k_, v_, l_, do_ = (_as(x, torch.bfloat16) for x in (q, k, v, l, do))
+        g_ = _as(g, torch.float32)
+        dq = torch.empty_like(q_)
+        dk = torch.empty_like(k_)
+        dv = torch.empty_like(v_)
+        dg = torch.empty_like(g_)
+        dl = torch.empty(l_.shape, dtype=torch.float32, device=l_.device)
+        ws = _workspace(lib.llattn_mamba2_bwd_workspace_bytes(B, T, H, G, K, V, L), q.device)
+        rc = lib.llattn_mamba2_bwd(q_.data_ptr(), k_.data_ptr(), v_.data_ptr(), g_.data_ptr(), l_.data_ptr(),
+                                   do_.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), dg.data_ptr(),
+                                   dl.data_ptr(), ws.data_ptr(), ws.numel(), B, T, H, G, K, V, L, _stream())
+        _lib.check(rc, "llattn_mamba2_bwd")
+    return dq, dk, dv, dg, dl

@@ -1,0 +1,123 @@
+"""Parity of the CUDA log-linear Mamba-2 path (through the Python boundary and the C ABI)
+against the CPU oracle and the reference-generated golden fixtures.
+
+Tolerance (bf16 inputs, fp32 accumulation): |got - want| <= 2e-2 * |want| + 2e-3 * max(1, max|want|).
+"""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import loglinear_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+RTOL, ATOL = 2e-2, 2e-3
+
+
+def assert_close(got, want, name):
+    got = got.detach().double().cpu()
+    want = want.detach().double().cpu()
+    assert got.shape == want.shape, (name, got.shape, want.shape)
+    assert torch.isfinite(got).all(), name
+    tol = RTOL * want.abs() + ATOL * max(1.0, want.abs().max().item())
+    err = (got - want).abs()
+    worst = (err / tol).max().item()
+    assert worst <= 1.0, f"{name}: worst err/tol = {worst:.3f}, max abs err {err.max().item():.3e}, max|want| {want.abs().max().item():.3e}"
+
+
+def run_cuda(q, k, v, g, l, do):
+    from hattention_b200 import HStruct, HType, hattention_kernel
+    dev = torch.device("cuda:0")
+    ins = [x.to(dev).requires_grad_(True) for x in (q.bfloat16(), k.bfloat16(), v.bfloat16(), g.float(), l.bfloat16())]
+    o = hattention_kernel(ins[0], ins[1], ins[2], None, ins[3], ins[4], None, False, 2, HType.WEAK, HStruct.MAMBA2)
+    grads = torch.autograd.grad((o.float() * do.to(dev).float()).sum(), ins)
+    torch.cuda.synchronize()
+    return o, grads
+
+
+def rounded_inputs(B, T, H, P, N, G, L, seed):
+    q, k, v, g, l = orc.make_mamba2_inputs(B, T, H, P, N, G, L, seed=seed)
+    q, k, v, l = (x.bfloat16().float() for x in (q, k, v, l))
+    do = torch.randn(B, T, H, P, generator=torch.Generator().manual_seed(seed + 100)).bfloat16().float()
+    return q, k, v, g, l, do
+
+
+def test_golden_fixture_from_reference(golden_dir):
+    z = np.load(os.path.join(golden_dir, "mamba2_c64.npz"))
+    d = {k: torch.from_numpy(z[k]) for k in z.files if z[k].ndim > 0}
+    o, grads = run_cuda(d["q"], d["k"], d["v"], d["g"], d["l"], d["do"])
+    assert_close(o, d["o_chunk"], "o")
+    assert_close(o, d["o_recurrent"], "o vs recurrent")
+    for got, key in zip(grads, ("dq", "dk", "dv", "dg", "dl")):
+        assert_close(got, d[key], key)
+
+
+@pytest.mark.parametrize("B,T,H,P,N,G,L", [
+    (1, 64, 2, 64, 128, 1, 7),        # a single chunk
+    (1, 128, 2, 64, 128, 1, 8),       # two chunks, one low level
+    (2, 512, 4, 64, 128, 1, 10),      # exactly one segment
+    (1, 1024, 4, 64, 128, 1, 12),     # two segments: one high level
+    (1, 704, 2, 64, 128, 2, 11),      # 11 chunks: ragged last segment, two q/k groups
+    (1, 4096, 2, 64, 128, 1, 13),     # eight segments: three high levels
+    (1, 2048, 2, 64, 64, 2, 15),      # K = 64, spare lambda levels
+])
+def test_forward_and_backward_match_oracle(B, T, H, P, N, G, L):
+    q, k, v, g, l, do = rounded_inputs(B, T, H, P, N, G, L, seed=T + H)
+    o, grads = run_cuda(q, k, v, g, l, do)
+    o_ref, g_ref = orc.mamba2_grads(q, k, v, g, l, do, fn=lambda *a: orc.mamba2_chunkwise(*a, chunk=64))
+    assert_close(o, o_ref, "o")
+    for got, want, key in zip(grads, g_ref, ("dq", "dk", "dv", "dg", "dl")):
+        assert_close(got, want, key)
+
+
+def test_forward_returns_in_chunk_cumsum():
+    from hattention_b200.base import HType
+    from hattention_b200.chunkwise import chunkwise_fwd
+    q, k, v, g, l, _ = rounded_inputs(1, 1024, 2, 64, 128, 1, 11, seed=5)
+    dev = torch.device("cuda:0")
+    o, g_cum, ht = chunkwise_fwd(q.bfloat16().to(dev), k.bfloat16().to(dev), v.bfloat16().to(dev), g.to(dev),
+                                 l.bfloat16().to(dev), False, 2, HType.WEAK, 64, False)
+    want = torch.cumsum(g.reshape(1, 16, 64, 2), dim=2).reshape(1, 1024, 2)
+    assert ht is None
+    assert torch.allclose(g_cum.cpu(), want, rtol=1e-5, atol=1e-6)
+
+
+def test_layer_api_matches_oracle():
+    """hmamba_chunk_scan_combined: softplus(dt), x*dt, A*dt, lambda=softplus(L*dl), +D*x."""
+    from hattention_b200.base import HStruct, HType
+    from hattention_b200.mamba_apis import hmamba_chunk_scan_combined
+    torch.manual_seed(0)
+    B, T, H, P, N, L = 1, 1024, 2, 64, 128, 12
+    dev = torch.device("cuda:0")
+    x = torch.randn(B, T, H, P).bfloat16()
+    dt = torch.randn(B, T, H) - 2
+    A = -torch.exp(torch.rand(H) * 2.7)
+    Bm = (torch.randn(B, T, 1, N) / N ** 0.5).bfloat16()
+    Cm = (torch.randn(B, T, 1, N) / N ** 0.5).bfloat16()
+    dl = torch.randn(B, T, H, L).bfloat16()
+    Lp = torch.ones(H, L).bfloat16()
+    D = torch.randn(H)
+    y, st = hmamba_chunk_scan_combined(
+        x.to(dev), dt.to(dev), A.to(dev), Bm.to(dev), Cm.to(dev), dl.to(dev), Lp.to(dev), 64, D=D.to(dev),
+        dt_softplus=True, lambda_mode="positive", lambda_level_max=L, lambda_level_base=2,
+        lambda_htype=HType.WEAK, lambda_hstruct=HStruct.MAMBA2, lambda_level_fixed=True)
+    assert st is None
+    dts = torch.nn.functional.softplus(dt)
+    v = (x.float() * dts[..., None]).bfloat16().float()
+    lam = torch.nn.functional.softplus(Lp.float()[None, None] * dl.float()).bfloat16().float()
+    want = orc.mamba2_chunkwise(Cm.double(), Bm.double(), v.double(), (A[None, None] * dts).double(), lam.double())
+    want = want + x.double() * D[None, None, :, None].double()
+    assert_close(y, want, "y")
+
+
+def test_batch_head_independence():
+    """Results for one (batch, head) do not depend on what else is in the launch: the property
+    the batch x head sharding across GPUs relies on."""
+    q, k, v, g, l, do = rounded_inputs(2, 1024, 4, 64, 128, 1, 11, seed=9)
+    o_full, gr_full = run_cuda(q, k, v, g, l, do)
+    o_part, gr_part = run_cuda(q[1:], k[1:], v[1:, :, 2:], g[1:, :, 2:], l[1:, :, 2:], do[1:, :, 2:])
+    assert torch.equal(o_full[1:, :, 2:], o_part)
+    assert torch.equal(gr_full[2][1:, :, 2:], gr_part[2])          # dv
+    assert torch.equal(gr_full[4][1:, :, 2:], gr_part[4])          # dl
