@@ -42,6 +42,7 @@ size_t setup(llattn::Mamba2Params& p, void* ws, bool backward) {
     p.NS = (p.NT + SEG - 1) / SEG;
     p.LH = ceil_log2i(p.NS);
     p.o_has_high = p.NS > 1;
+    p.LZ = llattn::M2_MLOW + p.LH;
     const size_t KV = (size_t)p.K * p.V, BH = (size_t)p.B * p.H;
     Carver c(ws);
     if (p.NS > 1) {
@@ -54,6 +55,9 @@ size_t setup(llattn::Mamba2Params& p, void* ws, bool backward) {
         p.dq_acc = c.take<float>((size_t)p.B * p.T * p.G * p.K);
         p.dk_acc = c.take<float>((size_t)p.B * p.T * p.G * p.K);
         p.wq = c.take<float>((size_t)p.B * p.T * p.H);
+        p.Yseg = c.take<float>(BH * p.NS * (p.LH > 0 ? p.LH : 1));
+        p.Zc = c.take<float>(BH * p.NT * p.LZ);
+        p.Yc = c.take<float>(BH * p.NT * (llattn::M2_MLOW + 1));
         if (p.NS > 1) {
             p.seg_dF = c.take<float>(BH * p.NS * p.LH * KV);
             p.seg_dHf = c.take<float>(BH * p.NS * KV);
@@ -118,13 +122,13 @@ int llattn_mamba2_bwd(const void* q, const void* k, const void* v, const float* 
     p.dv = (__nv_bfloat16*)dv; p.dl = dlambda;
     const size_t nqk = (size_t)B * T * G * K, nbth = (size_t)B * T * H;
     cudaError_t e;
-    // dq_acc, dk_acc and wq are adjacent in the workspace: one clear covers the three
-    if ((e = cudaMemsetAsync(p.dq_acc, 0, (size_t)((unsigned char*)p.wq - (unsigned char*)p.dq_acc) + nbth * sizeof(float), st)) != cudaSuccess) return (int)e;
+    // dq_acc, dk_acc, wq and Yseg are adjacent in the workspace: one clear covers the four
+    if ((e = cudaMemsetAsync(p.dq_acc, 0, (size_t)((unsigned char*)p.Zc - (unsigned char*)p.dq_acc), st)) != cudaSuccess) return (int)e;
     if ((e = cudaMemsetAsync(dlambda, 0, nbth * L * sizeof(float), st)) != cudaSuccess) return (int)e;
     llattn::mamba2_uncumsum(g_cum, const_cast<float*>(p.g), (long)B * T, H, st);
     rc = llattn::mamba2_bwd_dispatch(p, st);
     if (rc != 0) return rc;
-    llattn::mamba2_dg(p.wq, dg, B, T, H, st);
+    llattn::mamba2_dg(p, dg, st);
     llattn::cast_f32_to_bf16(p.dq_acc, dq, (long)nqk, st);
     llattn::cast_f32_to_bf16(p.dk_acc, dk, (long)nqk, st);
     return (int)cudaGetLastError();

@@ -31,6 +31,11 @@ struct Mamba2Params {
     __nv_bfloat16* seg_H0;       // (B,H,NS,LH,K,V)
     float* seg_dF;               // (B,H,NS,LH,K,V) reader summaries (backward)
     float* seg_dHf;              // (B,H,NS,K,V) gradient w.r.t. the segment summaries (backward)
+    // per-chunk scalars from which the decay gradient across chunk boundaries is assembled
+    float* Zc;                   // (B,H,NT,LZ)      reader side: sum_t lambda * dlambda per level
+    float* Yc;                   // (B,H,NT,MLOW+1)  contributor side: <KV_c, adjoint state> per low level, + combined high
+    float* Yseg;                 // (B,H,NS,LH)      contributor side per segment and high level
+    int LZ;                      // MLOW + LH
     int B, T, H, G, K, V, L;
     int NT, NS, LH;
     int o_has_high;
@@ -41,7 +46,7 @@ int mamba2_bwd_dispatch(Mamba2Params p, cudaStream_t stream);
 // segment summaries and the per-level scan over segments only (needs NS > 1)
 int mamba2_fwd_states_dispatch(Mamba2Params p, cudaStream_t stream);
 void mamba2_uncumsum(const float* gc, float* g, long BT, int H, cudaStream_t stream);
-void mamba2_dg(const float* w, float* dg, int B, int T, int H, cudaStream_t stream);
+void mamba2_dg(const Mamba2Params& p, float* dg, cudaStream_t stream);
 void cast_f32_to_bf16(const float* src, void* dst, long n, cudaStream_t stream);
 
 }  // namespace llattn

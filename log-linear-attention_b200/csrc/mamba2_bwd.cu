@@ -13,9 +13,10 @@
 //       part of dk.
 //   m2_hi_bwd_q_kernel / m2_seg_dstate_kernel / m2_seg_dscan_kernel : the high levels at
 //       segment granularity (dq, dlambda of readers; adjoint of the segment summaries).
-//   m2_dg_kernel : dg[r] = sum_{t>=r} (q_t.dq_t - k_t.dk_t) per head, which equals the
-//       reference's dG bookkeeping (chunkwise.py:793-874, 938, 1596) because o depends on g only
-//       through exp(sum_{s<r<=t} g_r) for pairs s < t.
+//   m2_dg_kernel : dg = reverse in-chunk cumsum of (q_t.dq_t - k_t.dk_t) plus, per chunk, the
+//       gradient carried across the chunk's end, assembled from per-chunk / per-level scalar
+//       totals written by the kernels above (the reference's dG bookkeeping,
+//       chunkwise.py:793-874, 938, 1596, without materialising h and dh).
 // dq / dk are accumulated over the heads of a group in fp32 with red.global.add and converted to
 // bf16 at the end (the reference writes per-head bf16 tensors and sums them on the host,
 // chunkwise.py:1583-1591).
@@ -335,6 +336,19 @@ __global__ void __launch_bounds__(256, 1) m2_bwd_fwdorder_kernel(const Mamba2Par
             const int i = e / (INTRA_LEVELS + MLOW), lv = e % (INTRA_LEVELS + MLOW);
             if (lv < L) p.dl[(((long)b * p.T + t0 + i) * p.H + h) * L + lv] = sDL[i * 16 + lv] + sDL[(CH + i) * 16 + lv];
         }
+        // reader totals Z[c][lv] = sum_i lambda_i * dlambda_i for the low levels read by this chunk
+        if (warp < MLOW && ((cl >> warp) & 1)) {
+            const int col = INTRA_LEVELS + warp;
+            float z = 0.f;
+#pragma unroll
+            for (int rr = 0; rr < 2; ++rr) {
+                const int i = lane + rr * 32;
+                z += cLam[i * L + col] * (sDL[i * 16 + col] + sDL[(CH + i) * 16 + col]);
+            }
+#pragma unroll
+            for (int d = 16; d > 0; d >>= 1) z += __shfl_xor_sync(0xffffffffu, z, d);
+            if (lane == 0) p.Zc[(((long)b * p.H + h) * p.NT + r * SEG + cl) * p.LZ + warp] = z;
+        }
         __syncthreads();
     }
 }
@@ -356,7 +370,8 @@ struct Bwd2Smem {
     static constexpr size_t lam_off = qs_off + 1ull * CH * LDK * 2;            // float [2][64*MAX_L]
     static constexpr size_t g_off = lam_off + 2ull * CH * MAX_L * 4;
     static constexpr size_t gc_off = g_off + 2ull * CH * 4;
-    static constexpr size_t total = gc_off + CH * 4;
+    static constexpr size_t y_off = gc_off + CH * 4;                           // float [8][MLOW+1]
+    static constexpr size_t total = y_off + 8 * (MLOW + 1) * 4 + 16;
 };
 
 template <int KD, int VD, int MLOW>
@@ -376,6 +391,7 @@ __global__ void __launch_bounds__(256, 1) m2_bwd_revorder_kernel(const Mamba2Par
     float* sLam = reinterpret_cast<float*>(smem + SM::lam_off);
     float* sG = reinterpret_cast<float*>(smem + SM::g_off);
     float* sGc = reinterpret_cast<float*>(smem + SM::gc_off);
+    float* sY = reinterpret_cast<float*>(smem + SM::y_off);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int h = blockIdx.x % p.H;
@@ -519,6 +535,28 @@ __global__ void __launch_bounds__(256, 1) m2_bwd_revorder_kernel(const Mamba2Par
         }
         __syncthreads();
 
+        // ---- Y[c][lv] = <KV_c, adjoint state lv> for the levels this chunk contributes to
+        {
+            float kv[MT][2 * NPS][4];
+            zero_acc(kv);
+            warp_gemm<MT, NPS, true, true>(kv, cK, LDK, wr * 16 * MT, sVs, LDV, wc * (VD / 2), CH, lane);
+#pragma unroll
+            for (int lv = 0; lv <= MLOW; ++lv) {
+                float y = 0.f;
+                if (lv == MLOW || !((cl >> lv) & 1)) {
+#pragma unroll
+                    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                        for (int nt = 0; nt < 2 * NPS; ++nt)
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) y += kv[mt][nt][e] * RM[lv][mt][nt][e];
+                }
+#pragma unroll
+                for (int d = 16; d > 0; d >>= 1) y += __shfl_xor_sync(0xffffffffu, y, d);
+                if (lane == 0) sY[warp * (MLOW + 1) + lv] = y;
+            }
+        }
+
         // ---- dv = P^T do + decay_j * (k . dKV)
         {
             float acc[1][2 * NPS][4], tmp[1][2 * NPS][4];
@@ -584,6 +622,12 @@ __global__ void __launch_bounds__(256, 1) m2_bwd_revorder_kernel(const Mamba2Par
         }
         if (it + 1 < nc) store_small(st ^ 1);
         __syncthreads();
+        if (tid <= MLOW) {
+            float y = 0.f;
+#pragma unroll
+            for (int w = 0; w < 8; ++w) y += sY[w * (MLOW + 1) + tid];
+            p.Yc[(((long)b * p.H + h) * p.NT + r * SEG + cl) * (MLOW + 1) + tid] = y;
+        }
     }
 }
 
@@ -693,6 +737,17 @@ __global__ void __launch_bounds__(256, 1) m2_hi_bwd_q_kernel(const Mamba2Params 
         }
         __syncthreads();
         if (tid < CH) p.dl[(((long)b * p.T + t0 + tid) * p.H + h) * p.L + lcol] = sDL[tid] + sDL[CH + tid];
+        if (warp == 2) {
+            float z = 0.f;
+#pragma unroll
+            for (int rr = 0; rr < 2; ++rr) {
+                const int i = lane + rr * 32;
+                z += __bfloat162float(p.l[(((long)b * p.T + t0 + i) * p.H + h) * p.L + lcol]) * (sDL[i] + sDL[CH + i]);
+            }
+#pragma unroll
+            for (int d = 16; d > 0; d >>= 1) z += __shfl_xor_sync(0xffffffffu, z, d);
+            if (lane == 0) p.Zc[(((long)b * p.H + h) * p.NT + c) * p.LZ + MLOW + j] = z;
+        }
         if (jn < 0) break;
         j = jn;
         rem &= rem - 1;
@@ -823,20 +878,32 @@ __global__ void __launch_bounds__(256) m2_seg_dscan_kernel(const Mamba2Params p,
     const int e4 = (blockIdx.x * 256 + threadIdx.x) * 4;
     if (e4 >= KV) return;
     const float* dF = p.seg_dF + bh * p.NS * p.LH * KV + e4;
+    const float* F = p.seg_F + bh * p.NS * KV + e4;
     const float* D = p.seg_D + bh * p.NS;
     float* dH = p.seg_dHf + bh * p.NS * KV + e4;
+    float* Yseg = p.Yseg + bh * p.NS * p.LH;
+    const int lane = threadIdx.x & 31;
     float st[MAX_LH_B][4];
 #pragma unroll
     for (int j = 0; j < MAX_LH_B; ++j) st[j][0] = st[j][1] = st[j][2] = st[j][3] = 0.f;
     for (int r = p.NS - 1; r >= 0; --r) {
         float4 out = make_float4(0.f, 0.f, 0.f, 0.f);
+        float4 f = make_float4(0.f, 0.f, 0.f, 0.f);
         const float d = (r < p.NS - 1) ? __expf(D[r]) : 0.f;
+        if (r < p.NS - 1) f = *reinterpret_cast<const float4*>(F + (long)r * KV);
 #pragma unroll
         for (int j = 0; j < MAX_LH_B; ++j) {
             if (j < p.LH) {
                 const bool bit = (r >> j) & 1;
                 if (!bit) {
                     out.x += st[j][0]; out.y += st[j][1]; out.z += st[j][2]; out.w += st[j][3];
+                    if (r < p.NS - 1) {
+                        // <F_r, adjoint of level j after segment r>
+                        float y = f.x * st[j][0] + f.y * st[j][1] + f.z * st[j][2] + f.w * st[j][3];
+#pragma unroll
+                        for (int dd = 16; dd > 0; dd >>= 1) y += __shfl_xor_sync(0xffffffffu, y, dd);
+                        if (lane == 0) atomicAdd(Yseg + (long)r * p.LH + j, y);
+                    }
                 }
                 const int period = 2 << j;
                 if ((r % period) == 0) {
@@ -867,26 +934,81 @@ __global__ void m2_uncumsum_kernel(const float* __restrict__ gc, float* __restri
     g[idx] = x;
 }
 
-// dg[b, r, h] = sum_{t >= r} w[b, t, h]; block = (32 heads) x (32 time slices)
-__global__ void __launch_bounds__(1024) m2_dg_kernel(const float* __restrict__ w, float* __restrict__ dg, int T, int H) {
-    __shared__ float tot[32][33];
-    const int hl = threadIdx.x, sl = threadIdx.y;
-    const int h = blockIdx.x * 32 + hl;
-    const int b = blockIdx.y;
-    const int per = (T + 31) / 32;
-    const int tb = sl * per, te = min(T, tb + per);
-    float s = 0.f;
-    if (h < H)
-        for (int t = tb; t < te; ++t) s += w[((long)b * T + t) * H + h];
-    tot[sl][hl] = s;
+// dg for one (batch, head) per CTA.
+//   dg[r] = sum_{t >= r, t in chunk(r)} w[t]  +  X[chunk(r)]
+// w[t] = q_t.dq_t - k_t.dk_t is the gradient w.r.t. the in-chunk cumulative sum G_t (the
+// reference's dg before its reverse in-chunk cumsum, chunkwise.py:793-874, 1596); X[c] is the
+// gradient that reaches the end of chunk c from every (target, source) pair that straddles it
+// (the reference's dg_last: sum_j dk_j.k_j + exp(g_last) sum h*dh, chunkwise.py:865-874).  For
+// level l and the block pair that contains c, X gets: the running sum of the contributor totals
+// Y over the block's contributor chunks up to c (bit l of c clear), or the sum of the reader
+// totals Z over the reader chunks after c (bit set).  Sums never extend beyond one block pair, so
+// rounding differences between the two sides do not accumulate along the sequence.
+template <int MLOW>
+__global__ void __launch_bounds__(256) m2_dg_kernel(const Mamba2Params p, float* __restrict__ dg) {
+    extern __shared__ float sx[];
+    constexpr int SEG = 1 << MLOW;
+    float* X = sx;                 // [NT]
+    float* XS = sx + p.NT;         // [NS]
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int h = blockIdx.x % p.H, b = blockIdx.x / p.H;
+    const long bh = (long)b * p.H + h;
+    const float* Zc = p.Zc + bh * p.NT * p.LZ;
+    const float* Yc = p.Yc + bh * p.NT * (MLOW + 1);
+    const float* Yseg = p.Yseg + bh * p.NS * p.LH;
+    for (int i = tid; i < p.NT + p.NS; i += 256) sx[i] = 0.f;
     __syncthreads();
-    float run = 0.f;
-    for (int s2 = sl + 1; s2 < 32; ++s2) run += tot[s2][hl];
-    if (h < H)
-        for (int t = te - 1; t >= tb; --t) {
-            run += w[((long)b * T + t) * H + h];
-            dg[((long)b * T + t) * H + h] = run;
+    int nlev = 0;
+    while ((1 << nlev) < p.NT) ++nlev;          // inter-chunk levels in use
+    if (tid < nlev) {
+        const int lv = tid, period = 2 << lv;
+        if (lv < MLOW) {
+            float run = 0.f;
+            for (int c = 0; c < p.NT; ++c) {
+                if ((c & (period - 1)) == 0) run = 0.f;
+                if (!((c >> lv) & 1)) {
+                    run += Yc[(long)c * (MLOW + 1) + lv];
+                    atomicAdd(&X[c], run);
+                }
+            }
+        } else {
+            const int j = lv - MLOW, pj = 2 << j;
+            float run = 0.f;
+            for (int r = 0; r < p.NS; ++r) {
+                if ((r & (pj - 1)) == 0) run = 0.f;
+                if (!((r >> j) & 1)) {
+                    atomicAdd(&XS[r], run);
+                    if (r < p.NS - 1) run += Yseg[(long)r * p.LH + j];
+                }
+            }
         }
+        float run = 0.f;
+        for (int c = p.NT - 1; c >= 0; --c) {
+            if ((c >> lv) & 1) {
+                atomicAdd(&X[c], run);
+                run += Zc[(long)c * p.LZ + lv];
+            }
+            if ((c & (period - 1)) == 0) run = 0.f;
+        }
+    } else if (tid == 32) {
+        // combined high levels inside a segment
+        float run = 0.f;
+        for (int c = 0; c < p.NT; ++c) {
+            if ((c & (SEG - 1)) == 0) run = 0.f;
+            run += Yc[(long)c * (MLOW + 1) + MLOW];
+            atomicAdd(&X[c], run);
+        }
+    }
+    __syncthreads();
+    for (int c = warp; c < p.NT; c += 8) {
+        const long base = ((long)b * p.T + (long)c * CH) * p.H + h;
+        float x0 = p.wq[base + (long)(63 - 2 * lane) * p.H];
+        float x1 = p.wq[base + (long)(62 - 2 * lane) * p.H];
+        warp_cumsum64(x0, x1, lane);
+        const float add = X[c] + XS[c / SEG];
+        dg[base + (long)(63 - 2 * lane) * p.H] = x0 + add;
+        dg[base + (long)(62 - 2 * lane) * p.H] = x1 + add;
+    }
 }
 
 __global__ void m2_cast_bf16_kernel(const float* __restrict__ src, bf16* __restrict__ dst, long n) {
@@ -959,9 +1081,8 @@ void mamba2_uncumsum(const float* gc, float* g, long BT, int H, cudaStream_t str
     m2_uncumsum_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(gc, g, BT, H);
 }
 
-void mamba2_dg(const float* w, float* dg, int B, int T, int H, cudaStream_t stream) {
-    dim3 grid((H + 31) / 32, B), block(32, 32);
-    m2_dg_kernel<<<grid, block, 0, stream>>>(w, dg, T, H);
+void mamba2_dg(const Mamba2Params& p, float* dg, cudaStream_t stream) {
+    m2_dg_kernel<M2_MLOW><<<p.B * p.H, 256, (size_t)(p.NT + p.NS) * sizeof(float), stream>>>(p, dg);
 }
 
 void cast_f32_to_bf16(const float* src, void* dst, long n, cudaStream_t stream) {
