@@ -28,6 +28,10 @@ extern "C" {
 #define LLATTN_ERR_BAD_GROUPS (-4)          /* H % G != 0                                    */
 #define LLATTN_ERR_WORKSPACE (-5)           /* workspace NULL, misaligned or too small       */
 #define LLATTN_ERR_NULL (-6)                /* a required pointer is NULL                    */
+#define LLATTN_ERR_STATIC_SCRATCH (-7)      /* problem needs more than LLATTN_STATIC_SCRATCH_BYTES */
+
+/* Size of the built-in scratch array used by llattn_mamba2_fwd_static (16 MiB). */
+#define LLATTN_STATIC_SCRATCH_BYTES (16u << 20)
 
 /* Library / ABI version, for the loader's sanity check. */
 int llattn_version(void);
@@ -41,6 +45,31 @@ size_t llattn_mamba2_fwd_workspace_bytes(int B, int T, int H, int G, int K, int 
 int llattn_mamba2_fwd(const void* q, const void* k, const void* v, const float* g, const void* lambda,
                       void* o, float* g_cum, void* workspace, size_t workspace_bytes,
                       int B, int T, int H, int G, int K, int V, int L, void* stream);
+
+/* Forward for callers that cannot hand the library a scratch buffer.  (No counterpart in the
+ * reference: its drivers allocate with torch on every call.)
+ *
+ * Who needs it: code that must not call cudaMalloc / cudaFree or any allocator behind them at the
+ * point where the operator runs - for instance a serving loop that has handed all device memory to
+ * its own pool, a host that embeds this library without torch, or a latency-critical section where
+ * the device-wide synchronisation of cudaMalloc is not acceptable - and that has no spare buffer
+ * of its own to pass as `workspace`.
+ *
+ * Same computation and results as llattn_mamba2_fwd, but the segment-level scratch lives in an
+ * array compiled into the library (LLATTN_STATIC_SCRATCH_BYTES = 16 MiB of device memory on every
+ * GPU that loads the library, held until the process exits).  The call allocates and frees
+ * nothing.  Shapes whose scratch need (llattn_mamba2_fwd_workspace_bytes) exceeds the array are
+ * rejected with LLATTN_ERR_STATIC_SCRATCH; e.g. B*H = 8 at T = 4096, K = 128, V = 64 needs 5.0 MiB.
+ *
+ * The first call on each device looks up the array's device address (cudaGetSymbolAddress) for
+ * the device that is current at that moment and caches it; make that first call with the right
+ * device current and before starting any stream capture.  All calls on one device share the one
+ * array, and it keeps whatever the previous call left in it (the kernels overwrite every element
+ * before reading it, so no clearing is needed): two calls whose kernels can overlap on the GPU
+ * - different streams, or different host threads - race on it and must be serialised by the caller. */
+size_t llattn_static_scratch_bytes(void);
+int llattn_mamba2_fwd_static(const void* q, const void* k, const void* v, const float* g, const void* lambda,
+                             void* o, float* g_cum, int B, int T, int H, int G, int K, int V, int L, void* stream);
 
 /* Log-linear Mamba-2 backward.  Replaces hattention.chunkwise.chunkwise_bwd
  * (hattention/chunkwise.py:1286-1597).  `g_cum` is the in-chunk cumulative sum that the forward

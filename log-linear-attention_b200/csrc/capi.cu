@@ -66,6 +66,12 @@ size_t setup(llattn::Mamba2Params& p, void* ws, bool backward) {
     return c.off;
 }
 
+// Scratch for llattn_mamba2_fwd_static.  The array lives in the library's device image: every GPU
+// that loads the library carries these bytes until the process exits.  In host code the symbol is
+// only a handle; the device address is obtained once per device with cudaGetSymbolAddress.
+static __device__ __align__(256) unsigned char g_static_scratch[LLATTN_STATIC_SCRATCH_BYTES];
+static void* g_static_scratch_addr[64] = {nullptr};
+
 }  // namespace
 
 extern "C" {
@@ -91,6 +97,38 @@ int llattn_mamba2_fwd(const void* q, const void* k, const void* v, const float* 
     const size_t need = setup(p, nullptr, false);
     if (need > 0 && (!workspace || workspace_bytes < need || ((uintptr_t)workspace & 255))) return LLATTN_ERR_WORKSPACE;
     setup(p, workspace, false);
+    p.q = (const __nv_bfloat16*)q; p.k = (const __nv_bfloat16*)k; p.v = (const __nv_bfloat16*)v;
+    p.g = g; p.l = (const __nv_bfloat16*)lambda;
+    p.o = (__nv_bfloat16*)o; p.g_cum = g_cum;
+    return llattn::mamba2_fwd_dispatch(p, (cudaStream_t)stream);
+}
+
+size_t llattn_static_scratch_bytes(void) { return LLATTN_STATIC_SCRATCH_BYTES; }
+
+int llattn_mamba2_fwd_static(const void* q, const void* k, const void* v, const float* g, const void* lambda,
+                             void* o, float* g_cum, int B, int T, int H, int G, int K, int V, int L, void* stream) {
+    int rc = check_shape(B, T, H, G, K, V, L);
+    if (rc != 0) return rc;
+    if (!q || !k || !v || !g || !lambda || !o || !g_cum) return LLATTN_ERR_NULL;
+    llattn::Mamba2Params p = {};
+    p.B = B; p.T = T; p.H = H; p.G = G; p.K = K; p.V = V; p.L = L;
+    const size_t need = setup(p, nullptr, false);
+    if (need > (size_t)LLATTN_STATIC_SCRATCH_BYTES) return LLATTN_ERR_STATIC_SCRATCH;
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= 64) return LLATTN_ERR_UNSUPPORTED_SHAPE;
+    if (g_static_scratch_addr[dev] == nullptr) {
+        // first call on this device (it is the current one): resolve the device address of the array
+        void* addr = nullptr;
+        e = cudaGetSymbolAddress(&addr, g_static_scratch);
+        if (e != cudaSuccess) return (int)e;
+        if (addr == nullptr) return LLATTN_ERR_WORKSPACE;
+        g_static_scratch_addr[dev] = addr;
+    }
+    // every scratch element that a kernel reads is written earlier in the same call, so nothing
+    // has to be cleared even though the previous call's contents are still there
+    setup(p, g_static_scratch_addr[dev], false);
     p.q = (const __nv_bfloat16*)q; p.k = (const __nv_bfloat16*)k; p.v = (const __nv_bfloat16*)v;
     p.g = g; p.l = (const __nv_bfloat16*)lambda;
     p.o = (__nv_bfloat16*)o; p.g_cum = g_cum;

@@ -13,6 +13,7 @@ ERRORS = {
     -4: "number of heads is not a multiple of the number of q/k groups",
     -5: "workspace missing, misaligned or too small",
     -6: "null pointer",
+    -7: "problem needs more scratch than the built-in static array holds",
 }
 
 _SHAPE = [ctypes.c_int] * 7
@@ -37,6 +38,9 @@ def lib():
     L.llattn_mamba2_bwd_workspace_bytes.argtypes = _SHAPE
     L.llattn_mamba2_fwd.restype = ctypes.c_int
     L.llattn_mamba2_fwd.argtypes = [_P] * 7 + [_P, ctypes.c_size_t] + _SHAPE + [_P]
+    L.llattn_static_scratch_bytes.restype = ctypes.c_size_t
+    L.llattn_mamba2_fwd_static.restype = ctypes.c_int
+    L.llattn_mamba2_fwd_static.argtypes = [_P] * 7 + _SHAPE + [_P]
     L.llattn_mamba2_bwd.restype = ctypes.c_int
     L.llattn_mamba2_bwd.argtypes = [_P] * 11 + [_P, ctypes.c_size_t] + _SHAPE + [_P]
     _lib = L
