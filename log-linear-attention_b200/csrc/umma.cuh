@@ -1,0 +1,168 @@
+// Blackwell (sm_100a) 5th-generation tensor core helpers: tcgen05.mma with shared-memory operand
+// descriptors, tensor memory (TMEM) allocation and readback, mbarrier completion tracking.
+//
+// Shared-memory operand tiles use ONE physical layout everywhere: a tile of R rows x C bf16
+// columns is stored as C/64 "panels"; a panel is R rows of 128 bytes (64 bf16) and is 128-byte
+// swizzled (16-byte chunk index XOR (row & 7)); panels are 1024-byte aligned.  This is what a TMA
+// box of 64 columns with SWIZZLE_128B produces, and the same bytes serve as
+//   * a K-major operand  (MMA's M/N index = row, reduction index = column), and
+//   * an MN-major operand (MMA's M/N index = column, reduction index = row).
+#pragma once
+#include <cuda_bf16.h>
+#include <stdint.h>
+
+namespace llattn {
+namespace umma {
+
+constexpr int PANEL_COLS = 64;          // bf16 elements per 128-byte row
+constexpr int ROW_BYTES = 128;
+constexpr uint32_t SPIN_LIMIT = 1u << 24;   // bounded waits: give up and flag instead of hanging
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+// byte offset of element (row, col) inside a tile of `rows` rows stored as 64-column panels
+__device__ __forceinline__ uint32_t tile_offset(int row, int col, int rows) {
+    const int panel = col >> 6, c = col & 63;
+    const int chunk = (c >> 3) ^ (row & 7);
+    return (uint32_t)(panel * rows * ROW_BYTES + row * ROW_BYTES + chunk * 16 + (c & 7) * 2);
+}
+
+// ---- shared memory matrix descriptors (SWIZZLE_128B, sm_100 version field = 1)
+__device__ __forceinline__ uint64_t desc_base() {
+    return (uint64_t(1) << 46) | (uint64_t(2) << 61);
+}
+// K-major: 8-row groups are 1024 bytes apart; the leading-dimension field is unused with swizzle
+__device__ __forceinline__ uint64_t desc_kmajor(uint32_t saddr) {
+    return desc_base() | uint64_t((saddr >> 4) & 0x3FFF) | (uint64_t(1) << 16) | (uint64_t(1024 >> 4) << 32);
+}
+// MN-major: consecutive 64-element blocks of the M/N index are `panel_bytes` apart (leading
+// offset), consecutive 8-row groups of the reduction index are 1024 bytes apart (stride offset)
+__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t saddr, uint32_t panel_bytes) {
+    return desc_base() | uint64_t((saddr >> 4) & 0x3FFF) | (uint64_t((panel_bytes >> 4) & 0x3FFF) << 16) |
+           (uint64_t(1024 >> 4) << 32);
+}
+
+// ---- instruction descriptor: bf16 x bf16 -> fp32, dense
+__host__ __device__ constexpr uint32_t idesc_bf16(int M, int N, bool a_mn_major, bool b_mn_major) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(a_mn_major) << 15) | (uint32_t(b_mn_major) << 16) |
+           (uint32_t(N >> 3) << 17) | (uint32_t(M >> 4) << 24);
+}
+
+__device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, bool accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"((uint32_t)accumulate)
+        : "memory");
+}
+// A operand from tensor memory (bf16 pairs packed in 32-bit columns), B from shared memory
+__device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, bool accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}\n"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"((uint32_t)accumulate)
+        : "memory");
+}
+
+// D[128 x N] (+)= A[128 x kred] * B[kred x N], both operands K-major tiles (rows = M or N index)
+// a_rows / b_rows: number of rows of the stored tiles (panel stride = rows * 128 bytes)
+__device__ __forceinline__ void gemm_kk(uint32_t d_tmem, uint32_t a_saddr, int a_rows, uint32_t b_saddr, int b_rows,
+                                        int kred, uint32_t idesc, bool accumulate) {
+    for (int kk = 0; kk < kred; kk += 16) {
+        const uint32_t ka = (kk >> 6) * a_rows * ROW_BYTES + (kk & 63) * 2;
+        const uint32_t kb = (kk >> 6) * b_rows * ROW_BYTES + (kk & 63) * 2;
+        mma_ss(d_tmem, desc_kmajor(a_saddr + ka), desc_kmajor(b_saddr + kb), idesc, accumulate || kk > 0);
+    }
+}
+// A K-major tile (rows = M index), B stored [kred rows][N cols] (MN-major)
+__device__ __forceinline__ void gemm_km(uint32_t d_tmem, uint32_t a_saddr, int a_rows, uint32_t b_saddr, int b_rows,
+                                        int kred, uint32_t idesc, bool accumulate) {
+    for (int kk = 0; kk < kred; kk += 16) {
+        const uint32_t ka = (kk >> 6) * a_rows * ROW_BYTES + (kk & 63) * 2;
+        mma_ss(d_tmem, desc_kmajor(a_saddr + ka), desc_mnmajor(b_saddr + kk * ROW_BYTES, b_rows * ROW_BYTES), idesc,
+               accumulate || kk > 0);
+    }
+}
+// A stored [kred rows][M cols], B stored [kred rows][N cols] (both MN-major): D = A^T B
+__device__ __forceinline__ void gemm_mm(uint32_t d_tmem, uint32_t a_saddr, int a_rows, uint32_t b_saddr, int b_rows,
+                                        int kred, uint32_t idesc, bool accumulate) {
+    for (int kk = 0; kk < kred; kk += 16) {
+        mma_ss(d_tmem, desc_mnmajor(a_saddr + kk * ROW_BYTES, a_rows * ROW_BYTES),
+               desc_mnmajor(b_saddr + kk * ROW_BYTES, b_rows * ROW_BYTES), idesc, accumulate || kk > 0);
+    }
+}
+
+// ---- completion tracking
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_addr(bar)), "r"(count));
+}
+__device__ __forceinline__ void fence_mbar_init() { asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory"); }
+// arrive on `bar` when every tcgen05.mma issued so far by this thread has completed
+__device__ __forceinline__ void commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_addr(bar)) : "memory");
+}
+// bounded wait; returns false if the phase did not complete within the spin limit
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    const uint32_t a = smem_addr(bar);
+    for (uint32_t it = 0; it < SPIN_LIMIT; ++it) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"
+            : "=r"(done)
+            : "r"(a), "r"(parity)
+            : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+// make generic-proxy shared memory writes (st.shared, cp.async) visible to the tensor core's async proxy
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
+
+// ---- tensor memory
+// one full warp allocates `ncols` (power of two >= 32) columns and publishes the base address
+__device__ __forceinline__ void tmem_alloc(uint32_t* slot_in_smem, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_addr(slot_in_smem)), "r"(ncols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// 32 consecutive fp32 columns of this thread's lane (lane = 32 * (warp % 4) + laneid)
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};\n"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+          "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+          "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+          "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
+
+// address of (lane quarter of this warp, column) relative to an allocation base
+__device__ __forceinline__ uint32_t tmem_addr(uint32_t base, int warp, int col) {
+    return base + (uint32_t((warp & 3) * 32) << 16) + (uint32_t)col;
+}
+
+}  // namespace umma
+}  // namespace llattn
