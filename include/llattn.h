@@ -35,6 +35,10 @@ extern "C" {
 
 /* Library / ABI version, for the loader's sanity check. */
 int llattn_version(void);
+/* Process-wide switch between the tcgen05 (tensor memory) chunk kernels (1, default) and the
+ * warp-level mma.sync kernels (0) where both exist; for A/B comparison.  The first word of every
+ * workspace is a status word: kernels set it to 1 if a bounded wait on the tensor core gave up. */
+void llattn_set_tensor_core_path(int enabled);
 /* Chunk length the kernels are built for (64, as hattention/kernel.py:355-356 fixes it). */
 int llattn_chunk(void);
 

@@ -45,6 +45,7 @@ size_t setup(llattn::Mamba2Params& p, void* ws, bool backward) {
     p.LZ = llattn::M2_MLOW + p.LH;
     const size_t KV = (size_t)p.K * p.V, BH = (size_t)p.B * p.H;
     Carver c(ws);
+    p.err = c.take<int>(64);      // status word first (256 bytes)
     if (p.NS > 1) {
         p.seg_F = c.take<float>(BH * p.NS * KV);
         p.seg_D = c.take<float>(BH * p.NS);
@@ -77,6 +78,7 @@ static void* g_static_scratch_addr[64] = {nullptr};
 extern "C" {
 
 int llattn_version(void) { return 1; }
+void llattn_set_tensor_core_path(int enabled) { llattn::g_use_tensor_core_path = enabled ? 1 : 0; }
 int llattn_chunk(void) { return 64; }
 
 size_t llattn_mamba2_fwd_workspace_bytes(int B, int T, int H, int G, int K, int V, int L) {
@@ -95,11 +97,13 @@ int llattn_mamba2_fwd(const void* q, const void* k, const void* v, const float* 
     llattn::Mamba2Params p = {};
     p.B = B; p.T = T; p.H = H; p.G = G; p.K = K; p.V = V; p.L = L;
     const size_t need = setup(p, nullptr, false);
-    if (need > 0 && (!workspace || workspace_bytes < need || ((uintptr_t)workspace & 255))) return LLATTN_ERR_WORKSPACE;
+    if (!workspace || workspace_bytes < need || ((uintptr_t)workspace & 255)) return LLATTN_ERR_WORKSPACE;
     setup(p, workspace, false);
     p.q = (const __nv_bfloat16*)q; p.k = (const __nv_bfloat16*)k; p.v = (const __nv_bfloat16*)v;
     p.g = g; p.l = (const __nv_bfloat16*)lambda;
     p.o = (__nv_bfloat16*)o; p.g_cum = g_cum;
+    cudaError_t e = cudaMemsetAsync(p.err, 0, sizeof(int), (cudaStream_t)stream);
+    if (e != cudaSuccess) return (int)e;
     return llattn::mamba2_fwd_dispatch(p, (cudaStream_t)stream);
 }
 
@@ -132,6 +136,8 @@ int llattn_mamba2_fwd_static(const void* q, const void* k, const void* v, const 
     p.q = (const __nv_bfloat16*)q; p.k = (const __nv_bfloat16*)k; p.v = (const __nv_bfloat16*)v;
     p.g = g; p.l = (const __nv_bfloat16*)lambda;
     p.o = (__nv_bfloat16*)o; p.g_cum = g_cum;
+    e = cudaMemsetAsync(p.err, 0, sizeof(int), (cudaStream_t)stream);
+    if (e != cudaSuccess) return (int)e;
     return llattn::mamba2_fwd_dispatch(p, (cudaStream_t)stream);
 }
 
@@ -160,6 +166,7 @@ int llattn_mamba2_bwd(const void* q, const void* k, const void* v, const float* 
     p.dv = (__nv_bfloat16*)dv; p.dl = dlambda;
     const size_t nqk = (size_t)B * T * G * K, nbth = (size_t)B * T * H;
     cudaError_t e;
+    if ((e = cudaMemsetAsync(p.err, 0, sizeof(int), st)) != cudaSuccess) return (int)e;
     // dq_acc, dk_acc, wq and Yseg are adjacent in the workspace: one clear covers the four
     if ((e = cudaMemsetAsync(p.dq_acc, 0, (size_t)((unsigned char*)p.Zc - (unsigned char*)p.dq_acc), st)) != cudaSuccess) return (int)e;
     if ((e = cudaMemsetAsync(dlambda, 0, nbth * L * sizeof(float), st)) != cudaSuccess) return (int)e;

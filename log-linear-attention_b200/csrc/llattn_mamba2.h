@@ -36,6 +36,7 @@ struct Mamba2Params {
     float* Yc;                   // (B,H,NT,MLOW+1)  contributor side: <KV_c, adjoint state> per low level, + combined high
     float* Yseg;                 // (B,H,NS,LH)      contributor side per segment and high level
     int LZ;                      // MLOW + LH
+    int* err;                    // device status word: set to 1 when a bounded wait on the tensor core gave up
     int B, T, H, G, K, V, L;
     int NT, NS, LH;
     int o_has_high;
@@ -45,6 +46,9 @@ int mamba2_fwd_dispatch(Mamba2Params p, cudaStream_t stream);
 int mamba2_bwd_dispatch(Mamba2Params p, cudaStream_t stream);
 // segment summaries and the per-level scan over segments only (needs NS > 1)
 int mamba2_fwd_states_dispatch(Mamba2Params p, cudaStream_t stream);
+// tcgen05 version of the chunk kernel (K = 128, V = 64, even number of chunks)
+int mamba2_fwd_tc_launch(const Mamba2Params& p, cudaStream_t stream);
+extern int g_use_tensor_core_path;
 void mamba2_uncumsum(const float* gc, float* g, long BT, int H, cudaStream_t stream);
 void mamba2_dg(const Mamba2Params& p, float* dg, cudaStream_t stream);
 void cast_f32_to_bf16(const float* src, void* dst, long n, cudaStream_t stream);

@@ -566,6 +566,9 @@ static int launch_fwd(Mamba2Params p, cudaStream_t stream) {
         if ((e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm)) != cudaSuccess) return (int)e;
         kern<<<p.B * p.H * (p.NT - (1 << MLOW)), 256, sm, stream>>>(p);
     }
+    if (KD == 128 && VD == 64 && (p.NT % 2) == 0 && g_use_tensor_core_path) {
+        return mamba2_fwd_tc_launch(p, stream);
+    }
     {
         auto kern = m2_chunk_fwd_kernel<KD, VD, MLOW>;
         size_t sm = FwdSmem<KD, VD, MLOW>::total;
@@ -574,6 +577,8 @@ static int launch_fwd(Mamba2Params p, cudaStream_t stream) {
     }
     return (int)cudaGetLastError();
 }
+
+int g_use_tensor_core_path = 1;
 
 int mamba2_fwd_dispatch(Mamba2Params p, cudaStream_t stream) {
     if (p.K == 128 && p.V == 64) return launch_fwd<128, 64, M2_MLOW>(p, stream);

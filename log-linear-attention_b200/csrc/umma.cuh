@@ -16,7 +16,7 @@ namespace umma {
 
 constexpr int PANEL_COLS = 64;          // bf16 elements per 128-byte row
 constexpr int ROW_BYTES = 128;
-constexpr uint32_t SPIN_LIMIT = 1u << 24;   // bounded waits: give up and flag instead of hanging
+constexpr uint32_t SPIN_LIMIT = 1u << 20;   // bounded waits: give up and flag instead of hanging
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -103,7 +103,23 @@ __device__ __forceinline__ void fence_mbar_init() { asm volatile("fence.mbarrier
 __device__ __forceinline__ void commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_addr(bar)) : "memory");
 }
-// bounded wait; returns false if the phase did not complete within the spin limit
+// bounded wait; returns false if the phase did not complete within the spin limit, or at once if
+// another thread of the CTA has already given up (*abort != 0); sets *abort on giving up
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort) {
+    const uint32_t a = smem_addr(bar);
+    for (uint32_t it = 0; it < SPIN_LIMIT; ++it) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"
+            : "=r"(done)
+            : "r"(a), "r"(parity)
+            : "memory");
+        if (done) return true;
+        if ((it & 255) == 255 && *abort) return false;
+    }
+    *abort = 1;
+    return false;
+}
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     const uint32_t a = smem_addr(bar);
     for (uint32_t it = 0; it < SPIN_LIMIT; ++it) {

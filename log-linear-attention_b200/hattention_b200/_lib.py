@@ -43,6 +43,8 @@ def lib():
     L.llattn_mamba2_fwd_static.argtypes = [_P] * 7 + _SHAPE + [_P]
     L.llattn_mamba2_bwd.restype = ctypes.c_int
     L.llattn_mamba2_bwd.argtypes = [_P] * 11 + [_P, ctypes.c_size_t] + _SHAPE + [_P]
+    L.llattn_set_tensor_core_path.restype = None
+    L.llattn_set_tensor_core_path.argtypes = [ctypes.c_int]
     L.llattn_selftest_umma.restype = ctypes.c_int
     L.llattn_selftest_umma.argtypes = [_P, _P, _P, ctypes.c_int, ctypes.c_int, ctypes.c_int, _P, _P]
     _lib = L

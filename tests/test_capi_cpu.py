@@ -36,8 +36,8 @@ def test_version_and_chunk(lib):
 
 
 def test_workspace_sizes(lib):
-    # one segment (T <= 512): the forward needs no scratch
-    assert lib.llattn_mamba2_fwd_workspace_bytes(1, 512, 2, 1, 128, 64, 10) == 0
+    # one segment (T <= 512): only the 256-byte status word
+    assert lib.llattn_mamba2_fwd_workspace_bytes(1, 512, 2, 1, 128, 64, 10) == 256
     small = lib.llattn_mamba2_fwd_workspace_bytes(1, 1024, 2, 1, 128, 64, 11)
     big = lib.llattn_mamba2_fwd_workspace_bytes(2, 16384, 32, 1, 128, 64, 15)
     assert 0 < small < big

@@ -121,3 +121,28 @@ def test_batch_head_independence():
     assert torch.equal(o_full[1:, :, 2:], o_part)
     assert torch.equal(gr_full[2][1:, :, 2:], gr_part[2])          # dv
     assert torch.equal(gr_full[4][1:, :, 2:], gr_part[4])          # dl
+
+
+def test_tensor_core_and_warp_mma_forward_agree():
+    """The tcgen05 chunk kernel and the mma.sync chunk kernel compute the same forward."""
+    from hattention_b200 import _lib
+    from hattention_b200.base import HType
+    from hattention_b200.chunkwise import chunkwise_fwd
+    lib = _lib.lib()
+    dev = torch.device("cuda:0")
+    q, k, v, g, l, _ = rounded_inputs(1, 2048, 4, 64, 128, 1, 12, seed=21)
+    args = (q.bfloat16().to(dev), k.bfloat16().to(dev), v.bfloat16().to(dev), g.to(dev), l.bfloat16().to(dev),
+            False, 2, HType.WEAK, 64, False)
+    try:
+        lib.llattn_set_tensor_core_path(0)
+        o_warp, gc_warp, _ = chunkwise_fwd(*args)
+        lib.llattn_set_tensor_core_path(1)
+        o_tc, gc_tc, _ = chunkwise_fwd(*args)
+    finally:
+        lib.llattn_set_tensor_core_path(1)
+    torch.cuda.synchronize()
+    assert torch.equal(gc_warp, gc_tc)
+    o_ref = orc.mamba2_chunkwise(q.double(), k.double(), v.double(), g.double(), l.double())
+    assert_close(o_tc, o_ref, "o (tcgen05)")
+    assert_close(o_warp, o_ref, "o (mma.sync)")
+    assert (o_tc.float() - o_warp.float()).abs().max().item() < 0.05 * o_ref.abs().max().item()
