@@ -50,6 +50,7 @@ size_t setup(llattn::Mamba2Params& p, void* ws, bool backward) {
         p.seg_F = c.take<float>(BH * p.NS * KV);
         p.seg_D = c.take<float>(BH * p.NS);
         p.seg_H0 = c.take<__nv_bfloat16>(BH * p.NS * p.LH * KV);
+        p.o_hi = c.take<__nv_bfloat16>((size_t)p.B * p.T * p.H * p.V);
     }
     if (backward) {
         p.g = c.take<float>((size_t)p.B * p.T * p.H);

@@ -1,5 +1,6 @@
 // Internal launch parameters shared by the log-linear Mamba-2 kernels.
 #pragma once
+#include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
@@ -10,6 +11,8 @@ namespace llattn {
 constexpr int M2_MLOW = 3;   // a segment is 2^M2_MLOW chunks (512 tokens)
 
 struct Mamba2Params {
+    // tensor maps (64-column panels, 128 rows) for the tcgen05 kernels; valid only when those run
+    alignas(64) CUtensorMap tm_q, tm_k, tm_v, tm_do;
     // inputs
     const __nv_bfloat16* q;      // (B,T,G,K)
     const __nv_bfloat16* k;      // (B,T,G,K)
@@ -29,6 +32,7 @@ struct Mamba2Params {
     float* seg_F;                // (B,H,NS,K,V)
     float* seg_D;                // (B,H,NS)
     __nv_bfloat16* seg_H0;       // (B,H,NS,LH,K,V)
+    __nv_bfloat16* o_hi;         // (B*H, NT/2, 8, 128, 8) high-level partial output, column-chunk major (tcgen05 chunk kernel)
     float* seg_dF;               // (B,H,NS,LH,K,V) reader summaries (backward)
     float* seg_dHf;              // (B,H,NS,K,V) gradient w.r.t. the segment summaries (backward)
     // per-chunk scalars from which the decay gradient across chunk boundaries is assembled

@@ -528,6 +528,20 @@ __global__ void __launch_bounds__(256, 1) m2_hi_out_kernel(const Mamba2Params p)
         rem &= rem - 1;
         slot ^= 1;
     }
+    if (p.o_has_high == 2) {
+        // column-chunk-major scratch read by the tcgen05 chunk kernel: [bh][pair][8-col chunk][128 rows][8]
+        bf16* gh = p.o_hi + (((long)b * p.H + h) * (p.NT / 2) + (c >> 1)) * (8 * 128 * 8);
+#pragma unroll
+        for (int nt = 0; nt < 2 * NPS; ++nt)
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+                const int i = (c & 1) * CH + row0 + lr + hh * 8;
+                const int cc = col0 + nt * 8;
+                *reinterpret_cast<uint32_t*>(gh + ((long)(cc >> 3) * 128 + i) * 8 + lc2) =
+                    pack_bf16(acc[0][nt][hh * 2], acc[0][nt][hh * 2 + 1]);
+            }
+        return;
+    }
     bf16* go = p.o + (((long)b * p.T + t0) * p.H + h) * VD;
 #pragma unroll
     for (int nt = 0; nt < 2 * NPS; ++nt)
@@ -558,7 +572,9 @@ static int launch_states(Mamba2Params p, cudaStream_t stream) {
 template <int KD, int VD, int MLOW>
 static int launch_fwd(Mamba2Params p, cudaStream_t stream) {
     cudaError_t e;
+    const bool use_tc = (KD == 128 && VD == 64 && (p.NT % 2) == 0 && p.L <= 20 && g_use_tensor_core_path);
     if (p.NS > 1) {
+        p.o_has_high = use_tc ? 2 : 1;      // 2: partial output goes to the column-chunk-major scratch
         int rc = launch_states<KD, VD, MLOW>(p, stream);
         if (rc != 0) return rc;
         auto kern = m2_hi_out_kernel<KD, VD, MLOW>;
@@ -566,7 +582,7 @@ static int launch_fwd(Mamba2Params p, cudaStream_t stream) {
         if ((e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm)) != cudaSuccess) return (int)e;
         kern<<<p.B * p.H * (p.NT - (1 << MLOW)), 256, sm, stream>>>(p);
     }
-    if (KD == 128 && VD == 64 && (p.NT % 2) == 0 && g_use_tensor_core_path) {
+    if (use_tc) {
         return mamba2_fwd_tc_launch(p, stream);
     }
     {

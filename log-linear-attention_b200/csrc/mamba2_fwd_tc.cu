@@ -13,9 +13,22 @@
 //     state row per thread), their bf16 copies are written once as MN-major operands.
 #include "llattn_common.cuh"
 #include "llattn_mamba2.h"
+#include "tma.cuh"
 #include "umma.cuh"
 
 namespace llattn {
+
+// Optional phase timing for tuning (build with -DLLATTN_STAMPS): three threads of one CTA record
+// clock64() at fixed points of one pair; llattn_debug_read_stamps copies the table to the host.
+#ifdef LLATTN_STAMPS
+__device__ long long g_stamps[3][32];
+#define STAMP()                                                             \
+    do {                                                                    \
+        if (stamp_slot >= 0 && nstamp < 32) g_stamps[stamp_slot][nstamp++] = clock64(); \
+    } while (0)
+#else
+#define STAMP() do { } while (0)
+#endif
 
 namespace tc {
 constexpr int KD = 128, VD = 64, PT = 128;          // pair of chunks = 128 tokens
@@ -24,20 +37,27 @@ constexpr uint32_t V_BYTES = PT * VD * 2;            // 16 KB
 constexpr uint32_t H_BYTES = KD * VD * 2;            // 16 KB
 // tensor memory columns
 constexpr int TM_S = 0, TM_O = 128, TM_T0 = 192, TM_T1 = 256, TM_KV = 320, TM_COLS = 512;
+// warps 0..7 do the element-wise work (two per tensor-memory lane quarter), warp 8 issues the MMAs;
+// the CTA is launched with three warpgroups so that registers can be moved from the third to the
+// first two (setmaxnreg); warps 9..11 exit at once
+constexpr int NTHREADS = 384, MMA_WARP = 8;
+constexpr int MAX_L_TC = 20;        // lambda levels supported by this kernel (T up to 64 * 2^13)
+constexpr int LAM_LD = MAX_L + 2;   // row stride of the staged lambda tile: odd number of 32-bit words, no bank conflicts
 }  // namespace tc
 
 template <int MLOW>
 struct FwdTcSmem {
     static constexpr int MP = MLOW - 1;              // pair levels kept on chip
-    static constexpr uint32_t q_off = 0;                               // [2]
-    static constexpr uint32_t v_off = q_off + 2 * tc::Q_BYTES;         // [2]
-    static constexpr uint32_t k_off = v_off + 2 * tc::V_BYTES;
-    static constexpr uint32_t p_off = k_off + tc::Q_BYTES;
+    static constexpr uint32_t q_off = 0;
+    static constexpr uint32_t v_off = q_off + tc::Q_BYTES;             // [2]
+    static constexpr uint32_t k_off = v_off + 2 * tc::V_BYTES;         // [2]
+    static constexpr uint32_t p_off = k_off + 2 * tc::Q_BYTES;
     static constexpr uint32_t vs_off = p_off + tc::PT * tc::PT * 2;
     static constexpr uint32_t h_off = vs_off + tc::V_BYTES;
-    static constexpr uint32_t gp_off = h_off + (MP > 0 ? MP : 1) * tc::H_BYTES;   // float [128]
-    static constexpr uint32_t bar_off = gp_off + 128 * 4;              // 4 mbarriers + tmem slot + abort flag
-    static constexpr uint32_t total = bar_off + 64 + 1024;             // + slack for 1024-byte alignment
+    static constexpr uint32_t gp_off = h_off + (MP > 0 ? MP : 1) * tc::H_BYTES;   // float [3][128]
+    static constexpr uint32_t lam_off = gp_off + 3 * 128 * 4;          // bf16 [128][L <= 32]
+    static constexpr uint32_t bar_off = lam_off + 128 * (MAX_L + 2) * 2;   // 10 mbarriers + tmem slot + abort flag     // 4 mbarriers + tmem slot + abort flag
+    static constexpr uint32_t total = bar_off + 128 + 1024;             // + slack for 1024-byte alignment
 };
 
 // 128 x COLS bf16 tile from global (row stride g_stride elements) into the swizzled panel layout
@@ -51,23 +71,35 @@ __device__ __forceinline__ void load_tile_swz(unsigned char* s, const bf16* g, l
     }
 }
 
+// CTA-wide barrier over the 8 element-wise warps and the MMA warp (the spare warps of the third
+// warpgroup exit at once and never take part)
+__device__ __forceinline__ void bar_work() { asm volatile("bar.sync 1, 288;\n" ::: "memory"); }
+
 template <int MLOW>
-__global__ void __launch_bounds__(256, 1) m2_chunk_fwd_tc_kernel(const Mamba2Params p) {
+__global__ void __launch_bounds__(tc::NTHREADS, 1) m2_chunk_fwd_tc_kernel(const __grid_constant__ Mamba2Params p) {
     using SM = FwdTcSmem<MLOW>;
     constexpr int MP = SM::MP;
     constexpr int SEGP = 1 << MP;                    // pairs per segment
+    constexpr int NLAM = 8 + (MP > 0 ? MP : 1);
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    unsigned char* sQ = smem + SM::q_off;
-    unsigned char* sV = smem + SM::v_off;
-    unsigned char* sK = smem + SM::k_off;
+    unsigned char* sQ = smem + SM::q_off;            // single buffer, refilled as soon as S and T are done
+    unsigned char* sV = smem + SM::v_off;            // [2]
+    unsigned char* sK = smem + SM::k_off;            // [2]
     unsigned char* sP = smem + SM::p_off;
     unsigned char* sVs = smem + SM::vs_off;
     unsigned char* sH = smem + SM::h_off;
-    float* sGp = reinterpret_cast<float*>(smem + SM::gp_off);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SM::bar_off);     // S, T, O, KV
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + SM::bar_off + 32);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + SM::bar_off + 40);
+    float* sGp = reinterpret_cast<float*>(smem + SM::gp_off);      // pair-wide inclusive cumsum of g
+    float* sCf = sGp + 128;                                        // exp(G[end of 32-block] - G[j])
+    float* sVf = sGp + 256;                                        // exp(G[127] - G[j])
+    bf16* sLam = reinterpret_cast<bf16*>(smem + SM::lam_off);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SM::bar_off);     // MMA completion: S, T, O, KV
+    uint64_t* full_q = bars + 4;                     // TMA completion: q tile
+    uint64_t* full_kv = bars + 5;                    // [2] k and v tiles of a stage
+    uint64_t* empty_q = bars + 7;                    // tensor core is done reading the q tile
+    uint64_t* empty_kv = bars + 8;                   // [2] ... the k and v tiles of a stage
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + SM::bar_off + 80);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + SM::bar_off + 88);
     static_assert(MP <= 2, "two tensor-memory slots for level reads");
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -78,33 +110,134 @@ __global__ void __launch_bounds__(256, 1) m2_chunk_fwd_tc_kernel(const Mamba2Par
     const int L = p.L;
     const int npairs = min(SEGP, p.NT / 2 - r * SEGP);
     const bool hi_init = (p.o_has_high != 0) && (r != 0);
-    const int row = (warp & 3) * 32 + lane;          // tensor-memory lane of this thread
-    const int ch = warp >> 2;                        // which half of the columns this thread handles
 
     if (tid == 0) {
 #pragma unroll
-        for (int i = 0; i < 4; ++i) umma::mbar_init(&bars[i], 1);
+        for (int i = 0; i < 10; ++i) umma::mbar_init(&bars[i], 1);
         umma::fence_mbar_init();
         *abort_flag = *p.err;                        // an earlier CTA gave up: do not pile on
     }
     __syncthreads();
     if (*abort_flag) return;                         // uniform: every thread reads the same shared word
-    if (warp == 0) umma::tmem_alloc(tmem_slot, tc::TM_COLS);
-    auto issue_qv = [&](int pl, int st) {
+
+    constexpr uint32_t ID_S = umma::idesc_bf16(128, 128, false, false);
+    constexpr uint32_t ID_KM = umma::idesc_bf16(128, 64, false, true);
+    constexpr uint32_t ID_MM = umma::idesc_bf16(128, 64, true, true);
+
+    if (warp >= tc::MMA_WARP) {
+        // ================= third warpgroup: one warp issues the tensor-core work =================
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 40;\n");
+        if (warp == tc::MMA_WARP + 1) {
+            // ---- TMA producer: one lane streams the tiles of the segment through the stages
+            if (lane == 0) {
+                const int brow = b * p.T + r * SEGP * tc::PT;
+                for (int pl = 0; pl < npairs; ++pl) {
+                    const int st = pl & 1, row0 = brow + pl * tc::PT;
+                    if (pl >= 2 && !umma::mbar_wait(&empty_kv[st], ((pl - 2) >> 1) & 1, abort_flag)) break;
+                    tma::expect_tx(&full_kv[st], tc::Q_BYTES + tc::V_BYTES);
+                    tma::load_panel(sK + st * tc::Q_BYTES, &p.tm_k, 0, grp, row0, &full_kv[st]);
+                    tma::load_panel(sK + st * tc::Q_BYTES + tc::Q_BYTES / 2, &p.tm_k, 64, grp, row0, &full_kv[st]);
+                    tma::load_panel(sV + st * tc::V_BYTES, &p.tm_v, 0, h, row0, &full_kv[st]);
+                    if (pl >= 1 && !umma::mbar_wait(empty_q, (pl - 1) & 1, abort_flag)) break;
+                    tma::expect_tx(full_q, tc::Q_BYTES);
+                    tma::load_panel(sQ, &p.tm_q, 0, grp, row0, full_q);
+                    tma::load_panel(sQ + tc::Q_BYTES / 2, &p.tm_q, 64, grp, row0, full_q);
+                }
+            }
+            return;
+        }
+        if (warp > tc::MMA_WARP) return;
+        umma::tmem_alloc(tmem_slot, tc::TM_COLS);
+        umma::fence_before_sync();
+        bar_work();                                  // publishes the tensor-memory base address
+        umma::fence_after_sync();
+        const uint32_t tbase = *tmem_slot;
+        for (int pl = 0; pl < npairs; ++pl) {
+            const int st = pl & 1;
+            const uint32_t aQ = umma::smem_addr(sQ), aK = umma::smem_addr(sK + st * tc::Q_BYTES);
+            const uint32_t aV = umma::smem_addr(sV + st * tc::V_BYTES);
+            bar_work();                              // barrier 1: tiles and decay tables of this pair are in place
+            umma::fence_after_sync();
+            if (lane == 0) {
+                umma::mbar_wait(full_q, pl & 1, abort_flag);
+                umma::mbar_wait(&full_kv[st], (pl >> 1) & 1, abort_flag);
+                umma::gemm_kk<tc::PT, tc::PT, tc::KD>(tbase + tc::TM_S, aQ, aK, ID_S, false);
+                umma::commit(&bars[0]);
+                int slot = 0;
+#pragma unroll
+                for (int lv = 0; lv < MP; ++lv)
+                    if ((pl >> lv) & 1) {
+                        umma::gemm_km<tc::PT, tc::KD, tc::KD>(tbase + (slot == 0 ? tc::TM_T0 : tc::TM_T1), aQ,
+                                                              umma::smem_addr(sH + lv * tc::H_BYTES), ID_KM, false);
+                        ++slot;
+                    }
+                if (slot > 0) umma::commit(&bars[1]);
+                umma::commit(empty_q);               // q tile may be overwritten once S and the level reads are done
+            }
+            __syncwarp();
+            umma::fence_before_sync();
+            bar_work();                              // barrier 2: P and Vs are written
+            umma::fence_after_sync();
+            if (lane == 0) {
+                umma::gemm_km<tc::PT, tc::PT, tc::PT>(tbase + tc::TM_O, umma::smem_addr(sP), aV, ID_KM, false);
+                umma::commit(&bars[2]);
+                umma::gemm_mm<tc::PT, tc::PT, tc::PT>(tbase + tc::TM_KV, aK, umma::smem_addr(sVs), ID_MM, false);
+                umma::commit(&bars[3]);
+                umma::commit(&empty_kv[st]);         // k / v stage may be refilled
+            }
+            __syncwarp();
+            umma::fence_before_sync();
+            bar_work();                              // barrier 3: end of the pair
+            umma::fence_after_sync();
+            if (*abort_flag) break;
+        }
+        if (*abort_flag && lane == 0) atomicExch(p.err, 1);
+        umma::fence_before_sync();
+        bar_work();                                  // everybody is done with tensor memory
+        umma::tmem_dealloc(tbase, tc::TM_COLS);
+        return;
+    }
+
+    // ================= warps 0..7: loads, decay / mask / lambda, outputs, level states =================
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 232;\n");
+    const int rb = warp & 3;                         // 32-row block of this thread's tensor-memory lane
+    const int row = rb * 32 + lane;
+    const int ch = warp >> 2;                        // column half handled by this thread
+
+    // lambda rows of the pair (two threads per row, staged through shared memory) and raw g of the
+    // pair (warps 0 and 1), fetched one pair ahead
+    float g_n[4];
+    constexpr int LAMR = (tc::PT * tc::MAX_L_TC) / 256;   // elements per thread, consecutive threads on consecutive elements
+    uint32_t lam_r[LAMR];                            // one 32-bit register per 16-bit element
+    uint32_t lam_rc[LAMR];                           // (row << 8) | column of each element, 0xffffffff = none
+#pragma unroll
+    for (int i = 0; i < LAMR; ++i) {
+        const int e = tid + i * 256;
+        const int rr = e / L, cc = e - rr * L;
+        lam_rc[i] = (rr < tc::PT) ? (uint32_t)((rr << 8) | cc) : 0xffffffffu;
+    }
+    auto fetch_small = [&](int pl) {
         const long t0 = (long)(r * SEGP + pl) * tc::PT;
-        load_tile_swz<tc::KD>(sQ + st * tc::Q_BYTES, p.q + (((long)b * p.T + t0) * p.G + grp) * tc::KD, (long)p.G * tc::KD, tid);
-        load_tile_swz<tc::VD>(sV + st * tc::V_BYTES, p.v + (((long)b * p.T + t0) * p.H + h) * tc::VD, (long)p.H * tc::VD, tid);
-        cp_async_commit();
+        const unsigned short* lp = reinterpret_cast<const unsigned short*>(p.l) + (((long)b * p.T + t0) * p.H + h) * L;
+#pragma unroll
+        for (int i = 0; i < LAMR; ++i)
+            if (lam_rc[i] != 0xffffffffu) lam_r[i] = lp[(long)(lam_rc[i] >> 8) * p.H * L + (lam_rc[i] & 255)];
+        if (warp < 2) {
+            const float* gp = p.g + ((long)b * p.T + t0 + 4 * lane) * p.H + h;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) g_n[i] = gp[(long)i * p.H];
+        }
     };
-    auto issue_k = [&](int pl) {
-        const long t0 = (long)(r * SEGP + pl) * tc::PT;
-        load_tile_swz<tc::KD>(sK, p.k + (((long)b * p.T + t0) * p.G + grp) * tc::KD, (long)p.G * tc::KD, tid);
-        cp_async_commit();
+    auto store_lam = [&]() {
+#pragma unroll
+        for (int i = 0; i < LAMR; ++i)
+            if (lam_rc[i] != 0xffffffffu)
+                sLam[(lam_rc[i] >> 8) * tc::LAM_LD + (lam_rc[i] & 255)] = __ushort_as_bfloat16((unsigned short)lam_r[i]);
     };
-    issue_qv(0, 0);
-    issue_k(0);
+    fetch_small(0);
+    store_lam();
     umma::fence_before_sync();
-    __syncthreads();
+    bar_work();
     umma::fence_after_sync();
     const uint32_t tbase = *tmem_slot;
 
@@ -113,71 +246,82 @@ __global__ void __launch_bounds__(256, 1) m2_chunk_fwd_tc_kernel(const Mamba2Par
 #pragma unroll
     for (int i = 0; i < (MP > 0 ? MP : 1); ++i) dsum[i] = 0.f;
     uint32_t phS = 0, phT = 0, phO = 0, phKV = 0;
-    bool ok = true;
-
-    constexpr uint32_t ID_S = umma::idesc_bf16(128, 128, false, false);
-    constexpr uint32_t ID_KM = umma::idesc_bf16(128, 64, false, true);
-    constexpr uint32_t ID_MM = umma::idesc_bf16(128, 64, true, true);
 
     for (int pl = 0; pl < npairs; ++pl) {
+#ifdef LLATTN_STAMPS
+        int nstamp = 0;
+        const int stamp_slot = (blockIdx.x == 300 && pl == 2) ? (tid == 0 ? 0 : (tid == 200 ? 1 : (tid == 96 ? 2 : -1))) : -1;
+#endif
+        STAMP();                                     // 0: top of the pair
         const int st = pl & 1;
         const long t0 = (long)(r * SEGP + pl) * tc::PT;
-        // lambda of this thread's row: levels 0..7 (inside the pair) and the low pair levels
-        float lam[8 + (MP > 0 ? MP : 1)];
-        {
-            const bf16* lp = p.l + (((long)b * p.T + t0 + row) * p.H + h) * L;
+        float gq[4];
 #pragma unroll
-            for (int i = 0; i < 8 + MP; ++i) lam[i] = (i < L) ? __bfloat162float(lp[i]) : 0.f;
+        for (int i = 0; i < 4; ++i) gq[i] = g_n[i];
+        if (pl + 1 < npairs) fetch_small(pl + 1);
+        // partial output of the high levels for this thread's row / column half (issued early, used late)
+        uint4 ohi[4];
+        if (hi_init) {
+            // scratch layout [batch*head][pair][8-column chunk][128 rows][8]: a warp reads 512 contiguous bytes
+            const bf16* gh = p.o_hi + ((((long)b * p.H + h) * (p.NT / 2) + (r * SEGP + pl)) * 8 + ch * 4) * (tc::PT * 8) + row * 8;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) ohi[c] = *reinterpret_cast<const uint4*>(gh + c * tc::PT * 8);
         }
-        cp_async_wait<0>();
-        if (pl + 1 < npairs) issue_qv(pl + 1, st ^ 1);
-        // in-chunk cumulative sums of g (output) and the pair-wide cumulative sum
+        STAMP();                                     // 1: small fetches issued
+        umma::mbar_wait(full_q, pl & 1, abort_flag);
+        umma::mbar_wait(&full_kv[st], (pl >> 1) & 1, abort_flag);
+        STAMP();                                     // 2: tiles landed
+        // cumulative sums of g: both warps scan the pair, each publishes one chunk
         if (warp < 2) {
-            const float* gp = p.g + ((long)b * p.T + t0 + warp * CH) * p.H + h;
-            float x0 = gp[(long)(2 * lane) * p.H], x1 = gp[(long)(2 * lane + 1) * p.H];
-            warp_cumsum64(x0, x1, lane);
-            float* gc = p.g_cum + ((long)b * p.T + t0 + warp * CH) * p.H + h;
-            gc[(long)(2 * lane) * p.H] = x0;
-            gc[(long)(2 * lane + 1) * p.H] = x1;
-            sGp[warp * CH + 2 * lane] = x0;
-            sGp[warp * CH + 2 * lane + 1] = x1;
+            gq[1] += gq[0];
+            gq[2] += gq[1];
+            gq[3] += gq[2];
+            float tot = gq[3];                       // inclusive scan of lane totals inside each chunk (16 lanes)
+#pragma unroll
+            for (int d = 1; d < 16; d <<= 1) {
+                const float t = __shfl_up_sync(0xffffffffu, tot, d);
+                if ((lane & 15) >= d) tot += t;
+            }
+            const float gla = __shfl_sync(0xffffffffu, tot, 15);        // end of the first chunk
+            const float glb = __shfl_sync(0xffffffffu, tot, 31);        // end of the second chunk (in-chunk)
+            const float glp = gla + glb;
+            const float cbase = tot - gq[3];                            // in-chunk exclusive prefix of this lane
+            const float pbase = cbase + (lane >= 16 ? gla : 0.f);       // pair-wide
+            const float gend = __shfl_sync(0xffffffffu, tot, (lane & ~7) + 7) + (lane >= 16 ? gla : 0.f);
+            if ((lane >> 4) == warp) {
+                float* gc = p.g_cum + ((long)b * p.T + t0 + 4 * lane) * p.H + h;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float G = pbase + gq[i];
+                    sGp[4 * lane + i] = G;
+                    sCf[4 * lane + i] = fexp(gend - G);
+                    sVf[4 * lane + i] = fexp(glp - G);
+                    gc[(long)i * p.H] = cbase + gq[i];
+                }
+            }
         }
         umma::fence_async_smem();
         umma::fence_before_sync();
-        __syncthreads();
+        bar_work();                                  // barrier 1
         umma::fence_after_sync();
-        const uint32_t aQ = umma::smem_addr(sQ + st * tc::Q_BYTES), aK = umma::smem_addr(sK);
-        const uint32_t aV = umma::smem_addr(sV + st * tc::V_BYTES);
+        STAMP();                                     // 3: after barrier 1
         int nread = 0;
 #pragma unroll
         for (int lv = 0; lv < MP; ++lv) nread += (pl >> lv) & 1;
-        if (tid == 0) {
-            umma::gemm_kk(tbase + tc::TM_S, aQ, tc::PT, aK, tc::PT, tc::KD, ID_S, false);
-            umma::commit(&bars[0]);
-            if (nread > 0) {
-                int slot = 0;
+        const float Gi = sGp[row];
+        const float glp = sGp[tc::PT - 1];
+        // this row's lambda: levels 0..7 inside the pair, then the low pair levels
+        float lam[NLAM];
 #pragma unroll
-                for (int lv = 0; lv < MP; ++lv)
-                    if ((pl >> lv) & 1) {
-                        umma::gemm_km(tbase + (slot == 0 ? tc::TM_T0 : tc::TM_T1), aQ, tc::PT,
-                                      umma::smem_addr(sH + lv * tc::H_BYTES), tc::KD, tc::KD, ID_KM, false);
-                        ++slot;
-                    }
-                umma::commit(&bars[1]);
-            }
-        }
-        // pair-wide cumulative decay: second chunk continues from the end of the first
-        const float gla = sGp[CH - 1];
-        const float Gi = sGp[row] + (row >= CH ? gla : 0.f);
-        const float glp = gla + sGp[2 * CH - 1];
+        for (int i = 0; i < NLAM; ++i) lam[i] = (i < L) ? __bfloat162float(sLam[row * tc::LAM_LD + i]) : 0.f;
 
-        // ---- Vs = v * exp(glp - Gp_j)   (same swizzled offsets as v)
+        // ---- Vs = v * exp(glp - G_j)   (same swizzled offsets as v)
         {
             const unsigned char* cV = sV + st * tc::V_BYTES;
 #pragma unroll
             for (int i = tid; i < tc::PT * (tc::VD / 8); i += 256) {
                 const int j = i / (tc::VD / 8), c = (i % (tc::VD / 8)) * 8;
-                const float sc = fexp(glp - (sGp[j] + (j >= CH ? gla : 0.f)));
+                const float sc = sVf[j];
                 const uint32_t off = umma::tile_offset(j, c, tc::PT);
                 uint4 x = *reinterpret_cast<const uint4*>(cV + off);
                 uint32_t* xw = reinterpret_cast<uint32_t*>(&x);
@@ -189,64 +333,82 @@ __global__ void __launch_bounds__(256, 1) m2_chunk_fwd_tc_kernel(const Mamba2Par
                 *reinterpret_cast<uint4*>(sVs + off) = x;
             }
         }
-        // ---- S -> P (bf16, K-major A operand of P v).  This thread: row `row`, 32-column blocks ch and ch+2
-        ok = umma::mbar_wait(&bars[0], phS, abort_flag);
+        STAMP();                                     // 4: Vs written
+        // ---- wait for S (and the level reads); the q tile is then free for the next pair
+        umma::mbar_wait(&bars[0], phS, abort_flag);
         phS ^= 1;
+        if (nread > 0) {
+            umma::mbar_wait(&bars[1], phT, abort_flag);
+            phT ^= 1;
+        }
         umma::fence_after_sync();
+        STAMP();                                     // 5: S (and T) complete
+        STAMP();                                     // 6
+        // ---- S -> P (bf16, K-major A operand of P v).  This thread: row `row`, and in every 32-column
+        //      block jb <= rb the 16 columns [jb*32 + ch*16, +16)
 #pragma unroll
-        for (int blk = 0; blk < 2; ++blk) {
-            const int j0 = (ch + 2 * blk) * 32;
-            uint32_t packed[16];
-            if (j0 > row) {
+        for (int jb = 0; jb < 4; ++jb) {
+            const int j0 = jb * 32 + ch * 16;
+            uint32_t packed[8];
+            if (jb > rb) {
 #pragma unroll
-                for (int e = 0; e < 16; ++e) packed[e] = 0u;
+                for (int e = 0; e < 8; ++e) packed[e] = 0u;
             } else {
-                float s[32];
-                umma::tmem_ld32(umma::tmem_addr(tbase + tc::TM_S, warp, j0), s);
+                float s[16];
+                umma::tmem_ld16(umma::tmem_addr(tbase + tc::TM_S, warp, j0), s);
+                if (jb < rb) {
+                    // block below the diagonal: one level, decay factorised through the block end
+                    const float lm = ((rb ^ jb) == 1) ? lam[6] : lam[7];
+                    const float rf = lm * fexp(Gi - sGp[jb * 32 + 31]);
 #pragma unroll
-                for (int e = 0; e < 32; e += 2) {
-                    float pv[2];
-#pragma unroll
-                    for (int u = 0; u < 2; ++u) {
-                        const int j = j0 + e + u;
-                        float val = 0.f;
-                        if (j <= row) {
-                            const float Gj = sGp[j] + (j >= CH ? gla : 0.f);
-                            const int lev = level_of(row, j);
-                            float lm = lam[0];
-#pragma unroll
-                            for (int q = 1; q < 8; ++q) lm = (lev == q) ? lam[q] : lm;
-                            val = s[e + u] * fexp(Gi - Gj) * lm;
-                        }
-                        pv[u] = val;
+                    for (int e = 0; e < 16; e += 4) {
+                        const float4 cf = *reinterpret_cast<const float4*>(sCf + j0 + e);
+                        packed[e >> 1] = pack_bf16(s[e] * rf * cf.x, s[e + 1] * rf * cf.y);
+                        packed[(e >> 1) + 1] = pack_bf16(s[e + 2] * rf * cf.z, s[e + 3] * rf * cf.w);
                     }
-                    packed[e >> 1] = pack_bf16(pv[0], pv[1]);
+                } else {
+                    // diagonal block: levels 0..5, causal mask folded into the exponent
+                    const int li = lane;             // row - jb*32
+#pragma unroll
+                    for (int e = 0; e < 16; e += 4) {
+                        const float4 gj = *reinterpret_cast<const float4*>(sGp + j0 + e);
+                        const float gjv[4] = {gj.x, gj.y, gj.z, gj.w};
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) {
+                            const int jj = ch * 16 + e + u;      // column inside the block
+                            const int x = li ^ jj;
+                            float lm = lam[0];
+                            lm = (x >= 1) ? lam[1] : lm;
+                            lm = (x >= 2) ? lam[2] : lm;
+                            lm = (x >= 4) ? lam[3] : lm;
+                            lm = (x >= 8) ? lam[4] : lm;
+                            lm = (x >= 16) ? lam[5] : lm;
+                            const float d = (jj <= li) ? (Gi - gjv[u]) : -INFINITY;
+                            s[e + u] = s[e + u] * fexp(d) * lm;
+                        }
+                        packed[e >> 1] = pack_bf16(s[e], s[e + 1]);
+                        packed[(e >> 1) + 1] = pack_bf16(s[e + 2], s[e + 3]);
+                    }
                 }
             }
 #pragma unroll
-            for (int c = 0; c < 4; ++c)
+            for (int c = 0; c < 2; ++c)
                 *reinterpret_cast<uint4*>(sP + umma::tile_offset(row, j0 + c * 8, tc::PT)) =
                     make_uint4(packed[c * 4], packed[c * 4 + 1], packed[c * 4 + 2], packed[c * 4 + 3]);
         }
+        STAMP();                                     // 7: P written
         umma::fence_async_smem();
         umma::fence_before_sync();
-        __syncthreads();
+        bar_work();                                  // barrier 2
         umma::fence_after_sync();
-        if (tid == 0) {
-            umma::gemm_km(tbase + tc::TM_O, umma::smem_addr(sP), tc::PT, aV, tc::PT, tc::PT, ID_KM, false);
-            umma::commit(&bars[2]);
-            umma::gemm_mm(tbase + tc::TM_KV, aK, tc::PT, umma::smem_addr(sVs), tc::PT, tc::PT, ID_MM, false);
-            umma::commit(&bars[3]);
-        }
+        STAMP();                                     // 8: after barrier 2
 
         // ---- output row of this thread: columns ch*32 .. +31
         float o[32];
-        bf16* go = p.o + (((long)b * p.T + t0 + row) * p.H + h) * tc::VD + ch * 32;
         if (hi_init) {
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
-                uint4 x = *reinterpret_cast<const uint4*>(go + c * 8);
-                const uint32_t* xw = reinterpret_cast<const uint32_t*>(&x);
+                const uint32_t* xw = reinterpret_cast<const uint32_t*>(&ohi[c]);
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     __nv_bfloat162 v2 = *reinterpret_cast<const __nv_bfloat162*>(&xw[e]);
@@ -258,10 +420,7 @@ __global__ void __launch_bounds__(256, 1) m2_chunk_fwd_tc_kernel(const Mamba2Par
 #pragma unroll
             for (int e = 0; e < 32; ++e) o[e] = 0.f;
         }
-        if (nread > 0 && ok) {
-            ok = umma::mbar_wait(&bars[1], phT, abort_flag);
-            phT ^= 1;
-            umma::fence_after_sync();
+        if (nread > 0) {
             int slot = 0;
 #pragma unroll
             for (int lv = 0; lv < MP; ++lv)
@@ -274,29 +433,39 @@ __global__ void __launch_bounds__(256, 1) m2_chunk_fwd_tc_kernel(const Mamba2Par
                     ++slot;
                 }
         }
-        if (ok) {
-            ok = umma::mbar_wait(&bars[2], phO, abort_flag);
+        STAMP();                                     // 9: level reads accumulated
+        {
+            umma::mbar_wait(&bars[2], phO, abort_flag);
             phO ^= 1;
             umma::fence_after_sync();
             float t[32];
             umma::tmem_ld32(umma::tmem_addr(tbase + tc::TM_O, warp, ch * 32), t);
+            // P v has completed, so the P tile is free: stage the bf16 output rows there and copy
+            // them out with 8 lanes per 128-byte row (coalesced) instead of one row per lane
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 uint4 x;
                 uint32_t* xw = reinterpret_cast<uint32_t*>(&x);
 #pragma unroll
                 for (int e = 0; e < 4; ++e) xw[e] = pack_bf16(o[c * 8 + e * 2] + t[c * 8 + e * 2], o[c * 8 + e * 2 + 1] + t[c * 8 + e * 2 + 1]);
-                *reinterpret_cast<uint4*>(go + c * 8) = x;
+                *reinterpret_cast<uint4*>(sP + umma::tile_offset(row, ch * 32 + c * 8, tc::PT)) = x;
+            }
+            asm volatile("bar.sync 2, 256;\n" ::: "memory");
+            bf16* go = p.o + (((long)b * p.T + t0) * p.H + h) * tc::VD;
+#pragma unroll
+            for (int i = tid; i < tc::PT * 8; i += 256) {
+                const int rr = i >> 3, c = (i & 7) * 8;
+                *reinterpret_cast<uint4*>(go + (long)rr * p.H * tc::VD + c) =
+                    *reinterpret_cast<const uint4*>(sP + umma::tile_offset(rr, c, tc::PT));
             }
         }
+        STAMP();                                     // 10: output stored
         // ---- pair summary and the Fenwick carry over pair levels (thread = state row `row`)
-        if (ok) {
-            ok = umma::mbar_wait(&bars[3], phKV, abort_flag);
-            phKV ^= 1;
-            umma::fence_after_sync();
-        }
-        if (pl + 1 < npairs) issue_k(pl + 1);        // k tile is free once S and KV are done
-        if (MP > 0 && pl + 1 < npairs && ok) {
+        umma::mbar_wait(&bars[3], phKV, abort_flag);
+        STAMP();                                     // 11: pair summary complete
+        phKV ^= 1;
+        umma::fence_after_sync();
+        if (MP > 0 && pl + 1 < npairs) {
             const int j = __ffs(~pl) - 1;
             if (j < MP) {
                 float kv[32];
@@ -329,25 +498,37 @@ __global__ void __launch_bounds__(256, 1) m2_chunk_fwd_tc_kernel(const Mamba2Par
                 for (int lv = 0; lv < MP; ++lv) dsum[lv] += glp;
             }
         }
+        if (pl + 1 < npairs) store_lam();            // every read of this pair's lambda is done (barrier 2)
+        STAMP();                                     // 12: states merged
+        umma::fence_async_smem();
         umma::fence_before_sync();
-        __syncthreads();
+        bar_work();                                  // barrier 3
         umma::fence_after_sync();
+        STAMP();                                     // 13: after barrier 3
         if (*abort_flag) break;                      // uniform: read after the barrier
     }
-    if (*abort_flag && tid == 0) atomicExch(p.err, 1);
-    cp_async_wait<0>();
     umma::fence_before_sync();
-    __syncthreads();
-    if (warp == 0) umma::tmem_dealloc(tbase, tc::TM_COLS);
+    bar_work();
 }
 
-int mamba2_fwd_tc_launch(const Mamba2Params& p, cudaStream_t stream) {
+int mamba2_fwd_tc_launch(const Mamba2Params& p_in, cudaStream_t stream) {
+    Mamba2Params p = p_in;
+    int rc;
+    if ((rc = tma::make_panel_map(&p.tm_q, p.q, (long)p.B * p.T, p.G, p.K, tc::PT)) != 0) return rc;
+    if ((rc = tma::make_panel_map(&p.tm_k, p.k, (long)p.B * p.T, p.G, p.K, tc::PT)) != 0) return rc;
+    if ((rc = tma::make_panel_map(&p.tm_v, p.v, (long)p.B * p.T, p.H, p.V, tc::PT)) != 0) return rc;
     auto kern = m2_chunk_fwd_tc_kernel<M2_MLOW>;
     const size_t sm = FwdTcSmem<M2_MLOW>::total;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
     if (e != cudaSuccess) return (int)e;
-    kern<<<p.B * p.H * p.NS, 256, sm, stream>>>(p);
+    kern<<<p.B * p.H * p.NS, tc::NTHREADS, sm, stream>>>(p);
     return (int)cudaGetLastError();
 }
 
 }  // namespace llattn
+
+#ifdef LLATTN_STAMPS
+extern "C" int llattn_debug_read_stamps(long long* host_dst) {
+    return (int)cudaMemcpyFromSymbol(host_dst, llattn::g_stamps, sizeof(long long) * 3 * 32);
+}
+#endif

@@ -1,0 +1,50 @@
+// Tensor Memory Accelerator helpers: host-side tensor-map construction for (rows, heads, columns)
+// tensors and the device-side bulk tensor load (no multicast) with mbarrier transaction counting.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace llattn {
+namespace tma {
+
+// A (BT, NH, C) bf16 tensor (C contiguous) seen as a rank-3 map; a box is 64 columns x 1 head x
+// `box_rows` rows, 128-byte swizzled: exactly one 64-column panel of a shared-memory operand tile.
+inline int make_panel_map(CUtensorMap* out, const void* base, long BT, int NH, int C, int box_rows) {
+    typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                 const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static EncodeFn fn = nullptr;
+    if (!fn) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres);
+        if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || !ptr) return 999;
+        fn = reinterpret_cast<EncodeFn>(ptr);
+    }
+    const cuuint64_t dims[3] = {(cuuint64_t)C, (cuuint64_t)NH, (cuuint64_t)BT};
+    const cuuint64_t strides[2] = {(cuuint64_t)C * 2, (cuuint64_t)NH * C * 2};
+    const cuuint32_t box[3] = {64, 1, (cuuint32_t)box_rows};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : 1000 + (int)r;
+}
+
+#ifdef __CUDACC__
+__device__ __forceinline__ void expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"((uint32_t)__cvta_generic_to_shared(bar)), "r"(bytes) : "memory");
+}
+// one panel: columns [col0, col0+64) of head `head`, rows [row0, row0 + box_rows); col0 * 2 bytes must be a multiple of 16
+__device__ __forceinline__ void load_panel(void* smem_dst, const CUtensorMap* map, int col0, int head, int row0, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];\n"
+        ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(map), "r"(col0), "r"(head), "r"(row0),
+          "r"((uint32_t)__cvta_generic_to_shared(bar))
+        : "memory");
+}
+#endif
+
+}  // namespace tma
+}  // namespace llattn

@@ -66,8 +66,42 @@ __device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_
         : "memory");
 }
 
-// D[128 x N] (+)= A[128 x kred] * B[kred x N], both operands K-major tiles (rows = M or N index)
-// a_rows / b_rows: number of rows of the stored tiles (panel stride = rows * 128 bytes)
+// The three operand-layout combinations.  Tile row counts and the reduction length are template
+// parameters so that every descriptor is "base + constant"; the start-address field occupies the
+// low 14 bits (16-byte units) and shared memory addresses stay below 256 KB, so adding a byte
+// offset >> 4 to the 64-bit descriptor never carries into another field.
+//
+// D[128 x N] (+)= A[128 x KRED] * B[N x KRED]^T : both operands K-major tiles (rows = M / N index)
+template <int A_ROWS, int B_ROWS, int KRED>
+__device__ __forceinline__ void gemm_kk(uint32_t d_tmem, uint32_t a_saddr, uint32_t b_saddr, uint32_t idesc, bool accumulate) {
+    const uint64_t da = desc_kmajor(a_saddr), db = desc_kmajor(b_saddr);
+#pragma unroll
+    for (int kk = 0; kk < KRED; kk += 16) {
+        const uint32_t ka = (kk >> 6) * A_ROWS * ROW_BYTES + (kk & 63) * 2;
+        const uint32_t kb = (kk >> 6) * B_ROWS * ROW_BYTES + (kk & 63) * 2;
+        mma_ss(d_tmem, da + (ka >> 4), db + (kb >> 4), idesc, accumulate || kk > 0);
+    }
+}
+// A K-major tile (rows = M index), B stored [KRED rows][N cols] (MN-major)
+template <int A_ROWS, int B_ROWS, int KRED>
+__device__ __forceinline__ void gemm_km(uint32_t d_tmem, uint32_t a_saddr, uint32_t b_saddr, uint32_t idesc, bool accumulate) {
+    const uint64_t da = desc_kmajor(a_saddr), db = desc_mnmajor(b_saddr, B_ROWS * ROW_BYTES);
+#pragma unroll
+    for (int kk = 0; kk < KRED; kk += 16) {
+        const uint32_t ka = (kk >> 6) * A_ROWS * ROW_BYTES + (kk & 63) * 2;
+        mma_ss(d_tmem, da + (ka >> 4), db + ((kk * ROW_BYTES) >> 4), idesc, accumulate || kk > 0);
+    }
+}
+// A stored [KRED rows][M cols], B stored [KRED rows][N cols] (both MN-major): D = A^T B
+template <int A_ROWS, int B_ROWS, int KRED>
+__device__ __forceinline__ void gemm_mm(uint32_t d_tmem, uint32_t a_saddr, uint32_t b_saddr, uint32_t idesc, bool accumulate) {
+    const uint64_t da = desc_mnmajor(a_saddr, A_ROWS * ROW_BYTES), db = desc_mnmajor(b_saddr, B_ROWS * ROW_BYTES);
+#pragma unroll
+    for (int kk = 0; kk < KRED; kk += 16) {
+        mma_ss(d_tmem, da + ((kk * ROW_BYTES) >> 4), db + ((kk * ROW_BYTES) >> 4), idesc, accumulate || kk > 0);
+    }
+}
+// run-time sized variants (self-test)
 __device__ __forceinline__ void gemm_kk(uint32_t d_tmem, uint32_t a_saddr, int a_rows, uint32_t b_saddr, int b_rows,
                                         int kred, uint32_t idesc, bool accumulate) {
     for (int kk = 0; kk < kred; kk += 16) {
@@ -76,7 +110,6 @@ __device__ __forceinline__ void gemm_kk(uint32_t d_tmem, uint32_t a_saddr, int a
         mma_ss(d_tmem, desc_kmajor(a_saddr + ka), desc_kmajor(b_saddr + kb), idesc, accumulate || kk > 0);
     }
 }
-// A K-major tile (rows = M index), B stored [kred rows][N cols] (MN-major)
 __device__ __forceinline__ void gemm_km(uint32_t d_tmem, uint32_t a_saddr, int a_rows, uint32_t b_saddr, int b_rows,
                                         int kred, uint32_t idesc, bool accumulate) {
     for (int kk = 0; kk < kred; kk += 16) {
@@ -85,7 +118,6 @@ __device__ __forceinline__ void gemm_km(uint32_t d_tmem, uint32_t a_saddr, int a
                accumulate || kk > 0);
     }
 }
-// A stored [kred rows][M cols], B stored [kred rows][N cols] (both MN-major): D = A^T B
 __device__ __forceinline__ void gemm_mm(uint32_t d_tmem, uint32_t a_saddr, int a_rows, uint32_t b_saddr, int b_rows,
                                         int kred, uint32_t idesc, bool accumulate) {
     for (int kk = 0; kk < kred; kk += 16) {
@@ -162,6 +194,20 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
 #pragma unroll
     for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+// 16 consecutive fp32 columns of this thread's lane
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
+    uint32_t r[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
     asm volatile(
