@@ -86,6 +86,18 @@ int llattn_mamba2_bwd(const void* q, const void* k, const void* v, const float* 
                       void* workspace, size_t workspace_bytes,
                       int B, int T, int H, int G, int K, int V, int L, void* stream);
 
+/* Log-linear Gated DeltaNet forward.  Replaces hattention.chunkwise_hgdn.chunkwise_fwd
+ * (hattention/chunkwise_hgdn.py:566-788) with output_final_state=False.  q and k are per head,
+ * (B,T,H,K), and must already be L2-normalised (q also scaled) as the reference's autograd
+ * function does before the call (hattention/kernel.py:110-111); beta is (B,T,H) bf16; g is the raw
+ * log decay.  Writes o, the in-chunk cumulative g, and the two 64x64 UT-transform inverses per
+ * chunk, Aw and Au, as (B,T,H,64) bf16 (the reference returns and saves them for the backward).
+ * Constraints: T % 64 == 0, K == 128, V in {64,128}, 7 + ceil(log2(T/64)) <= L <= 32, T <= 16384. */
+size_t llattn_gdn_fwd_workspace_bytes(int B, int T, int H, int K, int V, int L);
+int llattn_gdn_fwd(const void* q, const void* k, const void* v, const void* beta, const float* g, const void* lambda,
+                   void* o, float* g_cum, void* Aw, void* Au, void* workspace, size_t workspace_bytes,
+                   int B, int T, int H, int K, int V, int L, void* stream);
+
 /* Diagnostic: one 128 x N x kred bf16 tensor-core product (tcgen05.mma, accumulator in tensor
  * memory) per operand-layout combination used by the kernels: mode 0: D = A B^T with A [128][kred],
  * B [N][kred]; mode 1: D = A B with B [kred][N]; mode 2: D = A^T B with A [kred][128], B [kred][N].

@@ -1,6 +1,7 @@
 // extern "C" entry points of libllattn.so: argument checks, workspace carving, launches.
 #include <stdint.h>
 
+#include "llattn_gdn.h"
 #include "llattn_mamba2.h"
 
 namespace {
@@ -178,6 +179,54 @@ int llattn_mamba2_bwd(const void* q, const void* k, const void* v, const float* 
     llattn::cast_f32_to_bf16(p.dq_acc, dq, (long)nqk, st);
     llattn::cast_f32_to_bf16(p.dk_acc, dk, (long)nqk, st);
     return (int)cudaGetLastError();
+}
+
+// ---------------------------------------------------------------- Gated DeltaNet
+static int gdn_check(int B, int T, int H, int K, int V, int L) {
+    if (B <= 0 || T <= 0 || H <= 0) return LLATTN_ERR_UNSUPPORTED_SHAPE;
+    if (T % 64 != 0) return LLATTN_ERR_BAD_LENGTH;
+    if (!(K == 128 && (V == 64 || V == 128))) return LLATTN_ERR_UNSUPPORTED_SHAPE;
+    if (L > 32) return LLATTN_ERR_UNSUPPORTED_SHAPE;
+    const int nlev = ceil_log2i(T / 64);
+    if (nlev > 8) return LLATTN_ERR_UNSUPPORTED_SHAPE;
+    if (L < 7 + nlev) return LLATTN_ERR_TOO_FEW_LEVELS;
+    return 0;
+}
+
+static size_t gdn_setup(llattn::GdnParams& p, void* ws) {
+    p.NT = p.T / 64;
+    p.NLEV = ceil_log2i(p.NT);
+    Carver c(ws);
+    const size_t n = (size_t)p.B * p.T * p.H;
+    p.kd = c.take<__nv_bfloat16>(n * p.K);
+    p.wd = c.take<__nv_bfloat16>(n * p.K);
+    p.qd = c.take<__nv_bfloat16>(n * p.K);
+    p.u = c.take<__nv_bfloat16>(n * p.V);
+    return c.off;
+}
+
+size_t llattn_gdn_fwd_workspace_bytes(int B, int T, int H, int K, int V, int L) {
+    if (gdn_check(B, T, H, K, V, L) != 0) return 0;
+    llattn::GdnParams p = {};
+    p.B = B; p.T = T; p.H = H; p.K = K; p.V = V; p.L = L;
+    return gdn_setup(p, nullptr);
+}
+
+int llattn_gdn_fwd(const void* q, const void* k, const void* v, const void* beta, const float* g, const void* lambda,
+                   void* o, float* g_cum, void* Aw, void* Au, void* workspace, size_t workspace_bytes,
+                   int B, int T, int H, int K, int V, int L, void* stream) {
+    int rc = gdn_check(B, T, H, K, V, L);
+    if (rc != 0) return rc;
+    if (!q || !k || !v || !beta || !g || !lambda || !o || !g_cum || !Aw || !Au) return LLATTN_ERR_NULL;
+    llattn::GdnParams p = {};
+    p.B = B; p.T = T; p.H = H; p.K = K; p.V = V; p.L = L;
+    const size_t need = gdn_setup(p, nullptr);
+    if (!workspace || workspace_bytes < need || ((uintptr_t)workspace & 255)) return LLATTN_ERR_WORKSPACE;
+    gdn_setup(p, workspace);
+    p.q = (const __nv_bfloat16*)q; p.k = (const __nv_bfloat16*)k; p.v = (const __nv_bfloat16*)v;
+    p.beta = (const __nv_bfloat16*)beta; p.g = g; p.l = (const __nv_bfloat16*)lambda;
+    p.o = (__nv_bfloat16*)o; p.g_cum = g_cum; p.Aw = (__nv_bfloat16*)Aw; p.Au = (__nv_bfloat16*)Au;
+    return llattn::gdn_fwd_dispatch(p, (cudaStream_t)stream);
 }
 
 }  // extern "C"

@@ -953,6 +953,9 @@ __global__ void __launch_bounds__(256) m2_dg_kernel(const Mamba2Params p, float*
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int h = blockIdx.x % p.H, b = blockIdx.x / p.H;
     const long bh = (long)b * p.H + h;
+    // blockIdx.y selects a slice of 64 chunks for the token pass; every CTA of a (batch, head)
+    // rebuilds the small per-chunk table X (a few thousand scalar operations)
+    const int c_begin = blockIdx.y * 64, c_end = min(p.NT, c_begin + 64);
     const float* Zc = p.Zc + bh * p.NT * p.LZ;
     const float* Yc = p.Yc + bh * p.NT * (MLOW + 1);
     const float* Yseg = p.Yseg + bh * p.NS * p.LH;
@@ -1000,7 +1003,7 @@ __global__ void __launch_bounds__(256) m2_dg_kernel(const Mamba2Params p, float*
         }
     }
     __syncthreads();
-    for (int c = warp; c < p.NT; c += 8) {
+    for (int c = c_begin + warp; c < c_end; c += 8) {
         const long base = ((long)b * p.T + (long)c * CH) * p.H + h;
         float x0 = p.wq[base + (long)(63 - 2 * lane) * p.H];
         float x1 = p.wq[base + (long)(62 - 2 * lane) * p.H];
@@ -1082,7 +1085,8 @@ void mamba2_uncumsum(const float* gc, float* g, long BT, int H, cudaStream_t str
 }
 
 void mamba2_dg(const Mamba2Params& p, float* dg, cudaStream_t stream) {
-    m2_dg_kernel<M2_MLOW><<<p.B * p.H, 256, (size_t)(p.NT + p.NS) * sizeof(float), stream>>>(p, dg);
+    dim3 grid(p.B * p.H, (p.NT + 63) / 64);
+    m2_dg_kernel<M2_MLOW><<<grid, 256, (size_t)(p.NT + p.NS) * sizeof(float), stream>>>(p, dg);
 }
 
 void cast_f32_to_bf16(const float* src, void* dst, long n, cudaStream_t stream) {

@@ -1,0 +1,112 @@
+"""Host drivers of the log-linear Gated DeltaNet chunkwise path, with the interface of the
+reference's `hattention/chunkwise_hgdn.py` (`chunkwise_fwd` :566-578, `chunkwise_bwd` :799-817).
+
+`chunkwise_fwd` takes q and k already L2-normalised (q also scaled), exactly like the reference
+driver; `gdn_forward` / `gdn_backward` are what the autograd boundary calls and include the
+l2norm / scale step that the reference's `HAttentionFunction` applies around the driver
+(hattention/kernel.py:20-29, 100-120, 198-225).
+"""
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+from .base import HType, ceil_log, get_num_levels
+
+CHUNK = 64
+
+
+def l2norm_fwd(x: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
+    """x * rsqrt(sum(x^2) + eps) over the last dim, computed in fp32 (fla's l2norm_fwd)."""
+    xf = x.float()
+    return (xf * torch.rsqrt((xf * xf).sum(-1, keepdim=True) + eps)).to(x.dtype)
+
+
+def l2norm_bwd(x: torch.Tensor, dy: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
+    """Gradient of l2norm_fwd w.r.t. x: (dy - y (y . dy)) * rstd."""
+    xf, dyf = x.float(), dy.float()
+    rstd = torch.rsqrt((xf * xf).sum(-1, keepdim=True) + eps)
+    y = xf * rstd
+    return ((dyf - y * (y * dyf).sum(-1, keepdim=True)) * rstd).to(x.dtype)
+
+
+def _check(q, k, v, b, g, l, head_first, level_base, htype, chunk_size):
+    if head_first:
+        raise NotImplementedError("head_first=True is not supported")
+    if level_base != 2:
+        raise NotImplementedError("level_base must be 2")
+    if htype != HType.WEAK:
+        raise NotImplementedError("only HType.WEAK is supported")
+    if chunk_size != CHUNK:
+        raise NotImplementedError("chunk_size must be 64")
+    if not all(x.is_cuda for x in (q, k, v, b, g, l)):
+        raise RuntimeError("log-linear attention kernels need CUDA tensors (there is no CPU path)")
+    B, T, G, K = k.shape
+    _, _, H, V = v.shape
+    L = l.shape[-1]
+    if q.shape != k.shape or b.shape != (B, T, H) or g.shape != (B, T, H) or l.shape[:3] != (B, T, H):
+        raise ValueError("inconsistent shapes")
+    if H % G != 0:
+        raise ValueError(f"H={H} is not a multiple of G={G}")
+    if K > 256:
+        raise NotImplementedError("current kernel does not support head dimension larger than 256.")
+    if T % CHUNK != 0:
+        raise ValueError(f"T={T} and BT={CHUNK}")
+    if get_num_levels(CHUNK, 2) + ceil_log(T // CHUNK, 2) > L:
+        raise ValueError("not enough lambda levels for this length")
+    return B, T, H, G, K, V, L
+
+
+def chunkwise_fwd(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    b: torch.Tensor,
+    g: torch.Tensor,
+    l: torch.Tensor,
+    head_first: bool,
+    level_base: int,
+    htype: HType,
+    chunk_size: int,
+    output_final_state: bool,
+) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, Optional[torch.Tensor]]:
+    """Returns (g_cum, o, Aw, Au, None) like the reference driver (chunkwise_hgdn.py:566-788)."""
+    if output_final_state:
+        raise NotImplementedError("output_final_state=True (prefill hand-off) is not implemented")
+    B, T, H, G, K, V, L = _check(q, k, v, b, g, l, head_first, level_base, htype, chunk_size)
+    lib = _lib.lib()
+    with torch.cuda.device(q.device):
+        if G != H:   # one q/k per head, as the reference expands them (chunkwise_hgdn.py:613-620)
+            q = q.repeat_interleave(H // G, dim=2)
+            k = k.repeat_interleave(H // G, dim=2)
+        q_, k_, v_, b_, l_ = (x.to(torch.bfloat16).contiguous() for x in (q, k, v, b, l))
+        g_ = g.to(torch.float32).contiguous()
+        o = torch.empty_like(v_)
+        g_cum = torch.empty_like(g_)
+        Aw = torch.empty(B, T, H, CHUNK, dtype=torch.bfloat16, device=q.device)
+        Au = torch.empty_like(Aw)
+        n = lib.llattn_gdn_fwd_workspace_bytes(B, T, H, K, V, L)
+        if n == 0:
+            raise ValueError("unsupported GDN shape (K must be 128, V 64 or 128, T <= 16384)")
+        ws = torch.empty(n, dtype=torch.uint8, device=q.device)
+        rc = lib.llattn_gdn_fwd(q_.data_ptr(), k_.data_ptr(), v_.data_ptr(), b_.data_ptr(), g_.data_ptr(), l_.data_ptr(),
+                                o.data_ptr(), g_cum.data_ptr(), Aw.data_ptr(), Au.data_ptr(), ws.data_ptr(), ws.numel(),
+                                B, T, H, K, V, L, torch.cuda.current_stream().cuda_stream)
+        _lib.check(rc, "llattn_gdn_fwd")
+    return g_cum, o, Aw, Au, None
+
+
+def chunkwise_bwd(*args, **kwargs):
+    raise NotImplementedError("the log-linear Gated DeltaNet backward is not implemented yet")
+
+
+def gdn_forward(q, k, v, b, g, l, scale, head_first, level_base, htype, chunk_size):
+    """l2norm(q) * scale, l2norm(k), then the driver (hattention/kernel.py:109-120)."""
+    qn = (l2norm_fwd(q).float() * scale).to(q.dtype)
+    kn = l2norm_fwd(k)
+    g_cum, o, Aw, Au, _ = chunkwise_fwd(qn, kn, v, b, g, l, head_first, level_base, htype, chunk_size, False)
+    return g_cum, o, Aw, Au
+
+
+def gdn_backward(*args, **kwargs):
+    raise NotImplementedError("the log-linear Gated DeltaNet backward is not implemented yet")

@@ -18,7 +18,7 @@ so that a bf16 kernel sees exactly the same numbers):
     mamba2_c64.npz  B=1,T=512,H=2,P=64,N=64,G=1,L=10, chunk 64 : same functions
     gdn_c1.npz      B=1,T=128,H=2,Dk=Dv=16,L=8, chunk 16 : hgdn_minimal, hattention_recurrent
                     (GDELTA), autograd grads through hgdn_minimal
-    gdn_c64.npz     B=1,T=256,H=2,Dk=Dv=64,L=9, chunk 64 : same
+    gdn_c64.npz     B=1,T=256,H=2,Dk=128,Dv=64,L=9, chunk 64 : same
     levels.npz      make_levels_matrix(256) and get_num_levels for several lengths
 """
 import importlib
@@ -124,7 +124,7 @@ def main():
     mamba2_case(base, rec, hm, "mamba2_c1.npz", 1, 256, 2, 16, 16, 1, 9, 16, False)
     mamba2_case(base, rec, hm, "mamba2_c64.npz", 1, 512, 2, 64, 64, 1, 10, 64, True)
     gdn_case(base, rec, hm, "gdn_c1.npz", 1, 128, 2, 16, 16, 8, 16, False)
-    gdn_case(base, rec, hm, "gdn_c64.npz", 1, 256, 2, 64, 64, 9, 64, True)
+    gdn_case(base, rec, hm, "gdn_c64.npz", 1, 256, 2, 128, 64, 9, 64, True)
 
 
 if __name__ == "__main__":

@@ -79,3 +79,39 @@ def test_gdn_materialized_matches_recurrence():
     o1 = orc.gdn_materialized(qn, kn, v, b, g.double(), l)
     o2, _ = orc.recurrent(qn, kn, v, g.double(), l, b=b)
     assert torch.allclose(o1, o2, rtol=1e-9, atol=1e-11)
+
+
+def test_gdn_reference_rounding_points_error_level():
+    """With bf16 rounding applied exactly where the reference's GDN path rounds (q*scale, lambda/scale,
+    tril(q k^T), the UT inverse, the probability tile), an otherwise exact evaluation of the
+    intra-chunk formula differs from the fp64 recurrence by more than 2e-3 of the output scale but
+    less than 4e-3: the reason the GPU parity test uses the wider absolute tolerance."""
+    B, T, H, Dk, Dv, L = 1, 64, 2, 128, 64, 7
+    q, k, v, b, g, l = orc.make_gdn_inputs(B, T, H, Dk, Dv, L, seed=T + Dv)
+    q, k, v, b, l = (x.bfloat16().float() for x in (q, k, v, b, l))
+    scale = Dk ** -0.5
+    qn, kn = orc.gdn_layer_inputs(q.double(), k.double(), scale)
+    want, _ = orc.recurrent(qn, kn, v.double(), g.double(), l.double() / scale, b=b.double())
+
+    def r(x):
+        return x.bfloat16().float()
+
+    q32 = r(r(q * torch.rsqrt((q * q).sum(-1, keepdim=True) + 1e-6)) * scale)
+    k32 = r(k * torch.rsqrt((k * k).sum(-1, keepdim=True) + 1e-6))
+    ls = r(l / scale)
+    lev = torch.from_numpy(orc.levels_matrix(64)).clamp(min=0)
+    out = torch.zeros(B, T, H, Dv)
+    for h in range(H):
+        Q, K, V, be = q32[0, :, h], k32[0, :, h], v[0, :, h], b[0, :, h]
+        G = torch.cumsum(g[0, :, h], 0)
+        A = torch.tril(be[:, None] * (K @ K.T), -1)
+        Aw = r(torch.linalg.inv(torch.eye(64) + A))
+        QK = r(torch.tril(Q @ K.T))
+        Gam = torch.tril(torch.exp(G[:, None] - G[None, :]))
+        lam = ls[0, :, h][torch.arange(64)[:, None], lev]
+        out[0, :, h] = r((QK @ Aw) * Gam * be[None, :] * lam) @ V
+    err = (out.double() - want).abs()
+    scale_o = max(1.0, want.abs().max().item())
+    worst = lambda atol: (err / (2e-2 * want.abs() + atol * scale_o)).max().item()
+    assert worst(2e-3) > 1.0
+    assert worst(4e-3) < 1.0
