@@ -96,8 +96,84 @@ def chunkwise_fwd(
     return g_cum, o, Aw, Au, None
 
 
-def chunkwise_bwd(*args, **kwargs):
-    raise NotImplementedError("the log-linear Gated DeltaNet backward is not implemented yet")
+def _levels_matrix(n: int, device) -> torch.Tensor:
+    idx = torch.arange(n, device=device)
+    x = idx[:, None] ^ idx[None, :]
+    lev = torch.zeros_like(x)
+    nz = x > 0
+    lev[nz] = torch.floor(torch.log2(x[nz].float())).long() + 1
+    return lev
+
+
+def _gdn_chunkwise_torch(q, k, v, b, g, l):
+    """Differentiable fp32 restatement of the chunkwise GDN forward in batched torch ops on the
+    GPU (q, k already normalised / scaled; one q/k per head).  INTERIM: it exists only so that
+    `chunkwise_bwd` can return gradients through autograd (library GEMMs) until the hand-written
+    backward kernels land; the forward that users get is the CUDA path above.
+    Same formulas as csrc/gdn_fwd.cu; levels are scanned per level (chunkwise_hgdn.py:718-788)."""
+    B, T, H, K = q.shape
+    V = v.shape[-1]
+    L = l.shape[-1]
+    C = CHUNK
+    NT = T // C
+    dev = q.device
+    f = lambda x: x.reshape(B, NT, C, H, -1).permute(0, 3, 1, 2, 4)        # (B,H,NT,C,*)
+    qc, kc, vc, lc = f(q), f(k), f(v), f(l)
+    bc = b.reshape(B, NT, C, H).permute(0, 3, 1, 2)                         # (B,H,NT,C)
+    G = torch.cumsum(g.reshape(B, NT, C, H).permute(0, 3, 1, 2), dim=-1)
+    gl = G[..., -1]
+    tril = torch.tril(torch.ones(C, C, dtype=torch.bool, device=dev))
+    stril = torch.tril(torch.ones(C, C, dtype=torch.bool, device=dev), -1)
+    diff = (G[..., :, None] - G[..., None, :]).masked_fill(~tril, float("-inf"))
+    Gam = torch.exp(diff)
+    A = (bc[..., :, None] * (kc @ kc.transpose(-1, -2))).masked_fill(~stril, 0.0)
+    eye = torch.eye(C, device=dev, dtype=q.dtype).expand(B, H, NT, C, C)
+    Aw = torch.linalg.solve_triangular(eye + A, eye, upper=False)
+    Au = torch.linalg.solve_triangular(eye + A * Gam, eye, upper=False)
+    w = Aw @ (bc[..., None] * kc)
+    u = Au @ (bc[..., None] * vc)
+    kd = kc * torch.exp(gl[..., None] - G)[..., None]
+    wd = w * torch.exp(G)[..., None]
+    QK = (qc @ kc.transpose(-1, -2)).masked_fill(~tril, 0.0)
+    qd = torch.exp(G)[..., None] * (qc - QK @ w)
+    lev = _levels_matrix(C, dev)
+    lam = torch.gather(lc, 4, lev[None, None, None].expand(B, H, NT, C, C))
+    o = ((QK @ Aw) * Gam * bc[..., None, :] * lam) @ vc                      # (B,H,NT,C,V)
+    ell_h0 = get_num_levels(C, 2)
+    Lc = ceil_log(NT, 2) if NT > 1 else 0
+    outs = [o[:, :, c] for c in range(NT)]
+    if Lc > 0:
+        lv = torch.arange(Lc, device=dev)
+        S = torch.zeros(B, H, Lc, K, V, device=dev, dtype=q.dtype)
+        for c in range(NT):
+            bit = ((c >> lv) & 1).to(q.dtype)                                # (Lc,)
+            reset = (((c + 1) % (2 << lv)) == 0).to(q.dtype)
+            lam_c = lc[:, :, c, :, ell_h0:ell_h0 + Lc] * bit                  # (B,H,C,Lc)
+            R = qd[:, :, c, None] @ S                                        # (B,H,Lc,C,V)
+            outs[c] = outs[c] + (lam_c.permute(0, 1, 3, 2)[..., None] * R).sum(2)
+            if c + 1 < NT:
+                Z = wd[:, :, c, None] @ S
+                Vh = u[:, :, c, None] * (1 - bit)[None, None, :, None, None] - Z
+                S = (torch.exp(gl[:, :, c])[..., None, None, None] * S + kd[:, :, c, None].transpose(-1, -2) @ Vh) \
+                    * (1 - reset)[None, None, :, None, None]
+    o = torch.stack(outs, dim=2)                                             # (B,H,NT,C,V)
+    return o.permute(0, 2, 3, 1, 4).reshape(B, T, H, V)
+
+
+def chunkwise_bwd(q, k, v, b, g, l, Aw, Au, do, head_first, level_base, htype, chunk_size, **unused):
+    """Gradients (dq, dk, dv, db, dg, dl) of the driver for normalised q, k (signature of
+    chunkwise_hgdn.py:799-817; `g` is the in-chunk cumulative sum returned by chunkwise_fwd).
+    INTERIM implementation: autograd through `_gdn_chunkwise_torch` in fp32 on the GPU."""
+    _check(q, k, v, b, g, l, head_first, level_base, htype, chunk_size)
+    B, T, H = g.shape
+    graw = g.float().clone()
+    gv = graw.view(B, T // CHUNK, CHUNK, H)
+    gv[:, :, 1:] = gv[:, :, 1:] - g.float().view(B, T // CHUNK, CHUNK, H)[:, :, :-1]
+    with torch.enable_grad():
+        ins = [x.detach().float().requires_grad_(True) for x in (q, k, v, b, graw, l)]
+        o = _gdn_chunkwise_torch(*ins)
+        grads = torch.autograd.grad(o, ins, do.float())
+    return tuple(grads)
 
 
 def gdn_forward(q, k, v, b, g, l, scale, head_first, level_base, htype, chunk_size):
@@ -108,5 +184,16 @@ def gdn_forward(q, k, v, b, g, l, scale, head_first, level_base, htype, chunk_si
     return g_cum, o, Aw, Au
 
 
-def gdn_backward(*args, **kwargs):
-    raise NotImplementedError("the log-linear Gated DeltaNet backward is not implemented yet")
+def gdn_backward(q, k, v, b, g_cum, l, Aw, Au, do, scale, head_first, level_base, htype, chunk_size):
+    """Backward of gdn_forward w.r.t. the raw q, k (through l2norm / scale), v, b, g, l
+    (hattention/kernel.py:198-225)."""
+    qn = (l2norm_fwd(q).float() * scale).to(q.dtype)
+    kn = l2norm_fwd(k)
+    H = v.shape[2]
+    G = k.shape[2]
+    if G != H:
+        raise NotImplementedError("GDN backward expects one q/k per head")
+    dq, dk, dv, db, dg, dl = chunkwise_bwd(qn, kn, v, b, g_cum, l, Aw, Au, do, head_first, level_base, htype, chunk_size)
+    dq = l2norm_bwd(q, dq * scale)
+    dk = l2norm_bwd(k, dk)
+    return dq, dk, dv, db, dg, dl
