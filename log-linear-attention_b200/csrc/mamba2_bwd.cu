@@ -1060,12 +1060,19 @@ static int launch_bwd(Mamba2Params p, cudaStream_t stream) {
             m2_seg_dscan_kernel<<<grid, 256, 0, stream>>>(p, KV);
         }
     }
-    {
+    const bool use_tc = (KD == 128 && VD == 64 && (p.NT % 2) == 0 && p.L <= 20 && g_use_tensor_core_path);
+    if (use_tc) {
+        int rc = mamba2_bwd1_tc_launch(p, stream);
+        if (rc != 0) return rc;
+    } else {
         auto kern = m2_bwd_fwdorder_kernel<KD, VD, MLOW>;
         if ((e = set_smem(kern, Bwd1Smem<KD, VD, MLOW>::total)) != cudaSuccess) return (int)e;
         kern<<<p.B * p.H * p.NS, 256, Bwd1Smem<KD, VD, MLOW>::total, stream>>>(p);
     }
-    {
+    if (use_tc) {
+        int rc = mamba2_bwd2_tc_launch(p, stream);
+        if (rc != 0) return rc;
+    } else {
         auto kern = m2_bwd_revorder_kernel<KD, VD, MLOW>;
         if ((e = set_smem(kern, Bwd2Smem<KD, VD, MLOW>::total)) != cudaSuccess) return (int)e;
         kern<<<p.B * p.H * p.NS, 256, Bwd2Smem<KD, VD, MLOW>::total, stream>>>(p);

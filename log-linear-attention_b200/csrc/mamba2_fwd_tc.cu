@@ -11,39 +11,9 @@
 //     the masks / decays / lambda weights are applied on the way from tensor memory to the bf16
 //     P tile; level-state masters stay in registers in the tensor-memory readout layout (one
 //     state row per thread), their bf16 copies are written once as MN-major operands.
-#include "llattn_common.cuh"
-#include "llattn_mamba2.h"
-#include "tma.cuh"
-#include "umma.cuh"
+#include "tc_common.cuh"
 
 namespace llattn {
-
-// Optional phase timing for tuning (build with -DLLATTN_STAMPS): three threads of one CTA record
-// clock64() at fixed points of one pair; llattn_debug_read_stamps copies the table to the host.
-#ifdef LLATTN_STAMPS
-__device__ long long g_stamps[3][32];
-#define STAMP()                                                             \
-    do {                                                                    \
-        if (stamp_slot >= 0 && nstamp < 32) g_stamps[stamp_slot][nstamp++] = clock64(); \
-    } while (0)
-#else
-#define STAMP() do { } while (0)
-#endif
-
-namespace tc {
-constexpr int KD = 128, VD = 64, PT = 128;          // pair of chunks = 128 tokens
-constexpr uint32_t Q_BYTES = PT * KD * 2;            // 32 KB
-constexpr uint32_t V_BYTES = PT * VD * 2;            // 16 KB
-constexpr uint32_t H_BYTES = KD * VD * 2;            // 16 KB
-// tensor memory columns
-constexpr int TM_S = 0, TM_O = 128, TM_T0 = 192, TM_T1 = 256, TM_KV = 320, TM_COLS = 512;
-// warps 0..7 do the element-wise work (two per tensor-memory lane quarter), warp 8 issues the MMAs;
-// the CTA is launched with three warpgroups so that registers can be moved from the third to the
-// first two (setmaxnreg); warps 9..11 exit at once
-constexpr int NTHREADS = 384, MMA_WARP = 8;
-constexpr int MAX_L_TC = 20;        // lambda levels supported by this kernel (T up to 64 * 2^13)
-constexpr int LAM_LD = MAX_L + 2;   // row stride of the staged lambda tile: odd number of 32-bit words, no bank conflicts
-}  // namespace tc
 
 template <int MLOW>
 struct FwdTcSmem {
@@ -59,21 +29,6 @@ struct FwdTcSmem {
     static constexpr uint32_t bar_off = lam_off + 128 * (MAX_L + 2) * 2;   // 10 mbarriers + tmem slot + abort flag     // 4 mbarriers + tmem slot + abort flag
     static constexpr uint32_t total = bar_off + 128 + 1024;             // + slack for 1024-byte alignment
 };
-
-// 128 x COLS bf16 tile from global (row stride g_stride elements) into the swizzled panel layout
-template <int COLS>
-__device__ __forceinline__ void load_tile_swz(unsigned char* s, const bf16* g, long g_stride, int tid) {
-    constexpr int CPR = COLS / 8;
-#pragma unroll
-    for (int i = tid; i < tc::PT * CPR; i += 256) {
-        const int r = i / CPR, c = (i % CPR) * 8;
-        cp_async16(s + umma::tile_offset(r, c, tc::PT), g + (long)r * g_stride + c);
-    }
-}
-
-// CTA-wide barrier over the 8 element-wise warps and the MMA warp (the spare warps of the third
-// warpgroup exit at once and never take part)
-__device__ __forceinline__ void bar_work() { asm volatile("bar.sync 1, 288;\n" ::: "memory"); }
 
 template <int MLOW>
 __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_chunk_fwd_tc_kernel(const __grid_constant__ Mamba2Params p) {
