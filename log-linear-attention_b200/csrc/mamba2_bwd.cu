@@ -959,7 +959,17 @@ __global__ void __launch_bounds__(256) m2_dg_kernel(const Mamba2Params p, float*
     const float* Zc = p.Zc + bh * p.NT * p.LZ;
     const float* Yc = p.Yc + bh * p.NT * (MLOW + 1);
     const float* Yseg = p.Yseg + bh * p.NS * p.LH;
+    // stage the per-chunk scalar tables in shared memory: the sweeps below are serial chains
+    float* sZ = sx + p.NT + p.NS;                       // [NT][LZ]
+    float* sY = sZ + p.NT * p.LZ;                       // [NT][MLOW+1]
+    float* sYs = sY + p.NT * (MLOW + 1);                // [NS][LH]
     for (int i = tid; i < p.NT + p.NS; i += 256) sx[i] = 0.f;
+    for (int i = tid; i < p.NT * p.LZ; i += 256) {
+        const int c = i / p.LZ, lvz = i - c * p.LZ;
+        sZ[i] = ((c >> lvz) & 1) ? Zc[i] : 0.f;          // only reader entries were written
+    }
+    for (int i = tid; i < p.NT * (MLOW + 1); i += 256) sY[i] = Yc[i];
+    for (int i = tid; i < p.NS * p.LH; i += 256) sYs[i] = Yseg[i];
     __syncthreads();
     int nlev = 0;
     while ((1 << nlev) < p.NT) ++nlev;          // inter-chunk levels in use
@@ -970,7 +980,7 @@ __global__ void __launch_bounds__(256) m2_dg_kernel(const Mamba2Params p, float*
             for (int c = 0; c < p.NT; ++c) {
                 if ((c & (period - 1)) == 0) run = 0.f;
                 if (!((c >> lv) & 1)) {
-                    run += Yc[(long)c * (MLOW + 1) + lv];
+                    run += sY[c * (MLOW + 1) + lv];
                     atomicAdd(&X[c], run);
                 }
             }
@@ -981,7 +991,7 @@ __global__ void __launch_bounds__(256) m2_dg_kernel(const Mamba2Params p, float*
                 if ((r & (pj - 1)) == 0) run = 0.f;
                 if (!((r >> j) & 1)) {
                     atomicAdd(&XS[r], run);
-                    if (r < p.NS - 1) run += Yseg[(long)r * p.LH + j];
+                    if (r < p.NS - 1) run += sYs[r * p.LH + j];
                 }
             }
         }
@@ -989,7 +999,7 @@ __global__ void __launch_bounds__(256) m2_dg_kernel(const Mamba2Params p, float*
         for (int c = p.NT - 1; c >= 0; --c) {
             if ((c >> lv) & 1) {
                 atomicAdd(&X[c], run);
-                run += Zc[(long)c * p.LZ + lv];
+                run += sZ[c * p.LZ + lv];
             }
             if ((c & (period - 1)) == 0) run = 0.f;
         }
@@ -998,7 +1008,7 @@ __global__ void __launch_bounds__(256) m2_dg_kernel(const Mamba2Params p, float*
         float run = 0.f;
         for (int c = 0; c < p.NT; ++c) {
             if ((c & (SEG - 1)) == 0) run = 0.f;
-            run += Yc[(long)c * (MLOW + 1) + MLOW];
+            run += sY[c * (MLOW + 1) + MLOW];
             atomicAdd(&X[c], run);
         }
     }
@@ -1093,7 +1103,9 @@ void mamba2_uncumsum(const float* gc, float* g, long BT, int H, cudaStream_t str
 
 void mamba2_dg(const Mamba2Params& p, float* dg, cudaStream_t stream) {
     dim3 grid(p.B * p.H, (p.NT + 63) / 64);
-    m2_dg_kernel<M2_MLOW><<<grid, 256, (size_t)(p.NT + p.NS) * sizeof(float), stream>>>(p, dg);
+    const size_t smem = (size_t)(p.NT + p.NS + p.NT * p.LZ + p.NT * (M2_MLOW + 1) + p.NS * (p.LH > 0 ? p.LH : 1)) * sizeof(float);
+    if (smem > 48 * 1024) cudaFuncSetAttribute(m2_dg_kernel<M2_MLOW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    m2_dg_kernel<M2_MLOW><<<grid, 256, smem, stream>>>(p, dg);
 }
 
 void cast_f32_to_bf16(const float* src, void* dst, long n, cudaStream_t stream) {
