@@ -13,6 +13,7 @@ constexpr int M2_MLOW = 3;   // a segment is 2^M2_MLOW chunks (512 tokens)
 struct Mamba2Params {
     // tensor maps (64-column panels, 128 rows) for the tcgen05 kernels; valid only when those run
     alignas(64) CUtensorMap tm_q, tm_k, tm_v, tm_do;
+    alignas(64) CUtensorMap tm_h0;             // level states of the segments as a (B*H*NS*LH*K, V) matrix
     alignas(64) CUtensorMap tm_dq, tm_dk;      // fp32 (B*T, G, K) accumulators, 32-column boxes (reduce-add)
     // inputs
     const __nv_bfloat16* q;      // (B,T,G,K)
@@ -55,6 +56,7 @@ int mamba2_fwd_states_dispatch(Mamba2Params p, cudaStream_t stream);
 int mamba2_fwd_tc_launch(const Mamba2Params& p, cudaStream_t stream);
 int mamba2_bwd1_tc_launch(const Mamba2Params& p, cudaStream_t stream);
 int mamba2_bwd2_tc_launch(const Mamba2Params& p, cudaStream_t stream);
+int mamba2_hi_bwd_tc_launch(const Mamba2Params& p, cudaStream_t stream);
 extern int g_use_tensor_core_path;
 void mamba2_uncumsum(const float* gc, float* g, long BT, int H, cudaStream_t stream);
 void mamba2_dg(const Mamba2Params& p, float* dg, cudaStream_t stream);

@@ -1054,16 +1054,22 @@ static int launch_bwd(Mamba2Params p, cudaStream_t stream) {
         // forward high-level states are recomputed (the autograd boundary saves only the inputs)
         int rc = mamba2_fwd_states_dispatch(p, stream);
         if (rc != 0) return rc;
-        {
-            auto kern = m2_hi_bwd_q_kernel<KD, VD, MLOW>;
-            if ((e = set_smem(kern, HiBwdSmem<KD, VD>::total)) != cudaSuccess) return (int)e;
-            kern<<<p.B * p.H * (p.NT - SEG), 256, HiBwdSmem<KD, VD>::total, stream>>>(p);
-        }
-        {
-            auto kern = m2_seg_dstate_kernel<KD, VD, MLOW>;
-            if ((e = set_smem(kern, SegDSmem<KD, VD, MLOW>::total)) != cudaSuccess) return (int)e;
-            dim3 grid(p.B * p.H * (p.NS - 1), p.LH);
-            kern<<<grid, 256, SegDSmem<KD, VD, MLOW>::total, stream>>>(p);
+        const bool hi_tc = (KD == 128 && VD == 64 && (p.NT % 2) == 0 && p.L <= 20 && p.LH <= 5 && g_use_tensor_core_path);
+        if (hi_tc) {
+            rc = mamba2_hi_bwd_tc_launch(p, stream);
+            if (rc != 0) return rc;
+        } else {
+            {
+                auto kern = m2_hi_bwd_q_kernel<KD, VD, MLOW>;
+                if ((e = set_smem(kern, HiBwdSmem<KD, VD>::total)) != cudaSuccess) return (int)e;
+                kern<<<p.B * p.H * (p.NT - SEG), 256, HiBwdSmem<KD, VD>::total, stream>>>(p);
+            }
+            {
+                auto kern = m2_seg_dstate_kernel<KD, VD, MLOW>;
+                if ((e = set_smem(kern, SegDSmem<KD, VD, MLOW>::total)) != cudaSuccess) return (int)e;
+                dim3 grid(p.B * p.H * (p.NS - 1), p.LH);
+                kern<<<grid, 256, SegDSmem<KD, VD, MLOW>::total, stream>>>(p);
+            }
         }
         {
             dim3 grid((KV / 4 + 255) / 256, p.B * p.H);

@@ -1,0 +1,315 @@
+// Segment-level ("high" Fenwick levels) kernels of the log-linear Mamba-2 path on tcgen05 / TMA
+// (K = 128, V = 64, segments of 2^MLOW chunks = 2^(MLOW-1) pairs of 128 tokens).  Same mathematics
+// as m2_seg_state_kernel / m2_hi_out_kernel (mamba2_fwd.cu) and m2_seg_dstate_kernel /
+// m2_hi_bwd_q_kernel (mamba2_bwd.cu); one CTA per (batch, head, segment) handles every high level
+// of its segment, so q / do / k / v tiles and the level states are loaded once per segment.
+//   seg_state  : F_r      = sum_pairs k^T (v * exp(G_end - G))                      (fp32 K x V)
+//   hi_out     : o_hi     = sum_{j set in r} lambda_j exp(G) * (q H0[r][j])         (bf16, column-chunk-major scratch)
+//   seg_dstate : dF[r][j] = sum_pairs q^T (do * lambda_j exp(G))                     (fp32 K x V per set level)
+//   hi_bwd_q   : dlambda_j = exp(G) (do . (q H0_j)) ; dq += (do * lambda_j exp(G)) H0_j^T   (TMA reduce-add)
+// G is the cumulative log decay from the start of the segment (inclusive).
+#include "tc_common.cuh"
+
+namespace llattn {
+
+namespace tcs {
+constexpr int MAXLH = 5;            // high levels handled by these kernels (T <= 64 * 2^(MLOW+5))
+}
+
+__device__ __forceinline__ uint32_t box_offset_f32(int row, int col) {
+    return (uint32_t)(row * 128 + (((col >> 2) ^ (row & 7)) << 4) + (col & 3) * 4);
+}
+
+// cumulative log decay of a whole segment (SEG chunks) from its start, inclusive, into sGs[SEG*64];
+// all 256 compute threads call it; returns after a bar_compute
+template <int SEG>
+__device__ __forceinline__ void segment_cumsum(const Mamba2Params& p, int b, int h, int r, int nchunks, float* sGs, float* sTot,
+                                               int warp, int lane, int tid) {
+    for (int c = warp; c < nchunks; c += 8) {
+        const float* gp = p.g + ((long)b * p.T + (long)(r * SEG + c) * CH) * p.H + h;
+        float x0 = gp[(long)(2 * lane) * p.H], x1 = gp[(long)(2 * lane + 1) * p.H];
+        warp_cumsum64(x0, x1, lane);
+        sGs[c * CH + 2 * lane] = x0;
+        sGs[c * CH + 2 * lane + 1] = x1;
+        if (lane == 31) sTot[c] = x1;
+    }
+    bar_compute();
+    if (tid == 0) {
+        float run = 0.f;
+        for (int c = 0; c < nchunks; ++c) {
+            const float t = sTot[c];
+            sTot[c] = run;
+            run += t;
+        }
+        sTot[SEG] = run;
+    }
+    bar_compute();
+    for (int i = tid; i < nchunks * CH; i += 256) sGs[i] += sTot[i / CH];
+    bar_compute();
+}
+
+// ------------------------------------------------------------------------------------------
+// backward: reader summaries dF[r][j] and, in the same pass over the segment, dq / dlambda of the
+// high levels.  Per pair: T_j = q H0_j (one 64-column slot, level after level), dlambda_j and
+// the scaled copy do * (lambda_j exp(G)); then dq (+)= that copy times H0_j^T and dF_j += q^T times it.
+// ------------------------------------------------------------------------------------------
+template <int MLOW>
+struct HiBwdTcSmem {
+    static constexpr int SEG = 1 << MLOW;
+    static constexpr uint32_t q_off = 0;                                   // 32 KB
+    static constexpr uint32_t do_off = q_off + tc::Q_BYTES;                // 16 KB
+    static constexpr uint32_t h_off = do_off + tc::V_BYTES;                // MAXLH x 16 KB states
+    static constexpr uint32_t dos_off = h_off + tcs::MAXLH * tc::H_BYTES;  // MAXLH x 16 KB scaled do ; first 64 KB double as fp32 staging
+    static constexpr uint32_t gs_off = dos_off + tcs::MAXLH * tc::V_BYTES; // float [SEG*64] + [SEG+1]
+    static constexpr uint32_t misc_off = gs_off + (SEG * 64 + SEG + 32) * 4;  // float [2][128][MAXLH+1] dlambda halves
+    static constexpr uint32_t bar_off = misc_off + 2 * 128 * (tcs::MAXLH + 1) * 4;
+    static constexpr uint32_t total = bar_off + 128 + 1024;
+};
+
+template <int MLOW>
+__global__ void __launch_bounds__(tc::NTHREADS, 1) m2_hi_bwd_tc_kernel(const __grid_constant__ Mamba2Params p) {
+    using SM = HiBwdTcSmem<MLOW>;
+    constexpr int SEG = SM::SEG, NDLH = tcs::MAXLH + 1;
+    // tensor memory: dF slots 0..4 (64 columns each), dq (128 columns), T (64 columns)
+    constexpr int TM_DF = 0, TM_DQ = 320, TM_T = 448;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    unsigned char* sQ = smem + SM::q_off;
+    unsigned char* sDO = smem + SM::do_off;
+    unsigned char* sH = smem + SM::h_off;
+    unsigned char* sDOs = smem + SM::dos_off;
+    unsigned char* sStage = smem + SM::dos_off;
+    float* sGs = reinterpret_cast<float*>(smem + SM::gs_off);
+    float* sTot = sGs + SEG * 64;
+    float* sDL = reinterpret_cast<float*>(smem + SM::misc_off);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SM::bar_off);
+    uint64_t* barT = bars + 0;       // one level read T_j complete
+    uint64_t* barB = bars + 1;       // second batch of a pair complete
+    uint64_t* full_t = bars + 2;     // q and do tiles of a pair
+    uint64_t* full_h = bars + 3;     // the level states of the segment
+    uint64_t* empty_t = bars + 4;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + SM::bar_off + 64);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + SM::bar_off + 72);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int h = blockIdx.x % p.H;
+    const int r = 1 + (blockIdx.x / p.H) % (p.NS - 1);
+    const int b = blockIdx.x / (p.H * (p.NS - 1));
+    const int grp = h / (p.H / p.G);
+    const int nchunks = min(SEG, p.NT - r * SEG);
+    const int npairs = nchunks / 2;
+    // set high levels of this segment, in increasing order
+    int lev[tcs::MAXLH], nl = 0;
+#pragma unroll
+    for (int j = 0; j < tcs::MAXLH; ++j)
+        if (j < p.LH && ((r >> j) & 1)) lev[nl++] = j;
+
+    if (tid == 0) {
+#pragma unroll
+        for (int i = 0; i < 5; ++i) umma::mbar_init(&bars[i], 1);
+        umma::fence_mbar_init();
+        *abort_flag = *p.err;
+    }
+    __syncthreads();
+    if (*abort_flag) return;
+
+    constexpr uint32_t ID_KM64 = umma::idesc_bf16(128, 64, false, true);
+    constexpr uint32_t ID_KK128 = umma::idesc_bf16(128, 128, false, false);
+    constexpr uint32_t ID_MM64 = umma::idesc_bf16(128, 64, true, true);
+
+    if (warp >= tc::MMA_WARP) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 40;\n");
+        if (warp == tc::MMA_WARP + 1) {
+            if (lane == 0) {
+                // level states of the segment: rows of the (B*H*NS*LH*K, V) matrix
+                tma::expect_tx(full_h, nl * tc::H_BYTES);
+                for (int i = 0; i < nl; ++i) {
+                    const int row0 = ((((b * p.H + h) * p.NS + r) * p.LH) + lev[i]) * tc::KD;
+                    tma::load_panel(sH + i * tc::H_BYTES, &p.tm_h0, 0, 0, row0, full_h);
+                }
+                const int brow = b * p.T + r * SEG * CH;
+                for (int pl = 0; pl < npairs; ++pl) {
+                    const int row0 = brow + pl * tc::PT;
+                    if (pl >= 1 && !umma::mbar_wait(empty_t, (pl - 1) & 1, abort_flag)) break;
+                    tma::expect_tx(full_t, tc::Q_BYTES + tc::V_BYTES);
+                    tma::load_panel(sQ, &p.tm_q, 0, grp, row0, full_t);
+                    tma::load_panel(sQ + tc::Q_BYTES / 2, &p.tm_q, 64, grp, row0, full_t);
+                    tma::load_panel(sDO, &p.tm_do, 0, h, row0, full_t);
+                }
+            }
+            return;
+        }
+        if (warp > tc::MMA_WARP) return;
+        umma::tmem_alloc(tmem_slot, tc::TM_COLS);
+        umma::fence_before_sync();
+        bar_work();
+        umma::fence_after_sync();
+        const uint32_t tbase = *tmem_slot;
+        const uint32_t aQ = umma::smem_addr(sQ), aH = umma::smem_addr(sH), aDOs = umma::smem_addr(sDOs);
+        if (lane == 0) umma::mbar_wait(full_h, 0, abort_flag);
+        for (int pl = 0; pl < npairs; ++pl) {
+            if (lane == 0) umma::mbar_wait(full_t, pl & 1, abort_flag);
+            for (int i = 0; i < nl; ++i) {
+                bar_work();                          // T slot is free (previous read consumed)
+                umma::fence_after_sync();
+                if (lane == 0) {
+                    umma::gemm_km<tc::PT, tc::KD, tc::KD>(tbase + TM_T, aQ, aH + i * tc::H_BYTES, ID_KM64, false);
+                    umma::commit(barT);
+                }
+                __syncwarp();
+            }
+            umma::fence_before_sync();
+            bar_work();                              // scaled copies of do are written
+            umma::fence_after_sync();
+            if (lane == 0) {
+                for (int i = 0; i < nl; ++i) {
+                    umma::gemm_kk<tc::PT, tc::KD, tc::VD>(tbase + TM_DQ, aDOs + i * tc::V_BYTES, aH + i * tc::H_BYTES, ID_KK128, i > 0);
+                    umma::gemm_mm<tc::PT, tc::PT, tc::PT>(tbase + TM_DF + i * 64, aQ, aDOs + i * tc::V_BYTES, ID_MM64, pl > 0);
+                }
+                umma::commit(barB);
+            }
+            __syncwarp();
+            umma::fence_before_sync();
+            bar_work();                              // end of the pair: tiles and staging are free
+            umma::fence_after_sync();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(umma::smem_addr(empty_t)) : "memory");
+            if (*abort_flag) break;
+        }
+        if (*abort_flag && lane == 0) atomicExch(p.err, 1);
+        umma::fence_before_sync();
+        bar_work();
+        umma::tmem_dealloc(tbase, tc::TM_COLS);
+        return;
+    }
+
+    // ================= warps 0..7 =================
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 232;\n");
+    const int rb = warp & 3;
+    const int row = rb * 32 + lane;
+    const int ch = warp >> 2;
+    segment_cumsum<SEG>(p, b, h, r, nchunks, sGs, sTot, warp, lane, tid);
+    umma::fence_before_sync();
+    bar_work();
+    umma::fence_after_sync();
+    const uint32_t tbase = *tmem_slot;
+    uint32_t phT = 0;
+
+    for (int pl = 0; pl < npairs; ++pl) {
+        const long t0 = (long)(r * SEG) * CH + (long)pl * tc::PT;
+        const float sc = fexp(sGs[pl * tc::PT + row]);          // exp(G_i) from the segment start
+        const bf16* lrow = p.l + (((long)b * p.T + t0 + row) * p.H + h) * p.L + INTRA_LEVELS + MLOW;
+        float lamv[tcs::MAXLH];
+#pragma unroll
+        for (int i = 0; i < tcs::MAXLH; ++i) lamv[i] = (i < nl) ? __bfloat162float(lrow[lev[i]]) : 0.f;
+        umma::mbar_wait(full_t, pl & 1, abort_flag);
+        uint4 dox[4];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) dox[c] = *reinterpret_cast<const uint4*>(sDO + umma::tile_offset(row, ch * 32 + c * 8, tc::PT));
+        float* myDL = sDL + (ch * 128 + row) * NDLH;
+        for (int i = 0; i < nl; ++i) {
+            umma::fence_before_sync();
+            bar_work();
+            umma::mbar_wait(barT, phT, abort_flag);
+            phT ^= 1;
+            umma::fence_after_sync();
+            float t[32];
+            umma::tmem_ld32(umma::tmem_addr(tbase + TM_T, warp, ch * 32), t);
+            const float rs = lamv[i] * sc;
+            float dot = 0.f;
+            unsigned char* dst = sDOs + i * tc::V_BYTES;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const uint32_t* xw = reinterpret_cast<const uint32_t*>(&dox[c]);
+                uint32_t outw[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    __nv_bfloat162 v2 = *reinterpret_cast<const __nv_bfloat162*>(&xw[e]);
+                    const float a0 = __bfloat162float(v2.x), a1 = __bfloat162float(v2.y);
+                    dot += a0 * t[c * 8 + e * 2] + a1 * t[c * 8 + e * 2 + 1];
+                    outw[e] = pack_bf16(a0 * rs, a1 * rs);
+                }
+                *reinterpret_cast<uint4*>(dst + umma::tile_offset(row, ch * 32 + c * 8, tc::PT)) = make_uint4(outw[0], outw[1], outw[2], outw[3]);
+            }
+            myDL[i] = sc * dot;
+        }
+        umma::fence_async_smem();
+        umma::fence_before_sync();
+        bar_work();                                  // scaled copies written; second batch may start
+        umma::fence_after_sync();
+        // ---- dlambda out, reader totals Z per chunk, q.dq contribution
+        if (ch == 0) {
+            float* gdl = p.dl + (((long)b * p.T + t0 + row) * p.H + h) * p.L + INTRA_LEVELS + MLOW;
+            float wsum = 0.f;
+            for (int i = 0; i < nl; ++i) {
+                const float dlv = sDL[row * NDLH + i] + sDL[(128 + row) * NDLH + i];
+                gdl[lev[i]] = dlv;
+                float z = lamv[i] * dlv;
+                wsum += z;
+#pragma unroll
+                for (int d = 16; d > 0; d >>= 1) z += __shfl_xor_sync(0xffffffffu, z, d);
+                if (lane == 0) sTot[SEG + 1 + warp * tcs::MAXLH + i] = z;      // per 32-row block
+            }
+            red_add_f32(p.wq + ((long)b * p.T + t0 + row) * p.H + h, wsum);
+        }
+        umma::mbar_wait(barB, pl & 1, abort_flag);
+        umma::fence_after_sync();
+        // ---- dq tile -> fp32 staging (the scaled copies are no longer needed) -> TMA reduce-add
+#pragma unroll
+        for (int hb = 0; hb < 2; ++hb) {
+            float t[32];
+            umma::tmem_ld32(umma::tmem_addr(tbase + TM_DQ, warp, ch * 64 + hb * 32), t);
+            unsigned char* box = sStage + (ch * 2 + hb) * 16384;
+#pragma unroll
+            for (int c = 0; c < 8; ++c)
+                *reinterpret_cast<float4*>(box + box_offset_f32(row, c * 4)) = make_float4(t[c * 4], t[c * 4 + 1], t[c * 4 + 2], t[c * 4 + 3]);
+        }
+        umma::fence_async_smem();
+        bar_compute();
+        if (tid == 0) {
+            const int grow = b * p.T + (int)t0;
+#pragma unroll
+            for (int bx = 0; bx < 4; ++bx) tma::reduce_add_box(&p.tm_dq, bx * 32, grp, grow, sStage + bx * 16384);
+            tma::commit_group();
+            tma::wait_group_read0();
+        }
+        if (tid < 2 * nl) {
+            const int i = tid >> 1, cpart = tid & 1;
+            const float z = sTot[SEG + 1 + (cpart * 2) * tcs::MAXLH + i] + sTot[SEG + 1 + (cpart * 2 + 1) * tcs::MAXLH + i];
+            const long cidx = ((long)b * p.H + h) * p.NT + r * SEG + pl * 2 + cpart;
+            p.Zc[cidx * p.LZ + MLOW + lev[i]] = z;
+        }
+        umma::fence_before_sync();
+        bar_work();                                  // end of the pair
+        umma::fence_after_sync();
+        if (*abort_flag) break;
+    }
+    // ---- dF[r][j] out
+    for (int i = 0; i < nl; ++i) {
+        float t[32];
+        umma::tmem_ld32(umma::tmem_addr(tbase + TM_DF + i * 64, warp, ch * 32), t);
+        float* dF = p.seg_dF + ((((long)b * p.H + h) * p.NS + r) * p.LH + lev[i]) * tc::KD * tc::VD + row * tc::VD + ch * 32;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) *reinterpret_cast<float4*>(dF + c * 4) = make_float4(t[c * 4], t[c * 4 + 1], t[c * 4 + 2], t[c * 4 + 3]);
+    }
+    if (tid == 0) tma::wait_group0();
+    umma::fence_before_sync();
+    bar_work();
+}
+
+int mamba2_hi_bwd_tc_launch(const Mamba2Params& p_in, cudaStream_t stream) {
+    Mamba2Params p = p_in;
+    int rc;
+    const long BT = (long)p.B * p.T;
+    if ((rc = tma::make_panel_map(&p.tm_q, p.q, BT, p.G, p.K, tc::PT)) != 0) return rc;
+    if ((rc = tma::make_panel_map(&p.tm_do, p.d_o, BT, p.H, p.V, tc::PT)) != 0) return rc;
+    if ((rc = tma::make_panel_map(&p.tm_h0, p.seg_H0, (long)p.B * p.H * p.NS * p.LH * p.K, 1, p.V, tc::KD)) != 0) return rc;
+    if ((rc = tma::make_f32_box_map(&p.tm_dq, p.dq_acc, BT, p.G, p.K, tc::PT)) != 0) return rc;
+    auto kern = m2_hi_bwd_tc_kernel<M2_MLOW>;
+    const size_t sm = HiBwdTcSmem<M2_MLOW>::total;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
+    if (e != cudaSuccess) return (int)e;
+    kern<<<p.B * p.H * (p.NS - 1), tc::NTHREADS, sm, stream>>>(p);
+    return (int)cudaGetLastError();
+}
+
+}  // namespace llattn
