@@ -57,6 +57,8 @@ int mamba2_fwd_tc_launch(const Mamba2Params& p, cudaStream_t stream);
 int mamba2_bwd1_tc_launch(const Mamba2Params& p, cudaStream_t stream);
 int mamba2_bwd2_tc_launch(const Mamba2Params& p, cudaStream_t stream);
 int mamba2_hi_bwd_tc_launch(const Mamba2Params& p, cudaStream_t stream);
+int mamba2_seg_state_tc_launch(const Mamba2Params& p, cudaStream_t stream);
+int mamba2_hi_out_tc_launch(const Mamba2Params& p, cudaStream_t stream);
 extern int g_use_tensor_core_path;
 void mamba2_uncumsum(const float* gc, float* g, long BT, int H, cudaStream_t stream);
 void mamba2_dg(const Mamba2Params& p, float* dg, cudaStream_t stream);

@@ -559,10 +559,15 @@ __global__ void __launch_bounds__(256, 1) m2_hi_out_kernel(const Mamba2Params p)
 template <int KD, int VD, int MLOW>
 static int launch_states(Mamba2Params p, cudaStream_t stream) {
     cudaError_t e;
-    auto kern = m2_seg_state_kernel<KD, VD, MLOW>;
-    size_t sm = SegSmem<KD, VD, MLOW>::total;
-    if ((e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm)) != cudaSuccess) return (int)e;
-    kern<<<p.B * p.H * (p.NS - 1), 256, sm, stream>>>(p);
+    if (KD == 128 && VD == 64 && g_use_tensor_core_path) {
+        int rc = mamba2_seg_state_tc_launch(p, stream);
+        if (rc != 0) return rc;
+    } else {
+        auto kern = m2_seg_state_kernel<KD, VD, MLOW>;
+        size_t sm = SegSmem<KD, VD, MLOW>::total;
+        if ((e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm)) != cudaSuccess) return (int)e;
+        kern<<<p.B * p.H * (p.NS - 1), 256, sm, stream>>>(p);
+    }
     const int KV = KD * VD;
     dim3 grid((KV / 4 + 255) / 256, p.B * p.H);
     m2_seg_scan_kernel<<<grid, 256, 0, stream>>>(p, KV);
@@ -577,10 +582,15 @@ static int launch_fwd(Mamba2Params p, cudaStream_t stream) {
         p.o_has_high = use_tc ? 2 : 1;      // 2: partial output goes to the column-chunk-major scratch
         int rc = launch_states<KD, VD, MLOW>(p, stream);
         if (rc != 0) return rc;
-        auto kern = m2_hi_out_kernel<KD, VD, MLOW>;
-        size_t sm = HiSmem<KD, VD>::total;
-        if ((e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm)) != cudaSuccess) return (int)e;
-        kern<<<p.B * p.H * (p.NT - (1 << MLOW)), 256, sm, stream>>>(p);
+        if (use_tc && p.LH <= 5) {
+            rc = mamba2_hi_out_tc_launch(p, stream);
+            if (rc != 0) return rc;
+        } else {
+            auto kern = m2_hi_out_kernel<KD, VD, MLOW>;
+            size_t sm = HiSmem<KD, VD>::total;
+            if ((e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm)) != cudaSuccess) return (int)e;
+            kern<<<p.B * p.H * (p.NT - (1 << MLOW)), 256, sm, stream>>>(p);
+        }
     }
     if (use_tc) {
         return mamba2_fwd_tc_launch(p, stream);

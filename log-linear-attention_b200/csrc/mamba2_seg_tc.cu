@@ -296,6 +296,318 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_hi_bwd_tc_kernel(const __g
     bar_work();
 }
 
+// ------------------------------------------------------------------------------------------
+// forward: partial output of the high levels, o_hi = sum_j lambda_j exp(G) (q H0[r][j])
+// ------------------------------------------------------------------------------------------
+template <int MLOW>
+struct HiOutTcSmem {
+    static constexpr int SEG = 1 << MLOW;
+    static constexpr uint32_t q_off = 0;                                   // [2] 32 KB
+    static constexpr uint32_t h_off = q_off + 2 * tc::Q_BYTES;
+    static constexpr uint32_t gs_off = h_off + tcs::MAXLH * tc::H_BYTES;
+    static constexpr uint32_t bar_off = gs_off + (SEG * 64 + SEG + 32) * 4;
+    static constexpr uint32_t total = bar_off + 128 + 1024;
+};
+
+template <int MLOW>
+__global__ void __launch_bounds__(tc::NTHREADS, 1) m2_hi_out_tc_kernel(const __grid_constant__ Mamba2Params p) {
+    using SM = HiOutTcSmem<MLOW>;
+    constexpr int SEG = SM::SEG;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    unsigned char* sQ = smem + SM::q_off;
+    unsigned char* sH = smem + SM::h_off;
+    float* sGs = reinterpret_cast<float*>(smem + SM::gs_off);
+    float* sTot = sGs + SEG * 64;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SM::bar_off);
+    uint64_t* barA = bars + 0;       // level reads of a pair complete
+    uint64_t* full_q = bars + 1;     // [2]
+    uint64_t* full_h = bars + 3;
+    uint64_t* empty_q = bars + 4;    // [2]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + SM::bar_off + 64);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + SM::bar_off + 72);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int h = blockIdx.x % p.H;
+    const int r = 1 + (blockIdx.x / p.H) % (p.NS - 1);
+    const int b = blockIdx.x / (p.H * (p.NS - 1));
+    const int grp = h / (p.H / p.G);
+    const int nchunks = min(SEG, p.NT - r * SEG);
+    const int npairs = nchunks / 2;
+    int lev[tcs::MAXLH], nl = 0;
+#pragma unroll
+    for (int j = 0; j < tcs::MAXLH; ++j)
+        if (j < p.LH && ((r >> j) & 1)) lev[nl++] = j;
+
+    if (tid == 0) {
+#pragma unroll
+        for (int i = 0; i < 6; ++i) umma::mbar_init(&bars[i], 1);
+        umma::fence_mbar_init();
+        *abort_flag = *p.err;
+    }
+    __syncthreads();
+    if (*abort_flag) return;
+    constexpr uint32_t ID_KM64 = umma::idesc_bf16(128, 64, false, true);
+
+    if (warp >= tc::MMA_WARP) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 40;\n");
+        if (warp == tc::MMA_WARP + 1) {
+            if (lane == 0) {
+                tma::expect_tx(full_h, nl * tc::H_BYTES);
+                for (int i = 0; i < nl; ++i) {
+                    const int row0 = ((((b * p.H + h) * p.NS + r) * p.LH) + lev[i]) * tc::KD;
+                    tma::load_panel(sH + i * tc::H_BYTES, &p.tm_h0, 0, 0, row0, full_h);
+                }
+                const int brow = b * p.T + r * SEG * CH;
+                for (int pl = 0; pl < npairs; ++pl) {
+                    const int st = pl & 1, row0 = brow + pl * tc::PT;
+                    if (pl >= 2 && !umma::mbar_wait(&empty_q[st], ((pl - 2) >> 1) & 1, abort_flag)) break;
+                    tma::expect_tx(&full_q[st], tc::Q_BYTES);
+                    tma::load_panel(sQ + st * tc::Q_BYTES, &p.tm_q, 0, grp, row0, &full_q[st]);
+                    tma::load_panel(sQ + st * tc::Q_BYTES + tc::Q_BYTES / 2, &p.tm_q, 64, grp, row0, &full_q[st]);
+                }
+            }
+            return;
+        }
+        if (warp > tc::MMA_WARP) return;
+        umma::tmem_alloc(tmem_slot, tc::TM_COLS);
+        umma::fence_before_sync();
+        bar_work();
+        umma::fence_after_sync();
+        const uint32_t tbase = *tmem_slot;
+        if (lane == 0) umma::mbar_wait(full_h, 0, abort_flag);
+        for (int pl = 0; pl < npairs; ++pl) {
+            const int st = pl & 1;
+            bar_work();                              // the slots of the previous pair have been read
+            umma::fence_after_sync();
+            if (lane == 0) {
+                umma::mbar_wait(&full_q[st], (pl >> 1) & 1, abort_flag);
+                for (int i = 0; i < nl; ++i)
+                    umma::gemm_km<tc::PT, tc::KD, tc::KD>(tbase + i * 64, umma::smem_addr(sQ + st * tc::Q_BYTES),
+                                                          umma::smem_addr(sH + i * tc::H_BYTES), ID_KM64, false);
+                umma::commit(barA);
+                umma::commit(&empty_q[st]);
+            }
+            __syncwarp();
+            if (*abort_flag) break;
+        }
+        umma::fence_before_sync();
+        bar_work();
+        if (*abort_flag && lane == 0) atomicExch(p.err, 1);
+        umma::tmem_dealloc(tbase, tc::TM_COLS);
+        return;
+    }
+
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 232;\n");
+    const int rb = warp & 3;
+    const int row = rb * 32 + lane;
+    const int ch = warp >> 2;
+    segment_cumsum<SEG>(p, b, h, r, nchunks, sGs, sTot, warp, lane, tid);
+    umma::fence_before_sync();
+    bar_work();
+    umma::fence_after_sync();
+    const uint32_t tbase = *tmem_slot;
+
+    for (int pl = 0; pl < npairs; ++pl) {
+        const long t0 = (long)(r * SEG) * CH + (long)pl * tc::PT;
+        const float sc = fexp(sGs[pl * tc::PT + row]);
+        const bf16* lrow = p.l + (((long)b * p.T + t0 + row) * p.H + h) * p.L + INTRA_LEVELS + MLOW;
+        float lamv[tcs::MAXLH];
+#pragma unroll
+        for (int i = 0; i < tcs::MAXLH; ++i) lamv[i] = (i < nl) ? __bfloat162float(lrow[lev[i]]) * sc : 0.f;
+        umma::fence_before_sync();
+        bar_work();
+        umma::mbar_wait(barA, pl & 1, abort_flag);
+        umma::fence_after_sync();
+        float o[32];
+#pragma unroll
+        for (int e = 0; e < 32; ++e) o[e] = 0.f;
+        for (int i = 0; i < nl; ++i) {
+            float t[32];
+            umma::tmem_ld32(umma::tmem_addr(tbase + i * 64, warp, ch * 32), t);
+#pragma unroll
+            for (int e = 0; e < 32; ++e) o[e] += lamv[i] * t[e];
+        }
+        // column-chunk-major scratch [bh][pair][8-col chunk][128 rows][8]
+        bf16* gh = p.o_hi + ((((long)b * p.H + h) * (p.NT / 2) + (r * (SEG / 2) + pl)) * 8 + ch * 4) * (tc::PT * 8) + row * 8;
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+            *reinterpret_cast<uint4*>(gh + c * tc::PT * 8) =
+                make_uint4(pack_bf16(o[c * 8], o[c * 8 + 1]), pack_bf16(o[c * 8 + 2], o[c * 8 + 3]),
+                           pack_bf16(o[c * 8 + 4], o[c * 8 + 5]), pack_bf16(o[c * 8 + 6], o[c * 8 + 7]));
+        if (*abort_flag) break;
+    }
+    umma::fence_before_sync();
+    bar_work();
+}
+
+// ------------------------------------------------------------------------------------------
+// forward: segment summaries F_r = sum_j k_j^T v_j exp(G_end - G_j), D_r = G_end
+// ------------------------------------------------------------------------------------------
+template <int MLOW>
+struct SegStateTcSmem {
+    static constexpr int SEG = 1 << MLOW;
+    static constexpr uint32_t k_off = 0;                                   // [2] 32 KB
+    static constexpr uint32_t v_off = k_off + 2 * tc::Q_BYTES;             // [2] 16 KB
+    static constexpr uint32_t vs_off = v_off + 2 * tc::V_BYTES;            // [2] 16 KB
+    static constexpr uint32_t gs_off = vs_off + 2 * tc::V_BYTES;
+    static constexpr uint32_t bar_off = gs_off + (SEG * 64 + SEG + 32) * 4;
+    static constexpr uint32_t total = bar_off + 128 + 1024;
+};
+
+template <int MLOW>
+__global__ void __launch_bounds__(tc::NTHREADS, 1) m2_seg_state_tc_kernel(const __grid_constant__ Mamba2Params p) {
+    using SM = SegStateTcSmem<MLOW>;
+    constexpr int SEG = SM::SEG, SEGP = SEG / 2;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    unsigned char* sK = smem + SM::k_off;
+    unsigned char* sV = smem + SM::v_off;
+    unsigned char* sVs = smem + SM::vs_off;
+    float* sGs = reinterpret_cast<float*>(smem + SM::gs_off);
+    float* sTot = sGs + SEG * 64;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SM::bar_off);
+    uint64_t* barF = bars + 0;
+    uint64_t* full_kv = bars + 1;    // [2]
+    uint64_t* empty_kv = bars + 3;   // [2] tensor core is done with the k / v / Vs stage
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + SM::bar_off + 64);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + SM::bar_off + 72);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int h = blockIdx.x % p.H;
+    const int r = (blockIdx.x / p.H) % (p.NS - 1);          // the last segment has no reader
+    const int b = blockIdx.x / (p.H * (p.NS - 1));
+    const int grp = h / (p.H / p.G);
+
+    if (tid == 0) {
+#pragma unroll
+        for (int i = 0; i < 5; ++i) umma::mbar_init(&bars[i], 1);
+        umma::fence_mbar_init();
+        *abort_flag = *p.err;
+    }
+    __syncthreads();
+    if (*abort_flag) return;
+    constexpr uint32_t ID_MM64 = umma::idesc_bf16(128, 64, true, true);
+
+    if (warp >= tc::MMA_WARP) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 40;\n");
+        if (warp == tc::MMA_WARP + 1) {
+            if (lane == 0) {
+                const int brow = b * p.T + r * SEG * CH;
+                for (int pl = 0; pl < SEGP; ++pl) {
+                    const int st = pl & 1, row0 = brow + pl * tc::PT;
+                    if (pl >= 2 && !umma::mbar_wait(&empty_kv[st], ((pl - 2) >> 1) & 1, abort_flag)) break;
+                    tma::expect_tx(&full_kv[st], tc::Q_BYTES + tc::V_BYTES);
+                    tma::load_panel(sK + st * tc::Q_BYTES, &p.tm_k, 0, grp, row0, &full_kv[st]);
+                    tma::load_panel(sK + st * tc::Q_BYTES + tc::Q_BYTES / 2, &p.tm_k, 64, grp, row0, &full_kv[st]);
+                    tma::load_panel(sV + st * tc::V_BYTES, &p.tm_v, 0, h, row0, &full_kv[st]);
+                }
+            }
+            return;
+        }
+        if (warp > tc::MMA_WARP) return;
+        umma::tmem_alloc(tmem_slot, 64);
+        umma::fence_before_sync();
+        bar_work();
+        umma::fence_after_sync();
+        const uint32_t tbase = *tmem_slot;
+        for (int pl = 0; pl < SEGP; ++pl) {
+            const int st = pl & 1;
+            bar_work();                              // Vs of this pair is written
+            umma::fence_after_sync();
+            if (lane == 0) {
+                umma::gemm_mm<tc::PT, tc::PT, tc::PT>(tbase, umma::smem_addr(sK + st * tc::Q_BYTES),
+                                                      umma::smem_addr(sVs + st * tc::V_BYTES), ID_MM64, pl > 0);
+                umma::commit(&empty_kv[st]);
+                if (pl == SEGP - 1) umma::commit(barF);
+            }
+            __syncwarp();
+            if (*abort_flag) break;
+        }
+        umma::fence_before_sync();
+        bar_work();
+        if (*abort_flag && lane == 0) atomicExch(p.err, 1);
+        umma::tmem_dealloc(tbase, 64);
+        return;
+    }
+
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 232;\n");
+    const int rb = warp & 3;
+    const int row = rb * 32 + lane;
+    const int ch = warp >> 2;
+    segment_cumsum<SEG>(p, b, h, r, SEG, sGs, sTot, warp, lane, tid);
+    const float gend = sTot[SEG];
+    umma::fence_before_sync();
+    bar_work();
+    umma::fence_after_sync();
+    const uint32_t tbase = *tmem_slot;
+
+    for (int pl = 0; pl < SEGP; ++pl) {
+        const int st = pl & 1;
+        umma::mbar_wait(&full_kv[st], (pl >> 1) & 1, abort_flag);
+        if (pl >= 2) umma::mbar_wait(&empty_kv[st], ((pl - 2) >> 1) & 1, abort_flag);     // Vs stage is free
+#pragma unroll
+        for (int i = tid; i < tc::PT * (tc::VD / 8); i += 256) {
+            const int j = i / (tc::VD / 8), c = (i % (tc::VD / 8)) * 8;
+            const float sc = fexp(gend - sGs[pl * tc::PT + j]);
+            const uint32_t off = umma::tile_offset(j, c, tc::PT);
+            uint4 x = *reinterpret_cast<const uint4*>(sV + st * tc::V_BYTES + off);
+            uint32_t* xw = reinterpret_cast<uint32_t*>(&x);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                __nv_bfloat162 v2 = *reinterpret_cast<__nv_bfloat162*>(&xw[e]);
+                xw[e] = pack_bf16(__bfloat162float(v2.x) * sc, __bfloat162float(v2.y) * sc);
+            }
+            *reinterpret_cast<uint4*>(sVs + st * tc::V_BYTES + off) = x;
+        }
+        umma::fence_async_smem();
+        umma::fence_before_sync();
+        bar_work();
+        umma::fence_after_sync();
+        if (*abort_flag) break;
+    }
+    umma::mbar_wait(barF, 0, abort_flag);
+    umma::fence_after_sync();
+    {
+        float t[32];
+        umma::tmem_ld32(umma::tmem_addr(tbase, warp, ch * 32), t);
+        float* F = p.seg_F + (((long)b * p.H + h) * p.NS + r) * tc::KD * tc::VD + row * tc::VD + ch * 32;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) *reinterpret_cast<float4*>(F + c * 4) = make_float4(t[c * 4], t[c * 4 + 1], t[c * 4 + 2], t[c * 4 + 3]);
+    }
+    if (tid == 0) p.seg_D[((long)b * p.H + h) * p.NS + r] = gend;
+    umma::fence_before_sync();
+    bar_work();
+}
+
+int mamba2_seg_state_tc_launch(const Mamba2Params& p_in, cudaStream_t stream) {
+    Mamba2Params p = p_in;
+    int rc;
+    const long BT = (long)p.B * p.T;
+    if ((rc = tma::make_panel_map(&p.tm_k, p.k, BT, p.G, p.K, tc::PT)) != 0) return rc;
+    if ((rc = tma::make_panel_map(&p.tm_v, p.v, BT, p.H, p.V, tc::PT)) != 0) return rc;
+    auto kern = m2_seg_state_tc_kernel<M2_MLOW>;
+    const size_t sm = SegStateTcSmem<M2_MLOW>::total;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
+    if (e != cudaSuccess) return (int)e;
+    kern<<<p.B * p.H * (p.NS - 1), tc::NTHREADS, sm, stream>>>(p);
+    return (int)cudaGetLastError();
+}
+
+int mamba2_hi_out_tc_launch(const Mamba2Params& p_in, cudaStream_t stream) {
+    Mamba2Params p = p_in;
+    int rc;
+    const long BT = (long)p.B * p.T;
+    if ((rc = tma::make_panel_map(&p.tm_q, p.q, BT, p.G, p.K, tc::PT)) != 0) return rc;
+    if ((rc = tma::make_panel_map(&p.tm_h0, p.seg_H0, (long)p.B * p.H * p.NS * p.LH * p.K, 1, p.V, tc::KD)) != 0) return rc;
+    auto kern = m2_hi_out_tc_kernel<M2_MLOW>;
+    const size_t sm = HiOutTcSmem<M2_MLOW>::total;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
+    if (e != cudaSuccess) return (int)e;
+    kern<<<p.B * p.H * (p.NS - 1), tc::NTHREADS, sm, stream>>>(p);
+    return (int)cudaGetLastError();
+}
+
 int mamba2_hi_bwd_tc_launch(const Mamba2Params& p_in, cudaStream_t stream) {
     Mamba2Params p = p_in;
     int rc;
