@@ -278,7 +278,10 @@ def main():
         achieved = flops / (per_step * 1e-3) / 1e12
         NT = w["T"] // 64
         NS = (NT + 7) // 8
-        launches_per_step = (4 if NS > 1 else 1) + 1 + (5 if NS > 1 else 0) + 2 + 1 + 2
+        # forward: segment summaries, segment scan, high-level output, chunk kernel; backward: un-cumsum,
+        # segment summaries + scan (recomputed), high-level backward, reverse segment scan, two chunk passes,
+        # dg, two casts
+        launches_per_step = (4 if NS > 1 else 1) + 1 + (4 if NS > 1 else 0) + 2 + 1 + 2
         line = {
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
             "ms_per_step": per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,

@@ -948,8 +948,8 @@ template <int MLOW>
 __global__ void __launch_bounds__(256) m2_dg_kernel(const Mamba2Params p, float* __restrict__ dg) {
     extern __shared__ float sx[];
     constexpr int SEG = 1 << MLOW;
-    float* X = sx;                 // [NT]
-    float* XS = sx + p.NT;         // [NS]
+    float* X = sx;                 // [NT]  (combined-high prefix inside a segment)
+    float* XS = sx + p.NT;         // [NS]  (sum over high levels of the prefix over earlier segments)
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int h = blockIdx.x % p.H, b = blockIdx.x / p.H;
     const long bh = (long)b * p.H + h;
@@ -973,15 +973,19 @@ __global__ void __launch_bounds__(256) m2_dg_kernel(const Mamba2Params p, float*
     __syncthreads();
     int nlev = 0;
     while ((1 << nlev) < p.NT) ++nlev;          // inter-chunk levels in use
+    // every level writes its own row XL[lv][c] (no shared-memory atomics); rows are summed per chunk below
+    float* XL = sYs + p.NS * (p.LH > 0 ? p.LH : 1);     // [nlev][NT]
     if (tid < nlev) {
         const int lv = tid, period = 2 << lv;
+        float* xl = XL + lv * p.NT;
+        for (int c = 0; c < p.NT; ++c) xl[c] = 0.f;
         if (lv < MLOW) {
             float run = 0.f;
             for (int c = 0; c < p.NT; ++c) {
                 if ((c & (period - 1)) == 0) run = 0.f;
                 if (!((c >> lv) & 1)) {
                     run += sY[c * (MLOW + 1) + lv];
-                    atomicAdd(&X[c], run);
+                    xl[c] = run;
                 }
             }
         } else {
@@ -998,7 +1002,7 @@ __global__ void __launch_bounds__(256) m2_dg_kernel(const Mamba2Params p, float*
         float run = 0.f;
         for (int c = p.NT - 1; c >= 0; --c) {
             if ((c >> lv) & 1) {
-                atomicAdd(&X[c], run);
+                xl[c] = run;
                 run += sZ[c * p.LZ + lv];
             }
             if ((c & (period - 1)) == 0) run = 0.f;
@@ -1009,7 +1013,7 @@ __global__ void __launch_bounds__(256) m2_dg_kernel(const Mamba2Params p, float*
         for (int c = 0; c < p.NT; ++c) {
             if ((c & (SEG - 1)) == 0) run = 0.f;
             run += sY[c * (MLOW + 1) + MLOW];
-            atomicAdd(&X[c], run);
+            X[c] = run;
         }
     }
     __syncthreads();
@@ -1018,7 +1022,8 @@ __global__ void __launch_bounds__(256) m2_dg_kernel(const Mamba2Params p, float*
         float x0 = p.wq[base + (long)(63 - 2 * lane) * p.H];
         float x1 = p.wq[base + (long)(62 - 2 * lane) * p.H];
         warp_cumsum64(x0, x1, lane);
-        const float add = X[c] + XS[c / SEG];
+        float add = X[c] + XS[c / SEG];
+        for (int lv = 0; lv < nlev; ++lv) add += XL[lv * p.NT + c];
         dg[base + (long)(63 - 2 * lane) * p.H] = x0 + add;
         dg[base + (long)(62 - 2 * lane) * p.H] = x1 + add;
     }
@@ -1109,7 +1114,7 @@ void mamba2_uncumsum(const float* gc, float* g, long BT, int H, cudaStream_t str
 
 void mamba2_dg(const Mamba2Params& p, float* dg, cudaStream_t stream) {
     dim3 grid(p.B * p.H, (p.NT + 63) / 64);
-    const size_t smem = (size_t)(p.NT + p.NS + p.NT * p.LZ + p.NT * (M2_MLOW + 1) + p.NS * (p.LH > 0 ? p.LH : 1)) * sizeof(float);
+    const size_t smem = (size_t)(p.NT + p.NS + p.NT * p.LZ + p.NT * (M2_MLOW + 1) + p.NS * (p.LH > 0 ? p.LH : 1) + (size_t)p.LZ * p.NT) * sizeof(float);
     if (smem > 48 * 1024) cudaFuncSetAttribute(m2_dg_kernel<M2_MLOW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     m2_dg_kernel<M2_MLOW><<<grid, 256, smem, stream>>>(p, dg);
 }

@@ -17,7 +17,8 @@ namespace tcb {
 // tensor memory columns
 constexpr int TB_S = 0, TB_DP = 128, TB_KV = 256, TB_T0 = 320, TB_T1 = 384;   // first batch (+ KV in the second)
 constexpr int TB_DQ = 0, TB_DK = 128;                                         // second batch reuses S / dP
-constexpr int NDL = 12;                         // dlambda staging columns: 8 intra-pair levels + low pair levels
+constexpr int NDL = 11;                         // dlambda staging columns: 8 levels inside the pair, low pair levels, tile row sum
+constexpr int LAMC = 12;                        // lambda columns staged per row (levels 0..7 and the low pair levels)
 }  // namespace tcb
 
 template <int MLOW>
@@ -29,11 +30,12 @@ struct Bwd1TcSmem {
     static constexpr uint32_t do_off = v_off + tc::V_BYTES;
     static constexpr uint32_t ds_off = do_off + tc::V_BYTES;               // dS tile (32 KB) ...
     static constexpr uint32_t dos_off = ds_off + tc::PT * tc::PT * 2;      // ... + 2 scaled do tiles (32 KB): also the 64 KB fp32 staging
-    static constexpr uint32_t vs_off = dos_off + 2 * tc::V_BYTES;          // Vs (16 KB); before that: dlambda / row-sum staging
+    static constexpr uint32_t vs_off = dos_off + 2 * tc::V_BYTES;          // Vs (16 KB)
     static constexpr uint32_t h_off = vs_off + tc::V_BYTES;
     static constexpr uint32_t gp_off = h_off + (MP > 0 ? MP : 1) * tc::H_BYTES;   // float [3][128]
-    static constexpr uint32_t lam_off = gp_off + 3 * 128 * 4;              // bf16 [128][LAM_LD]
-    static constexpr uint32_t misc_off = lam_off + 128 * tc::LAM_LD * 2;   // float [512]: k.dk halves, per-chunk Z partials
+    static constexpr uint32_t lam_off = gp_off + 3 * 128 * 4;              // bf16 [128][LAMC] (only the columns this kernel reads)
+    static constexpr uint32_t dl_off = lam_off + 128 * tcb::LAMC * 2;      // float [2][128][NDL] dlambda halves
+    static constexpr uint32_t misc_off = dl_off + 2 * 128 * tcb::NDL * 4;  // float [512]: k.dk halves, per-chunk Z partials
     static constexpr uint32_t bar_off = misc_off + 2048;                   // mbarriers, tmem slot, abort flag
     static constexpr uint32_t total = bar_off + 128 + 1024;
 };
@@ -58,9 +60,10 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_fwdorder_tc_kernel(con
     unsigned char* sDO = smem + SM::do_off;
     unsigned char* sDS = smem + SM::ds_off;
     unsigned char* sDOs = smem + SM::dos_off;
-    unsigned char* sStage = smem + SM::ds_off;          // 64 KB fp32 staging = dS + scaled do (free once the second batch is done)
+    unsigned char* sStage = smem + SM::ds_off;          // 64 KB fp32 staging for dq = dS + scaled do (free once the second batch is done)
+    unsigned char* sStage2 = smem + SM::q_off;          // 64 KB fp32 staging for dk = q + k tiles (free once the second batch and the k row sums are done)
     unsigned char* sVs = smem + SM::vs_off;
-    float* sDL = reinterpret_cast<float*>(smem + SM::vs_off);            // [2][128][NDL] while Vs is not yet needed
+    float* sDL = reinterpret_cast<float*>(smem + SM::dl_off);            // [2][128][NDL]
     float* sWk = reinterpret_cast<float*>(smem + SM::misc_off);          // [2][128] partial k.dk, then [4][16] Z partials
     unsigned char* sH = smem + SM::h_off;
     float* sGp = reinterpret_cast<float*>(smem + SM::gp_off);
@@ -216,7 +219,7 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_fwdorder_tc_kernel(con
 #pragma unroll
         for (int i = 0; i < LAMR; ++i)
             if (lam_rc[i] != 0xffffffffu)
-                sLam[(lam_rc[i] >> 8) * tc::LAM_LD + (lam_rc[i] & 255)] = __ushort_as_bfloat16((unsigned short)lam_r[i]);
+                if ((lam_rc[i] & 255) < tcb::LAMC) sLam[(lam_rc[i] >> 8) * tcb::LAMC + (lam_rc[i] & 255)] = __ushort_as_bfloat16((unsigned short)lam_r[i]);
     };
     fetch_small(0);
     store_lam();
@@ -231,6 +234,11 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_fwdorder_tc_kernel(con
     for (int i = 0; i < (MP > 0 ? MP : 1); ++i) dsum[i] = 0.f;
 
     for (int pl = 0; pl < npairs; ++pl) {
+#ifdef LLATTN_STAMPS
+        int nstamp = 0;
+        const int stamp_slot = (blockIdx.x == 300 && pl == 2) ? (tid == 0 ? 0 : (tid == 200 ? 1 : (tid == 96 ? 2 : -1))) : -1;
+#endif
+        STAMP();   // 0 top
         const long t0 = (long)(r * SEGP + pl) * tc::PT;
         float gq[4];
 #pragma unroll
@@ -264,6 +272,7 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_fwdorder_tc_kernel(con
         umma::fence_before_sync();
         bar_work();                                  // barrier 1
         umma::fence_after_sync();
+        STAMP();   // 1 after barrier 1
         int nread = 0;
 #pragma unroll
         for (int lv = 0; lv < MP; ++lv) nread += (pl >> lv) & 1;
@@ -271,13 +280,14 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_fwdorder_tc_kernel(con
         const float glp = sGp[tc::PT - 1];
         float lam[NLAM];
 #pragma unroll
-        for (int i = 0; i < NLAM; ++i) lam[i] = (i < L) ? __bfloat162float(sLam[row * tc::LAM_LD + i]) : 0.f;
+        for (int i = 0; i < NLAM; ++i) lam[i] = (i < L) ? __bfloat162float(sLam[row * tcb::LAMC + i]) : 0.f;
 
         umma::mbar_wait(full_vd, pl & 1, abort_flag);
         umma::mbar_wait(full_qk, pl & 1, abort_flag);
         umma::mbar_wait(barA, pl & 1, abort_flag);
         umma::fence_after_sync();
 
+        STAMP();   // 2 batch A complete
         // ---- S, dP -> dS (bf16 tile) and the dlambda sums of the 8 levels inside the pair
         float bins[8];
         float wq_tile = 0.f;                         // sum_j bf16(dS_ij) S_ij: q_i.dq_i of the tile product, same rounding as dk
@@ -354,6 +364,7 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_fwdorder_tc_kernel(con
                 *reinterpret_cast<uint4*>(sDS + umma::tile_offset(row, j0 + c * 8, tc::PT)) =
                     make_uint4(packed[c * 4], packed[c * 4 + 1], packed[c * 4 + 2], packed[c * 4 + 3]);
         }
+        STAMP();   // 3 dS written
         float* myDL = sDL + (ch * 128 + row) * tcb::NDL;
 #pragma unroll
         for (int i = 0; i < 8; ++i) myDL[i] = bins[i];
@@ -394,45 +405,8 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_fwdorder_tc_kernel(con
                 myDL[8 + lv] = val;
             }
         }
-        bar_compute();                               // dlambda halves of every row are in shared memory
-        // ---- dlambda out, q.dq row sums, reader totals Z per 64-token chunk
-        float wq_row = 0.f;                          // valid for ch == 0 threads: q_i . dq_i
-        if (ch == 0) {
-            float* gdl = p.dl + (((long)b * p.T + t0 + row) * p.H + h) * L;
-            float zl[NLAM];
-#pragma unroll
-            for (int i = 0; i < NLAM; ++i) {
-                const float dlv = sDL[row * tcb::NDL + i] + sDL[(128 + row) * tcb::NDL + i];
-                if (i < L) gdl[i] = dlv;
-                zl[i] = lam[i] * dlv;
-                if (i >= 8) wq_row += zl[i];         // level reads; the 8 levels inside the pair come from the tile sum
-            }
-            wq_row += sDL[row * tcb::NDL + tcb::NDL - 1] + sDL[(128 + row) * tcb::NDL + tcb::NDL - 1];
-            // per-chunk (32-lane pairs of warps: rows 0..63 = warps 0,1 ; 64..127 = warps 2,3) totals
-#pragma unroll
-            for (int i = 7; i < NLAM; ++i) {
-                float z = zl[i];
-#pragma unroll
-                for (int d = 16; d > 0; d >>= 1) z += __shfl_xor_sync(0xffffffffu, z, d);
-                if (lane == 0) sWk[256 + warp * 16 + i] = z;
-            }
-        }
-        // ---- Vs = v * exp(glp - G_j) (overwrites the dlambda staging after the next barrier)
-        bar_compute();
-        if (tid < 2 * (NLAM - 7)) {
-            // tid -> (chunk of the pair, level index i >= 7): Z[c][lv] for readers, Y[c][0] for the level inside the pair
-            const int cpart = tid / (NLAM - 7), i = 7 + tid % (NLAM - 7);
-            const float z = sWk[256 + (cpart * 2) * 16 + i] + sWk[256 + (cpart * 2 + 1) * 16 + i];
-            const long cidx = ((long)b * p.H + h) * p.NT + (r * SEGP + pl) * 2 + cpart;
-            if (i == 7) {
-                if (cpart == 1) {
-                    p.Zc[cidx * p.LZ + 0] = z;                         // chunk level 0: reader is the second chunk
-                    p.Yc[(cidx - 1) * (MLOW + 1) + 0] = z;             // ... and its contributor total, same block pair
-                }
-            } else if ((pl >> (i - 8)) & 1) {
-                p.Zc[cidx * p.LZ + (i - 7)] = z;                       // pair level i-8 = chunk level i-7
-            }
-        }
+        STAMP();   // 4 level reads done
+        // ---- Vs = v * exp(glp - G_j)
         {
 #pragma unroll
             for (int i = tid; i < tc::PT * (tc::VD / 8); i += 256) {
@@ -449,33 +423,59 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_fwdorder_tc_kernel(con
                 *reinterpret_cast<uint4*>(sVs + off) = x;
             }
         }
+        STAMP();   // 5 Vs written
         umma::fence_async_smem();
         umma::fence_before_sync();
-        bar_work();                                  // barrier 2
+        bar_work();                                  // barrier 2 (also: dlambda halves of every row are in shared memory)
         umma::fence_after_sync();
+        STAMP();   // 6 after barrier 2
+        // ---- while the second batch runs: dlambda out (coalesced), q.dq row sums, reader totals Z per chunk
+        {
+            float* gdl = p.dl + (((long)b * p.T + t0) * p.H + h) * L;
+#pragma unroll
+            for (int e = tid; e < tc::PT * NLAM; e += 256) {
+                const int rr = e / NLAM, i = e - rr * NLAM;
+                if (i < L) gdl[(long)rr * p.H * L + i] = sDL[rr * tcb::NDL + i] + sDL[(128 + rr) * tcb::NDL + i];
+            }
+        }
+        float wq_row = 0.f;                          // valid for ch == 0 threads: q_i . dq_i
+        if (ch == 0) {
+            float zl[NLAM];
+#pragma unroll
+            for (int i = 0; i < NLAM; ++i) {
+                zl[i] = lam[i] * (sDL[row * tcb::NDL + i] + sDL[(128 + row) * tcb::NDL + i]);
+                if (i >= 8) wq_row += zl[i];         // level reads; the 8 levels inside the pair come from the tile sum
+            }
+            wq_row += sDL[row * tcb::NDL + tcb::NDL - 1] + sDL[(128 + row) * tcb::NDL + tcb::NDL - 1];
+#pragma unroll
+            for (int i = 7; i < NLAM; ++i) {
+                float z = zl[i];
+#pragma unroll
+                for (int d = 16; d > 0; d >>= 1) z += __shfl_xor_sync(0xffffffffu, z, d);
+                if (lane == 0) sWk[256 + warp * 16 + i] = z;
+            }
+        }
+        bar_compute();
+        if (tid < 2 * (NLAM - 7)) {
+            // tid -> (chunk of the pair, level index i >= 7): Z[c][lv] for readers, Y[c][0] for the level inside the pair
+            const int cpart = tid / (NLAM - 7), i = 7 + tid % (NLAM - 7);
+            const float z = sWk[256 + (cpart * 2) * 16 + i] + sWk[256 + (cpart * 2 + 1) * 16 + i];
+            const long cidx = ((long)b * p.H + h) * p.NT + (r * SEGP + pl) * 2 + cpart;
+            if (i == 7) {
+                if (cpart == 1) {
+                    p.Zc[cidx * p.LZ + 0] = z;                         // chunk level 0: reader is the second chunk
+                    p.Yc[(cidx - 1) * (MLOW + 1) + 0] = z;             // ... and its contributor total, same block pair
+                }
+            } else if ((pl >> (i - 8)) & 1) {
+                p.Zc[cidx * p.LZ + (i - 7)] = z;                       // pair level i-8 = chunk level i-7
+            }
+        }
+        STAMP();   // 7 dl / Z out
 
         umma::mbar_wait(barB, pl & 1, abort_flag);
         umma::fence_after_sync();
-        // ---- dq tile -> fp32 staging -> TMA reduce-add
-#pragma unroll
-        for (int hb = 0; hb < 2; ++hb) {
-            float t[32];
-            umma::tmem_ld32(umma::tmem_addr(tbase + tcb::TB_DQ, warp, ch * 64 + hb * 32), t);
-            unsigned char* box = sStage + (ch * 2 + hb) * 16384;
-#pragma unroll
-            for (int c = 0; c < 8; ++c)
-                *reinterpret_cast<float4*>(box + box_offset(row, c * 4)) = make_float4(t[c * 4], t[c * 4 + 1], t[c * 4 + 2], t[c * 4 + 3]);
-        }
-        umma::fence_async_smem();
-        bar_compute();
-        if (tid == 0) {
-            const int grow = b * p.T + (int)t0;
-#pragma unroll
-            for (int bx = 0; bx < 4; ++bx) tma::reduce_add_box(&p.tm_dq, bx * 32, grp, grow, sStage + bx * 16384);
-            tma::commit_group();
-            tma::wait_group_read0();
-        }
-        // ---- dk tile: k_j . dk_j row sums, then the same path
+        STAMP();   // 8 batch B complete
+        // ---- dk tile first: k_j . dk_j row sums need the k tile, which then becomes staging space
         float wk_part = 0.f;
         float dkv[2][32];
 #pragma unroll
@@ -493,27 +493,48 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_fwdorder_tc_kernel(con
             }
         }
         sWk[ch * 128 + row] = wk_part;
-        bar_compute();                               // the dq boxes have been read by the TMA unit (thread 0 waited)
+        // ---- dq tile -> fp32 staging (dS + scaled do space) -> TMA reduce-add
 #pragma unroll
         for (int hb = 0; hb < 2; ++hb) {
+            float t[32];
+            umma::tmem_ld32(umma::tmem_addr(tbase + tcb::TB_DQ, warp, ch * 64 + hb * 32), t);
             unsigned char* box = sStage + (ch * 2 + hb) * 16384;
+#pragma unroll
+            for (int c = 0; c < 8; ++c)
+                *reinterpret_cast<float4*>(box + box_offset(row, c * 4)) = make_float4(t[c * 4], t[c * 4 + 1], t[c * 4 + 2], t[c * 4 + 3]);
+        }
+        STAMP();   // 9 dk read, dq staged
+        umma::fence_async_smem();
+        bar_compute();                               // dq staged; every thread is done with the k tile
+        if (tid == 0) {
+            const int grow = b * p.T + (int)t0;
+#pragma unroll
+            for (int bx = 0; bx < 4; ++bx) tma::reduce_add_box(&p.tm_dq, bx * 32, grp, grow, sStage + bx * 16384);
+            tma::commit_group();
+        }
+        // ---- dk tile -> fp32 staging in the q / k tile space -> TMA reduce-add
+#pragma unroll
+        for (int hb = 0; hb < 2; ++hb) {
+            unsigned char* box = sStage2 + (ch * 2 + hb) * 16384;
 #pragma unroll
             for (int c = 0; c < 8; ++c)
                 *reinterpret_cast<float4*>(box + box_offset(row, c * 4)) =
                     make_float4(dkv[hb][c * 4], dkv[hb][c * 4 + 1], dkv[hb][c * 4 + 2], dkv[hb][c * 4 + 3]);
         }
+        STAMP();   // 10 dk staged
         umma::fence_async_smem();
         bar_compute();
         if (tid == 0) {
             const int grow = b * p.T + (int)t0;
 #pragma unroll
-            for (int bx = 0; bx < 4; ++bx) tma::reduce_add_box(&p.tm_dk, bx * 32, grp, grow, sStage + bx * 16384);
+            for (int bx = 0; bx < 4; ++bx) tma::reduce_add_box(&p.tm_dk, bx * 32, grp, grow, sStage2 + bx * 16384);
             tma::commit_group();
         }
         if (ch == 0) {
             const float w = wq_row - (sWk[row] + sWk[128 + row]);
             red_add_f32(p.wq + ((long)b * p.T + t0 + row) * p.H + h, w);
         }
+        STAMP();   // 11 reduces issued
         // ---- pair summary and the Fenwick carry over pair levels
         if (MP > 0 && pl + 1 < npairs) {
             const int j = __ffs(~pl) - 1;
@@ -548,11 +569,13 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_fwdorder_tc_kernel(con
                 for (int lv = 0; lv < MP; ++lv) dsum[lv] += glp;
             }
         }
+        STAMP();   // 12 states merged
         if (pl + 1 < npairs) store_lam();
         if (tid == 0) tma::wait_group_read0();       // staging is rewritten by the next pair
         umma::fence_async_smem();
         umma::fence_before_sync();
         bar_work();                                  // barrier 3
+        STAMP();   // 13 after barrier 3
         umma::fence_after_sync();
         if (*abort_flag) break;
     }
@@ -1084,3 +1107,9 @@ int mamba2_bwd1_tc_launch(const Mamba2Params& p_in, cudaStream_t stream) {
 }
 
 }  // namespace llattn
+
+#ifdef LLATTN_STAMPS
+extern "C" int llattn_debug_read_stamps_bwd(long long* host_dst) {
+    return (int)cudaMemcpyFromSymbol(host_dst, llattn::g_stamps, sizeof(long long) * 3 * 32);
+}
+#endif
