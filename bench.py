@@ -178,6 +178,77 @@ def run_reference(args, rank, world):
     print(json.dumps(line), flush=True)
 
 
+def run_gdn(args, rank, world, local):
+    """Secondary bench line: log-linear Gated DeltaNet, B=4 T=8192 H=16 Dk=Dv=128 chunk=64 L=14 per GPU.
+    The forward is the CUDA path; the backward is the interim autograd-through-torch path, so the
+    forward is also timed on its own."""
+    import math
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the hot path has no CPU fallback")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    from hattention_b200.gated_delta_rule_apis import chunk_h_gated_delta_rule
+    B, T, H, Dk, Dv, L = 4, 8192, 16, 128, 128, 14
+    gen = torch.Generator().manual_seed(rank)
+    q = torch.randn(B, T, H, Dk, generator=gen).bfloat16().to(dev)
+    k = torch.randn(B, T, H, Dk, generator=gen).bfloat16().to(dev)
+    v = torch.randn(B, T, H, Dv, generator=gen).bfloat16().to(dev)
+    beta = torch.sigmoid(torch.randn(B, T, H, generator=gen)).bfloat16().to(dev)
+    g = torch.nn.functional.logsigmoid(torch.randn(B, T, H, generator=gen) + 3.0).float().to(dev)
+    lam = torch.nn.functional.softplus(torch.randn(B, T, H, L, generator=gen)).bfloat16().to(dev)
+    do = torch.randn(B, T, H, Dv, generator=gen).bfloat16().to(dev)
+
+    def fwd():
+        return chunk_h_gated_delta_rule(q, k, v, g, lam, beta, use_qk_l2norm_in_kernel=True)[0]
+
+    W, K = max(args.warmup, 3), args.steps
+    for _ in range(W):
+        fwd()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler = ClockSampler(local)
+    e0.record()
+    for _ in range(K):
+        fwd()
+    e1.record()
+    torch.cuda.synchronize()
+    ms_fwd = e0.elapsed_time(e1) / K
+    clocks = sampler.stop()
+    ins = [x.clone().requires_grad_(True) for x in (q, k, v, g, lam, beta)]
+
+    def fwdbwd():
+        o = chunk_h_gated_delta_rule(ins[0], ins[1], ins[2], ins[3], ins[4], ins[5], use_qk_l2norm_in_kernel=True)[0]
+        torch.autograd.grad(o, ins, do)
+
+    fwdbwd()
+    torch.cuda.synchronize()
+    Kb = max(1, min(K, 3))
+    e0.record()
+    for _ in range(Kb):
+        fwdbwd()
+    e1.record()
+    torch.cuda.synchronize()
+    ms_fb = e0.elapsed_time(e1) / Kb
+    C, NT = 64, T // 64
+    Lc = (NT - 1).bit_length()
+    CK, CV, S = 2 * C * C * Dk, 2 * C * C * Dv, 2 * C * Dk * Dv
+    flops_fwd = (5 * CK + 2 * CV + 2 * C ** 3 + Lc * 2.5 * S) * B * H * NT     # reference-formulation count
+    pk = peaks()
+    line = {
+        "metric": "log-linear Gated DeltaNet chunkwise tokens/s at T=8K", "value": B * T / (ms_fb * 1e-3), "unit": "tokens/s",
+        "n_gpus": 1, "steps": Kb, "warmup": W, "ms_per_step": ms_fb, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "log-linear Gated DeltaNet fwd+bwd, B=4 T=8192 H=16 Dk=Dv=128 chunk=64 L=14",
+                   "note": "forward = CUDA kernels; backward = interim autograd through batched torch ops on the GPU"},
+        "forward_only": {"ms": ms_fwd, "tokens_per_s": B * T / (ms_fwd * 1e-3)},
+        "roofline": {"bound": "tensor", "achieved": flops_fwd / (ms_fwd * 1e-3) / 1e12, "peak": pk["tflops"], "unit": "TFLOP/s",
+                     "frac": flops_fwd / (ms_fwd * 1e-3) / 1e12 / pk["tflops"], "traffic": None, "peak_source": pk["source"],
+                     "kernel": "GDN forward launch chain (chunk preparation + state scan), reference-formulation flops"},
+        "gpu_launches": 2 * K, "clocks": clocks,
+    }
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -185,6 +256,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", default="mamba2", choices=["mamba2", "gdn"],
+                    help="mamba2 = the headline workload; gdn = log-linear Gated DeltaNet layer, B=4 T=8192 H=16 Dk=Dv=128 L=14")
     ap.add_argument("--batch", type=int, default=WORKLOAD["B"],
                     help="per-GPU batch; the headline workload is 2, profiler captures use 1")
     args = ap.parse_args()
@@ -195,6 +268,9 @@ def main():
 
     if args.impl == "reference":
         run_reference(args, rank, world)
+        return
+    if args.workload == "gdn":
+        run_gdn(args, rank, world, local)
         return
 
     if not torch.cuda.is_available():

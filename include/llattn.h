@@ -98,6 +98,23 @@ int llattn_gdn_fwd(const void* q, const void* k, const void* v, const void* beta
                    void* o, float* g_cum, void* Aw, void* Au, void* workspace, size_t workspace_bytes,
                    int B, int T, int H, int K, int V, int L, void* stream);
 
+/* Log-linear Gated DeltaNet backward, first stage: everything that involves the inter-chunk level
+ * states.  Replaces, inside hattention.chunkwise_hgdn.chunkwise_bwd (hattention/chunkwise_hgdn.py:
+ * 799-1010), the per-level loop over chunk_gated_delta_rule_fwd_h (state recomputation),
+ * chunk_gated_delta_rule_bwd_dhu (adjoint states) and the state-dependent parts of chunk_bwd_dqkwg /
+ * chunk_bwd_dv_local.  Inputs are those the reference saves for its backward: q, k (normalised, as in
+ * the forward), v, beta, the in-chunk cumulative g, lambda, Aw, Au, and d_o.  Per chunk, with
+ * kd = k exp(gl - G), wd = w exp(G), qd = exp(G)(q - tril(q k^T) w), u as in the forward, writes the
+ * gradients with respect to those chunk matrices, fp32 (B,T,H,K): d_qd, d_wd, d_kd; bf16 (B,T,H,V):
+ * d_u; the part of the gradient of each chunk's total log decay that comes from the state decay,
+ * d_gl fp32 (B,T/64,H); and columns 7 .. 7+ceil(log2(T/64))-1 of dlambda, fp32 (B,T,H,L) (other
+ * columns are left untouched).  Same shape constraints as llattn_gdn_fwd. */
+size_t llattn_gdn_bwd_levels_workspace_bytes(int B, int T, int H, int K, int V, int L);
+int llattn_gdn_bwd_levels(const void* q, const void* k, const void* v, const void* beta, const float* g_cum, const void* lambda,
+                          const void* Aw, const void* Au, const void* d_o, float* d_qd, float* d_wd, float* d_kd, void* d_u,
+                          float* d_gl, float* dlambda, void* workspace, size_t workspace_bytes,
+                          int B, int T, int H, int K, int V, int L, void* stream);
+
 /* Diagnostic: one 128 x N x kred bf16 tensor-core product (tcgen05.mma, accumulator in tensor
  * memory) per operand-layout combination used by the kernels: mode 0: D = A B^T with A [128][kred],
  * B [N][kred]; mode 1: D = A B with B [kred][N]; mode 2: D = A^T B with A [kred][128], B [kred][N].

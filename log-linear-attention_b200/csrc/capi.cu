@@ -193,7 +193,7 @@ static int gdn_check(int B, int T, int H, int K, int V, int L) {
     return 0;
 }
 
-static size_t gdn_setup(llattn::GdnParams& p, void* ws) {
+static size_t gdn_setup(llattn::GdnParams& p, void* ws, bool bwd = false) {
     p.NT = p.T / 64;
     p.NLEV = ceil_log2i(p.NT);
     Carver c(ws);
@@ -202,6 +202,12 @@ static size_t gdn_setup(llattn::GdnParams& p, void* ws) {
     p.wd = c.take<__nv_bfloat16>(n * p.K);
     p.qd = c.take<__nv_bfloat16>(n * p.K);
     p.u = c.take<__nv_bfloat16>(n * p.V);
+    if (bwd) {
+        // level states and their adjoints: one K x 32 tile per (batch, head, 32-column slice, chunk, level)
+        const size_t tiles = (size_t)p.B * p.H * (p.V / llattn::GDN_VS) * p.NT * (p.NLEV > 0 ? p.NLEV : 1);
+        p.hs = c.take<__nv_bfloat16>(tiles * p.K * llattn::GDN_VS);
+        p.dhs = c.take<__nv_bfloat16>(tiles * p.K * llattn::GDN_VS);
+    }
     return c.off;
 }
 
@@ -227,6 +233,38 @@ int llattn_gdn_fwd(const void* q, const void* k, const void* v, const void* beta
     p.beta = (const __nv_bfloat16*)beta; p.g = g; p.l = (const __nv_bfloat16*)lambda;
     p.o = (__nv_bfloat16*)o; p.g_cum = g_cum; p.Aw = (__nv_bfloat16*)Aw; p.Au = (__nv_bfloat16*)Au;
     return llattn::gdn_fwd_dispatch(p, (cudaStream_t)stream);
+}
+
+size_t llattn_gdn_bwd_levels_workspace_bytes(int B, int T, int H, int K, int V, int L) {
+    if (gdn_check(B, T, H, K, V, L) != 0) return 0;
+    llattn::GdnParams p = {};
+    p.B = B; p.T = T; p.H = H; p.K = K; p.V = V; p.L = L;
+    return gdn_setup(p, nullptr, true);
+}
+
+int llattn_gdn_bwd_levels(const void* q, const void* k, const void* v, const void* beta, const float* g_cum, const void* lambda,
+                          const void* Aw, const void* Au, const void* d_o, float* d_qd, float* d_wd, float* d_kd, void* d_u,
+                          float* d_gl, float* dlambda, void* workspace, size_t workspace_bytes,
+                          int B, int T, int H, int K, int V, int L, void* stream) {
+    int rc = gdn_check(B, T, H, K, V, L);
+    if (rc != 0) return rc;
+    if (!q || !k || !v || !beta || !g_cum || !lambda || !Aw || !Au || !d_o || !d_qd || !d_wd || !d_kd || !d_u || !d_gl || !dlambda)
+        return LLATTN_ERR_NULL;
+    llattn::GdnParams p = {};
+    p.B = B; p.T = T; p.H = H; p.K = K; p.V = V; p.L = L;
+    const size_t need = gdn_setup(p, nullptr, true);
+    if (!workspace || workspace_bytes < need || ((uintptr_t)workspace & 255)) return LLATTN_ERR_WORKSPACE;
+    gdn_setup(p, workspace, true);
+    p.q = (const __nv_bfloat16*)q; p.k = (const __nv_bfloat16*)k; p.v = (const __nv_bfloat16*)v;
+    p.beta = (const __nv_bfloat16*)beta; p.g = nullptr; p.l = (const __nv_bfloat16*)lambda;
+    p.g_cum = const_cast<float*>(g_cum);
+    p.Aw = (__nv_bfloat16*)const_cast<void*>(Aw); p.Au = (__nv_bfloat16*)const_cast<void*>(Au);
+    p.d_o = (const __nv_bfloat16*)d_o;
+    p.d_qd = d_qd; p.d_wd = d_wd; p.d_kd = d_kd; p.d_u = (__nv_bfloat16*)d_u; p.d_gl = d_gl; p.dl = dlambda;
+    cudaStream_t st = (cudaStream_t)stream;
+    if ((rc = llattn::gdn_recompute_dispatch(p, st)) != 0) return rc;
+    if ((rc = llattn::gdn_bwd_scan_dispatch(p, st)) != 0) return rc;
+    return llattn::gdn_bwd_levels_dispatch(p, st);
 }
 
 }  // extern "C"

@@ -47,7 +47,9 @@ struct PrepSmem {
     static constexpr size_t total = x_off + 128ull * LDA * 4;
 };
 
-template <int KD, int VD>
+// FROM_SAVED = true is the backward's recomputation: G and the two inverses are read back instead of
+// being solved for, and the intra-chunk output is skipped.
+template <int KD, int VD, bool FROM_SAVED>
 __global__ void __launch_bounds__(256, 1) gdn_chunk_prep_kernel(const GdnParams p) {
     using SM = PrepSmem<KD, VD>;
     constexpr int LDK = SM::LDK, LDV = SM::LDV, LDP = SM::LDP, LDA = SM::LDA;
@@ -83,12 +85,24 @@ __global__ void __launch_bounds__(256, 1) gdn_chunk_prep_kernel(const GdnParams 
     load_tile_async<CH, VD, 256>(sV, p.v + rowbase * VD, (long)p.H * VD, tid);
     cp_async_commit();
     if (warp == 0) {
-        float x0 = p.g[rowbase + (long)(2 * lane) * p.H], x1 = p.g[rowbase + (long)(2 * lane + 1) * p.H];
-        warp_cumsum64(x0, x1, lane);
-        sGc[2 * lane] = x0;
-        sGc[2 * lane + 1] = x1;
-        p.g_cum[rowbase + (long)(2 * lane) * p.H] = x0;
-        p.g_cum[rowbase + (long)(2 * lane + 1) * p.H] = x1;
+        if (FROM_SAVED) {
+            sGc[2 * lane] = p.g_cum[rowbase + (long)(2 * lane) * p.H];
+            sGc[2 * lane + 1] = p.g_cum[rowbase + (long)(2 * lane + 1) * p.H];
+        } else {
+            float x0 = p.g[rowbase + (long)(2 * lane) * p.H], x1 = p.g[rowbase + (long)(2 * lane + 1) * p.H];
+            warp_cumsum64(x0, x1, lane);
+            sGc[2 * lane] = x0;
+            sGc[2 * lane + 1] = x1;
+            p.g_cum[rowbase + (long)(2 * lane) * p.H] = x0;
+            p.g_cum[rowbase + (long)(2 * lane + 1) * p.H] = x1;
+        }
+    }
+    if (FROM_SAVED) {
+        for (int e = tid; e < 2 * CH * (CH / 8); e += 256) {
+            const int which = e / (CH * (CH / 8)), r = (e / (CH / 8)) % CH, c8 = (e % (CH / 8)) * 8;
+            const bf16* src = (which ? p.Au : p.Aw) + (rowbase + (long)r * p.H) * CH + c8;
+            *reinterpret_cast<uint4*>((which ? sAu : sAw) + r * LDP + c8) = *reinterpret_cast<const uint4*>(src);
+        }
     }
     if (tid >= 64 && tid < 128) sBe[tid - 64] = __bfloat162float(p.beta[rowbase + (long)(tid - 64) * p.H]);
     for (int e = tid; e < CH * 8; e += 256) {
@@ -117,9 +131,11 @@ __global__ void __launch_bounds__(256, 1) gdn_chunk_prep_kernel(const GdnParams 
 #pragma unroll
                 for (int e = 0; e < 2; ++e) {
                     const int jj = j + e;
-                    const float a = (jj < i) ? bi * accK[0][nt][hh * 2 + e] : 0.f;
-                    sA[i * LDA + jj] = a;
-                    sAg[i * LDA + jj] = (jj < i) ? a * fexp(gi - sGc[jj]) : 0.f;
+                    if (!FROM_SAVED) {
+                        const float a = (jj < i) ? bi * accK[0][nt][hh * 2 + e] : 0.f;
+                        sA[i * LDA + jj] = a;
+                        sAg[i * LDA + jj] = (jj < i) ? a * fexp(gi - sGc[jj]) : 0.f;
+                    }
                     qk[e] = (jj <= i) ? accQ[0][nt][hh * 2 + e] : 0.f;
                 }
                 *reinterpret_cast<uint32_t*>(sQK + i * LDP + j) = pack_bf16(qk[0], qk[1]);
@@ -143,7 +159,7 @@ __global__ void __launch_bounds__(256, 1) gdn_chunk_prep_kernel(const GdnParams 
     // ---- (I + A)^-1 and (I + Ag)^-1 by forward substitution: thread tid < 64 solves column tid of the
     //      first matrix, threads 64..127 column tid-64 of the second.  x_i = [i == col] - sum_{j<i} M[i][j] x_j;
     //      the solved part of the column lives in shared memory (one padded row per thread).
-    if (tid < 128) {
+    if (!FROM_SAVED && tid < 128) {
         const float* M = (tid < 64) ? sA : sAg;
         bf16* X = (tid < 64) ? sAw : sAu;
         bf16* gX = ((tid < 64) ? p.Aw : p.Au) + rowbase * CH;
@@ -231,6 +247,7 @@ __global__ void __launch_bounds__(256, 1) gdn_chunk_prep_kernel(const GdnParams 
                     pack_bf16((__bfloat162float(x.x) - acc[0][nt][hh * 2]) * eg, (__bfloat162float(x.y) - acc[0][nt][hh * 2 + 1]) * eg);
             }
     }
+    if (FROM_SAVED) return;
     // ---- P = (tril(q k^T) Aw) * Gamma * beta_j * lambda ; o = P v
     {
         float acc[1][4][4];
@@ -273,8 +290,6 @@ __global__ void __launch_bounds__(256, 1) gdn_chunk_prep_kernel(const GdnParams 
 // ------------------------------------------------------------------------------------------
 // sequential scan over chunks with binary-indexed level states
 // ------------------------------------------------------------------------------------------
-constexpr int GDN_VS = 32;          // V columns per CTA
-constexpr int GDN_MAXLEV = 8;       // inter-chunk levels (T up to 64 * 2^8 = 16384)
 
 template <int KD>
 struct ScanSmem {
@@ -289,7 +304,9 @@ struct ScanSmem {
     static constexpr size_t total = gl_off + 16;
 };
 
-template <int KD>
+// SAVE = true (the backward's recomputation) also writes, for every chunk, the bf16 level states
+// that the chunk reads: hs[((b*H + h)*nvs + vs)*NT + c][level][KD][32].
+template <int KD, bool SAVE>
 __global__ void __launch_bounds__(256, 1) gdn_scan_kernel(const GdnParams p) {
     using SM = ScanSmem<KD>;
     constexpr int LDK = SM::LDK, LDS = SM::LDS;
@@ -365,6 +382,17 @@ __global__ void __launch_bounds__(256, 1) gdn_scan_kernel(const GdnParams p) {
             issue_ku(c + 1, st ^ 1);
             fetch_small(c + 1);
         }
+        if (SAVE) {
+            bf16* dst = p.hs + ((size_t)blockIdx.x * p.NT + c) * nlev * (KD * GDN_VS);
+            for (int lv = 0; lv < nlev; ++lv) {
+                if (!((c >> lv) & 1)) continue;
+                for (int e = tid; e < KD * (GDN_VS / 8); e += 256) {
+                    const int r = e / (GDN_VS / 8), c8 = (e % (GDN_VS / 8)) * 8;
+                    *reinterpret_cast<uint4*>(dst + (size_t)lv * KD * GDN_VS + r * GDN_VS + c8) =
+                        *reinterpret_cast<const uint4*>(sSt + lv * KD * LDS + r * LDS + c8);
+                }
+            }
+        }
         const bf16* cQW = sQW;
         const bf16* cKd = sKd + st * CH * LDK;
         const bf16* cU = sU + st * CH * LDS;
@@ -421,7 +449,7 @@ __global__ void __launch_bounds__(256, 1) gdn_scan_kernel(const GdnParams p) {
                     *reinterpret_cast<uint32_t*>(sVh + i * LDS + nt * 8 + lc2) =
                         pack_bf16(__bfloat162float(x.x) - zsum[0][nt][hh * 2], __bfloat162float(x.y) - zsum[0][nt][hh * 2 + 1]);
                 }
-        } else {
+        } else if (!SAVE) {
             // output rows: add the intra-chunk part and store
             const long rowbase = ((long)b * p.T + (long)c * CH) * p.H + h;
 #pragma unroll
@@ -498,17 +526,17 @@ __global__ void __launch_bounds__(256, 1) gdn_scan_kernel(const GdnParams p) {
 // ------------------------------------------------------------------------------------------
 // host side
 // ------------------------------------------------------------------------------------------
-template <int KD, int VD>
+template <int KD, int VD, bool BWD>
 static int launch_gdn_fwd(const GdnParams& p, cudaStream_t stream) {
     cudaError_t e;
     {
-        auto kern = gdn_chunk_prep_kernel<KD, VD>;
+        auto kern = gdn_chunk_prep_kernel<KD, VD, BWD>;
         const size_t sm = PrepSmem<KD, VD>::total;
         if ((e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm)) != cudaSuccess) return (int)e;
         kern<<<p.B * p.NT * p.H, 256, sm, stream>>>(p);
     }
     {
-        auto kern = gdn_scan_kernel<KD>;
+        auto kern = gdn_scan_kernel<KD, BWD>;
         const size_t sm = ScanSmem<KD>::total;
         if ((e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm)) != cudaSuccess) return (int)e;
         kern<<<p.B * p.H * (p.V / GDN_VS), 256, sm, stream>>>(p);
@@ -517,8 +545,16 @@ static int launch_gdn_fwd(const GdnParams& p, cudaStream_t stream) {
 }
 
 int gdn_fwd_dispatch(const GdnParams& p, cudaStream_t stream) {
-    if (p.K == 128 && p.V == 128) return launch_gdn_fwd<128, 128>(p, stream);
-    if (p.K == 128 && p.V == 64) return launch_gdn_fwd<128, 64>(p, stream);
+    if (p.K == 128 && p.V == 128) return launch_gdn_fwd<128, 128, false>(p, stream);
+    if (p.K == 128 && p.V == 64) return launch_gdn_fwd<128, 64, false>(p, stream);
+    return LLATTN_ERR_UNSUPPORTED_SHAPE;
+}
+
+// recomputation for the backward: w, u, kd, wd, qd from the saved inverses, then the scan with the
+// level states written out
+int gdn_recompute_dispatch(const GdnParams& p, cudaStream_t stream) {
+    if (p.K == 128 && p.V == 128) return launch_gdn_fwd<128, 128, true>(p, stream);
+    if (p.K == 128 && p.V == 64) return launch_gdn_fwd<128, 64, true>(p, stream);
     return LLATTN_ERR_UNSUPPORTED_SHAPE;
 }
 

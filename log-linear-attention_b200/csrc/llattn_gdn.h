@@ -7,6 +7,9 @@
 
 namespace llattn {
 
+constexpr int GDN_VS = 32;          // V columns per CTA of the sequential scans
+constexpr int GDN_MAXLEV = 8;       // inter-chunk levels (T up to 64 * 2^8 = 16384)
+
 struct GdnParams {
     // inputs (q, k already L2-normalised / scaled by the caller, one q/k per head)
     const __nv_bfloat16* q;      // (B,T,H,K)
@@ -25,10 +28,29 @@ struct GdnParams {
     __nv_bfloat16* wd;           // (B,T,H,K)  w exp(G)
     __nv_bfloat16* qd;           // (B,T,H,K)  exp(G) (q - tril(q k^T) w)
     __nv_bfloat16* u;            // (B,T,H,V)
+    // backward
+    const __nv_bfloat16* d_o;    // (B,T,H,V)
+    __nv_bfloat16* hs;           // [(b,h,slice)][chunk][level][K][32]  level states read by each chunk
+    __nv_bfloat16* dhs;          // same layout: adjoints of the level states written by each chunk
+    __nv_bfloat16* d_u;          // (B,T,H,V)
+    float* d_qd;                 // (B,T,H,K)
+    float* d_wd;                 // (B,T,H,K)
+    float* d_kd;                 // (B,T,H,K)
+    float* d_gl;                 // (B,NT,H)  gradient w.r.t. the chunk's total log decay, scan part
+    float* dq;                   // (B,T,H,K) fp32 results
+    float* dk;
+    float* dv;                   // (B,T,H,V)
+    float* dbeta;                // (B,T,H)
+    float* dg;                   // (B,T,H)
+    float* dl;                   // (B,T,H,L)
     int B, T, H, K, V, L;
     int NT, NLEV;
 };
 
 int gdn_fwd_dispatch(const GdnParams& p, cudaStream_t stream);
+int gdn_recompute_dispatch(const GdnParams& p, cudaStream_t stream);
+int gdn_bwd_scan_dispatch(const GdnParams& p, cudaStream_t stream);      // adjoint level states, d_u
+int gdn_bwd_levels_dispatch(const GdnParams& p, cudaStream_t stream);    // d_qd, d_wd, d_kd, d_gl, dl (inter-chunk levels)
+int gdn_bwd_chunk_dispatch(const GdnParams& p, cudaStream_t stream);     // dq, dk, dv, dbeta, dg, dl (intra-chunk levels)
 
 }  // namespace llattn

@@ -99,3 +99,31 @@ def test_gradients_match_oracle_multi_level():
     assert_close(o, want, "o")
     for got, w_, key in zip(grads, wg, ("dq", "dk", "dv", "db", "dg", "dl")):
         assert_close(got, w_, key)
+
+
+@pytest.mark.parametrize("B,T,H,Dv,L", [(1, 1408, 2, 128, 12), (2, 1024, 1, 64, 11)])
+def test_backward_stages_match_whole_path_autograd(B, T, H, Dv, L):
+    """Driver-level gradients (normalised q, k) from the CUDA stage + chunk-local stage against
+    autograd through the chunk-by-chunk torch restatement of the whole path; 22 chunks (not a power
+    of two, five levels) with V = 128, and 16 chunks with V = 64."""
+    from hattention_b200 import chunkwise_hgdn as hg
+    from hattention_b200.base import HType
+    dev = torch.device("cuda:0")
+    Dk = 128
+    q, k, v, b, g, l = orc.make_gdn_inputs(B, T, H, Dk, Dv, L, seed=T)
+    scale = Dk ** -0.5
+    qn, kn = orc.gdn_layer_inputs(q, k, scale)
+    qn, kn, v, b, l = (x.bfloat16().to(dev) for x in (qn, kn, v, b, l / scale))
+    g = g.float().to(dev)
+    do = torch.randn(B, T, H, Dv, generator=torch.Generator().manual_seed(3)).bfloat16().to(dev)
+    g_cum, o, Aw, Au, _ = hg.chunkwise_fwd(qn, kn, v, b, g, l, False, 2, HType.WEAK, 64, False)
+    got = hg.chunkwise_bwd(qn, kn, v, b, g_cum, l, Aw, Au, do, False, 2, HType.WEAK, 64)
+    want = hg._chunkwise_bwd_autograd(qn, kn, v, b, g_cum, l, do)
+    torch.cuda.synchronize()
+    # `want` is an fp32 evaluation with none of the bf16 rounding points of the kernels (chunk matrices,
+    # level states and their adjoints are bf16 tensor-core operands), so the whole-tensor error must be at
+    # bf16 rounding level and single elements get twice the absolute allowance of the other tests
+    for a, w_, key in zip(got, want, ("dq", "dk", "dv", "db", "dg", "dl")):
+        rel = ((a.double() - w_.double()).norm() / w_.double().norm()).item()
+        assert rel <= 5e-3, f"{key}: relative Frobenius error {rel:.2e}"
+        assert_close(a, w_, key, atol=8e-3)
