@@ -115,6 +115,21 @@ int llattn_gdn_bwd_levels(const void* q, const void* k, const void* v, const voi
                           float* d_gl, float* dlambda, void* workspace, size_t workspace_bytes,
                           int B, int T, int H, int K, int V, int L, void* stream);
 
+/* Log-linear Gated DeltaNet backward, complete.  Replaces hattention.chunkwise_hgdn.chunkwise_bwd
+ * (hattention/chunkwise_hgdn.py:799-1010): the stage above followed by the chunk-local part
+ * (gradients through kd, wd, qd, u, the UT transform, tril(q k^T) and the intra-chunk output).
+ * Inputs as saved by the reference's autograd function (hattention/kernel.py:113-120): normalised
+ * q, k, then v, beta, the in-chunk cumulative g, lambda, Aw, Au, and d_o (bf16 (B,T,H,V)).
+ * Outputs are fp32: dq, dk (B,T,H,K) with respect to the NORMALISED q, k (the caller applies the
+ * l2norm / scale backward as hattention/kernel.py:208-221 does), dv (B,T,H,V), dbeta, dg (B,T,H)
+ * with respect to the raw g, dlambda (B,T,H,L; every column is written).  Same shape constraints
+ * as llattn_gdn_fwd. */
+size_t llattn_gdn_bwd_workspace_bytes(int B, int T, int H, int K, int V, int L);
+int llattn_gdn_bwd(const void* q, const void* k, const void* v, const void* beta, const float* g_cum, const void* lambda,
+                   const void* Aw, const void* Au, const void* d_o, float* dq, float* dk, float* dv, float* dbeta, float* dg,
+                   float* dlambda, void* workspace, size_t workspace_bytes,
+                   int B, int T, int H, int K, int V, int L, void* stream);
+
 /* Diagnostic: one 128 x N x kred bf16 tensor-core product (tcgen05.mma, accumulator in tensor
  * memory) per operand-layout combination used by the kernels: mode 0: D = A B^T with A [128][kred],
  * B [N][kred]; mode 1: D = A B with B [kred][N]; mode 2: D = A^T B with A [kred][128], B [kred][N].

@@ -267,4 +267,52 @@ int llattn_gdn_bwd_levels(const void* q, const void* k, const void* v, const voi
     return llattn::gdn_bwd_levels_dispatch(p, st);
 }
 
+static size_t gdn_bwd_setup(llattn::GdnParams& p, void* ws) {
+    const size_t base = gdn_setup(p, ws, true);
+    Carver c(ws);
+    c.off = base;
+    const size_t n = (size_t)p.B * p.T * p.H;
+    p.d_qd = c.take<float>(n * p.K);
+    p.d_wd = c.take<float>(n * p.K);
+    p.d_kd = c.take<float>(n * p.K);
+    p.d_u = c.take<__nv_bfloat16>(n * p.V);
+    p.d_gl = c.take<float>((size_t)p.B * p.NT * p.H);
+    return c.off;
+}
+
+size_t llattn_gdn_bwd_workspace_bytes(int B, int T, int H, int K, int V, int L) {
+    if (gdn_check(B, T, H, K, V, L) != 0) return 0;
+    llattn::GdnParams p = {};
+    p.B = B; p.T = T; p.H = H; p.K = K; p.V = V; p.L = L;
+    return gdn_bwd_setup(p, nullptr);
+}
+
+int llattn_gdn_bwd(const void* q, const void* k, const void* v, const void* beta, const float* g_cum, const void* lambda,
+                   const void* Aw, const void* Au, const void* d_o, float* dq, float* dk, float* dv, float* dbeta, float* dg,
+                   float* dlambda, void* workspace, size_t workspace_bytes,
+                   int B, int T, int H, int K, int V, int L, void* stream) {
+    int rc = gdn_check(B, T, H, K, V, L);
+    if (rc != 0) return rc;
+    if (!q || !k || !v || !beta || !g_cum || !lambda || !Aw || !Au || !d_o || !dq || !dk || !dv || !dbeta || !dg || !dlambda)
+        return LLATTN_ERR_NULL;
+    llattn::GdnParams p = {};
+    p.B = B; p.T = T; p.H = H; p.K = K; p.V = V; p.L = L;
+    const size_t need = gdn_bwd_setup(p, nullptr);
+    if (!workspace || workspace_bytes < need || ((uintptr_t)workspace & 255)) return LLATTN_ERR_WORKSPACE;
+    gdn_bwd_setup(p, workspace);
+    p.q = (const __nv_bfloat16*)q; p.k = (const __nv_bfloat16*)k; p.v = (const __nv_bfloat16*)v;
+    p.beta = (const __nv_bfloat16*)beta; p.g = nullptr; p.l = (const __nv_bfloat16*)lambda;
+    p.g_cum = const_cast<float*>(g_cum);
+    p.Aw = (__nv_bfloat16*)const_cast<void*>(Aw); p.Au = (__nv_bfloat16*)const_cast<void*>(Au);
+    p.d_o = (const __nv_bfloat16*)d_o;
+    p.dq = dq; p.dk = dk; p.dv = dv; p.dbeta = dbeta; p.dg = dg; p.dl = dlambda;
+    cudaStream_t st = (cudaStream_t)stream;
+    cudaError_t e = cudaMemsetAsync(dlambda, 0, (size_t)B * T * H * L * sizeof(float), st);
+    if (e != cudaSuccess) return (int)e;
+    if ((rc = llattn::gdn_recompute_dispatch(p, st)) != 0) return rc;
+    if ((rc = llattn::gdn_bwd_scan_dispatch(p, st)) != 0) return rc;
+    if ((rc = llattn::gdn_bwd_levels_dispatch(p, st)) != 0) return rc;
+    return llattn::gdn_bwd_chunk_dispatch(p, st);
+}
+
 }  // extern "C"

@@ -1,0 +1,499 @@
+// Log-linear Gated DeltaNet chunkwise backward for sm_100a: the chunk-local part.
+//
+// Reference being replaced: the chunk-local kernels called by hattention/chunkwise_hgdn.py:799-1010
+// (chunk_bwd_kernel_dqkwg intra part, bwd_prepare_wy_repr, chunk_bwd_kernel_o_intra and the torch
+// glue).  One CTA per (batch, head, chunk) turns the gradients with respect to the chunk matrices
+// qd, wd, kd, u (from the level stage) and d_o into gradients with respect to q, k, v, beta, g and the
+// intra-chunk columns of lambda.  Forward being differentiated (G = in-chunk cumulative log decay,
+// gl = G at the chunk end, Gamma_ij = exp(G_i - G_j), Lambda_ij = lambda[i, bit_length(i^j)]):
+//     KK = k k^T           A = stril(beta_i KK_ij)       Aw = (I + A)^-1      Au = (I + A * Gamma)^-1
+//     w = Aw (beta k)      u = Au (beta v)               QK = tril(q k^T)
+//     kd = k exp(gl - G)   wd = w exp(G)                 qd = exp(G) (q - QK w)
+//     X = QK Aw            P = X * Gamma * beta_j * Lambda               o_intra = P v
+// Aw and Au come from the forward; d(M^-1) = -M^-T dM^-1 M^-T turns their gradients into dA.
+#include "llattn_common.cuh"
+#include "llattn_gdn.h"
+
+namespace llattn {
+
+template <int KD, int VD>
+struct ChunkBwdSmem {
+    static constexpr int LDK = KD + PAD, LDV = VD + PAD, LDP = CH + PAD;
+    static constexpr size_t q_off = 0;                                   // bf16 [64][LDK]
+    static constexpr size_t k_off = q_off + 1ull * CH * LDK * 2;
+    static constexpr size_t w_off = k_off + 1ull * CH * LDK * 2;          // w
+    static constexpr size_t dqd_off = w_off + 1ull * CH * LDK * 2;        // -(d_qd exp(G))
+    static constexpr size_t dw_off = dqd_off + 1ull * CH * LDK * 2;       // dw
+    static constexpr size_t v_off = dw_off + 1ull * CH * LDK * 2;         // bf16 [64][LDV]
+    static constexpr size_t do_off = v_off + 1ull * CH * LDV * 2;
+    static constexpr size_t du_off = do_off + 1ull * CH * LDV * 2;
+    static constexpr size_t qk_off = du_off + 1ull * CH * LDV * 2;        // bf16 [64][LDP] tril(q k^T), later dKK
+    static constexpr size_t aw_off = qk_off + 1ull * CH * LDP * 2;
+    static constexpr size_t au_off = aw_off + 1ull * CH * LDP * 2;
+    static constexpr size_t kk_off = au_off + 1ull * CH * LDP * 2;        // k k^T
+    static constexpr size_t ta_off = kk_off + 1ull * CH * LDP * 2;        // Aw*beta_j, P, dAw, dAu
+    static constexpr size_t tb_off = ta_off + 1ull * CH * LDP * 2;        // dX, dAw Aw^T, dAu Au^T
+    static constexpr size_t dqk_off = tb_off + 1ull * CH * LDP * 2;       // dQK
+    static constexpr size_t f_off = dqk_off + 1ull * CH * LDP * 2;        // floats
+    // floats: G[64] beta[64] eG[64] eGk[64] dG[64] dB[64] lam[64][8] dL[64][8] misc[8]
+    static constexpr size_t total = f_off + (6 * CH + 2 * CH * 8 + 8) * 4;
+};
+
+template <int KD, int VD>
+__global__ void __launch_bounds__(256, 1) gdn_bwd_chunk_kernel(const GdnParams p) {
+    using SM = ChunkBwdSmem<KD, VD>;
+    constexpr int LDK = SM::LDK, LDV = SM::LDV, LDP = SM::LDP;
+    constexpr int NPK = KD / 32, NPV = VD / 32;       // 16-column pairs per warp for 64 x K and 64 x V results
+    static_assert(KD == 128, "row passes assume one float4 per lane per row");
+    extern __shared__ __align__(16) unsigned char smem[];
+    bf16* sQ = reinterpret_cast<bf16*>(smem + SM::q_off);
+    bf16* sK = reinterpret_cast<bf16*>(smem + SM::k_off);
+    bf16* sW = reinterpret_cast<bf16*>(smem + SM::w_off);
+    bf16* sDqd = reinterpret_cast<bf16*>(smem + SM::dqd_off);
+    bf16* sDW = reinterpret_cast<bf16*>(smem + SM::dw_off);
+    bf16* sV = reinterpret_cast<bf16*>(smem + SM::v_off);
+    bf16* sDo = reinterpret_cast<bf16*>(smem + SM::do_off);
+    bf16* sDU = reinterpret_cast<bf16*>(smem + SM::du_off);
+    bf16* sQK = reinterpret_cast<bf16*>(smem + SM::qk_off);
+    bf16* sAw = reinterpret_cast<bf16*>(smem + SM::aw_off);
+    bf16* sAu = reinterpret_cast<bf16*>(smem + SM::au_off);
+    bf16* sKK = reinterpret_cast<bf16*>(smem + SM::kk_off);
+    bf16* sTa = reinterpret_cast<bf16*>(smem + SM::ta_off);
+    bf16* sTb = reinterpret_cast<bf16*>(smem + SM::tb_off);
+    bf16* sDQK = reinterpret_cast<bf16*>(smem + SM::dqk_off);
+    float* sG = reinterpret_cast<float*>(smem + SM::f_off);
+    float* sBe = sG + CH;
+    float* sEG = sBe + CH;
+    float* sEGk = sEG + CH;
+    float* sDG = sEGk + CH;
+    float* sDB = sDG + CH;
+    float* sLam = sDB + CH;           // [64][8]
+    float* sDL = sLam + CH * 8;       // [64][8]
+    float* sMisc = sDL + CH * 8;      // [0] = sum d_kd . kd
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int h = blockIdx.x % p.H;
+    const int c = (blockIdx.x / p.H) % p.NT;
+    const int b = blockIdx.x / (p.H * p.NT);
+    const long rowbase = ((long)b * p.T + (long)c * CH) * p.H + h;
+    const int r0 = (warp & 3) * 16, cw = warp >> 2;
+    const int lr = lane >> 2, lc2 = (lane & 3) * 2;
+
+    load_tile_async<CH, KD, 256>(sQ, p.q + rowbase * KD, (long)p.H * KD, tid);
+    load_tile_async<CH, KD, 256>(sK, p.k + rowbase * KD, (long)p.H * KD, tid);
+    load_tile_async<CH, VD, 256>(sV, p.v + rowbase * VD, (long)p.H * VD, tid);
+    load_tile_async<CH, VD, 256>(sDo, p.d_o + rowbase * VD, (long)p.H * VD, tid);
+    load_tile_async<CH, VD, 256>(sDU, p.d_u + rowbase * VD, (long)p.H * VD, tid);
+    load_tile_async<CH, CH, 256>(sAw, p.Aw + rowbase * CH, (long)p.H * CH, tid);
+    load_tile_async<CH, CH, 256>(sAu, p.Au + rowbase * CH, (long)p.H * CH, tid);
+    cp_async_commit();
+    if (tid < CH) {
+        sG[tid] = p.g_cum[rowbase + (long)tid * p.H];
+        sBe[tid] = __bfloat162float(p.beta[rowbase + (long)tid * p.H]);
+        sDG[tid] = 0.f;
+        sDB[tid] = 0.f;
+    }
+    for (int e = tid; e < CH * 8; e += 256) {
+        const int i = e >> 3, lv = e & 7;
+        sLam[e] = (lv < INTRA_LEVELS) ? __bfloat162float(p.l[(rowbase + (long)i * p.H) * p.L + lv]) : 0.f;
+        sDL[e] = 0.f;
+    }
+    if (tid == 0) sMisc[0] = 0.f;
+    __syncthreads();
+    if (tid < CH) {
+        sEG[tid] = fexp(sG[tid]);
+        sEGk[tid] = fexp(sG[CH - 1] - sG[tid]);
+    }
+    __syncthreads();
+
+    // ---- row pass over the K-wide gradients: -(d_qd exp(G)) as a bf16 operand; the decay terms
+    //      dG_i += d_qd.qd + d_wd.wd - d_kd.kd and the chunk total of d_kd.kd
+    {
+        float kdsum = 0.f;
+        for (int it = 0; it < CH / 8; ++it) {
+            const int i = it * 8 + warp;
+            const long off = (rowbase + (long)i * p.H) * KD + lane * 4;
+            const float4 a = *reinterpret_cast<const float4*>(p.d_qd + off);
+            const float4 bw = *reinterpret_cast<const float4*>(p.d_wd + off);
+            const float4 ck = *reinterpret_cast<const float4*>(p.d_kd + off);
+            const uint2 xq = *reinterpret_cast<const uint2*>(p.qd + off);
+            const uint2 xw = *reinterpret_cast<const uint2*>(p.wd + off);
+            const uint2 xk = *reinterpret_cast<const uint2*>(p.kd + off);
+            const __nv_bfloat162 q0 = *reinterpret_cast<const __nv_bfloat162*>(&xq.x), q1 = *reinterpret_cast<const __nv_bfloat162*>(&xq.y);
+            const __nv_bfloat162 w0 = *reinterpret_cast<const __nv_bfloat162*>(&xw.x), w1 = *reinterpret_cast<const __nv_bfloat162*>(&xw.y);
+            const __nv_bfloat162 k0 = *reinterpret_cast<const __nv_bfloat162*>(&xk.x), k1 = *reinterpret_cast<const __nv_bfloat162*>(&xk.y);
+            float dq_ = a.x * __bfloat162float(q0.x) + a.y * __bfloat162float(q0.y) + a.z * __bfloat162float(q1.x) + a.w * __bfloat162float(q1.y);
+            float dw_ = bw.x * __bfloat162float(w0.x) + bw.y * __bfloat162float(w0.y) + bw.z * __bfloat162float(w1.x) + bw.w * __bfloat162float(w1.y);
+            float dk_ = ck.x * __bfloat162float(k0.x) + ck.y * __bfloat162float(k0.y) + ck.z * __bfloat162float(k1.x) + ck.w * __bfloat162float(k1.y);
+            float r = dq_ + dw_ - dk_;
+#pragma unroll
+            for (int d = 16; d > 0; d >>= 1) {
+                r += __shfl_xor_sync(0xffffffffu, r, d);
+                dk_ += __shfl_xor_sync(0xffffffffu, dk_, d);
+            }
+            if (lane == 0) sDG[i] += r;          // one warp per row: no other writer at this point
+            kdsum += dk_;
+            const float eg = -sEG[i];
+            uint2 o;
+            o.x = pack_bf16(a.x * eg, a.y * eg);
+            o.y = pack_bf16(a.z * eg, a.w * eg);
+            *reinterpret_cast<uint2*>(sDqd + i * LDK + lane * 4) = o;
+        }
+        if (lane == 0) atomicAdd(&sMisc[0], kdsum);
+    }
+    cp_async_wait<0>();
+    __syncthreads();
+
+    // ---- KK = k k^T, QK = tril(q k^T), Aw * beta_j
+    {
+        float accK[1][4][4], accQ[1][4][4];
+        zero_acc(accK);
+        zero_acc(accQ);
+        warp_gemm<1, 2, false, false>(accK, sK, LDK, r0, sK, LDK, cw * 32, KD, lane);
+        warp_gemm<1, 2, false, false>(accQ, sQ, LDK, r0, sK, LDK, cw * 32, KD, lane);
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+                const int i = r0 + lr + hh * 8, j = cw * 32 + nt * 8 + lc2;
+                *reinterpret_cast<uint32_t*>(sKK + i * LDP + j) = pack_bf16(accK[0][nt][hh * 2], accK[0][nt][hh * 2 + 1]);
+                *reinterpret_cast<uint32_t*>(sQK + i * LDP + j) =
+                    pack_bf16(j <= i ? accQ[0][nt][hh * 2] : 0.f, j + 1 <= i ? accQ[0][nt][hh * 2 + 1] : 0.f);
+            }
+        for (int e = tid; e < CH * CH / 2; e += 256) {
+            const int i = e / (CH / 2), j = (e % (CH / 2)) * 2;
+            const __nv_bfloat162 x = *reinterpret_cast<const __nv_bfloat162*>(sAw + i * LDP + j);
+            *reinterpret_cast<uint32_t*>(sTa + i * LDP + j) = pack_bf16(__bfloat162float(x.x) * sBe[j], __bfloat162float(x.y) * sBe[j + 1]);
+        }
+    }
+    __syncthreads();
+
+    // ---- w = (Aw * beta_j) k ;  X = QK Aw ;  dP = do v^T
+    float accX[1][4][4], accP[1][4][4];
+    {
+        float acc[1][2 * NPK][4];
+        zero_acc(acc);
+        warp_gemm<1, NPK, false, true>(acc, sTa, LDP, r0, sK, LDK, cw * (KD / 2), CH, lane);
+#pragma unroll
+        for (int nt = 0; nt < 2 * NPK; ++nt)
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh)
+                *reinterpret_cast<uint32_t*>(sW + (r0 + lr + hh * 8) * LDK + cw * (KD / 2) + nt * 8 + lc2) =
+                    pack_bf16(acc[0][nt][hh * 2], acc[0][nt][hh * 2 + 1]);
+        zero_acc(accX);
+        zero_acc(accP);
+        warp_gemm<1, 2, false, true>(accX, sQK, LDP, r0, sAw, LDP, cw * 32, CH, lane);
+        warp_gemm<1, 2, false, false>(accP, sDo, LDV, r0, sV, LDV, cw * 32, VD, lane);
+    }
+    __syncthreads();                           // Aw * beta_j has been consumed: its tile becomes P
+    {
+        float rs[2] = {0.f, 0.f};
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) {
+            float cs[2] = {0.f, 0.f}, cb[2] = {0.f, 0.f};
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+                const int i = r0 + lr + hh * 8;
+                const float gi = sG[i];
+                float pv[2], dx[2];
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int j = cw * 32 + nt * 8 + lc2 + e;
+                    pv[e] = 0.f;
+                    dx[e] = 0.f;
+                    if (j <= i) {
+                        const int lev = level_of(i, j);
+                        const float gam = fexp(gi - sG[j]), bj = sBe[j], lm = sLam[i * 8 + lev];
+                        const float x = accX[0][nt][hh * 2 + e], dp = accP[0][nt][hh * 2 + e];
+                        const float xg = dp * x * gam;
+                        pv[e] = x * gam * bj * lm;
+                        dx[e] = dp * gam * bj * lm;
+                        atomicAdd(&sDL[i * 8 + lev], xg * bj);
+                        cb[e] += xg * lm;
+                        const float s = xg * bj * lm;
+                        rs[hh] += s;
+                        cs[e] += s;
+                    }
+                }
+                const int j0 = cw * 32 + nt * 8 + lc2;
+                *reinterpret_cast<uint32_t*>(sTa + i * LDP + j0) = pack_bf16(pv[0], pv[1]);
+                *reinterpret_cast<uint32_t*>(sTb + i * LDP + j0) = pack_bf16(dx[0], dx[1]);
+            }
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+#pragma unroll
+                for (int d = 4; d < 32; d <<= 1) {
+                    cs[e] += __shfl_xor_sync(0xffffffffu, cs[e], d);
+                    cb[e] += __shfl_xor_sync(0xffffffffu, cb[e], d);
+                }
+                if (lr == 0) {
+                    const int j = cw * 32 + nt * 8 + lc2 + e;
+                    atomicAdd(&sDG[j], -cs[e]);
+                    atomicAdd(&sDB[j], cb[e]);
+                }
+            }
+        }
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+            rs[hh] += __shfl_xor_sync(0xffffffffu, rs[hh], 1);
+            rs[hh] += __shfl_xor_sync(0xffffffffu, rs[hh], 2);
+            if ((lane & 3) == 0) atomicAdd(&sDG[r0 + lr + hh * 8], rs[hh]);
+        }
+    }
+    __syncthreads();
+
+    // ---- dv = P^T do + beta * (Au^T d_u) ;  dbeta_i += (Au^T d_u)_i . v_i
+    {
+        float acc[1][2 * NPV][4], acc2[1][2 * NPV][4];
+        zero_acc(acc);
+        zero_acc(acc2);
+        const int c0 = cw * (VD / 2);
+        warp_gemm<1, NPV, true, true>(acc, sTa, LDP, r0, sDo, LDV, c0, CH, lane);
+        warp_gemm<1, NPV, true, true>(acc2, sAu, LDP, r0, sDU, LDV, c0, CH, lane);
+        float rb[2] = {0.f, 0.f};
+#pragma unroll
+        for (int nt = 0; nt < 2 * NPV; ++nt)
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+                const int i = r0 + lr + hh * 8, j = c0 + nt * 8 + lc2;
+                const float bi = sBe[i];
+                const __nv_bfloat162 x = *reinterpret_cast<const __nv_bfloat162*>(sV + i * LDV + j);
+                rb[hh] += acc2[0][nt][hh * 2] * __bfloat162float(x.x) + acc2[0][nt][hh * 2 + 1] * __bfloat162float(x.y);
+                *reinterpret_cast<float2*>(p.dv + (rowbase + (long)i * p.H) * VD + j) =
+                    make_float2(acc[0][nt][hh * 2] + bi * acc2[0][nt][hh * 2], acc[0][nt][hh * 2 + 1] + bi * acc2[0][nt][hh * 2 + 1]);
+            }
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+            rb[hh] += __shfl_xor_sync(0xffffffffu, rb[hh], 1);
+            rb[hh] += __shfl_xor_sync(0xffffffffu, rb[hh], 2);
+            if ((lane & 3) == 0) atomicAdd(&sDB[r0 + lr + hh * 8], rb[hh]);
+        }
+    }
+    // ---- dQK = tril(dX Aw^T - (d_qd exp(G)) w^T)
+    {
+        float acc[1][4][4];
+        zero_acc(acc);
+        warp_gemm<1, 2, false, false>(acc, sTb, LDP, r0, sAw, LDP, cw * 32, CH, lane);
+        warp_gemm<1, 2, false, false>(acc, sDqd, LDK, r0, sW, LDK, cw * 32, KD, lane);
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+                const int i = r0 + lr + hh * 8, j = cw * 32 + nt * 8 + lc2;
+                *reinterpret_cast<uint32_t*>(sDQK + i * LDP + j) =
+                    pack_bf16(j <= i ? acc[0][nt][hh * 2] : 0.f, j + 1 <= i ? acc[0][nt][hh * 2 + 1] : 0.f);
+            }
+    }
+    // ---- dw = d_wd exp(G) - QK^T (d_qd exp(G))
+    {
+        float acc[1][2 * NPK][4];
+        zero_acc(acc);
+        const int c0 = cw * (KD / 2);
+        warp_gemm<1, NPK, true, true>(acc, sQK, LDP, r0, sDqd, LDK, c0, CH, lane);
+#pragma unroll
+        for (int nt = 0; nt < 2 * NPK; ++nt)
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+                const int i = r0 + lr + hh * 8, j = c0 + nt * 8 + lc2;
+                const float2 d = *reinterpret_cast<const float2*>(p.d_wd + (rowbase + (long)i * p.H) * KD + j);
+                const float eg = sEG[i];
+                *reinterpret_cast<uint32_t*>(sDW + i * LDK + j) = pack_bf16(acc[0][nt][hh * 2] + d.x * eg, acc[0][nt][hh * 2 + 1] + d.y * eg);
+            }
+    }
+    __syncthreads();                           // dw and dQK complete; P has been consumed
+    // ---- dAw = QK^T dX + (dw k^T) * beta_j   -> tile
+    {
+        float acc[1][4][4], acc2[1][4][4];
+        zero_acc(acc);
+        zero_acc(acc2);
+        warp_gemm<1, 2, true, true>(acc, sQK, LDP, r0, sTb, LDP, cw * 32, CH, lane);
+        warp_gemm<1, 2, false, false>(acc2, sDW, LDK, r0, sK, LDK, cw * 32, KD, lane);
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+                const int i = r0 + lr + hh * 8, j = cw * 32 + nt * 8 + lc2;
+                *reinterpret_cast<uint32_t*>(sTa + i * LDP + j) =
+                    pack_bf16(acc[0][nt][hh * 2] + acc2[0][nt][hh * 2] * sBe[j], acc[0][nt][hh * 2 + 1] + acc2[0][nt][hh * 2 + 1] * sBe[j + 1]);
+            }
+    }
+    __syncthreads();                           // dAw complete; dX and QK have been consumed
+    // ---- dAw Aw^T -> tile
+    {
+        float acc[1][4][4];
+        zero_acc(acc);
+        warp_gemm<1, 2, false, false>(acc, sTa, LDP, r0, sAw, LDP, cw * 32, CH, lane);
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh)
+                *reinterpret_cast<uint32_t*>(sTb + (r0 + lr + hh * 8) * LDP + cw * 32 + nt * 8 + lc2) = pack_bf16(acc[0][nt][hh * 2], acc[0][nt][hh * 2 + 1]);
+    }
+    __syncthreads();
+    // ---- dA (from Aw) = -Aw^T (dAw Aw^T) ;  d(beta k) = Aw^T dw starts the dk accumulator
+    float dA1[1][4][4];
+    float dk_acc[1][2 * NPK][4];
+    {
+        zero_acc(dA1);
+        warp_gemm<1, 2, true, true>(dA1, sAw, LDP, r0, sTb, LDP, cw * 32, CH, lane);
+        zero_acc(dk_acc);
+        const int c0 = cw * (KD / 2);
+        warp_gemm<1, NPK, true, true>(dk_acc, sAw, LDP, r0, sDW, LDK, c0, CH, lane);
+        float rb[2] = {0.f, 0.f};
+#pragma unroll
+        for (int nt = 0; nt < 2 * NPK; ++nt)
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+                const int i = r0 + lr + hh * 8, j = c0 + nt * 8 + lc2;
+                const __nv_bfloat162 x = *reinterpret_cast<const __nv_bfloat162*>(sK + i * LDK + j);
+                rb[hh] += dk_acc[0][nt][hh * 2] * __bfloat162float(x.x) + dk_acc[0][nt][hh * 2 + 1] * __bfloat162float(x.y);
+                const float bi = sBe[i];
+                const float2 d = *reinterpret_cast<const float2*>(p.d_kd + (rowbase + (long)i * p.H) * KD + j);
+                const float ek = sEGk[i];
+                dk_acc[0][nt][hh * 2] = dk_acc[0][nt][hh * 2] * bi + d.x * ek;
+                dk_acc[0][nt][hh * 2 + 1] = dk_acc[0][nt][hh * 2 + 1] * bi + d.y * ek;
+            }
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+            rb[hh] += __shfl_xor_sync(0xffffffffu, rb[hh], 1);
+            rb[hh] += __shfl_xor_sync(0xffffffffu, rb[hh], 2);
+            if ((lane & 3) == 0) atomicAdd(&sDB[r0 + lr + hh * 8], rb[hh]);
+        }
+    }
+    // ---- dAu = (d_u v^T) * beta_j -> tile (the dAw tile has been consumed before the last barrier)
+    {
+        float acc[1][4][4];
+        zero_acc(acc);
+        warp_gemm<1, 2, false, false>(acc, sDU, LDV, r0, sV, LDV, cw * 32, VD, lane);
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+                const int j = cw * 32 + nt * 8 + lc2;
+                *reinterpret_cast<uint32_t*>(sTa + (r0 + lr + hh * 8) * LDP + j) = pack_bf16(acc[0][nt][hh * 2] * sBe[j], acc[0][nt][hh * 2 + 1] * sBe[j + 1]);
+            }
+    }
+    __syncthreads();                           // dAu complete; (dAw Aw^T) consumed
+    {
+        float acc[1][4][4];
+        zero_acc(acc);
+        warp_gemm<1, 2, false, false>(acc, sTa, LDP, r0, sAu, LDP, cw * 32, CH, lane);
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh)
+                *reinterpret_cast<uint32_t*>(sTb + (r0 + lr + hh * 8) * LDP + cw * 32 + nt * 8 + lc2) = pack_bf16(acc[0][nt][hh * 2], acc[0][nt][hh * 2 + 1]);
+    }
+    __syncthreads();
+    // ---- dAg = -Au^T (dAu Au^T);  dA = dA1 + dAg * Gamma;  decay and beta terms;  dKK = beta_i dA
+    {
+        float dAg[1][4][4];
+        zero_acc(dAg);
+        warp_gemm<1, 2, true, true>(dAg, sAu, LDP, r0, sTb, LDP, cw * 32, CH, lane);
+        float rs[2] = {0.f, 0.f}, rb[2] = {0.f, 0.f};
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) {
+            float cs[2] = {0.f, 0.f};
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+                const int i = r0 + lr + hh * 8;
+                const float gi = sG[i], bi = sBe[i];
+                float dkk[2];
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int j = cw * 32 + nt * 8 + lc2 + e;
+                    dkk[e] = 0.f;
+                    if (j < i) {
+                        const float gam = fexp(gi - sG[j]);
+                        const float kk = __bfloat162float(sKK[i * LDP + j]);
+                        const float dag = -dAg[0][nt][hh * 2 + e];
+                        const float s = dag * bi * kk * gam;
+                        rs[hh] += s;
+                        cs[e] += s;
+                        const float da = -dA1[0][nt][hh * 2 + e] + dag * gam;
+                        rb[hh] += da * kk;
+                        dkk[e] = bi * da;
+                    }
+                }
+                *reinterpret_cast<uint32_t*>(sQK + i * LDP + cw * 32 + nt * 8 + lc2) = pack_bf16(dkk[0], dkk[1]);
+            }
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+#pragma unroll
+                for (int d = 4; d < 32; d <<= 1) cs[e] += __shfl_xor_sync(0xffffffffu, cs[e], d);
+                if (lr == 0) atomicAdd(&sDG[cw * 32 + nt * 8 + lc2 + e], -cs[e]);
+            }
+        }
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+            rs[hh] += __shfl_xor_sync(0xffffffffu, rs[hh], 1);
+            rs[hh] += __shfl_xor_sync(0xffffffffu, rs[hh], 2);
+            rb[hh] += __shfl_xor_sync(0xffffffffu, rb[hh], 1);
+            rb[hh] += __shfl_xor_sync(0xffffffffu, rb[hh], 2);
+            if ((lane & 3) == 0) {
+                atomicAdd(&sDG[r0 + lr + hh * 8], rs[hh]);
+                atomicAdd(&sDB[r0 + lr + hh * 8], rb[hh]);
+            }
+        }
+    }
+    __syncthreads();                           // dKK complete (in the QK tile)
+    // ---- dq = d_qd exp(G) + dQK k ;  dk += dQK^T q + (dKK + dKK^T) k
+    {
+        const int c0 = cw * (KD / 2);
+        float acc[1][2 * NPK][4];
+        zero_acc(acc);
+        warp_gemm<1, NPK, false, true>(acc, sDQK, LDP, r0, sK, LDK, c0, CH, lane);
+#pragma unroll
+        for (int nt = 0; nt < 2 * NPK; ++nt)
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+                const int i = r0 + lr + hh * 8, j = c0 + nt * 8 + lc2;
+                const long off = (rowbase + (long)i * p.H) * KD + j;
+                const float2 d = *reinterpret_cast<const float2*>(p.d_qd + off);
+                const float eg = sEG[i];
+                *reinterpret_cast<float2*>(p.dq + off) = make_float2(acc[0][nt][hh * 2] + d.x * eg, acc[0][nt][hh * 2 + 1] + d.y * eg);
+            }
+        warp_gemm<1, NPK, true, true>(dk_acc, sDQK, LDP, r0, sQ, LDK, c0, CH, lane);
+        warp_gemm<1, NPK, false, true>(dk_acc, sQK, LDP, r0, sK, LDK, c0, CH, lane);
+        warp_gemm<1, NPK, true, true>(dk_acc, sQK, LDP, r0, sK, LDK, c0, CH, lane);
+#pragma unroll
+        for (int nt = 0; nt < 2 * NPK; ++nt)
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+                const int i = r0 + lr + hh * 8, j = c0 + nt * 8 + lc2;
+                *reinterpret_cast<float2*>(p.dk + (rowbase + (long)i * p.H) * KD + j) = make_float2(dk_acc[0][nt][hh * 2], dk_acc[0][nt][hh * 2 + 1]);
+            }
+    }
+    // ---- dg = reverse cumulative sum of dG (the chunk total also collects the state-decay part and
+    //      the total of d_kd . kd) ;  dbeta ;  d lambda of the intra-chunk levels
+    if (warp == 0) {
+        float x0 = sDG[CH - 1 - 2 * lane], x1 = sDG[CH - 2 - 2 * lane];   // reversed order
+        if (lane == 0) x0 += sMisc[0] + p.d_gl[((long)b * p.NT + c) * p.H + h];
+        warp_cumsum64(x0, x1, lane);
+        p.dg[rowbase + (long)(CH - 1 - 2 * lane) * p.H] = x0;
+        p.dg[rowbase + (long)(CH - 2 - 2 * lane) * p.H] = x1;
+    }
+    if (tid >= 64 && tid < 128) p.dbeta[rowbase + (long)(tid - 64) * p.H] = sDB[tid - 64];
+    for (int e = tid; e < CH * 8; e += 256) {
+        const int i = e >> 3, lv = e & 7;
+        if (lv < INTRA_LEVELS) p.dl[(rowbase + (long)i * p.H) * p.L + lv] = sDL[e];
+    }
+}
+
+template <int KD, int VD>
+static int launch_chunk(const GdnParams& p, cudaStream_t stream) {
+    auto kern = gdn_bwd_chunk_kernel<KD, VD>;
+    const size_t sm = ChunkBwdSmem<KD, VD>::total;
+    cudaError_t e;
+    if ((e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm)) != cudaSuccess) return (int)e;
+    kern<<<p.B * p.NT * p.H, 256, sm, stream>>>(p);
+    return (int)cudaGetLastError();
+}
+
+int gdn_bwd_chunk_dispatch(const GdnParams& p, cudaStream_t stream) {
+    if (p.K == 128 && p.V == 128) return launch_chunk<128, 128>(p, stream);
+    if (p.K == 128 && p.V == 64) return launch_chunk<128, 64>(p, stream);
+    return LLATTN_ERR_UNSUPPORTED_SHAPE;
+}
+
+}  // namespace llattn

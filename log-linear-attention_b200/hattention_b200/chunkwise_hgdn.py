@@ -107,9 +107,8 @@ def _levels_matrix(n: int, device) -> torch.Tensor:
 
 def _gdn_chunkwise_torch(q, k, v, b, g, l):
     """Differentiable fp32 restatement of the chunkwise GDN forward in batched torch ops on the
-    GPU (q, k already normalised / scaled; one q/k per head).  INTERIM: it exists only so that
-    `chunkwise_bwd` can return gradients through autograd (library GEMMs) until the hand-written
-    backward kernels land; the forward that users get is the CUDA path above.
+    GPU (q, k already normalised / scaled; one q/k per head).  Test infrastructure for
+    `_chunkwise_bwd_autograd`; the product path is the CUDA kernels.
     Same formulas as csrc/gdn_fwd.cu; levels are scanned per level (chunkwise_hgdn.py:718-788)."""
     B, T, H, K = q.shape
     V = v.shape[-1]
@@ -163,8 +162,7 @@ def _gdn_chunkwise_torch(q, k, v, b, g, l):
 def _gdn_prologue_torch(q, k, v, b, g, l):
     """Chunk-local part of the forward (everything before the scan over chunks) as batched fp32
     torch ops: returns qd, wd, kd, u, the intra-chunk output and the chunk totals of g, all
-    (B,H,NT,C,*).  INTERIM: differentiated by autograd to turn the CUDA stage's gradients with respect
-    to qd, wd, kd, u into gradients with respect to the inputs."""
+    (B,H,NT,C,*).  Test infrastructure: differentiated by autograd in `_chunkwise_bwd_staged`."""
     B, T, H, K = q.shape
     C = CHUNK
     NT = T // C
@@ -195,12 +193,37 @@ def _gdn_prologue_torch(q, k, v, b, g, l):
 def chunkwise_bwd(q, k, v, b, g, l, Aw, Au, do, head_first, level_base, htype, chunk_size, **unused):
     """Gradients (dq, dk, dv, db, dg, dl), fp32, of the driver for normalised q, k (signature of
     chunkwise_hgdn.py:799-817; `g` is the in-chunk cumulative sum returned by chunkwise_fwd).
-    Stage 1 (CUDA): recomputation of the chunk matrices and level states, the reverse scan of the
-    adjoint states and the state-dependent gradients.  Stage 2 (interim, batched torch autograd over
-    all chunks at once): the chunk-local part."""
+    One C-ABI call: recomputation of the chunk matrices and level states, reverse scan of the adjoint
+    states, state-dependent gradients, chunk-local gradients."""
     B, T, H, G_, K, V, L = _check(q, k, v, b, g, l, head_first, level_base, htype, chunk_size)
     if G_ != H:
         raise NotImplementedError("GDN backward expects one q/k per head")
+    lib = _lib.lib()
+    with torch.cuda.device(q.device):
+        q_, k_, v_, b_, l_, do_, Aw_, Au_ = (x.to(torch.bfloat16).contiguous() for x in (q, k, v, b, l, do, Aw, Au))
+        gc_ = g.to(torch.float32).contiguous()
+        f32 = dict(dtype=torch.float32, device=q.device)
+        dq, dk = torch.empty(B, T, H, K, **f32), torch.empty(B, T, H, K, **f32)
+        dv = torch.empty(B, T, H, V, **f32)
+        db, dg = torch.empty(B, T, H, **f32), torch.empty(B, T, H, **f32)
+        dl = torch.empty(B, T, H, L, **f32)
+        n = lib.llattn_gdn_bwd_workspace_bytes(B, T, H, K, V, L)
+        if n == 0:
+            raise ValueError("unsupported GDN shape (K must be 128, V 64 or 128, T <= 16384)")
+        ws = torch.empty(n, dtype=torch.uint8, device=q.device)
+        rc = lib.llattn_gdn_bwd(q_.data_ptr(), k_.data_ptr(), v_.data_ptr(), b_.data_ptr(), gc_.data_ptr(), l_.data_ptr(),
+                                Aw_.data_ptr(), Au_.data_ptr(), do_.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
+                                db.data_ptr(), dg.data_ptr(), dl.data_ptr(), ws.data_ptr(), ws.numel(),
+                                B, T, H, K, V, L, torch.cuda.current_stream().cuda_stream)
+        _lib.check(rc, "llattn_gdn_bwd")
+    return dq, dk, dv, db, dg, dl
+
+
+def _chunkwise_bwd_staged(q, k, v, b, g, l, Aw, Au, do):
+    """Cross-check used by the test-suite: the CUDA level stage (`llattn_gdn_bwd_levels`) followed by
+    autograd through the batched torch restatement of the chunk-local part."""
+    B, T, H, K = q.shape
+    V, L = v.shape[-1], l.shape[-1]
     lib = _lib.lib()
     NT = T // CHUNK
     with torch.cuda.device(q.device):
@@ -212,10 +235,7 @@ def chunkwise_bwd(q, k, v, b, g, l, Aw, Au, do, head_first, level_base, htype, c
         d_u = torch.empty(B, T, H, V, dtype=torch.bfloat16, device=q.device)
         d_gl = torch.empty(B, NT, H, dtype=torch.float32, device=q.device)
         dl = torch.zeros(B, T, H, L, dtype=torch.float32, device=q.device)
-        n = lib.llattn_gdn_bwd_levels_workspace_bytes(B, T, H, K, V, L)
-        if n == 0:
-            raise ValueError("unsupported GDN shape (K must be 128, V 64 or 128, T <= 16384)")
-        ws = torch.empty(n, dtype=torch.uint8, device=q.device)
+        ws = torch.empty(lib.llattn_gdn_bwd_levels_workspace_bytes(B, T, H, K, V, L), dtype=torch.uint8, device=q.device)
         rc = lib.llattn_gdn_bwd_levels(q_.data_ptr(), k_.data_ptr(), v_.data_ptr(), b_.data_ptr(), gc_.data_ptr(), l_.data_ptr(),
                                        Aw_.data_ptr(), Au_.data_ptr(), do_.data_ptr(), d_qd.data_ptr(), d_wd.data_ptr(),
                                        d_kd.data_ptr(), d_u.data_ptr(), d_gl.data_ptr(), dl.data_ptr(), ws.data_ptr(), ws.numel(),

@@ -103,8 +103,8 @@ def test_gradients_match_oracle_multi_level():
 
 @pytest.mark.parametrize("B,T,H,Dv,L", [(1, 1408, 2, 128, 12), (2, 1024, 1, 64, 11)])
 def test_backward_stages_match_whole_path_autograd(B, T, H, Dv, L):
-    """Driver-level gradients (normalised q, k) from the CUDA stage + chunk-local stage against
-    autograd through the chunk-by-chunk torch restatement of the whole path; 22 chunks (not a power
+    """Driver-level gradients (normalised q, k) from the CUDA backward, and from its level stage
+    alone completed by a batched torch chunk-local stage, against autograd through the chunk-by-chunk torch restatement of the whole path; 22 chunks (not a power
     of two, five levels) with V = 128, and 16 chunks with V = 64."""
     from hattention_b200 import chunkwise_hgdn as hg
     from hattention_b200.base import HType
@@ -118,8 +118,12 @@ def test_backward_stages_match_whole_path_autograd(B, T, H, Dv, L):
     do = torch.randn(B, T, H, Dv, generator=torch.Generator().manual_seed(3)).bfloat16().to(dev)
     g_cum, o, Aw, Au, _ = hg.chunkwise_fwd(qn, kn, v, b, g, l, False, 2, HType.WEAK, 64, False)
     got = hg.chunkwise_bwd(qn, kn, v, b, g_cum, l, Aw, Au, do, False, 2, HType.WEAK, 64)
+    staged = hg._chunkwise_bwd_staged(qn, kn, v, b, g_cum, l, Aw, Au, do)
     want = hg._chunkwise_bwd_autograd(qn, kn, v, b, g_cum, l, do)
     torch.cuda.synchronize()
+    for a, w_, key in zip(staged, want, ("dq", "dk", "dv", "db", "dg", "dl")):
+        rel = ((a.double() - w_.double()).norm() / w_.double().norm()).item()
+        assert rel <= 5e-3, f"staged {key}: relative Frobenius error {rel:.2e}"
     # `want` is an fp32 evaluation with none of the bf16 rounding points of the kernels (chunk matrices,
     # level states and their adjoints are bf16 tensor-core operands), so the whole-tensor error must be at
     # bf16 rounding level and single elements get twice the absolute allowance of the other tests
