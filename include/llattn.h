@@ -130,6 +130,15 @@ int llattn_gdn_bwd(const void* q, const void* k, const void* v, const void* beta
                    float* dlambda, void* workspace, size_t workspace_bytes,
                    int B, int T, int H, int K, int V, int L, void* stream);
 
+/* Row-wise L2 normalisation of q / k and its backward, as applied around the Gated DeltaNet drivers
+ * when use_qk_l2norm_in_kernel is set.  Replace fla.modules.l2norm.l2norm_fwd / l2norm_bwd with the
+ * scale folded in (hattention/kernel.py:20-29: l2norm_and_scale_fwd / l2norm_and_scale_bwd).
+ *   fwd: y = bf16(bf16(x rsqrt(sum x^2 + 1e-6)) * scale)        x, y bf16 (rows, D)
+ *   bwd: dx = bf16((g - yhat (yhat . g)) rstd), g = dy * scale   dy fp32 (rows, D), dx bf16
+ * Constraints: D % 8 == 0, D <= 256. */
+int llattn_l2norm_fwd(const void* x, void* y, long rows, int D, float scale, void* stream);
+int llattn_l2norm_bwd(const void* x, const float* dy, void* dx, long rows, int D, float scale, void* stream);
+
 /* Diagnostic: one 128 x N x kred bf16 tensor-core product (tcgen05.mma, accumulator in tensor
  * memory) per operand-layout combination used by the kernels: mode 0: D = A B^T with A [128][kred],
  * B [N][kred]; mode 1: D = A B with B [kred][N]; mode 2: D = A^T B with A [kred][128], B [kred][N].

@@ -16,18 +16,34 @@ from .base import HType, ceil_log, get_num_levels
 CHUNK = 64
 
 
-def l2norm_fwd(x: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
-    """x * rsqrt(sum(x^2) + eps) over the last dim, computed in fp32 (fla's l2norm_fwd)."""
-    xf = x.float()
-    return (xf * torch.rsqrt((xf * xf).sum(-1, keepdim=True) + eps)).to(x.dtype)
+def l2norm_fwd(x: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
+    """bf16(bf16(x * rsqrt(sum(x^2) + 1e-6)) * scale) over the last dim (fla's l2norm_fwd followed by the
+    reference's `* scale`, hattention/kernel.py:20-23), one CUDA pass."""
+    if not x.is_cuda:
+        raise RuntimeError("l2norm_fwd needs a CUDA tensor (there is no CPU path)")
+    xb = x.to(torch.bfloat16).contiguous()
+    y = torch.empty_like(xb)
+    D = xb.shape[-1]
+    with torch.cuda.device(x.device):
+        rc = _lib.lib().llattn_l2norm_fwd(xb.data_ptr(), y.data_ptr(), xb.numel() // D, D, float(scale),
+                                          torch.cuda.current_stream().cuda_stream)
+    _lib.check(rc, "llattn_l2norm_fwd")
+    return y
 
 
-def l2norm_bwd(x: torch.Tensor, dy: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
-    """Gradient of l2norm_fwd w.r.t. x: (dy - y (y . dy)) * rstd."""
-    xf, dyf = x.float(), dy.float()
-    rstd = torch.rsqrt((xf * xf).sum(-1, keepdim=True) + eps)
-    y = xf * rstd
-    return ((dyf - y * (y * dyf).sum(-1, keepdim=True)) * rstd).to(x.dtype)
+def l2norm_bwd(x: torch.Tensor, dy: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
+    """Gradient w.r.t. x of l2norm_fwd(x, scale) given dy (hattention/kernel.py:26-29), bf16."""
+    if not x.is_cuda:
+        raise RuntimeError("l2norm_bwd needs CUDA tensors (there is no CPU path)")
+    xb = x.to(torch.bfloat16).contiguous()
+    g = dy.to(torch.float32).contiguous()
+    dx = torch.empty_like(xb)
+    D = xb.shape[-1]
+    with torch.cuda.device(x.device):
+        rc = _lib.lib().llattn_l2norm_bwd(xb.data_ptr(), g.data_ptr(), dx.data_ptr(), xb.numel() // D, D, float(scale),
+                                          torch.cuda.current_stream().cuda_stream)
+    _lib.check(rc, "llattn_l2norm_bwd")
+    return dx
 
 
 def _check(q, k, v, b, g, l, head_first, level_base, htype, chunk_size):
@@ -270,7 +286,7 @@ def _chunkwise_bwd_autograd(q, k, v, b, g, l, do):
 
 def gdn_forward(q, k, v, b, g, l, scale, head_first, level_base, htype, chunk_size):
     """l2norm(q) * scale, l2norm(k), then the driver (hattention/kernel.py:109-120)."""
-    qn = (l2norm_fwd(q).float() * scale).to(q.dtype)
+    qn = l2norm_fwd(q, scale)
     kn = l2norm_fwd(k)
     g_cum, o, Aw, Au, _ = chunkwise_fwd(qn, kn, v, b, g, l, head_first, level_base, htype, chunk_size, False)
     return g_cum, o, Aw, Au
@@ -279,13 +295,13 @@ def gdn_forward(q, k, v, b, g, l, scale, head_first, level_base, htype, chunk_si
 def gdn_backward(q, k, v, b, g_cum, l, Aw, Au, do, scale, head_first, level_base, htype, chunk_size):
     """Backward of gdn_forward w.r.t. the raw q, k (through l2norm / scale), v, b, g, l
     (hattention/kernel.py:198-225)."""
-    qn = (l2norm_fwd(q).float() * scale).to(q.dtype)
+    qn = l2norm_fwd(q, scale)
     kn = l2norm_fwd(k)
     H = v.shape[2]
     G = k.shape[2]
     if G != H:
         raise NotImplementedError("GDN backward expects one q/k per head")
     dq, dk, dv, db, dg, dl = chunkwise_bwd(qn, kn, v, b, g_cum, l, Aw, Au, do, head_first, level_base, htype, chunk_size)
-    dq = l2norm_bwd(q, dq * scale)
+    dq = l2norm_bwd(q, dq, scale)
     dk = l2norm_bwd(k, dk)
     return dq, dk, dv, db, dg, dl

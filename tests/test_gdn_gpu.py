@@ -131,3 +131,26 @@ def test_backward_stages_match_whole_path_autograd(B, T, H, Dv, L):
         rel = ((a.double() - w_.double()).norm() / w_.double().norm()).item()
         assert rel <= 5e-3, f"{key}: relative Frobenius error {rel:.2e}"
         assert_close(a, w_, key, atol=8e-3)
+
+
+@pytest.mark.parametrize("D", [64, 128, 256])
+def test_l2norm_kernels(D):
+    """l2norm forward (with the reference's two bf16 rounding points) and backward against torch."""
+    from hattention_b200 import chunkwise_hgdn as hg
+    dev = torch.device("cuda:0")
+    gen = torch.Generator().manual_seed(D)
+    x = torch.randn(3, 37, 5, D, generator=gen).bfloat16().to(dev)
+    dy = torch.randn(3, 37, 5, D, generator=gen).to(dev)
+    scale = D ** -0.5
+    y = hg.l2norm_fwd(x, scale)
+    xf = x.float()
+    rstd = torch.rsqrt((xf * xf).sum(-1, keepdim=True) + 1e-6)
+    want = ((xf * rstd).bfloat16().float() * scale).bfloat16()
+    # rsqrtf and the reduction order may move a value by one bf16 ulp
+    assert ((y.float() - want.float()).abs() <= 2.0 ** -7 * want.float().abs() + 1e-30).all()
+    assert (y == want).float().mean().item() > 0.98
+    dx = hg.l2norm_bwd(x, dy, scale)
+    xr = xf.clone().requires_grad_(True)
+    yr = xr * torch.rsqrt((xr * xr).sum(-1, keepdim=True) + 1e-6) * scale
+    (gx,) = torch.autograd.grad(yr, xr, dy)
+    torch.testing.assert_close(dx.float(), gx, rtol=1e-2, atol=1e-2 * gx.abs().max().item())
