@@ -86,6 +86,16 @@ int llattn_mamba2_bwd(const void* q, const void* k, const void* v, const float* 
                       void* workspace, size_t workspace_bytes,
                       int B, int T, int H, int G, int K, int V, int L, void* stream);
 
+/* Same as llattn_mamba2_bwd, but the segment-level states of the forward pass are read from the
+ * workspace that the matching llattn_mamba2_fwd call used (unmodified since), instead of being
+ * recomputed from k, v, g (two launches less).  fwd_workspace == NULL behaves exactly like
+ * llattn_mamba2_bwd.  No counterpart in the reference, whose autograd function keeps only the inputs
+ * (hattention/kernel.py:125) and recomputes the states per level (hattention/chunkwise.py:1464-1490). */
+int llattn_mamba2_bwd_saved(const void* q, const void* k, const void* v, const float* g_cum, const void* lambda,
+                            const void* d_o, void* dq, void* dk, void* dv, float* dg, float* dlambda,
+                            void* workspace, size_t workspace_bytes, const void* fwd_workspace, size_t fwd_workspace_bytes,
+                            int B, int T, int H, int G, int K, int V, int L, void* stream);
+
 /* Log-linear Gated DeltaNet forward.  Replaces hattention.chunkwise_hgdn.chunkwise_fwd
  * (hattention/chunkwise_hgdn.py:566-788) with output_final_state=False.  q and k are per head,
  * (B,T,H,K), and must already be L2-normalised (q also scaled) as the reference's autograd

@@ -154,6 +154,14 @@ int llattn_mamba2_bwd(const void* q, const void* k, const void* v, const float* 
                       const void* d_o, void* dq, void* dk, void* dv, float* dg, float* dlambda,
                       void* workspace, size_t workspace_bytes,
                       int B, int T, int H, int G, int K, int V, int L, void* stream) {
+    return llattn_mamba2_bwd_saved(q, k, v, g_cum, lambda, d_o, dq, dk, dv, dg, dlambda, workspace, workspace_bytes,
+                                   nullptr, 0, B, T, H, G, K, V, L, stream);
+}
+
+int llattn_mamba2_bwd_saved(const void* q, const void* k, const void* v, const float* g_cum, const void* lambda,
+                            const void* d_o, void* dq, void* dk, void* dv, float* dg, float* dlambda,
+                            void* workspace, size_t workspace_bytes, const void* fwd_workspace, size_t fwd_workspace_bytes,
+                            int B, int T, int H, int G, int K, int V, int L, void* stream) {
     int rc = check_shape(B, T, H, G, K, V, L);
     if (rc != 0) return rc;
     if (!q || !k || !v || !g_cum || !lambda || !d_o || !dq || !dk || !dv || !dg || !dlambda) return LLATTN_ERR_NULL;
@@ -162,6 +170,16 @@ int llattn_mamba2_bwd(const void* q, const void* k, const void* v, const float* 
     const size_t need = setup(p, nullptr, true);
     if (!workspace || workspace_bytes < need || ((uintptr_t)workspace & 255)) return LLATTN_ERR_WORKSPACE;
     setup(p, workspace, true);
+    if (fwd_workspace) {
+        // segment decays and level states as the forward call left them in its workspace
+        llattn::Mamba2Params pf = {};
+        pf.B = B; pf.T = T; pf.H = H; pf.G = G; pf.K = K; pf.V = V; pf.L = L;
+        const size_t fneed = setup(pf, nullptr, false);
+        if (fwd_workspace_bytes < fneed || ((uintptr_t)fwd_workspace & 255)) return LLATTN_ERR_WORKSPACE;
+        setup(pf, const_cast<void*>(fwd_workspace), false);
+        p.seg_F = pf.seg_F; p.seg_D = pf.seg_D; p.seg_H0 = pf.seg_H0;
+        p.reuse_states = 1;
+    }
     cudaStream_t st = (cudaStream_t)stream;
     p.q = (const __nv_bfloat16*)q; p.k = (const __nv_bfloat16*)k; p.v = (const __nv_bfloat16*)v;
     p.l = (const __nv_bfloat16*)lambda; p.d_o = (const __nv_bfloat16*)d_o;

@@ -46,6 +46,7 @@ struct Mamba2Params {
     int B, T, H, G, K, V, L;
     int NT, NS, LH;
     int o_has_high;
+    int reuse_states;            // backward: seg_D / seg_H0 come from the forward call, do not recompute them
 };
 
 int mamba2_fwd_dispatch(Mamba2Params p, cudaStream_t stream);

@@ -70,7 +70,9 @@ template <int MLOW>
 __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_hi_bwd_tc_kernel(const __grid_constant__ Mamba2Params p) {
     using SM = HiBwdTcSmem<MLOW>;
     constexpr int SEG = SM::SEG, NDLH = tcs::MAXLH + 1;
-    // tensor memory: dF slots 0..4 (64 columns each), dq (128 columns), T (64 columns)
+    // tensor memory: dF slots 0..4 (64 columns each), dq (128 columns), T (64 columns).  The level reads
+    // T_j use three 64-column slots: T and the two halves of dq (dq is only written after every T of the
+    // pair has been consumed), so up to three of them are in flight without a CTA barrier.
     constexpr int TM_DF = 0, TM_DQ = 320, TM_T = 448;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -83,13 +85,15 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_hi_bwd_tc_kernel(const __g
     float* sTot = sGs + SEG * 64;
     float* sDL = reinterpret_cast<float*>(smem + SM::misc_off);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SM::bar_off);
-    uint64_t* barT = bars + 0;       // one level read T_j complete
-    uint64_t* barB = bars + 1;       // second batch of a pair complete
-    uint64_t* full_t = bars + 2;     // q and do tiles of a pair
-    uint64_t* full_h = bars + 3;     // the level states of the segment
-    uint64_t* empty_t = bars + 4;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + SM::bar_off + 64);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + SM::bar_off + 72);
+    uint64_t* barT = bars + 0;       // [3] level read T_j in slot j % 3 complete
+    uint64_t* barB = bars + 3;       // second batch of a pair complete
+    uint64_t* full_q = bars + 4;     // q tile of a pair
+    uint64_t* full_do = bars + 5;    // do tile of a pair
+    uint64_t* full_h = bars + 6;     // the level states of the segment
+    uint64_t* empty_q = bars + 7;    // second batch done: q may be overwritten
+    uint64_t* empty_do = bars + 8;   // every compute thread holds its do row in registers (256 arrivals)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + SM::bar_off + 96);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + SM::bar_off + 104);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int h = blockIdx.x % p.H;
@@ -106,7 +110,8 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_hi_bwd_tc_kernel(const __g
 
     if (tid == 0) {
 #pragma unroll
-        for (int i = 0; i < 5; ++i) umma::mbar_init(&bars[i], 1);
+        for (int i = 0; i < 8; ++i) umma::mbar_init(&bars[i], 1);
+        umma::mbar_init(empty_do, 256);
         umma::fence_mbar_init();
         *abort_flag = *p.err;
     }
@@ -116,6 +121,7 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_hi_bwd_tc_kernel(const __g
     constexpr uint32_t ID_KM64 = umma::idesc_bf16(128, 64, false, true);
     constexpr uint32_t ID_KK128 = umma::idesc_bf16(128, 128, false, false);
     constexpr uint32_t ID_MM64 = umma::idesc_bf16(128, 64, true, true);
+    auto t_slot = [&](int i) -> uint32_t { return (i % 3 == 0) ? (uint32_t)TM_T : (uint32_t)(TM_DQ + (i % 3 - 1) * 64); };
 
     if (warp >= tc::MMA_WARP) {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 40;\n");
@@ -130,11 +136,13 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_hi_bwd_tc_kernel(const __g
                 const int brow = b * p.T + r * SEG * CH;
                 for (int pl = 0; pl < npairs; ++pl) {
                     const int row0 = brow + pl * tc::PT;
-                    if (pl >= 1 && !umma::mbar_wait(empty_t, (pl - 1) & 1, abort_flag)) break;
-                    tma::expect_tx(full_t, tc::Q_BYTES + tc::V_BYTES);
-                    tma::load_panel(sQ, &p.tm_q, 0, grp, row0, full_t);
-                    tma::load_panel(sQ + tc::Q_BYTES / 2, &p.tm_q, 64, grp, row0, full_t);
-                    tma::load_panel(sDO, &p.tm_do, 0, h, row0, full_t);
+                    if (pl >= 1 && !umma::mbar_wait(empty_do, (pl - 1) & 1, abort_flag)) break;
+                    tma::expect_tx(full_do, tc::V_BYTES);
+                    tma::load_panel(sDO, &p.tm_do, 0, h, row0, full_do);
+                    if (pl >= 1 && !umma::mbar_wait(empty_q, (pl - 1) & 1, abort_flag)) break;
+                    tma::expect_tx(full_q, tc::Q_BYTES);
+                    tma::load_panel(sQ, &p.tm_q, 0, grp, row0, full_q);
+                    tma::load_panel(sQ + tc::Q_BYTES / 2, &p.tm_q, 64, grp, row0, full_q);
                 }
             }
             return;
@@ -148,18 +156,22 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_hi_bwd_tc_kernel(const __g
         const uint32_t aQ = umma::smem_addr(sQ), aH = umma::smem_addr(sH), aDOs = umma::smem_addr(sDOs);
         if (lane == 0) umma::mbar_wait(full_h, 0, abort_flag);
         for (int pl = 0; pl < npairs; ++pl) {
-            if (lane == 0) umma::mbar_wait(full_t, pl & 1, abort_flag);
+            if (lane == 0) umma::mbar_wait(full_q, pl & 1, abort_flag);
+            __syncwarp();
+            umma::fence_after_sync();
             for (int i = 0; i < nl; ++i) {
-                bar_work();                          // T slot is free (previous read consumed)
-                umma::fence_after_sync();
+                if (i >= 3) {
+                    bar_work();                      // slot i % 3 has been read by the compute warps
+                    umma::fence_after_sync();
+                }
                 if (lane == 0) {
-                    umma::gemm_km<tc::PT, tc::KD, tc::KD>(tbase + TM_T, aQ, aH + i * tc::H_BYTES, ID_KM64, false);
-                    umma::commit(barT);
+                    umma::gemm_km<tc::PT, tc::KD, tc::KD>(tbase + t_slot(i), aQ, aH + i * tc::H_BYTES, ID_KM64, false);
+                    umma::commit(&barT[i % 3]);
                 }
                 __syncwarp();
             }
             umma::fence_before_sync();
-            bar_work();                              // scaled copies of do are written
+            bar_work();                              // scaled copies of do are written, every T consumed
             umma::fence_after_sync();
             if (lane == 0) {
                 for (int i = 0; i < nl; ++i) {
@@ -167,12 +179,14 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_hi_bwd_tc_kernel(const __g
                     umma::gemm_mm<tc::PT, tc::PT, tc::PT>(tbase + TM_DF + i * 64, aQ, aDOs + i * tc::V_BYTES, ID_MM64, pl > 0);
                 }
                 umma::commit(barB);
+                // q is free as soon as the batch is done: let the producer refill it while dq is read out
+                umma::mbar_wait(barB, pl & 1, abort_flag);
+                asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(umma::smem_addr(empty_q)) : "memory");
             }
             __syncwarp();
             umma::fence_before_sync();
-            bar_work();                              // end of the pair: tiles and staging are free
+            bar_work();                              // end of the pair: dq has left tensor memory
             umma::fence_after_sync();
-            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(umma::smem_addr(empty_t)) : "memory");
             if (*abort_flag) break;
         }
         if (*abort_flag && lane == 0) atomicExch(p.err, 1);
@@ -192,7 +206,7 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_hi_bwd_tc_kernel(const __g
     bar_work();
     umma::fence_after_sync();
     const uint32_t tbase = *tmem_slot;
-    uint32_t phT = 0;
+    uint32_t phT[3] = {0, 0, 0};
 
     for (int pl = 0; pl < npairs; ++pl) {
         const long t0 = (long)(r * SEG) * CH + (long)pl * tc::PT;
@@ -201,19 +215,28 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_hi_bwd_tc_kernel(const __g
         float lamv[tcs::MAXLH];
 #pragma unroll
         for (int i = 0; i < tcs::MAXLH; ++i) lamv[i] = (i < nl) ? __bfloat162float(lrow[lev[i]]) : 0.f;
-        umma::mbar_wait(full_t, pl & 1, abort_flag);
+        umma::mbar_wait(full_do, pl & 1, abort_flag);
         uint4 dox[4];
 #pragma unroll
         for (int c = 0; c < 4; ++c) dox[c] = *reinterpret_cast<const uint4*>(sDO + umma::tile_offset(row, ch * 32 + c * 8, tc::PT));
+        asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(umma::smem_addr(empty_do)) : "memory");
         float* myDL = sDL + (ch * 128 + row) * NDLH;
         for (int i = 0; i < nl; ++i) {
-            umma::fence_before_sync();
-            bar_work();
-            umma::mbar_wait(barT, phT, abort_flag);
-            phT ^= 1;
+            const int sl = i % 3;
+            umma::mbar_wait(&barT[sl], phT[sl], abort_flag);
+            phT[sl] ^= 1;
             umma::fence_after_sync();
             float t[32];
-            umma::tmem_ld32(umma::tmem_addr(tbase + TM_T, warp, ch * 32), t);
+            umma::tmem_ld32(umma::tmem_addr(tbase + t_slot(i), warp, ch * 32), t);
+            if (i + 3 < nl) {
+                umma::fence_before_sync();
+                bar_work();                          // the slot may be reused
+            }
+            if (i == 0) {
+                // the staging area of the previous pair (same memory as the scaled copies) has been read
+                if (tid == 0) tma::wait_group_read0();
+                bar_compute();
+            }
             const float rs = lamv[i] * sc;
             float dot = 0.f;
             unsigned char* dst = sDOs + i * tc::V_BYTES;
@@ -264,13 +287,13 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_hi_bwd_tc_kernel(const __g
                 *reinterpret_cast<float4*>(box + box_offset_f32(row, c * 4)) = make_float4(t[c * 4], t[c * 4 + 1], t[c * 4 + 2], t[c * 4 + 3]);
         }
         umma::fence_async_smem();
+        umma::fence_before_sync();
         bar_compute();
         if (tid == 0) {
             const int grow = b * p.T + (int)t0;
 #pragma unroll
             for (int bx = 0; bx < 4; ++bx) tma::reduce_add_box(&p.tm_dq, bx * 32, grp, grow, sStage + bx * 16384);
             tma::commit_group();
-            tma::wait_group_read0();
         }
         if (tid < 2 * nl) {
             const int i = tid >> 1, cpart = tid & 1;

@@ -43,6 +43,8 @@ def lib():
     L.llattn_mamba2_fwd_static.argtypes = [_P] * 7 + _SHAPE + [_P]
     L.llattn_mamba2_bwd.restype = ctypes.c_int
     L.llattn_mamba2_bwd.argtypes = [_P] * 11 + [_P, ctypes.c_size_t] + _SHAPE + [_P]
+    L.llattn_mamba2_bwd_saved.restype = ctypes.c_int
+    L.llattn_mamba2_bwd_saved.argtypes = [_P] * 11 + [_P, ctypes.c_size_t, _P, ctypes.c_size_t] + _SHAPE + [_P]
     L.llattn_gdn_fwd_workspace_bytes.restype = ctypes.c_size_t
     L.llattn_gdn_fwd_workspace_bytes.argtypes = [ctypes.c_int] * 6
     L.llattn_gdn_fwd.restype = ctypes.c_int

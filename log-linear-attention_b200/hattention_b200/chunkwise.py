@@ -67,9 +67,12 @@ def chunkwise_fwd(
     htype: HType,
     chunk_size: int,
     output_final_state: bool,
+    keep_workspace: Optional[list] = None,
 ) -> Tuple[torch.Tensor, torch.Tensor, Optional[torch.Tensor]]:
     """Returns (o, in-chunk cumulative g, None) like the reference driver
-    (chunkwise.py:1118-1275)."""
+    (chunkwise.py:1118-1275).  `keep_workspace` (not in the reference): a list that receives the
+    call's scratch tensor, which `chunkwise_bwd(fwd_workspace=...)` can read the segment-level states
+    from instead of recomputing them."""
     if output_final_state:
         raise NotImplementedError("output_final_state=True (prefill hand-off) is not implemented")
     B, T, H, G, K, V, L = _check(q, k, v, g, l, head_first, level_base, htype, chunk_size)
@@ -84,6 +87,8 @@ def chunkwise_fwd(
                                    o.data_ptr(), g_cum.data_ptr(), ws.data_ptr(), ws.numel(),
                                    B, T, H, G, K, V, L, _stream())
         _lib.check(rc, "llattn_mamba2_fwd")
+        if keep_workspace is not None:
+            keep_workspace.append(ws)
     return o, g_cum, None
 
 
@@ -98,6 +103,7 @@ def chunkwise_bwd(
     level_base: int,
     htype: HType,
     chunk_size: int,
+    fwd_workspace: Optional[torch.Tensor] = None,
 ):
     """`g` is the in-chunk cumulative sum returned by chunkwise_fwd (what the reference's
     autograd function saves, kernel.py:86,125).  Returns (dq, dk, dv, dg, dl) with dq, dk summed
@@ -113,8 +119,11 @@ def chunkwise_bwd(
         dg = torch.empty_like(g_)
         dl = torch.empty(l_.shape, dtype=torch.float32, device=l_.device)
         ws = _workspace(lib.llattn_mamba2_bwd_workspace_bytes(B, T, H, G, K, V, L), q.device)
-        rc = lib.llattn_mamba2_bwd(q_.data_ptr(), k_.data_ptr(), v_.data_ptr(), g_.data_ptr(), l_.data_ptr(),
-                                   do_.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), dg.data_ptr(),
-                                   dl.data_ptr(), ws.data_ptr(), ws.numel(), B, T, H, G, K, V, L, _stream())
-        _lib.check(rc, "llattn_mamba2_bwd")
+        fws = fwd_workspace if (fwd_workspace is not None and fwd_workspace.device == q.device) else None
+        rc = lib.llattn_mamba2_bwd_saved(q_.data_ptr(), k_.data_ptr(), v_.data_ptr(), g_.data_ptr(), l_.data_ptr(),
+                                         do_.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), dg.data_ptr(),
+                                         dl.data_ptr(), ws.data_ptr(), ws.numel(),
+                                         fws.data_ptr() if fws is not None else None, fws.numel() if fws is not None else 0,
+                                         B, T, H, G, K, V, L, _stream())
+        _lib.check(rc, "llattn_mamba2_bwd_saved")
     return dq, dk, dv, dg, dl

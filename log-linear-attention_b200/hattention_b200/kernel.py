@@ -8,6 +8,12 @@ from .base import HStruct, HType
 from .chunkwise import chunkwise_bwd, chunkwise_fwd
 
 
+# Keep the Mamba-2 forward call's scratch (segment-level states, about 0.2 GB at B=2, T=16384, H=32)
+# alive until the backward, which then skips their recomputation.  The reference keeps only the inputs
+# (kernel.py:125); set to False for that memory behaviour.
+KEEP_FORWARD_STATES = True
+
+
 class HAttentionFunction(torch.autograd.Function):
     """Same argument list, validation and saved tensors as the reference's function
     (kernel.py:37-136); the chunkwise=False ("parallel") form is not provided."""
@@ -25,8 +31,11 @@ class HAttentionFunction(torch.autograd.Function):
                 raise NotImplementedError
             if scale is not None:
                 raise NotImplementedError
+            kept = [] if KEEP_FORWARD_STATES else None
             o, g_cum, _ = chunkwise_fwd(q=q, k=k, v=v, g=g, l=l, head_first=head_first, level_base=level_base,
-                                        htype=htype, chunk_size=chunk_sizes[0], output_final_state=False)
+                                        htype=htype, chunk_size=chunk_sizes[0], output_final_state=False,
+                                        keep_workspace=kept)
+            ctx.fwd_workspace = kept[0] if kept else None
             Aw = Au = None
         elif hstruct == HStruct.GDELTA and chunkwise:
             from .chunkwise_hgdn import gdn_forward
@@ -59,7 +68,8 @@ class HAttentionFunction(torch.autograd.Function):
         if ctx.hstruct == HStruct.MAMBA2:
             dq, dk, dv, dg, dl = chunkwise_bwd(q=q, k=k, v=v, g=g_cum, l=l, do=do, head_first=ctx.head_first,
                                                level_base=ctx.level_base, htype=ctx.htype,
-                                               chunk_size=ctx.chunk_sizes[0])
+                                               chunk_size=ctx.chunk_sizes[0], fwd_workspace=ctx.fwd_workspace)
+            ctx.fwd_workspace = None
             db = None
         else:
             from .chunkwise_hgdn import gdn_backward

@@ -146,3 +146,27 @@ def test_tensor_core_and_warp_mma_forward_agree():
     assert_close(o_tc, o_ref, "o (tcgen05)")
     assert_close(o_warp, o_ref, "o (mma.sync)")
     assert (o_tc.float() - o_warp.float()).abs().max().item() < 0.05 * o_ref.abs().max().item()
+
+
+def test_backward_with_forward_states_kept():
+    """The backward that reads the segment-level states left in the forward call's scratch returns what
+    the recomputing backward returns (dv, dlambda, dg bit for bit; dq, dk up to the order of their
+    fp32 reduce-adds)."""
+    from hattention_b200.base import HType
+    from hattention_b200.chunkwise import chunkwise_bwd, chunkwise_fwd
+    dev = torch.device("cuda:0")
+    B, T, H, P, N, G, L = 1, 2048, 4, 64, 128, 1, 12
+    q, k, v, g, l = orc.make_mamba2_inputs(B, T, H, P, N, G, L, seed=11)
+    q, k, v, l = (x.bfloat16().to(dev) for x in (q, k, v, l))
+    g = g.float().to(dev)
+    do = torch.randn(B, T, H, P, generator=torch.Generator().manual_seed(2)).bfloat16().to(dev)
+    kept = []
+    o, g_cum, _ = chunkwise_fwd(q, k, v, g, l, False, 2, HType.WEAK, 64, False, keep_workspace=kept)
+    a = chunkwise_bwd(q, k, v, g_cum, l, do, False, 2, HType.WEAK, 64, fwd_workspace=kept[0])
+    b = chunkwise_bwd(q, k, v, g_cum, l, do, False, 2, HType.WEAK, 64)
+    torch.cuda.synchronize()
+    for i in (2, 4):
+        assert torch.equal(a[i], b[i])
+    torch.testing.assert_close(a[3], b[3], rtol=1e-5, atol=1e-5)
+    for i in (0, 1):
+        torch.testing.assert_close(a[i].float(), b[i].float(), rtol=2e-2, atol=1e-3 * b[i].float().abs().max().item())
