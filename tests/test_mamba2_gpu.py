@@ -150,7 +150,7 @@ def test_tensor_core_and_warp_mma_forward_agree():
 
 def test_backward_with_forward_states_kept():
     """The backward that reads the segment-level states left in the forward call's scratch returns what
-    the recomputing backward returns (dv, dlambda, dg bit for bit; dq, dk up to the order of their
+    the recomputing backward returns (dv bit for bit; dlambda, dg, dq, dk up to the order of their
     fp32 reduce-adds)."""
     from hattention_b200.base import HType
     from hattention_b200.chunkwise import chunkwise_bwd, chunkwise_fwd
@@ -165,8 +165,8 @@ def test_backward_with_forward_states_kept():
     a = chunkwise_bwd(q, k, v, g_cum, l, do, False, 2, HType.WEAK, 64, fwd_workspace=kept[0])
     b = chunkwise_bwd(q, k, v, g_cum, l, do, False, 2, HType.WEAK, 64)
     torch.cuda.synchronize()
-    for i in (2, 4):
-        assert torch.equal(a[i], b[i])
-    torch.testing.assert_close(a[3], b[3], rtol=1e-5, atol=1e-5)
+    assert torch.equal(a[2], b[2])
+    for i in (3, 4):
+        torch.testing.assert_close(a[i], b[i], rtol=1e-5, atol=1e-5 * b[i].abs().max().item())
     for i in (0, 1):
         torch.testing.assert_close(a[i].float(), b[i].float(), rtol=2e-2, atol=1e-3 * b[i].float().abs().max().item())
