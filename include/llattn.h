@@ -96,6 +96,25 @@ int llattn_mamba2_bwd_saved(const void* q, const void* k, const void* v, const f
                             void* workspace, size_t workspace_bytes, const void* fwd_workspace, size_t fwd_workspace_bytes,
                             int B, int T, int H, int G, int K, int V, int L, void* stream);
 
+/* Element-wise preparation of the log-linear Mamba-2 layer call, its backward, and the D residual.
+ * Replace the torch ops around the kernel in hmamba_chunk_scan_combined (hattention/mamba_apis.py:
+ * 346-366, 401-402) and compute_lambda (hattention/mamba_apis.py:70-85).  rows = B*T*H; x, v, dv, dx, dy, o, y
+ * are bf16 (rows, P); dt_raw, ddt bf16 (rows); dl, lambda, ddl bf16 (rows, L); g, dg fp32 (rows); dlambda fp32
+ * (rows, L); A, dt_bias (may be NULL), D (may be NULL) fp32 (H); Lp fp32 (H, L).  lambda_mode: 0 "positive"
+ * softplus(Lp dl), 1 "bounded" exp(-exp(Lp) softplus(dl)), 2 none Lp dl.
+ *   fwd: dt = softplus(dt_raw + dt_bias); v = x dt; g = A dt; lambda = f(Lp, dl)
+ *   bwd: dx = dv dt + D dy; ddt, ddl; dA, dbias, dD (H) and dLp (H, L) are ACCUMULATED with atomics into
+ *        buffers the caller has cleared
+ *   residual: y = o + D x, y fp32 (y_is_f32 != 0; what torch's promotion gives for fp32 D) or bf16
+ * Constraints: P % 8 == 0, P <= 256, L <= 64. */
+int llattn_mamba2_prep_fwd(const void* x, const void* dt_raw, const float* dt_bias, const float* A, const void* dl, const float* Lp,
+                           void* v, float* g, void* lambda, long rows, int H, int P, int L, int lambda_mode, void* stream);
+int llattn_mamba2_prep_bwd(const void* x, const void* dt_raw, const float* dt_bias, const float* A, const void* dl, const float* Lp,
+                           const float* D, const void* dv, const float* dg, const float* dlambda, const void* dy,
+                           void* dx, void* ddt, void* ddl, float* dA, float* dbias, float* dLp, float* dD,
+                           long rows, int H, int P, int L, int lambda_mode, void* stream);
+int llattn_mamba2_residual(const void* o, const void* x, const float* D, void* y, int y_is_f32, long rows, int H, int P, void* stream);
+
 /* Log-linear Gated DeltaNet forward.  Replaces hattention.chunkwise_hgdn.chunkwise_fwd
  * (hattention/chunkwise_hgdn.py:566-788) with output_final_state=False.  q and k are per head,
  * (B,T,H,K), and must already be L2-normalised (q also scaled) as the reference's autograd

@@ -53,6 +53,12 @@ def lib():
     L.llattn_gdn_bwd_levels_workspace_bytes.argtypes = [ctypes.c_int] * 6
     L.llattn_gdn_bwd_levels.restype = ctypes.c_int
     L.llattn_gdn_bwd_levels.argtypes = [_P] * 15 + [_P, ctypes.c_size_t] + [ctypes.c_int] * 6 + [_P]
+    L.llattn_mamba2_prep_fwd.restype = ctypes.c_int
+    L.llattn_mamba2_prep_fwd.argtypes = [_P] * 9 + [ctypes.c_long] + [ctypes.c_int] * 4 + [_P]
+    L.llattn_mamba2_prep_bwd.restype = ctypes.c_int
+    L.llattn_mamba2_prep_bwd.argtypes = [_P] * 18 + [ctypes.c_long] + [ctypes.c_int] * 4 + [_P]
+    L.llattn_mamba2_residual.restype = ctypes.c_int
+    L.llattn_mamba2_residual.argtypes = [_P] * 4 + [ctypes.c_int, ctypes.c_long, ctypes.c_int, ctypes.c_int, _P]
     L.llattn_l2norm_fwd.restype = ctypes.c_int
     L.llattn_l2norm_fwd.argtypes = [_P, _P, ctypes.c_long, ctypes.c_int, ctypes.c_float, _P]
     L.llattn_l2norm_bwd.restype = ctypes.c_int

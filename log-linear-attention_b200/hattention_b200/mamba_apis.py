@@ -5,8 +5,88 @@ from typing import Optional, Tuple
 
 import torch
 
+from . import _lib
 from .base import HStruct, HType
-from .kernel import hattention_kernel
+from .chunkwise import chunkwise_bwd, chunkwise_fwd
+from .kernel import KEEP_FORWARD_STATES, hattention_kernel
+
+_LAMBDA_MODES = {"positive": 0, "bounded": 1, None: 2}
+# bf16 CUDA activations take the fused element-wise kernels; False keeps the reference's sequence of
+# torch ops around the kernel for every dtype (used by the tests as the cross-check)
+FUSED_PREP = True
+
+
+def _ptr(t):
+    return t.data_ptr() if t is not None else None
+
+
+class HMambaCombinedFunction(torch.autograd.Function):
+    """The whole layer call for bf16 CUDA activations as one autograd node: fused element-wise
+    preparation (one pass), the chunkwise kernels, the D residual; backward in the opposite order with
+    one fused pass for every element-wise gradient (mamba_apis.py:346-366, 401-402 in the reference are
+    separate torch ops, each differentiated by autograd)."""
+
+    @staticmethod
+    def forward(ctx, x, dt, A, Bm, Cm, dl, Lp, D, dt_bias, lambda_mode, level_base, htype):
+        lib = _lib.lib()
+        Bsz, T, H, P = x.shape
+        L = dl.shape[-1]
+        rows = Bsz * T * H
+        x_, dt_, dl_ = x.contiguous(), dt.contiguous(), dl.contiguous()
+        A_, Lp_ = A.detach().float().contiguous(), Lp.detach().float().contiguous()
+        D_ = D.detach().float().contiguous() if D is not None else None
+        bias_ = dt_bias.detach().float().contiguous() if dt_bias is not None else None
+        mode = _LAMBDA_MODES[lambda_mode]
+        with torch.cuda.device(x.device):
+            stream = torch.cuda.current_stream().cuda_stream
+            v = torch.empty_like(x_)
+            g = torch.empty(Bsz, T, H, dtype=torch.float32, device=x.device)
+            lam = torch.empty_like(dl_)
+            rc = lib.llattn_mamba2_prep_fwd(x_.data_ptr(), dt_.data_ptr(), _ptr(bias_), A_.data_ptr(), dl_.data_ptr(), Lp_.data_ptr(),
+                                            v.data_ptr(), g.data_ptr(), lam.data_ptr(), rows, H, P, L, mode, stream)
+            _lib.check(rc, "llattn_mamba2_prep_fwd")
+            kept = [] if KEEP_FORWARD_STATES else None
+            o, g_cum, _ = chunkwise_fwd(q=Cm, k=Bm, v=v, g=g, l=lam, head_first=False, level_base=level_base, htype=htype,
+                                        chunk_size=64, output_final_state=False, keep_workspace=kept)
+            if D_ is not None:
+                y_dtype = torch.promote_types(o.dtype, D.dtype)      # fp32 for an fp32 D, as x * D[...] + y gives
+                y = torch.empty(o.shape, dtype=torch.float32 if y_dtype == torch.float32 else torch.bfloat16, device=o.device)
+                rc = lib.llattn_mamba2_residual(o.data_ptr(), x_.data_ptr(), D_.data_ptr(), y.data_ptr(),
+                                                1 if y.dtype == torch.float32 else 0, rows, H, P, stream)
+                _lib.check(rc, "llattn_mamba2_residual")
+            else:
+                y = o
+        ctx.save_for_backward(x_, dt_, A_, Bm, Cm, dl_, Lp_, D_, bias_, v, g_cum, lam)
+        ctx.fwd_workspace = kept[0] if kept else None
+        ctx.meta = (mode, level_base, htype, A.dtype, Lp.dtype, D.dtype if D is not None else None,
+                    dt_bias.dtype if dt_bias is not None else None)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x_, dt_, A_, Bm, Cm, dl_, Lp_, D_, bias_, v, g_cum, lam = ctx.saved_tensors
+        mode, level_base, htype, A_dt, L_dt, D_dt, b_dt = ctx.meta
+        lib = _lib.lib()
+        Bsz, T, H, P = x_.shape
+        L = dl_.shape[-1]
+        rows = Bsz * T * H
+        dy = dy.to(torch.bfloat16).contiguous()
+        dq, dk, dv, dg, dlam = chunkwise_bwd(q=Cm, k=Bm, v=v, g=g_cum, l=lam, do=dy, head_first=False, level_base=level_base,
+                                             htype=htype, chunk_size=64, fwd_workspace=ctx.fwd_workspace)
+        ctx.fwd_workspace = None
+        with torch.cuda.device(x_.device):
+            dx = torch.empty_like(x_)
+            ddt = torch.empty_like(dt_)
+            ddl = torch.empty_like(dl_)
+            acc = torch.zeros(3 * H + H * L, dtype=torch.float32, device=x_.device)
+            dA, dbias, dD, dLp = acc[:H], acc[H:2 * H], acc[2 * H:3 * H], acc[3 * H:].view(H, L)
+            rc = lib.llattn_mamba2_prep_bwd(x_.data_ptr(), dt_.data_ptr(), _ptr(bias_), A_.data_ptr(), dl_.data_ptr(), Lp_.data_ptr(),
+                                            _ptr(D_), dv.data_ptr(), dg.data_ptr(), dlam.data_ptr(), dy.data_ptr(),
+                                            dx.data_ptr(), ddt.data_ptr(), ddl.data_ptr(), dA.data_ptr(), dbias.data_ptr(),
+                                            dLp.data_ptr(), dD.data_ptr(), rows, H, P, L, mode, torch.cuda.current_stream().cuda_stream)
+            _lib.check(rc, "llattn_mamba2_prep_bwd")
+        return (dx, ddt, dA.to(A_dt), dk.to(Bm.dtype), dq.to(Cm.dtype), ddl, dLp.to(L_dt),
+                dD.to(D_dt) if D_ is not None else None, dbias.to(b_dt) if bias_ is not None else None, None, None, None)
 
 
 def compute_lambda(L: torch.Tensor, dl: torch.Tensor, lambda_mode: Optional[str]) -> torch.Tensor:
@@ -72,9 +152,15 @@ def hmamba_chunk_scan_combined(
         raise NotImplementedError("only fixed lambda levels are supported")
     if L.shape[-1] != lambda_level_max or dl.shape[-1] != lambda_level_max:
         raise ValueError
+    if D is not None and D.dim() != 1:
+        raise ValueError
+    bf16_cuda = all(t.is_cuda and t.dtype == torch.bfloat16 for t in (x, dt, B, C, dl))
+    if (FUSED_PREP and bf16_cuda and lambda_hstruct == HStruct.MAMBA2 and lambda_htype == HType.WEAK and lambda_level_base == 2
+            and lambda_mode in _LAMBDA_MODES and x.shape[-1] % 8 == 0 and x.shape[-1] <= 256 and L.dim() == 2):
+        y = HMambaCombinedFunction.apply(x, dt, A, B, C, dl, L, D, dt_bias, lambda_mode, lambda_level_base, lambda_htype)
+        return y, None
+    # other dtypes: the reference's own sequence of torch element-wise ops around the kernel
     if D is not None:
-        if D.dim() != 1:
-            raise ValueError
         D_residual = x * D[None, None, :, None]
     if dt_bias is not None:
         dt = dt + dt_bias[None, None, :]

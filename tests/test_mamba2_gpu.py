@@ -170,3 +170,46 @@ def test_backward_with_forward_states_kept():
         torch.testing.assert_close(a[i], b[i], rtol=1e-5, atol=1e-5 * b[i].abs().max().item())
     for i in (0, 1):
         torch.testing.assert_close(a[i].float(), b[i].float(), rtol=2e-2, atol=1e-3 * b[i].float().abs().max().item())
+
+
+@pytest.mark.parametrize("lambda_mode", ["positive", "bounded", None])
+def test_layer_api_fused_preparation(lambda_mode):
+    """bf16 activations go through the fused element-wise kernels (one autograd node for the whole
+    layer call); outputs and every gradient, parameters included, against the same call with the
+    reference's sequence of torch ops around the kernel."""
+    from hattention_b200 import mamba_apis
+    from hattention_b200.base import HStruct, HType
+    torch.manual_seed(1)
+    B, T, H, P, N, L = 2, 512, 4, 64, 128, 11
+    dev = torch.device("cuda:0")
+    mk = lambda t, dt=torch.bfloat16: t.to(dt).to(dev).requires_grad_(True)
+    base = dict(x=torch.randn(B, T, H, P), dt=torch.randn(B, T, H) - 2, A=-torch.exp(torch.rand(H) * 2.7),
+                Bm=torch.randn(B, T, 1, N) / N ** 0.5, Cm=torch.randn(B, T, 1, N) / N ** 0.5, dl=torch.randn(B, T, H, L),
+                Lp=torch.rand(H, L) + 0.5, D=torch.randn(H), bias=torch.randn(H) * 0.1)
+    dy = torch.randn(B, T, H, P).bfloat16().to(dev)
+
+    def run(fused):
+        mamba_apis.FUSED_PREP = fused
+        try:
+            t = {k_: mk(v_, torch.float32 if k_ in ("A", "Lp", "D", "bias") else torch.bfloat16) for k_, v_ in base.items()}
+            y, _ = mamba_apis.hmamba_chunk_scan_combined(
+                t["x"], t["dt"], t["A"], t["Bm"], t["Cm"], t["dl"], t["Lp"], 64, D=t["D"], dt_bias=t["bias"],
+                dt_softplus=True, lambda_mode=lambda_mode, lambda_level_max=L, lambda_level_base=2,
+                lambda_htype=HType.WEAK, lambda_hstruct=HStruct.MAMBA2, lambda_level_fixed=True)
+            grads = torch.autograd.grad(y, list(t.values()), dy)
+            torch.cuda.synchronize()
+            return y, dict(zip(t.keys(), grads))
+        finally:
+            mamba_apis.FUSED_PREP = True
+
+    y1, g1 = run(True)
+    y0, g0 = run(False)
+    assert y1.dtype == y0.dtype
+    torch.testing.assert_close(y1.float(), y0.float(), rtol=2e-2, atol=2e-3 * y0.float().abs().max().item())
+    for k_ in g0:
+        a, b = g1[k_].float(), g0[k_].float()
+        assert a.shape == b.shape, k_
+        # parameter gradients are sums over B*T rows of signed terms (the two runs differ by bf16 rounding
+        # of v / lambda and by the order of fp32 atomics), hence the wider bound for them
+        rel = ((a - b).norm() / b.norm()).item()
+        assert rel < (3e-2 if k_ in ("A", "Lp", "D", "bias") else 1e-2), f"{k_}: relative error {rel:.3e}"
