@@ -365,7 +365,11 @@ def main():
             "config": {"workload": NAME if w["B"] == 2 else NAME.replace("B=2", f"B={w['B']}"), "l2": "inputs_exceed_l2 (about 320 MB of inputs per step vs 126 MB L2)",
                        "sharding": f"batch x {world}, no collective"},
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": pk["tflops"], "unit": "TFLOP/s",
-                         "frac": achieved / pk["tflops"], "traffic": None, "peak_source": pk["source"],
+                         "frac": achieved / pk["tflops"],
+                         # DRAM read + write of the dominant kernel (forward-order backward pass) from an ncu
+                         # capture at B=1 (227.9 MB per launch), proportional to the batch
+                         "traffic": 227.9e6 * w["B"] if (w["T"], w["H"]) == (16384, 32) else None,
+                         "peak_source": pk["source"],
                          "kernel": "whole fwd+bwd launch chain of one step (algorithmic flops F_min / step time)",
                          "algorithmic_flops_per_step": flops,
                          "algorithmic_bytes_per_step": algorithmic_bytes(w["B"], w["T"], w["H"], w["P"], w["N"], w["G"], w["L"])},

@@ -873,6 +873,7 @@ __global__ void __launch_bounds__(256, 1) m2_seg_dstate_kernel(const Mamba2Param
 // ------------------------------------------------------------------------------------------
 constexpr int MAX_LH_B = 10;
 
+template <int MAXLH>
 __global__ void __launch_bounds__(256) m2_seg_dscan_kernel(const Mamba2Params p, int KV) {
     const long bh = blockIdx.y;
     const int e4 = (blockIdx.x * 256 + threadIdx.x) * 4;
@@ -883,16 +884,31 @@ __global__ void __launch_bounds__(256) m2_seg_dscan_kernel(const Mamba2Params p,
     float* dH = p.seg_dHf + bh * p.NS * KV + e4;
     float* Yseg = p.Yseg + bh * p.NS * p.LH;
     const int lane = threadIdx.x & 31;
-    float st[MAX_LH_B][4];
+    float st[MAXLH][4];
 #pragma unroll
-    for (int j = 0; j < MAX_LH_B; ++j) st[j][0] = st[j][1] = st[j][2] = st[j][3] = 0.f;
+    for (int j = 0; j < MAXLH; ++j) st[j][0] = st[j][1] = st[j][2] = st[j][3] = 0.f;
+    // the loads of segment r - 1 are issued before the arithmetic of segment r (the recurrence itself is
+    // only in registers), so that a thread always has one segment's worth of loads in flight
+    float4 nF = make_float4(0.f, 0.f, 0.f, 0.f);
+    float4 ndF[MAXLH];
+    auto fetch = [&](int r) {
+        nF = (r >= 0 && r < p.NS - 1) ? *reinterpret_cast<const float4*>(F + (long)r * KV) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int j = 0; j < MAXLH; ++j)
+            ndF[j] = (r >= 0 && j < p.LH && ((r >> j) & 1)) ? *reinterpret_cast<const float4*>(dF + ((long)r * p.LH + j) * KV)
+                                                            : make_float4(0.f, 0.f, 0.f, 0.f);
+    };
+    fetch(p.NS - 1);
     for (int r = p.NS - 1; r >= 0; --r) {
         float4 out = make_float4(0.f, 0.f, 0.f, 0.f);
-        float4 f = make_float4(0.f, 0.f, 0.f, 0.f);
-        const float d = (r < p.NS - 1) ? __expf(D[r]) : 0.f;
-        if (r < p.NS - 1) f = *reinterpret_cast<const float4*>(F + (long)r * KV);
+        const float4 f = nF;
+        float4 cdF[MAXLH];
 #pragma unroll
-        for (int j = 0; j < MAX_LH_B; ++j) {
+        for (int j = 0; j < MAXLH; ++j) cdF[j] = ndF[j];
+        const float d = (r < p.NS - 1) ? __expf(D[r]) : 0.f;
+        fetch(r - 1);
+#pragma unroll
+        for (int j = 0; j < MAXLH; ++j) {
             if (j < p.LH) {
                 const bool bit = (r >> j) & 1;
                 if (!bit) {
@@ -912,8 +928,7 @@ __global__ void __launch_bounds__(256) m2_seg_dscan_kernel(const Mamba2Params p,
                     st[j][0] *= d; st[j][1] *= d; st[j][2] *= d; st[j][3] *= d;
                 }
                 if (bit) {
-                    float4 f = *reinterpret_cast<const float4*>(dF + ((long)r * p.LH + j) * KV);
-                    st[j][0] += f.x; st[j][1] += f.y; st[j][2] += f.z; st[j][3] += f.w;
+                    st[j][0] += cdF[j].x; st[j][1] += cdF[j].y; st[j][2] += cdF[j].z; st[j][3] += cdF[j].w;
                 }
             }
         }
@@ -1078,7 +1093,8 @@ static int launch_bwd(Mamba2Params p, cudaStream_t stream) {
         }
         {
             dim3 grid((KV / 4 + 255) / 256, p.B * p.H);
-            m2_seg_dscan_kernel<<<grid, 256, 0, stream>>>(p, KV);
+            if (p.LH <= 5) m2_seg_dscan_kernel<5><<<grid, 256, 0, stream>>>(p, KV);
+            else m2_seg_dscan_kernel<MAX_LH_B><<<grid, 256, 0, stream>>>(p, KV);
         }
     }
     const bool use_tc = (KD == 128 && VD == 64 && (p.NT % 2) == 0 && p.L <= 20 && g_use_tensor_core_path);
