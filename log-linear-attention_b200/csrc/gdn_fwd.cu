@@ -162,30 +162,42 @@ __global__ void __launch_bounds__(256, 1) gdn_chunk_prep_kernel(const GdnParams 
     if (!FROM_SAVED && tid < 128) {
         const float* M = (tid < 64) ? sA : sAg;
         bf16* X = (tid < 64) ? sAw : sAu;
-        bf16* gX = ((tid < 64) ? p.Aw : p.Au) + rowbase * CH;
-        float* xs = sX + tid * LDA;
         const int col = tid & 63;
+        // The column lives in registers: both loops are fully unrolled, so every index is static; the
+        // matrix entries are warp-wide broadcast loads.  Entries with j >= i are zero in M and x[j] is
+        // still zero there, so whole float4 groups can be used.
+        float x[CH];
 #pragma unroll
-        for (int i = 0; i < CH; i += 4) *reinterpret_cast<float4*>(xs + i) = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int i = 0; i < CH; ++i) x[i] = 0.f;
+#pragma unroll
         for (int i = 0; i < CH; ++i) {
             float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
             const float* Mi = M + i * LDA;
-            for (int j4 = 0; j4 < i; j4 += 4) {        // entries with j >= i are zero in M
-                const float4 m = *reinterpret_cast<const float4*>(Mi + j4);
-                const float4 x = *reinterpret_cast<const float4*>(xs + j4);
-                a0 += m.x * x.x;
-                a1 += m.y * x.y;
-                a2 += m.z * x.z;
-                a3 += m.w * x.w;
+#pragma unroll
+            for (int j4 = 0; j4 < i; j4 += 4) {
+                float4 m;      // volatile: program order is kept, so the loads of later rows are not hoisted and spilled
+                asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];\n" : "=f"(m.x), "=f"(m.y), "=f"(m.z), "=f"(m.w) : "r"(smem_u32(Mi + j4)));
+                a0 += m.x * x[j4];
+                a1 += m.y * x[j4 + 1];
+                a2 += m.z * x[j4 + 2];
+                a3 += m.w * x[j4 + 3];
             }
             const float xi = ((i == col) ? 1.f : 0.f) - ((a0 + a1) + (a2 + a3));
-            xs[i] = xi;
+            x[i] = xi;
             const bf16 xb = __float2bfloat16(xi);
-            X[i * LDP + col] = xb;
-            gX[(long)i * p.H * CH + col] = xb;
+            // volatile store: the (volatile) loads of the next row stay behind it
+            asm volatile("st.shared.b16 [%0], %1;\n" ::"r"(smem_u32(X + i * LDP + col)), "h"(*reinterpret_cast<const unsigned short*>(&xb)) : "memory");
         }
     }
     __syncthreads();
+    if (!FROM_SAVED) {
+        // the two inverses leave for the backward as whole rows (16-byte stores)
+        for (int e = tid; e < 2 * CH * (CH / 8); e += 256) {
+            const int which = e / (CH * (CH / 8)), r = (e / (CH / 8)) % CH, c8 = (e % (CH / 8)) * 8;
+            bf16* dst = (which ? p.Au : p.Aw) + (rowbase + (long)r * p.H) * CH + c8;
+            *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>((which ? sAu : sAw) + r * LDP + c8);
+        }
+    }
 
     // ---- w = Aw (beta k) -> wd = w exp(G);  u = Au (beta v);  kd = k exp(gl - G)
     {
