@@ -56,8 +56,8 @@ __device__ __forceinline__ void warp_gemm_tt_bscale(float (&acc)[MT][2 * NP][4],
 template <int KD>
 struct ScanBwdSmem {
     static constexpr int LDK = KD + PAD, LDS = GDN_VS + PAD;
-    static constexpr size_t qw_off = 0;                                          // bf16 [128][LDK]: rows 0..63 qd, 64..127 wd
-    static constexpr size_t kd_off = qw_off + 1ull * 128 * LDK * 2;              // bf16 [64][LDK]
+    static constexpr size_t qw_off = 0;                                          // bf16 [2][128][LDK]: rows 0..63 qd, 64..127 wd
+    static constexpr size_t kd_off = qw_off + 2ull * 128 * LDK * 2;              // bf16 [64][LDK]
     static constexpr size_t do_off = kd_off + 1ull * CH * LDK * 2;               // bf16 [2][64][LDS]
     static constexpr size_t e_off = do_off + 2ull * CH * LDS * 2;                // bf16 [MAXLEV][KD][LDS] adjoint copies
     static constexpr size_t ke_off = e_off + (size_t)GDN_MAXLEV * KD * LDS * 2;  // bf16 [MAXLEV][64][LDS]  -(kd E)
@@ -72,7 +72,7 @@ __global__ void __launch_bounds__(256, 1) gdn_scan_bwd_kernel(const GdnParams p)
     constexpr int LDK = SM::LDK, LDS = SM::LDS;
     static_assert(KD == 128, "one 16-row state tile per warp");
     extern __shared__ __align__(16) unsigned char smem[];
-    bf16* sQW = reinterpret_cast<bf16*>(smem + SM::qw_off);
+    bf16* sQWb = reinterpret_cast<bf16*>(smem + SM::qw_off);
     bf16* sKd = reinterpret_cast<bf16*>(smem + SM::kd_off);
     bf16* sDo = reinterpret_cast<bf16*>(smem + SM::do_off);
     bf16* sE = reinterpret_cast<bf16*>(smem + SM::e_off);
@@ -89,16 +89,14 @@ __global__ void __launch_bounds__(256, 1) gdn_scan_bwd_kernel(const GdnParams p)
     const int nlev = p.NLEV;
     const int NT = p.NT;
 
-    auto issue_qw = [&](int c) {
-        const long rowbase = ((long)b * p.T + (long)c * CH) * p.H + h;
-        load_tile_async<CH, KD, 256>(sQW, p.qd + rowbase * KD, (long)p.H * KD, tid);
-        load_tile_async<CH, KD, 256>(sQW + 64 * LDK, p.wd + rowbase * KD, (long)p.H * KD, tid);
-        cp_async_commit();
-    };
-    auto issue_kd_do = [&](int c, int st) {
+    // one commit group per chunk: kd (single buffer, consumed in the first half of a chunk), do and the
+    // stacked qd / wd tile (double buffered)
+    auto issue_tiles = [&](int c, int st) {
         const long rowbase = ((long)b * p.T + (long)c * CH) * p.H + h;
         load_tile_async<CH, KD, 256>(sKd, p.kd + rowbase * KD, (long)p.H * KD, tid);
         load_tile_async<CH, GDN_VS, 256>(sDo + st * CH * LDS, p.d_o + rowbase * p.V + vs * GDN_VS, (long)p.H * p.V, tid);
+        load_tile_async<CH, KD, 256>(sQWb + st * 128 * LDK, p.qd + rowbase * KD, (long)p.H * KD, tid);
+        load_tile_async<CH, KD, 256>(sQWb + st * 128 * LDK + 64 * LDK, p.wd + rowbase * KD, (long)p.H * KD, tid);
         cp_async_commit();
     };
     bf16 lam_reg[(CH * GDN_MAXLEV + 255) / 256];
@@ -128,14 +126,14 @@ __global__ void __launch_bounds__(256, 1) gdn_scan_bwd_kernel(const GdnParams p)
 #pragma unroll
     for (int lv = 0; lv < GDN_MAXLEV; ++lv) zero_acc(dM[lv]);
 
-    issue_kd_do(NT - 1, (NT - 1) & 1);
-    issue_qw(NT - 1);
+    issue_tiles(NT - 1, (NT - 1) & 1);
     fetch_small(NT - 1);
     store_small((NT - 1) & 1);
 
     for (int c = NT - 1; c >= 0; --c) {
         const int st = c & 1;
-        cp_async_wait<1>();                    // kd and do of this chunk (qd / wd may still be in flight)
+        const bf16* sQW = sQWb + st * 128 * LDK;
+        cp_async_wait<0>();                    // the tiles of this chunk
         __syncthreads();
         const bool trans = (c + 1 < NT);       // the chunk's transition feeds later chunks
         const int cn = c + 1;                  // levels that hold a state after this chunk: the set bits of c + 1
@@ -188,10 +186,9 @@ __global__ void __launch_bounds__(256, 1) gdn_scan_bwd_kernel(const GdnParams p)
                     }
             }
         }
-        cp_async_wait<0>();                    // qd / wd of this chunk
-        __syncthreads();
+        __syncthreads();                       // kd has been consumed, the -(kd E) tiles are written
         if (c > 0) {
-            issue_kd_do(c - 1, st ^ 1);
+            issue_tiles(c - 1, st ^ 1);
             fetch_small(c - 1);
         }
 
@@ -242,11 +239,7 @@ __global__ void __launch_bounds__(256, 1) gdn_scan_bwd_kernel(const GdnParams p)
                     for (int e = 0; e < 4; ++e) dM[lv][0][nt][e] = 0.f;
             }
         }
-        __syncthreads();                       // qd / wd and the -(kd E) tiles are free again
-        if (c > 0) {
-            issue_qw(c - 1);
-            store_small(st ^ 1);
-        }
+        if (c > 0) store_small(st ^ 1);        // the barrier at the top of the next chunk publishes it
     }
 }
 

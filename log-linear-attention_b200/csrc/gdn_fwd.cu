@@ -412,6 +412,17 @@ __global__ void __launch_bounds__(256, 1) gdn_scan_kernel(const GdnParams p) {
         const float dec = fexp(sGl[st]);
         const int jc = __ffs(~c) - 1;          // carry: levels 0..jc-1 merge with this chunk's own state into level jc
 
+        // the intra-chunk part of the output rows (written by the preparation kernel) is fetched before the
+        // products so that its latency is off the chunk-to-chunk chain
+        uint32_t o_in[4][2];
+        if (!SAVE && warp < 4) {
+            const long rb = ((long)b * p.T + (long)c * CH) * p.H + h;
+#pragma unroll
+            for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+                for (int hh = 0; hh < 2; ++hh)
+                    o_in[nt][hh] = *reinterpret_cast<const uint32_t*>(p.o + (rb + (long)(warp * 16 + lr + hh * 8) * p.H) * p.V + vs * GDN_VS + nt * 8 + lc2);
+        }
         // ---- [qd; wd] H for every live level: rows 0..63 feed the output, rows 64..127 the transition
         float o_acc[1][4][4];                  // warps 0..3: output rows 16*warp.., 32 columns
         float zsum[1][4][4];                   // warps 4..7: sum over the merged levels of wd H
@@ -469,7 +480,7 @@ __global__ void __launch_bounds__(256, 1) gdn_scan_kernel(const GdnParams p) {
 #pragma unroll
                 for (int hh = 0; hh < 2; ++hh) {
                     bf16* go = p.o + (rowbase + (long)(warp * 16 + lr + hh * 8) * p.H) * p.V + vs * GDN_VS + nt * 8 + lc2;
-                    __nv_bfloat162 x = *reinterpret_cast<const __nv_bfloat162*>(go);
+                    const __nv_bfloat162 x = *reinterpret_cast<const __nv_bfloat162*>(&o_in[nt][hh]);
                     *reinterpret_cast<uint32_t*>(go) =
                         pack_bf16(__bfloat162float(x.x) + o_acc[0][nt][hh * 2], __bfloat162float(x.y) + o_acc[0][nt][hh * 2 + 1]);
                 }
@@ -531,7 +542,7 @@ __global__ void __launch_bounds__(256, 1) gdn_scan_kernel(const GdnParams p) {
             }
             store_small(st ^ 1);
         }
-        __syncthreads();
+        // no barrier here: the one at the top of the next chunk orders these writes before their readers
     }
 }
 
