@@ -115,6 +115,26 @@ int llattn_mamba2_prep_bwd(const void* x, const void* dt_raw, const float* dt_bi
                            long rows, int H, int P, int L, int lambda_mode, void* stream);
 int llattn_mamba2_residual(const void* o, const void* x, const float* D, void* y, int y_is_f32, long rows, int H, int P, void* stream);
 
+/* Prefill hand-off: the level states after T tokens, states fp32 (B,H,K,V,L), every level written.
+ * Level 0 is k_m v_m^T for the last token m = T-1; for each set bit j of m, level j+1 holds the 2^j
+ * tokens that follow the buckets of the higher set bits, each decayed to token m; other levels are zero.
+ * Replaces the state side of hattention_prefill (hattention/kernel.py:470-560): the final states `ht` of
+ * chunk_fwd_kernel_h (hattention/chunkwise.py:171-173, 278-280) for the inter-chunk levels together with
+ * postprocess_prefill_hstate_ (hattention/kernel.py:378-466) for the levels inside the last chunk and its
+ * clearing of unpopulated levels.  k (B,T,G,K), v (B,T,H,V) bf16, g (B,T,H) fp32 raw log decay.  Any T >= 1;
+ * K in {64,128}, V == 64, bit_length(T-1) + 1 <= L <= 32. */
+int llattn_mamba2_final_state(const void* k, const void* v, const float* g, float* states,
+                              int B, int T, int H, int G, int K, int V, int L, void* stream);
+
+/* One decode step (hattention_step, hattention/kernel.py:563-633, with HState.cascade_weak / insert and
+ * step_output, hattention/recurrent.py:42-54, 79-98, 134-166) for every (batch, head): levels 0..carry_level
+ * are summed into level carry_level (the caller runs the cascade on the token counts, which are the same
+ * for every sequence: carry_level is the first level that is not full), every level is multiplied by
+ * exp(g), level 0 becomes k v^T, and o = q . sum_l lambda_l S_l.  states fp32 (B,H,K,V,L) updated in place;
+ * q, k (B,G,K), v (B,H,V), lambda (B,H,L), o (B,H,V) bf16; g (B,H) fp32.  256 % V == 0, L <= 32. */
+int llattn_mamba2_step(float* states, const void* q, const void* k, const void* v, const float* g, const void* lambda, void* o,
+                       int B, int H, int G, int K, int V, int L, int carry_level, void* stream);
+
 /* Log-linear Gated DeltaNet forward.  Replaces hattention.chunkwise_hgdn.chunkwise_fwd
  * (hattention/chunkwise_hgdn.py:566-788) with output_final_state=False.  q and k are per head,
  * (B,T,H,K), and must already be L2-normalised (q also scaled) as the reference's autograd

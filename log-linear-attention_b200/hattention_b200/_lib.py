@@ -59,6 +59,10 @@ def lib():
     L.llattn_mamba2_prep_bwd.argtypes = [_P] * 18 + [ctypes.c_long] + [ctypes.c_int] * 4 + [_P]
     L.llattn_mamba2_residual.restype = ctypes.c_int
     L.llattn_mamba2_residual.argtypes = [_P] * 4 + [ctypes.c_int, ctypes.c_long, ctypes.c_int, ctypes.c_int, _P]
+    L.llattn_mamba2_final_state.restype = ctypes.c_int
+    L.llattn_mamba2_final_state.argtypes = [_P] * 4 + [ctypes.c_int] * 7 + [_P]
+    L.llattn_mamba2_step.restype = ctypes.c_int
+    L.llattn_mamba2_step.argtypes = [_P] * 7 + [ctypes.c_int] * 7 + [_P]
     L.llattn_l2norm_fwd.restype = ctypes.c_int
     L.llattn_l2norm_fwd.argtypes = [_P, _P, ctypes.c_long, ctypes.c_int, ctypes.c_float, _P]
     L.llattn_l2norm_bwd.restype = ctypes.c_int

@@ -73,8 +73,6 @@ def chunkwise_fwd(
     (chunkwise.py:1118-1275).  `keep_workspace` (not in the reference): a list that receives the
     call's scratch tensor, which `chunkwise_bwd(fwd_workspace=...)` can read the segment-level states
     from instead of recomputing them."""
-    if output_final_state:
-        raise NotImplementedError("output_final_state=True (prefill hand-off) is not implemented")
     B, T, H, G, K, V, L = _check(q, k, v, g, l, head_first, level_base, htype, chunk_size)
     lib = _lib.lib()
     with torch.cuda.device(q.device):
@@ -89,7 +87,26 @@ def chunkwise_fwd(
         _lib.check(rc, "llattn_mamba2_fwd")
         if keep_workspace is not None:
             keep_workspace.append(ws)
-    return o, g_cum, None
+        ht = final_states(k_, v_, g_, L) if output_final_state else None
+    return o, g_cum, ht
+
+
+def final_states(k: torch.Tensor, v: torch.Tensor, g: torch.Tensor, L: int) -> torch.Tensor:
+    """Level states (B,H,K,V,L) fp32 after the T tokens of k (B,T,G,K), v (B,T,H,V), g (B,T,H): what
+    the reference's prefill assembles from `ht` of its state kernel and `postprocess_prefill_hstate_`
+    (kernel.py:378-466, 521-557).  Every level is written (the reference's `ht` only carries the
+    inter-chunk levels)."""
+    lib = _lib.lib()
+    B, T, G, K = k.shape
+    H, V = v.shape[2], v.shape[3]
+    with torch.cuda.device(k.device):
+        k_, v_ = _as(k, torch.bfloat16), _as(v, torch.bfloat16)
+        g_ = _as(g, torch.float32)
+        st = torch.empty(B, H, K, V, L, dtype=torch.float32, device=k.device)
+        rc = lib.llattn_mamba2_final_state(k_.data_ptr(), v_.data_ptr(), g_.data_ptr(), st.data_ptr(),
+                                           B, T, H, G, K, V, L, _stream())
+        _lib.check(rc, "llattn_mamba2_final_state")
+    return st
 
 
 def chunkwise_bwd(

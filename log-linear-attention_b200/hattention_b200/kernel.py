@@ -5,7 +5,8 @@ from typing import Optional, Tuple
 import torch
 
 from .base import HStruct, HType
-from .chunkwise import chunkwise_bwd, chunkwise_fwd
+from . import _lib
+from .chunkwise import chunkwise_bwd, chunkwise_fwd, final_states
 
 
 # Keep the Mamba-2 forward call's scratch (segment-level states, about 0.2 GB at B=2, T=16384, H=32)
@@ -100,3 +101,113 @@ def hattention_kernel(
         chunk_sizes = (64, 64)
     return HAttentionFunction.apply(q, k, v, b, g, l, scale, head_first, level_base, htype, hstruct, chunk_sizes,
                                     chunkwise, use_qk_l2norm_in_kernel)
+
+
+class HState:
+    """Level states of one layer for decoding, with the fields of the reference's `HState`
+    (hattention/recurrent.py:9-131): `states` (B,H,K,V,L) in `dtype` and one token count per level.
+    The counts are identical for every sequence and are kept on the host, so that the cascade
+    (recurrent.py:42-54) costs no device synchronisation."""
+
+    def __init__(self, base: int, htype: HType, hstruct: HStruct, shape, dtype: torch.dtype, device) -> None:
+        if base != 2 or htype != HType.WEAK:
+            raise NotImplementedError
+        self.base, self.htype, self.hstruct = base, htype, hstruct
+        self.shape, self.dtype, self.device = tuple(shape), dtype, device
+        self.max_num_levels = self.shape[-1]
+        self.states = torch.zeros(self.shape, dtype=dtype, device=device)
+        self.counts = [0] * self.max_num_levels
+
+    def cascade_counts(self) -> int:
+        """Runs the cascade on the counts; returns the level that receives the merged levels."""
+        for level in range(self.max_num_levels):
+            cap = 1 << level
+            if self.counts[level] == cap:
+                if level + 1 >= self.max_num_levels:
+                    raise ValueError("more tokens than the levels can hold")
+                self.counts[level + 1] += self.counts[level]
+                self.counts[level] = 0
+            elif self.counts[level] < cap:
+                return level
+            else:
+                raise ValueError
+        return self.max_num_levels - 1
+
+    def set_counts_after(self, T: int) -> None:
+        """Counts after T tokens: level 0 holds the last token, level j+1 holds 2^j tokens for each set
+        bit j of T-1 (the bookkeeping at the end of kernel.py:452-463)."""
+        self.counts = [0] * self.max_num_levels
+        if T <= 0:
+            return
+        self.counts[0] = 1
+        m = T - 1
+        for j in range(m.bit_length()):
+            if (m >> j) & 1:
+                if j + 1 >= self.max_num_levels:
+                    raise ValueError("more tokens than the levels can hold")
+                self.counts[j + 1] = 1 << j
+
+
+@torch.no_grad()
+def hattention_step(hstate: HState, q, k, v, b, g, l, scale, level_base, htype, hstruct,
+                    use_qk_l2norm_in_kernel: bool = False):
+    """One decoding step, signature of the reference's `hattention_step` (kernel.py:563-633):
+    q, k (B,G,K), v (B,H,V), g (B,H), l (B,H,L) -> (o (B,H,V), hstate).  Mamba-2 structure only."""
+    if not (q.ndim == 3 and k.ndim == 3 and v.ndim == 3 and g.ndim == 2 and l.ndim == 3
+            and (b is None or b.ndim == 2) and g.dtype == hstate.dtype and q.dtype == k.dtype == v.dtype == l.dtype
+            and hstate.base == level_base and hstate.htype == htype and hstate.hstruct == hstruct):
+        raise TypeError
+    if hstruct != HStruct.MAMBA2 or b is not None:
+        raise NotImplementedError("the decode step is implemented for the Mamba-2 structure")
+    if use_qk_l2norm_in_kernel or scale is not None:
+        raise NotImplementedError
+    if hstate.dtype != torch.float32:
+        raise NotImplementedError("level states are kept in fp32")
+    B, G, K = k.shape
+    _, H, V = v.shape
+    L = l.shape[-1]
+    carry = hstate.cascade_counts()
+    hstate.counts[0] += 1
+    lib = _lib.lib()
+    with torch.cuda.device(v.device):
+        q_, k_, v_, l_ = (x.to(torch.bfloat16).contiguous() for x in (q, k, v, l))
+        g_ = g.to(torch.float32).contiguous()
+        o = torch.empty(B, H, V, dtype=torch.bfloat16, device=v.device)
+        rc = lib.llattn_mamba2_step(hstate.states.data_ptr(), q_.data_ptr(), k_.data_ptr(), v_.data_ptr(), g_.data_ptr(),
+                                    l_.data_ptr(), o.data_ptr(), B, H, G, K, V, L, carry,
+                                    torch.cuda.current_stream().cuda_stream)
+        _lib.check(rc, "llattn_mamba2_step")
+    return o.to(v.dtype), hstate
+
+
+@torch.no_grad()
+def hattention_prefill(q, k, v, b, g, l, scale, head_first, level_base, htype, hstruct,
+                       chunk_size: Optional[int] = None, use_qk_l2norm_in_kernel: bool = False):
+    """Outputs for a prompt and the level states to continue from, signature of the reference's
+    `hattention_prefill` (kernel.py:469-560).  The largest multiple of the chunk size goes through the
+    chunkwise kernels, its level states come from one kernel (`final_states`), the remaining tokens are
+    stepped.  Mamba-2 structure only."""
+    if chunk_size is None:
+        chunk_size = 64
+    if head_first:
+        raise NotImplementedError
+    if hstruct != HStruct.MAMBA2 or b is not None:
+        raise NotImplementedError("prefill is implemented for the Mamba-2 structure")
+    if use_qk_l2norm_in_kernel or scale is not None:
+        raise NotImplementedError
+    B, T, G, K = k.shape
+    _, _, H, V = v.shape
+    L = l.shape[-1]
+    T0 = T - (T % chunk_size)
+    o = torch.zeros_like(v)
+    hstate = HState(base=level_base, htype=htype, hstruct=hstruct, shape=(B, H, K, V, L), dtype=torch.float32, device=g.device)
+    if T0 != 0:
+        o0, _, ht = chunkwise_fwd(q[:, :T0], k[:, :T0], v[:, :T0], g[:, :T0], l[:, :T0], head_first, level_base, htype,
+                                  chunk_size, True)
+        o[:, :T0] = o0.to(v.dtype)
+        hstate.states = ht
+        hstate.set_counts_after(T0)
+    for t in range(T0, T):
+        o[:, t], hstate = hattention_step(hstate, q[:, t], k[:, t], v[:, t], None, g[:, t].float(), l[:, t], None,
+                                          level_base, htype, hstruct)
+    return o, hstate
