@@ -1,12 +1,14 @@
 """B200 (sm_100a) implementation of hattention's chunkwise log-linear attention.
 
 Mirrors the module layout of the reference package for the one path it replaces:
-`base` (level arithmetic, enums), `chunkwise` (Mamba-2 drivers), `kernel` (autograd boundary),
-`mamba_apis` (layer-level Mamba-2 API).  The CUDA kernels live in libllattn.so (C ABI, built
-from ../csrc) and are reached through ctypes; there is no CPU or Triton fallback.
+`base` (level arithmetic, enums), `chunkwise` (Mamba-2 drivers), `chunkwise_hgdn` (Gated DeltaNet
+drivers, l2norm), `kernel` (autograd boundary, prefill / decode step), `mamba_apis` and
+`gated_delta_rule_apis` (layer-level APIs), `sharding` (batch x head partition across GPUs).  The CUDA
+kernels live in libllattn.so (C ABI, built from ../csrc) and are reached through ctypes; there is no CPU
+or Triton fallback.
 """
 from .base import HType, HStruct, get_num_levels  # noqa: F401
-from .kernel import hattention_kernel  # noqa: F401
+from .kernel import HState, hattention_kernel, hattention_prefill, hattention_step  # noqa: F401
 
 
 def install_as_hattention():

@@ -173,3 +173,96 @@ def hmamba_chunk_scan_combined(
     if D is not None:
         y = y + D_residual
     return y, None
+
+
+def _causal_conv1d_silu(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor]) -> torch.Tensor:
+    """Depthwise causal convolution followed by SiLU on (B, D, T): what causal_conv1d_fn(..., activation="silu")
+    computes (call site mamba_apis.py:213-220 in the reference).  Outside the log-linear attention path:
+    a torch depthwise convolution."""
+    width = weight.shape[-1]
+    y = torch.nn.functional.conv1d(x, weight.unsqueeze(1).to(x.dtype), bias.to(x.dtype) if bias is not None else None,
+                                   padding=width - 1, groups=x.shape[1])[..., : x.shape[-1]]
+    return torch.nn.functional.silu(y)
+
+
+def _gated_rmsnorm(y: torch.Tensor, z: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    """RMSNorm(y * silu(z)) * weight in fp32, returned in y's dtype (rmsnorm_fn with norm_before_gate=False,
+    call site mamba_apis.py:251-258 in the reference)."""
+    x = y.float() * torch.nn.functional.silu(z.float())
+    out = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps) * weight.float()
+    return out.to(z.dtype)
+
+
+def hmamba_split_conv1d_scan_combined(
+    zxbcdtdl: torch.Tensor,
+    conv1d_weight: torch.Tensor,
+    conv1d_bias: torch.Tensor,
+    dt_bias: torch.Tensor,
+    A: torch.Tensor,
+    L: torch.Tensor,
+    D: torch.Tensor,
+    chunk_size: int,
+    initial_states: Optional[torch.Tensor] = None,
+    seq_idx: Optional[torch.Tensor] = None,
+    dt_limit: Tuple[float, float] = (0.0, float("inf")),
+    return_final_states: bool = False,
+    activation: str = "silu",
+    rmsnorm_weight: Optional[torch.Tensor] = None,
+    rmsnorm_eps: float = 1e-6,
+    outproj_weight: Optional[torch.Tensor] = None,
+    outproj_bias: Optional[torch.Tensor] = None,
+    headdim: Optional[int] = None,
+    ngroups: int = 1,
+    norm_before_gate: bool = True,
+    lambda_mode: Optional[str] = None,
+    lambda_level_max: Optional[int] = None,
+    lambda_level_base: Optional[int] = None,
+    lambda_htype: Optional[HType] = None,
+    lambda_hstruct: Optional[HStruct] = None,
+    lambda_level_fixed: Optional[bool] = None,
+    lambda_level_module=None,
+) -> torch.Tensor:
+    """Signature, checks and data flow of the reference's function of this name (mamba_apis.py:116-262):
+    split -> depthwise causal conv + SiLU on (x, B, C) -> hmamba_chunk_scan_combined -> gated RMSNorm ->
+    output projection.  The convolution, the norm and the projection are torch ops here (the reference
+    calls causal_conv1d / mamba_ssm kernels for the first two); the scan is this package's CUDA path."""
+    if initial_states is not None or seq_idx is not None:
+        raise NotImplementedError
+    if tuple(dt_limit) != (0.0, float("inf")):
+        raise NotImplementedError
+    if return_final_states is not False:
+        raise NotImplementedError
+    if norm_before_gate is not False:
+        raise NotImplementedError
+    if rmsnorm_weight is None:
+        raise NotImplementedError
+    if activation not in ["silu", "swish"]:
+        raise NotImplementedError
+    if D.dim() != 1:
+        raise ValueError
+    if headdim is None:
+        raise ValueError
+    batch, seqlen, _ = zxbcdtdl.shape
+    dlambda = L.shape[-1]
+    nheads, = D.shape
+    dim = nheads * headdim
+    dstate = (zxbcdtdl.shape[-1] - 2 * dim - nheads - nheads * dlambda) // ngroups // 2
+    if nheads % ngroups != 0:
+        raise ValueError
+    if zxbcdtdl.shape != (batch, seqlen, 2 * dim + 2 * ngroups * dstate + nheads + nheads * dlambda):
+        raise ValueError
+    if dt_bias.shape != (nheads,) or A.shape != (nheads,) or L.shape != (nheads, dlambda):
+        raise ValueError
+    z, xBC, dt, dl = torch.split(zxbcdtdl, [dim, dim + 2 * ngroups * dstate, nheads, nheads * dlambda], dim=-1)
+    xBC = _causal_conv1d_silu(xBC.transpose(1, 2), conv1d_weight, conv1d_bias).transpose(1, 2)
+    x, Bm, Cm = torch.split(xBC, [dim, ngroups * dstate, ngroups * dstate], dim=-1)
+    y, _ = hmamba_chunk_scan_combined(
+        x=x.reshape(batch, seqlen, nheads, headdim).contiguous(), dt=dt.contiguous(), A=A,
+        B=Bm.reshape(batch, seqlen, ngroups, dstate).contiguous(), C=Cm.reshape(batch, seqlen, ngroups, dstate).contiguous(),
+        dl=dl.reshape(batch, seqlen, nheads, dlambda).contiguous(), L=L, chunk_size=chunk_size, D=D, z=None, dt_bias=dt_bias,
+        dt_softplus=True, seq_idx=None, cu_seqlens=None, dt_limit=dt_limit, return_final_states=False,
+        return_varlen_states=False, lambda_mode=lambda_mode, lambda_level_max=lambda_level_max,
+        lambda_level_base=lambda_level_base, lambda_htype=lambda_htype, lambda_hstruct=lambda_hstruct,
+        lambda_level_fixed=lambda_level_fixed, lambda_level_module=lambda_level_module)
+    y = _gated_rmsnorm(y.reshape(batch, seqlen, dim), z, rmsnorm_weight, rmsnorm_eps)
+    return torch.nn.functional.linear(y, outproj_weight.to(y.dtype), outproj_bias.to(y.dtype) if outproj_bias is not None else None)

@@ -16,12 +16,12 @@ pytestmark = pytest.mark.gpu
 RTOL, ATOL = 2e-2, 2e-3
 
 
-def assert_close(got, want, name):
+def assert_close(got, want, name, atol=None):
     got = got.detach().double().cpu()
     want = want.detach().double().cpu()
     assert got.shape == want.shape, (name, got.shape, want.shape)
     assert torch.isfinite(got).all(), name
-    tol = RTOL * want.abs() + ATOL * max(1.0, want.abs().max().item())
+    tol = RTOL * want.abs() + (ATOL if atol is None else atol) * max(1.0, want.abs().max().item())
     err = (got - want).abs()
     worst = (err / tol).max().item()
     assert worst <= 1.0, f"{name}: worst err/tol = {worst:.3f}, max abs err {err.max().item():.3e}, max|want| {want.abs().max().item():.3e}"
@@ -213,3 +213,55 @@ def test_layer_api_fused_preparation(lambda_mode):
         # of v / lambda and by the order of fp32 atomics), hence the wider bound for them
         rel = ((a - b).norm() / b.norm()).item()
         assert rel < (3e-2 if k_ in ("A", "Lp", "D", "bias") else 1e-2), f"{k_}: relative error {rel:.3e}"
+
+
+def test_split_conv1d_scan_combined_layer():
+    """The whole mixer call: split, depthwise causal conv + SiLU, the scan, gated RMSNorm, output
+    projection; output and input / parameter gradients against the same pipeline with the scan replaced by
+    the CPU oracle's materialised form (fp64)."""
+    from hattention_b200.base import HStruct, HType
+    from hattention_b200.mamba_apis import hmamba_split_conv1d_scan_combined
+    torch.manual_seed(3)
+    B, T, H, P, N, G, L, W, OUT = 1, 256, 2, 64, 128, 1, 10, 4, 96
+    dim = H * P
+    width = 2 * dim + 2 * G * N + H + H * L
+    dev = torch.device("cuda:0")
+    zx = (torch.randn(B, T, width) * 0.5).bfloat16()
+    cw = (torch.randn(dim + 2 * G * N, W) * 0.3).bfloat16()
+    cb = (torch.randn(dim + 2 * G * N) * 0.1).bfloat16()
+    dt_bias, A = torch.randn(H) * 0.1 - 2.0, -torch.exp(torch.rand(H) * 2.0)
+    Lp, D = torch.rand(H, L) + 0.5, torch.randn(H)
+    nw = torch.rand(dim) + 0.5
+    ow = (torch.randn(OUT, dim) / dim ** 0.5).bfloat16()
+    kw = dict(chunk_size=64, rmsnorm_weight=None, headdim=P, ngroups=G, norm_before_gate=False, lambda_mode="positive",
+              lambda_level_max=L, lambda_level_base=2, lambda_htype=HType.WEAK, lambda_hstruct=HStruct.MAMBA2, lambda_level_fixed=True)
+    zx_d = zx.to(dev).requires_grad_(True)
+    cw_d = cw.to(dev).requires_grad_(True)
+    kw["rmsnorm_weight"] = nw.to(dev)
+    out = hmamba_split_conv1d_scan_combined(zx_d, cw_d, cb.to(dev), dt_bias.to(dev), A.to(dev), Lp.to(dev), D.to(dev),
+                                            outproj_weight=ow.to(dev), outproj_bias=None, **kw)
+    dout = torch.randn(B, T, OUT, generator=torch.Generator().manual_seed(4)).bfloat16()
+    g_zx, g_cw = torch.autograd.grad(out, [zx_d, cw_d], dout.to(dev))
+    torch.cuda.synchronize()
+    # reference pipeline in fp64 on the CPU
+    zr = zx.double().requires_grad_(True)
+    cr = cw.double().requires_grad_(True)
+    z, xBC, dt, dl = torch.split(zr, [dim, dim + 2 * G * N, H, H * L], dim=-1)
+    conv = torch.nn.functional.conv1d(xBC.transpose(1, 2), cr.unsqueeze(1), cb.double(), padding=W - 1, groups=dim + 2 * G * N)[..., :T]
+    xBC = torch.nn.functional.silu(conv).transpose(1, 2)
+    x, Bm, Cm = torch.split(xBC, [dim, G * N, G * N], dim=-1)
+    x = x.reshape(B, T, H, P)
+    dts = torch.nn.functional.softplus(dt + dt_bias.double())
+    lam = torch.nn.functional.softplus(Lp.double()[None, None] * dl.reshape(B, T, H, L))
+    y = orc.mamba2_materialized(Cm.reshape(B, T, G, N), Bm.reshape(B, T, G, N), x * dts[..., None], A.double()[None, None] * dts, lam)
+    y = (y + x * D.double()[None, None, :, None]).reshape(B, T, dim)
+    xg = y * torch.nn.functional.silu(z)
+    yn = xg * torch.rsqrt(xg.pow(2).mean(-1, keepdim=True) + 1e-6) * nw.double()
+    want = yn @ ow.double().t()
+    w_zx, w_cw = torch.autograd.grad(want, [zr, cr], dout.double())
+    # the conv / norm / projection stages are bf16 torch ops on the GPU against fp64: four times the kernel's
+    # absolute allowance
+    assert_close(out, want, "out", atol=8e-3)
+    for got, w_, name in ((g_zx, w_zx, "d zxbcdtdl"), (g_cw, w_cw, "d conv1d_weight")):
+        rel = ((got.double().cpu() - w_).norm() / w_.norm()).item()
+        assert rel < 3e-2, f"{name}: relative error {rel:.3e}"
