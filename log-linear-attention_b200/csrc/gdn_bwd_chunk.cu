@@ -110,6 +110,7 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_chunk_kernel(const GdnParams p
     //      dG_i += d_qd.qd + d_wd.wd - d_kd.kd and the chunk total of d_kd.kd
     {
         float kdsum = 0.f;
+#pragma unroll 4
         for (int it = 0; it < CH / 8; ++it) {
             const int i = it * 8 + warp;
             const long off = (rowbase + (long)i * p.H) * KD + lane * 4;
@@ -289,13 +290,20 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_chunk_kernel(const GdnParams p
         float acc[1][2 * NPK][4];
         zero_acc(acc);
         const int c0 = cw * (KD / 2);
+        // the fp32 gradient fragment is requested before the product so that its latency overlaps the MMAs
+        float2 pre[2 * NPK][2];
+#pragma unroll
+        for (int nt = 0; nt < 2 * NPK; ++nt)
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh)
+                pre[nt][hh] = *reinterpret_cast<const float2*>(p.d_wd + (rowbase + (long)(r0 + lr + hh * 8) * p.H) * KD + c0 + nt * 8 + lc2);
         warp_gemm<1, NPK, true, true>(acc, sQK, LDP, r0, sDqd, LDK, c0, CH, lane);
 #pragma unroll
         for (int nt = 0; nt < 2 * NPK; ++nt)
 #pragma unroll
             for (int hh = 0; hh < 2; ++hh) {
                 const int i = r0 + lr + hh * 8, j = c0 + nt * 8 + lc2;
-                const float2 d = *reinterpret_cast<const float2*>(p.d_wd + (rowbase + (long)i * p.H) * KD + j);
+                const float2 d = pre[nt][hh];
                 const float eg = sEG[i];
                 *reinterpret_cast<uint32_t*>(sDW + i * LDK + j) = pack_bf16(acc[0][nt][hh * 2] + d.x * eg, acc[0][nt][hh * 2 + 1] + d.y * eg);
             }
@@ -338,6 +346,12 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_chunk_kernel(const GdnParams p
         warp_gemm<1, 2, true, true>(dA1, sAw, LDP, r0, sTb, LDP, cw * 32, CH, lane);
         zero_acc(dk_acc);
         const int c0 = cw * (KD / 2);
+        float2 pre[2 * NPK][2];
+#pragma unroll
+        for (int nt = 0; nt < 2 * NPK; ++nt)
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh)
+                pre[nt][hh] = *reinterpret_cast<const float2*>(p.d_kd + (rowbase + (long)(r0 + lr + hh * 8) * p.H) * KD + c0 + nt * 8 + lc2);
         warp_gemm<1, NPK, true, true>(dk_acc, sAw, LDP, r0, sDW, LDK, c0, CH, lane);
         float rb[2] = {0.f, 0.f};
 #pragma unroll
@@ -348,7 +362,7 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_chunk_kernel(const GdnParams p
                 const __nv_bfloat162 x = *reinterpret_cast<const __nv_bfloat162*>(sK + i * LDK + j);
                 rb[hh] += dk_acc[0][nt][hh * 2] * __bfloat162float(x.x) + dk_acc[0][nt][hh * 2 + 1] * __bfloat162float(x.y);
                 const float bi = sBe[i];
-                const float2 d = *reinterpret_cast<const float2*>(p.d_kd + (rowbase + (long)i * p.H) * KD + j);
+                const float2 d = pre[nt][hh];
                 const float ek = sEGk[i];
                 dk_acc[0][nt][hh * 2] = dk_acc[0][nt][hh * 2] * bi + d.x * ek;
                 dk_acc[0][nt][hh * 2 + 1] = dk_acc[0][nt][hh * 2 + 1] * bi + d.y * ek;
@@ -442,6 +456,12 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_chunk_kernel(const GdnParams p
         const int c0 = cw * (KD / 2);
         float acc[1][2 * NPK][4];
         zero_acc(acc);
+        float2 pre[2 * NPK][2];
+#pragma unroll
+        for (int nt = 0; nt < 2 * NPK; ++nt)
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh)
+                pre[nt][hh] = *reinterpret_cast<const float2*>(p.d_qd + (rowbase + (long)(r0 + lr + hh * 8) * p.H) * KD + c0 + nt * 8 + lc2);
         warp_gemm<1, NPK, false, true>(acc, sDQK, LDP, r0, sK, LDK, c0, CH, lane);
 #pragma unroll
         for (int nt = 0; nt < 2 * NPK; ++nt)
@@ -449,7 +469,7 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_chunk_kernel(const GdnParams p
             for (int hh = 0; hh < 2; ++hh) {
                 const int i = r0 + lr + hh * 8, j = c0 + nt * 8 + lc2;
                 const long off = (rowbase + (long)i * p.H) * KD + j;
-                const float2 d = *reinterpret_cast<const float2*>(p.d_qd + off);
+                const float2 d = pre[nt][hh];
                 const float eg = sEG[i];
                 *reinterpret_cast<float2*>(p.dq + off) = make_float2(acc[0][nt][hh * 2] + d.x * eg, acc[0][nt][hh * 2 + 1] + d.y * eg);
             }
