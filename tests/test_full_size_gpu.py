@@ -111,3 +111,28 @@ def test_gdn_properties_at_config_size():
     sub = [ins[0][-1:, :, 8:], ins[1][-1:, :, 8:], ins[2][-1:, :, 8:], ins[3][-1:, :, 8:], ins[4][-1:, :, 8:], ins[5][-1:, :, 8:]]
     o3, _ = chunk_h_gated_delta_rule(*[x.detach().contiguous() for x in sub], use_qk_l2norm_in_kernel=True)
     assert torch.equal(o3, o.detach()[-1:, :, 8:])
+
+
+def test_mamba2_longest_sequence_identities():
+    """T = 65536 (1024 chunks, 128 segments, seven segment levels: the shapes of the multi-GPU scaling
+    configuration, one batch element and two heads of it): forward finite and causal, gradient identities."""
+    from hattention_b200.base import HType
+    from hattention_b200.chunkwise import chunkwise_bwd
+    B, T, H, L = 1, 65536, 2, 17
+    q, k, v, g, l = _m2_inputs(B, T, H, L, seed=6)
+    do = torch.randn(B, T, H, 64, generator=torch.Generator().manual_seed(8)).bfloat16().to(DEV)
+    o, g_cum, _ = _fwd(q, k, v, g, l)
+    assert torch.isfinite(o.float()).all()
+    t0 = 40000 - (40000 % 64)
+    o_head, _, _ = _fwd(q[:, :t0], k[:, :t0], v[:, :t0], g[:, :t0], l[:, :t0])
+    # the shorter call has fewer segment levels but the same buckets for every (target, source) pair
+    assert _rel(o_head.float(), o[:, :t0].float()) < 5e-3
+    dq, dk, dv, dg, dl = chunkwise_bwd(q, k, v, g_cum, l, do, False, 2, HType.WEAK, 64)
+    for t in (dq, dk, dv, dg, dl):
+        assert torch.isfinite(t.float()).all()
+    s_o = (do.double() * o.double()).sum().item()
+    s_v = (dv.double() * v.double()).sum().item()
+    s_l = (dl.double() * l.double()).sum().item()
+    scale = (do.double().abs() * o.double().abs()).sum().item()
+    assert abs(s_o - s_v) < 2e-3 * scale
+    assert abs(s_o - s_l) < 2e-3 * scale
