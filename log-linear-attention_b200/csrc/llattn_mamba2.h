@@ -46,6 +46,7 @@ struct Mamba2Params {
     int B, T, H, G, K, V, L;
     int NT, NS, LH;
     int o_has_high;
+    int lev_lo;                  // first segment level handled by one launch of the tensor-core high-level backward
     int reuse_states;            // backward: seg_D / seg_H0 come from the forward call, do not recompute them
 };
 

@@ -1074,7 +1074,7 @@ static int launch_bwd(Mamba2Params p, cudaStream_t stream) {
         // forward high-level states: recomputed unless the caller kept the forward call's workspace
         int rc = p.reuse_states ? 0 : mamba2_fwd_states_dispatch(p, stream);
         if (rc != 0) return rc;
-        const bool hi_tc = (KD == 128 && VD == 64 && (p.NT % 2) == 0 && p.L <= 20 && p.LH <= 5 && g_use_tensor_core_path);
+        const bool hi_tc = (KD == 128 && VD == 64 && (p.NT % 2) == 0 && p.L <= 20 && p.LH <= 10 && g_use_tensor_core_path);
         if (hi_tc) {
             rc = mamba2_hi_bwd_tc_launch(p, stream);
             if (rc != 0) return rc;

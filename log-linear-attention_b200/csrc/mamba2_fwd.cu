@@ -582,7 +582,7 @@ static int launch_fwd(Mamba2Params p, cudaStream_t stream) {
         p.o_has_high = use_tc ? 2 : 1;      // 2: partial output goes to the column-chunk-major scratch
         int rc = launch_states<KD, VD, MLOW>(p, stream);
         if (rc != 0) return rc;
-        if (use_tc && p.LH <= 5) {
+        if (use_tc && p.LH <= 8) {
             rc = mamba2_hi_out_tc_launch(p, stream);
             if (rc != 0) return rc;
         } else {

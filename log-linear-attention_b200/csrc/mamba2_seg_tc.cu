@@ -102,11 +102,14 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_hi_bwd_tc_kernel(const __g
     const int grp = h / (p.H / p.G);
     const int nchunks = min(SEG, p.NT - r * SEG);
     const int npairs = nchunks / 2;
-    // set high levels of this segment, in increasing order
+    // set high levels of this segment inside this launch's window of five levels, in increasing order
     int lev[tcs::MAXLH], nl = 0;
 #pragma unroll
-    for (int j = 0; j < tcs::MAXLH; ++j)
+    for (int jj = 0; jj < tcs::MAXLH; ++jj) {
+        const int j = p.lev_lo + jj;
         if (j < p.LH && ((r >> j) & 1)) lev[nl++] = j;
+    }
+    if (nl == 0) return;             // nothing to read in this window (uniform for the CTA)
 
     if (tid == 0) {
 #pragma unroll
@@ -322,19 +325,20 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_hi_bwd_tc_kernel(const __g
 // ------------------------------------------------------------------------------------------
 // forward: partial output of the high levels, o_hi = sum_j lambda_j exp(G) (q H0[r][j])
 // ------------------------------------------------------------------------------------------
-template <int MLOW>
+template <int MLOW, int MAXL>
 struct HiOutTcSmem {
     static constexpr int SEG = 1 << MLOW;
     static constexpr uint32_t q_off = 0;                                   // [2] 32 KB
     static constexpr uint32_t h_off = q_off + 2 * tc::Q_BYTES;
-    static constexpr uint32_t gs_off = h_off + tcs::MAXLH * tc::H_BYTES;
+    static constexpr uint32_t gs_off = h_off + MAXL * tc::H_BYTES;
     static constexpr uint32_t bar_off = gs_off + (SEG * 64 + SEG + 32) * 4;
     static constexpr uint32_t total = bar_off + 128 + 1024;
 };
 
-template <int MLOW>
+template <int MLOW, int MAXL>
 __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_hi_out_tc_kernel(const __grid_constant__ Mamba2Params p) {
-    using SM = HiOutTcSmem<MLOW>;
+    using SM = HiOutTcSmem<MLOW, MAXL>;
+    static_assert(MAXL * 64 <= tc::TM_COLS, "one 64-column tensor-memory slot per level");
     constexpr int SEG = SM::SEG;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -357,9 +361,9 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_hi_out_tc_kernel(const __g
     const int grp = h / (p.H / p.G);
     const int nchunks = min(SEG, p.NT - r * SEG);
     const int npairs = nchunks / 2;
-    int lev[tcs::MAXLH], nl = 0;
+    int lev[MAXL], nl = 0;
 #pragma unroll
-    for (int j = 0; j < tcs::MAXLH; ++j)
+    for (int j = 0; j < MAXL; ++j)
         if (j < p.LH && ((r >> j) & 1)) lev[nl++] = j;
 
     if (tid == 0) {
@@ -435,9 +439,9 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_hi_out_tc_kernel(const __g
         const long t0 = (long)(r * SEG) * CH + (long)pl * tc::PT;
         const float sc = fexp(sGs[pl * tc::PT + row]);
         const bf16* lrow = p.l + (((long)b * p.T + t0 + row) * p.H + h) * p.L + INTRA_LEVELS + MLOW;
-        float lamv[tcs::MAXLH];
+        float lamv[MAXL];
 #pragma unroll
-        for (int i = 0; i < tcs::MAXLH; ++i) lamv[i] = (i < nl) ? __bfloat162float(lrow[lev[i]]) * sc : 0.f;
+        for (int i = 0; i < MAXL; ++i) lamv[i] = (i < nl) ? __bfloat162float(lrow[lev[i]]) * sc : 0.f;
         umma::fence_before_sync();
         bar_work();
         umma::mbar_wait(barA, pl & 1, abort_flag);
@@ -623,11 +627,20 @@ int mamba2_hi_out_tc_launch(const Mamba2Params& p_in, cudaStream_t stream) {
     const long BT = (long)p.B * p.T;
     if ((rc = tma::make_panel_map(&p.tm_q, p.q, BT, p.G, p.K, tc::PT)) != 0) return rc;
     if ((rc = tma::make_panel_map(&p.tm_h0, p.seg_H0, (long)p.B * p.H * p.NS * p.LH * p.K, 1, p.V, tc::KD)) != 0) return rc;
-    auto kern = m2_hi_out_tc_kernel<M2_MLOW>;
-    const size_t sm = HiOutTcSmem<M2_MLOW>::total;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
-    if (e != cudaSuccess) return (int)e;
-    kern<<<p.B * p.H * (p.NS - 1), tc::NTHREADS, sm, stream>>>(p);
+    // up to five segment levels (T <= 16384) with the smaller shared-memory footprint, else up to eight
+    if (p.LH <= 5) {
+        auto kern = m2_hi_out_tc_kernel<M2_MLOW, 5>;
+        const size_t sm = HiOutTcSmem<M2_MLOW, 5>::total;
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
+        if (e != cudaSuccess) return (int)e;
+        kern<<<p.B * p.H * (p.NS - 1), tc::NTHREADS, sm, stream>>>(p);
+    } else {
+        auto kern = m2_hi_out_tc_kernel<M2_MLOW, 8>;
+        const size_t sm = HiOutTcSmem<M2_MLOW, 8>::total;
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
+        if (e != cudaSuccess) return (int)e;
+        kern<<<p.B * p.H * (p.NS - 1), tc::NTHREADS, sm, stream>>>(p);
+    }
     return (int)cudaGetLastError();
 }
 
@@ -643,7 +656,10 @@ int mamba2_hi_bwd_tc_launch(const Mamba2Params& p_in, cudaStream_t stream) {
     const size_t sm = HiBwdTcSmem<M2_MLOW>::total;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
     if (e != cudaSuccess) return (int)e;
-    kern<<<p.B * p.H * (p.NS - 1), tc::NTHREADS, sm, stream>>>(p);
+    // one launch per window of five segment levels (a single one up to T = 16384); dq, the q.dq totals and
+    // the per-level outputs of different windows add up or are disjoint
+    for (p.lev_lo = 0; p.lev_lo < p.LH; p.lev_lo += tcs::MAXLH)
+        kern<<<p.B * p.H * (p.NS - 1), tc::NTHREADS, sm, stream>>>(p);
     return (int)cudaGetLastError();
 }
 

@@ -113,7 +113,9 @@ def gdn_case(base, rec, hm, name, B, T, H, Dk, Dv, L, chunk, round_bf16):
 
 
 def main():
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_golden.py /path/to/log-linear-attention")
+    root = sys.argv[1]
     base, rec, hm = import_reference(root)
     torch.set_num_threads(max(1, os.cpu_count() or 1))
     W = base.HType.WEAK

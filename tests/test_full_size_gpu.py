@@ -136,3 +136,16 @@ def test_mamba2_longest_sequence_identities():
     scale = (do.double().abs() * o.double().abs()).sum().item()
     assert abs(s_o - s_v) < 2e-3 * scale
     assert abs(s_o - s_l) < 2e-3 * scale
+    # the same call on the warp-MMA kernels (seven segment levels take two level windows in the tensor-core
+    # high-level backward and the eight-slot variant of the high-level forward)
+    from hattention_b200 import _lib
+    _lib.lib().llattn_set_tensor_core_path(0)
+    try:
+        o_w, g_w, _ = _fwd(q, k, v, g, l)
+        gr_w = chunkwise_bwd(q, k, v, g_w, l, do, False, 2, HType.WEAK, 64)
+        torch.cuda.synchronize()
+    finally:
+        _lib.lib().llattn_set_tensor_core_path(1)
+    assert _rel(o.float(), o_w.float()) < 5e-3
+    for a, b_, name in zip((dq, dk, dv, dg, dl), gr_w, ("dq", "dk", "dv", "dg", "dl")):
+        assert _rel(a.float(), b_.float()) < 1e-2, name
