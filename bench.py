@@ -259,8 +259,14 @@ def main():
                     help="mamba2 = the headline workload; gdn = log-linear Gated DeltaNet layer, B=4 T=8192 H=16 Dk=Dv=128 L=14")
     ap.add_argument("--batch", type=int, default=WORKLOAD["B"],
                     help="per-GPU batch; the headline workload is 2, profiler captures use 1")
+    ap.add_argument("--seq-len", type=int, default=WORKLOAD["T"],
+                    help="sequence length; the headline workload is 16384 (65536 with --batch 1 is one GPU's share of the "
+                         "multi-GPU scaling configuration); L follows as 7 + ceil(log2(T/64))")
     args = ap.parse_args()
     WORKLOAD["B"] = args.batch
+    if args.seq_len != WORKLOAD["T"]:
+        WORKLOAD["T"] = args.seq_len
+        WORKLOAD["L"] = 7 + max(0, (args.seq_len // 64 - 1).bit_length())
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -383,7 +389,7 @@ def main():
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
             "ms_per_step": per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": NAME if w["B"] == 2 else NAME.replace("B=2", f"B={w['B']}"), "l2": "inputs_exceed_l2 (about 320 MB of inputs per step vs 126 MB L2)",
+            "config": {"workload": NAME.replace("B=2", f"B={w['B']}").replace("T=16384", f"T={w['T']}").replace("L=15", f"L={w['L']}"), "l2": "inputs_exceed_l2 (about 320 MB of inputs per step vs 126 MB L2)",
                        "sharding": f"batch x {world}, no collective"},
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": pk["tflops"], "unit": "TFLOP/s",
                          "frac": achieved / pk["tflops"],
