@@ -93,8 +93,8 @@ __global__ void __launch_bounds__(256) l2norm_bwd_kernel(const __nv_bfloat16* __
 extern "C" {
 
 static int l2norm_check(const void* a, const void* b, long rows, int D) {
-    if (!a || !b) return LLATTN_ERR_NULL;
     if (rows <= 0 || D <= 0 || D > 256 || D % 8 != 0) return LLATTN_ERR_UNSUPPORTED_SHAPE;
+    if (!a || !b) return LLATTN_ERR_NULL;
     return 0;
 }
 

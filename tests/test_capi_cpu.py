@@ -80,3 +80,59 @@ def test_python_wrappers_refuse_cpu_tensors():
         hattention_kernel(q, q, v, None, g, l, None, True, 2, HType.WEAK, HStruct.MAMBA2)
     with pytest.raises(ValueError):
         hattention_kernel(q, q, v, g, g, l, None, False, 2, HType.WEAK, HStruct.MAMBA2)
+
+
+def test_gdn_entry_points_reject_bad_arguments(lib):
+    null = ctypes.c_void_p(0)
+    # K must be 128, V 64 or 128, at most eight inter-chunk levels
+    assert lib.llattn_gdn_fwd_workspace_bytes(1, 1024, 2, 96, 64, 12) == 0
+    assert lib.llattn_gdn_fwd_workspace_bytes(1, 1024, 2, 128, 256, 12) == 0
+    assert lib.llattn_gdn_fwd_workspace_bytes(1, 32768, 2, 128, 64, 16) == 0
+    fwd = lib.llattn_gdn_fwd_workspace_bytes(1, 1024, 2, 128, 128, 11)
+    lev = lib.llattn_gdn_bwd_levels_workspace_bytes(1, 1024, 2, 128, 128, 11)
+    bwd = lib.llattn_gdn_bwd_workspace_bytes(1, 1024, 2, 128, 128, 11)
+    assert 0 < fwd < lev < bwd
+    assert lib.llattn_gdn_fwd(*([null] * 10), null, 0, 1, 1000, 2, 128, 64, 11, null) == -2
+    assert lib.llattn_gdn_fwd(*([null] * 10), null, 0, 1, 1024, 2, 128, 64, 10, null) == -3
+    assert lib.llattn_gdn_fwd(*([null] * 10), null, 0, 1, 1024, 2, 128, 64, 11, null) == -6
+    assert lib.llattn_gdn_bwd(*([null] * 15), null, 0, 1, 1024, 2, 64, 64, 11, null) == -1
+    assert lib.llattn_gdn_bwd(*([null] * 15), null, 0, 1, 1024, 2, 128, 64, 11, null) == -6
+    assert lib.llattn_gdn_bwd_levels(*([null] * 15), null, 0, 1, 1024, 2, 128, 64, 11, null) == -6
+
+
+def test_elementwise_entry_points_reject_bad_arguments(lib):
+    null = ctypes.c_void_p(0)
+    assert lib.llattn_l2norm_fwd(null, null, 10, 128, 1.0, null) == -6
+    assert lib.llattn_l2norm_fwd(null, null, 10, 100, 1.0, null) == -1          # D % 8
+    assert lib.llattn_l2norm_bwd(null, null, null, 10, 512, 1.0, null) == -1     # D > 256
+    assert lib.llattn_mamba2_prep_fwd(*([null] * 9), 64, 2, 64, 12, 7, null) == -1     # lambda mode
+    assert lib.llattn_mamba2_prep_fwd(*([null] * 9), 63, 2, 64, 12, 0, null) == -1     # rows % H
+    assert lib.llattn_mamba2_prep_fwd(*([null] * 9), 64, 2, 64, 12, 0, null) == -6
+    assert lib.llattn_mamba2_prep_bwd(*([null] * 18), 64, 2, 60, 12, 0, null) == -1    # P % 8
+    assert lib.llattn_mamba2_residual(null, null, null, null, 0, 64, 2, 64, null) == -6
+
+
+def test_prefill_and_step_entry_points_reject_bad_arguments(lib):
+    null = ctypes.c_void_p(0)
+    assert lib.llattn_mamba2_final_state(null, null, null, null, 1, 1000, 2, 1, 128, 64, 8, null) == -3    # 1000 tokens need 11 levels
+    assert lib.llattn_mamba2_final_state(null, null, null, null, 1, 1000, 2, 1, 128, 64, 11, null) == -6
+    assert lib.llattn_mamba2_final_state(null, null, null, null, 1, 1000, 3, 2, 128, 64, 11, null) == -1
+    assert lib.llattn_mamba2_step(*([null] * 7), 1, 2, 1, 128, 64, 11, 11, null) == -3                    # carry level out of range
+    assert lib.llattn_mamba2_step(*([null] * 7), 1, 2, 1, 128, 48, 11, 0, null) == -1                     # 256 % V
+    assert lib.llattn_mamba2_step(*([null] * 7), 1, 2, 1, 128, 64, 11, 0, null) == -6
+
+
+def test_decode_state_counts_follow_the_cascade():
+    """Host-side token counts of the decode state: after T tokens they are the binary decomposition of
+    T - 1 plus the newest token, whether reached by stepping the cascade or set directly."""
+    import torch
+    from hattention_b200 import HState, HStruct, HType
+    for T in (1, 2, 3, 64, 65, 200, 255, 256, 1000):
+        hs = HState(2, HType.WEAK, HStruct.MAMBA2, (1, 1, 1, 1, 12), torch.float32, torch.device("cpu"))
+        for _ in range(T):
+            hs.cascade_counts()
+            hs.counts[0] += 1
+        ref = HState(2, HType.WEAK, HStruct.MAMBA2, (1, 1, 1, 1, 12), torch.float32, torch.device("cpu"))
+        ref.set_counts_after(T)
+        assert hs.counts == ref.counts, T
+        assert sum(hs.counts) == T
