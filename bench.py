@@ -187,7 +187,7 @@ def run_gdn(args, rank, world, local):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     from hattention_b200.gated_delta_rule_apis import chunk_h_gated_delta_rule
-    B, T, H, Dk, Dv, L = 4, 8192, 16, 128, 128, 14
+    B, T, H, Dk, Dv, L = (args.batch if args.batch_given else 4), 8192, 16, 128, 128, 14
     gen = torch.Generator().manual_seed(rank)
     q = torch.randn(B, T, H, Dk, generator=gen).bfloat16().to(dev)
     k = torch.randn(B, T, H, Dk, generator=gen).bfloat16().to(dev)
@@ -237,7 +237,7 @@ def run_gdn(args, rank, world, local):
         "metric": "log-linear Gated DeltaNet chunkwise tokens/s at T=8K", "value": B * T / (ms_fb * 1e-3), "unit": "tokens/s",
         "n_gpus": 1, "steps": Kb, "warmup": W, "ms_per_step": ms_fb, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": "log-linear Gated DeltaNet fwd+bwd, B=4 T=8192 H=16 Dk=Dv=128 chunk=64 L=14",
+        "config": {"workload": f"log-linear Gated DeltaNet fwd+bwd, B={B} T=8192 H=16 Dk=Dv=128 chunk=64 L=14",
                    "note": "l2norm / scale of q, k and their backward are torch elementwise ops around the CUDA kernels"},
         "forward_only": {"ms": ms_fwd, "tokens_per_s": B * T / (ms_fwd * 1e-3)},
         "roofline": {"bound": "tensor", "achieved": flops_fwd / (ms_fwd * 1e-3) / 1e12, "peak": pk["tflops"], "unit": "TFLOP/s",
@@ -263,6 +263,7 @@ def main():
                     help="sequence length; the headline workload is 16384 (65536 with --batch 1 is one GPU's share of the "
                          "multi-GPU scaling configuration); L follows as 7 + ceil(log2(T/64))")
     args = ap.parse_args()
+    args.batch_given = any(a == "--batch" or a.startswith("--batch=") for a in sys.argv[1:])
     WORKLOAD["B"] = args.batch
     if args.seq_len != WORKLOAD["T"]:
         WORKLOAD["T"] = args.seq_len

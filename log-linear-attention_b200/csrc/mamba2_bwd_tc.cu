@@ -638,7 +638,8 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_revorder_tc_kernel(con
     uint64_t* barB = bars + 1;
     uint64_t* full_qk = bars + 2;
     uint64_t* full_vd = bars + 3;
-    uint64_t* empty_all = bars + 4;
+    uint64_t* empty_qvd = bars + 4;    // the second batch is complete: q, v and do may be overwritten
+    uint64_t* empty_k = bars + 5;      // ... and the compute warps have taken their k row sums
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + SM::bar_off + 64);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + SM::bar_off + 72);
 
@@ -652,7 +653,7 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_revorder_tc_kernel(con
 
     if (tid == 0) {
 #pragma unroll
-        for (int i = 0; i < 5; ++i) umma::mbar_init(&bars[i], 1);
+        for (int i = 0; i < 6; ++i) umma::mbar_init(&bars[i], 1);
         umma::fence_mbar_init();
         *abort_flag = *p.err;
     }
@@ -670,15 +671,18 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_revorder_tc_kernel(con
                 const int brow = b * p.T + r * SEGP * tc::PT;
                 for (int it = 0; it < npairs; ++it) {
                     const int row0 = brow + (npairs - 1 - it) * tc::PT;
-                    if (it >= 1 && !umma::mbar_wait(empty_all, (it - 1) & 1, abort_flag)) break;
+                    // q, v, do are free as soon as the previous pair's second batch is done; k a little later,
+                    // after its row sums: the loads then overlap the read-out of that pair's results
+                    if (it >= 1 && !umma::mbar_wait(empty_qvd, (it - 1) & 1, abort_flag)) break;
                     tma::expect_tx(full_qk, 2 * tc::Q_BYTES);
                     tma::load_panel(sQ, &p.tm_q, 0, grp, row0, full_qk);
                     tma::load_panel(sQ + tc::Q_BYTES / 2, &p.tm_q, 64, grp, row0, full_qk);
-                    tma::load_panel(sK, &p.tm_k, 0, grp, row0, full_qk);
-                    tma::load_panel(sK + tc::Q_BYTES / 2, &p.tm_k, 64, grp, row0, full_qk);
                     tma::expect_tx(full_vd, 2 * tc::V_BYTES);
                     tma::load_panel(sV, &p.tm_v, 0, h, row0, full_vd);
                     tma::load_panel(sDO, &p.tm_do, 0, h, row0, full_vd);
+                    if (it >= 1 && !umma::mbar_wait(empty_k, (it - 1) & 1, abort_flag)) break;
+                    tma::load_panel(sK, &p.tm_k, 0, grp, row0, full_qk);
+                    tma::load_panel(sK + tc::Q_BYTES / 2, &p.tm_k, 64, grp, row0, full_qk);
                 }
             }
             return;
@@ -720,12 +724,13 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_revorder_tc_kernel(con
                         ++slot;
                     }
                 umma::commit(barB);
+                umma::mbar_wait(barB, it & 1, abort_flag);
+                asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(umma::smem_addr(empty_qvd)) : "memory");
             }
             __syncwarp();
             umma::fence_before_sync();
             bar_work();                              // barrier 3
             umma::fence_after_sync();
-            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(umma::smem_addr(empty_all)) : "memory");
             if (*abort_flag) break;
         }
         if (*abort_flag && lane == 0) atomicExch(p.err, 1);
@@ -823,6 +828,7 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_revorder_tc_kernel(con
                 }
             }
         }
+        if (tid == 0) tma::wait_group_read0();       // the previous pair's staging tile (P / scaled do space) has been read
         umma::fence_before_sync();
         bar_work();                                  // barrier 1
         umma::fence_after_sync();
@@ -1034,6 +1040,8 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_revorder_tc_kernel(con
         umma::fence_async_smem();
         bar_compute();
         if (tid == 0) {
+            // every compute thread has read its part of the k tile
+            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(umma::smem_addr(empty_k)) : "memory");
             const int grow = b * p.T + (int)t0;
 #pragma unroll
             for (int bx = 0; bx < 4; ++bx) tma::reduce_add_box(&p.tm_dk, bx * 32, grp, grow, sStage + bx * 16384);
@@ -1059,7 +1067,6 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_revorder_tc_kernel(con
             p.Yc[cidx * (MLOW + 1) + (lv == MP ? MLOW : lv + 1)] = y;
         }
         if (it + 1 < npairs) store_lam();
-        if (tid == 0) tma::wait_group_read0();
         umma::fence_async_smem();
         umma::fence_before_sync();
         bar_work();                                  // barrier 3

@@ -162,25 +162,38 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_hi_bwd_tc_kernel(const __g
             if (lane == 0) umma::mbar_wait(full_q, pl & 1, abort_flag);
             __syncwarp();
             umma::fence_after_sync();
-            for (int i = 0; i < nl; ++i) {
-                if (i >= 3) {
-                    bar_work();                      // slot i % 3 has been read by the compute warps
-                    umma::fence_after_sync();
-                }
+            for (int i = 0; i < nl && i < 3; ++i) {
                 if (lane == 0) {
                     umma::gemm_km<tc::PT, tc::KD, tc::KD>(tbase + t_slot(i), aQ, aH + i * tc::H_BYTES, ID_KM64, false);
                     umma::commit(&barT[i % 3]);
                 }
                 __syncwarp();
             }
+            // same order of events as the compute warps: after level i's T has been read, its slot takes level
+            // i + 3; after level i's scaled copy of do is written (per-level barrier, the compute warps only
+            // arrive), its reader-summary product dF_i starts while the later levels are still being read out
+            for (int i = 0; i < nl; ++i) {
+                if (i + 3 < nl) {
+                    bar_work();                      // slot i % 3 has been read by the compute warps
+                    umma::fence_after_sync();
+                    if (lane == 0) {
+                        umma::gemm_km<tc::PT, tc::KD, tc::KD>(tbase + t_slot(i + 3), aQ, aH + (i + 3) * tc::H_BYTES, ID_KM64, false);
+                        umma::commit(&barT[(i + 3) % 3]);
+                    }
+                    __syncwarp();
+                }
+                asm volatile("bar.sync %0, 288;\n" ::"r"(3 + i) : "memory");
+                umma::fence_after_sync();
+                if (lane == 0)
+                    umma::gemm_mm<tc::PT, tc::PT, tc::PT>(tbase + TM_DF + i * 64, aQ, aDOs + i * tc::V_BYTES, ID_MM64, pl > 0);
+                __syncwarp();
+            }
             umma::fence_before_sync();
-            bar_work();                              // scaled copies of do are written, every T consumed
+            bar_work();                              // every T consumed: the dq columns are free
             umma::fence_after_sync();
             if (lane == 0) {
-                for (int i = 0; i < nl; ++i) {
+                for (int i = 0; i < nl; ++i)
                     umma::gemm_kk<tc::PT, tc::KD, tc::VD>(tbase + TM_DQ, aDOs + i * tc::V_BYTES, aH + i * tc::H_BYTES, ID_KK128, i > 0);
-                    umma::gemm_mm<tc::PT, tc::PT, tc::PT>(tbase + TM_DF + i * 64, aQ, aDOs + i * tc::V_BYTES, ID_MM64, pl > 0);
-                }
                 umma::commit(barB);
                 // q is free as soon as the batch is done: let the producer refill it while dq is read out
                 umma::mbar_wait(barB, pl & 1, abort_flag);
@@ -257,10 +270,12 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_hi_bwd_tc_kernel(const __g
                 *reinterpret_cast<uint4*>(dst + umma::tile_offset(row, ch * 32 + c * 8, tc::PT)) = make_uint4(outw[0], outw[1], outw[2], outw[3]);
             }
             myDL[i] = sc * dot;
+            umma::fence_async_smem();
+            umma::fence_before_sync();
+            asm volatile("bar.arrive %0, 288;\n" ::"r"(3 + i) : "memory");     // level i's scaled copy is in place
         }
-        umma::fence_async_smem();
         umma::fence_before_sync();
-        bar_work();                                  // scaled copies written; second batch may start
+        bar_work();                                  // every T consumed; the dq products may start
         umma::fence_after_sync();
         // ---- dlambda out, reader totals Z per chunk, q.dq contribution
         if (ch == 0) {
