@@ -195,6 +195,12 @@ int llattn_l2norm_bwd(const void* x, const float* dy, void* dx, long rows, int D
  * the kernel's bounded wait.  (No counterpart in the reference; used by the test-suite.) */
 int llattn_selftest_umma(const void* A, const void* B, float* D, int N, int kred, int mode, int* err_flag, void* stream);
 
+/* Diagnostic: SM clock cycles from the issue of `reps` back-to-back 128 x N x kred products of one layout
+ * combination (modes as above, operands resident in shared memory, accumulator in tensor memory) to their
+ * completion, written to *cycles (device memory); issuers = 2 lets two warps issue `reps` products each at the
+ * same time into separate accumulators.  (No counterpart in the reference.) */
+int llattn_selftest_umma_cycles(int N, int kred, int mode, int reps, int issuers, long long* cycles, int* err_flag, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

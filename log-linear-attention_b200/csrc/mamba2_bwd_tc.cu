@@ -104,7 +104,7 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_fwdorder_tc_kernel(con
     constexpr uint32_t ID_MM64 = umma::idesc_bf16(128, 64, true, true);
 
     if (warp >= tc::MMA_WARP) {
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 40;\n");
+        RegisterSplit<80, 208>::release();
         if (warp == tc::MMA_WARP + 1) {
             // ---- TMA producer
             if (lane == 0) {
@@ -188,7 +188,7 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_fwdorder_tc_kernel(con
     }
 
     // ================= warps 0..7 =================
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 232;\n");
+    RegisterSplit<80, 208>::acquire();
     const int rb = warp & 3;
     const int row = rb * 32 + lane;
     const int ch = warp >> 2;
@@ -665,7 +665,7 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_revorder_tc_kernel(con
     constexpr uint32_t ID_MM64 = umma::idesc_bf16(128, 64, true, true);
 
     if (warp >= tc::MMA_WARP) {
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 40;\n");
+        RegisterSplit<80, 208>::release();
         if (warp == tc::MMA_WARP + 1) {
             if (lane == 0) {
                 const int brow = b * p.T + r * SEGP * tc::PT;
@@ -741,7 +741,7 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_revorder_tc_kernel(con
     }
 
     // ================= warps 0..7 =================
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 232;\n");
+    RegisterSplit<80, 208>::acquire();
     const int rb = warp & 3;
     const int row = rb * 32 + lane;
     const int ch = warp >> 2;

@@ -71,9 +71,9 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_hi_bwd_tc_kernel(const __g
     using SM = HiBwdTcSmem<MLOW>;
     constexpr int SEG = SM::SEG, NDLH = tcs::MAXLH + 1;
     // tensor memory: dF slots 0..4 (64 columns each), dq (128 columns), T (64 columns).  The level reads
-    // T_j use three 64-column slots: T and the two halves of dq (dq is only written after every T of the
-    // pair has been consumed), so up to three of them are in flight without a CTA barrier.
-    constexpr int TM_DF = 0, TM_DQ = 320, TM_T = 448;
+    // T_j use three adjacent 64-column slots: the two halves of dq (only written after every T of the pair
+    // has been consumed) and T.
+    constexpr int TM_DF = 0, TM_DQ = 320;      // the third T slot is the 64 columns after dq (448..511)
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     unsigned char* sQ = smem + SM::q_off;
@@ -85,7 +85,7 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_hi_bwd_tc_kernel(const __g
     float* sTot = sGs + SEG * 64;
     float* sDL = reinterpret_cast<float*>(smem + SM::misc_off);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SM::bar_off);
-    uint64_t* barT = bars + 0;       // [3] level read T_j in slot j % 3 complete
+    uint64_t* barT = bars + 0;       // [2] first / second chain of level reads complete ([2] unused)
     uint64_t* barB = bars + 3;       // second batch of a pair complete
     uint64_t* full_q = bars + 4;     // q tile of a pair
     uint64_t* full_do = bars + 5;    // do tile of a pair
@@ -121,13 +121,12 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_hi_bwd_tc_kernel(const __g
     __syncthreads();
     if (*abort_flag) return;
 
-    constexpr uint32_t ID_KM64 = umma::idesc_bf16(128, 64, false, true);
     constexpr uint32_t ID_KK128 = umma::idesc_bf16(128, 128, false, false);
     constexpr uint32_t ID_MM64 = umma::idesc_bf16(128, 64, true, true);
-    auto t_slot = [&](int i) -> uint32_t { return (i % 3 == 0) ? (uint32_t)TM_T : (uint32_t)(TM_DQ + (i % 3 - 1) * 64); };
+    auto t_slot = [&](int i) -> uint32_t { return (uint32_t)(TM_DQ + (i % 3) * 64); };   // three adjacent 64-column slots
 
     if (warp >= tc::MMA_WARP) {
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 40;\n");
+        RegisterSplit<104, 200>::release();
         if (warp == tc::MMA_WARP + 1) {
             if (lane == 0) {
                 // level states of the segment: rows of the (B*H*NS*LH*K, V) matrix
@@ -162,36 +161,36 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_hi_bwd_tc_kernel(const __g
             if (lane == 0) umma::mbar_wait(full_q, pl & 1, abort_flag);
             __syncwarp();
             umma::fence_after_sync();
-            for (int i = 0; i < nl && i < 3; ++i) {
+            // The issue of a tcgen05.mma costs about as much for N = 64 as for N = 256, so the level reads of up
+            // to three levels are ONE chain of eight instructions: the level states are adjacent 64-column
+            // panels of an MN-major B operand and their results adjacent tensor-memory slots.
+            {
+                const int n0 = nl < 3 ? nl : 3;
                 if (lane == 0) {
-                    umma::gemm_km<tc::PT, tc::KD, tc::KD>(tbase + t_slot(i), aQ, aH + i * tc::H_BYTES, ID_KM64, false);
-                    umma::commit(&barT[i % 3]);
+                    umma::gemm_km<tc::PT, tc::KD, tc::KD>(tbase + TM_DQ, aQ, aH, umma::idesc_bf16(128, 64 * n0, false, true), false);
+                    umma::commit(&barT[0]);
                 }
                 __syncwarp();
-            }
-            // same order of events as the compute warps: after level i's T has been read, its slot takes level
-            // i + 3; after level i's scaled copy of do is written (per-level barrier, the compute warps only
-            // arrive), its reader-summary product dF_i starts while the later levels are still being read out
-            for (int i = 0; i < nl; ++i) {
-                if (i + 3 < nl) {
-                    bar_work();                      // slot i % 3 has been read by the compute warps
+                if (nl > 3) {
+                    bar_work();                      // the three slots have been read by the compute warps
                     umma::fence_after_sync();
                     if (lane == 0) {
-                        umma::gemm_km<tc::PT, tc::KD, tc::KD>(tbase + t_slot(i + 3), aQ, aH + (i + 3) * tc::H_BYTES, ID_KM64, false);
-                        umma::commit(&barT[(i + 3) % 3]);
+                        umma::gemm_km<tc::PT, tc::KD, tc::KD>(tbase + TM_DQ, aQ, aH + 3 * tc::H_BYTES,
+                                                              umma::idesc_bf16(128, 64 * (nl - 3), false, true), false);
+                        umma::commit(&barT[1]);
                     }
                     __syncwarp();
                 }
-                asm volatile("bar.sync %0, 288;\n" ::"r"(3 + i) : "memory");
-                umma::fence_after_sync();
-                if (lane == 0)
-                    umma::gemm_mm<tc::PT, tc::PT, tc::PT>(tbase + TM_DF + i * 64, aQ, aDOs + i * tc::V_BYTES, ID_MM64, pl > 0);
-                __syncwarp();
             }
             umma::fence_before_sync();
-            bar_work();                              // every T consumed: the dq columns are free
+            bar_work();                              // scaled copies of do are written, every T consumed
             umma::fence_after_sync();
             if (lane == 0) {
+                // reader summaries of up to four levels per chain (N = 256), then dq over all levels
+                const int n0 = nl < 4 ? nl : 4;
+                umma::gemm_mm<tc::PT, tc::PT, tc::PT>(tbase + TM_DF, aQ, aDOs, umma::idesc_bf16(128, 64 * n0, true, true), pl > 0);
+                if (nl > 4)
+                    umma::gemm_mm<tc::PT, tc::PT, tc::PT>(tbase + TM_DF + 4 * 64, aQ, aDOs + 4 * tc::V_BYTES, ID_MM64, pl > 0);
                 for (int i = 0; i < nl; ++i)
                     umma::gemm_kk<tc::PT, tc::KD, tc::VD>(tbase + TM_DQ, aDOs + i * tc::V_BYTES, aH + i * tc::H_BYTES, ID_KK128, i > 0);
                 umma::commit(barB);
@@ -213,7 +212,7 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_hi_bwd_tc_kernel(const __g
     }
 
     // ================= warps 0..7 =================
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 232;\n");
+    RegisterSplit<104, 200>::acquire();
     const int rb = warp & 3;
     const int row = rb * 32 + lane;
     const int ch = warp >> 2;
@@ -222,7 +221,7 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_hi_bwd_tc_kernel(const __g
     bar_work();
     umma::fence_after_sync();
     const uint32_t tbase = *tmem_slot;
-    uint32_t phT[3] = {0, 0, 0};
+    uint32_t phT[2] = {0, 0};
 
     for (int pl = 0; pl < npairs; ++pl) {
         const long t0 = (long)(r * SEG) * CH + (long)pl * tc::PT;
@@ -238,15 +237,16 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_hi_bwd_tc_kernel(const __g
         asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(umma::smem_addr(empty_do)) : "memory");
         float* myDL = sDL + (ch * 128 + row) * NDLH;
         for (int i = 0; i < nl; ++i) {
-            const int sl = i % 3;
-            umma::mbar_wait(&barT[sl], phT[sl], abort_flag);
-            phT[sl] ^= 1;
-            umma::fence_after_sync();
+            if (i == 0 || i == 3) {                  // one completion per chain of level reads
+                umma::mbar_wait(&barT[i / 3], phT[i / 3], abort_flag);
+                phT[i / 3] ^= 1;
+                umma::fence_after_sync();
+            }
             float t[32];
             umma::tmem_ld32(umma::tmem_addr(tbase + t_slot(i), warp, ch * 32), t);
-            if (i + 3 < nl) {
+            if (i == 2 && nl > 3) {
                 umma::fence_before_sync();
-                bar_work();                          // the slot may be reused
+                bar_work();                          // the three slots may be reused
             }
             if (i == 0) {
                 // the staging area of the previous pair (same memory as the scaled copies) has been read
@@ -270,12 +270,10 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_hi_bwd_tc_kernel(const __g
                 *reinterpret_cast<uint4*>(dst + umma::tile_offset(row, ch * 32 + c * 8, tc::PT)) = make_uint4(outw[0], outw[1], outw[2], outw[3]);
             }
             myDL[i] = sc * dot;
-            umma::fence_async_smem();
-            umma::fence_before_sync();
-            asm volatile("bar.arrive %0, 288;\n" ::"r"(3 + i) : "memory");     // level i's scaled copy is in place
         }
+        umma::fence_async_smem();
         umma::fence_before_sync();
-        bar_work();                                  // every T consumed; the dq products may start
+        bar_work();                                  // scaled copies written; second batch may start
         umma::fence_after_sync();
         // ---- dlambda out, reader totals Z per chunk, q.dq contribution
         if (ch == 0) {
@@ -389,10 +387,9 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_hi_out_tc_kernel(const __g
     }
     __syncthreads();
     if (*abort_flag) return;
-    constexpr uint32_t ID_KM64 = umma::idesc_bf16(128, 64, false, true);
 
     if (warp >= tc::MMA_WARP) {
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 40;\n");
+        RegisterSplit<64, 216>::release();
         if (warp == tc::MMA_WARP + 1) {
             if (lane == 0) {
                 tma::expect_tx(full_h, nl * tc::H_BYTES);
@@ -424,9 +421,13 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_hi_out_tc_kernel(const __g
             umma::fence_after_sync();
             if (lane == 0) {
                 umma::mbar_wait(&full_q[st], (pl >> 1) & 1, abort_flag);
-                for (int i = 0; i < nl; ++i)
-                    umma::gemm_km<tc::PT, tc::KD, tc::KD>(tbase + i * 64, umma::smem_addr(sQ + st * tc::Q_BYTES),
-                                                          umma::smem_addr(sH + i * tc::H_BYTES), ID_KM64, false);
+                // adjacent level states / adjacent result slots: chains of up to four levels (N = 256)
+                for (int i0 = 0; i0 < nl; i0 += 4) {
+                    const int n = (nl - i0) < 4 ? (nl - i0) : 4;
+                    umma::gemm_km<tc::PT, tc::KD, tc::KD>(tbase + i0 * 64, umma::smem_addr(sQ + st * tc::Q_BYTES),
+                                                          umma::smem_addr(sH + i0 * tc::H_BYTES),
+                                                          umma::idesc_bf16(128, 64 * n, false, true), false);
+                }
                 umma::commit(barA);
                 umma::commit(&empty_q[st]);
             }
@@ -440,7 +441,7 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_hi_out_tc_kernel(const __g
         return;
     }
 
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 232;\n");
+    RegisterSplit<64, 216>::acquire();
     const int rb = warp & 3;
     const int row = rb * 32 + lane;
     const int ch = warp >> 2;
@@ -532,7 +533,7 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_seg_state_tc_kernel(const 
     constexpr uint32_t ID_MM64 = umma::idesc_bf16(128, 64, true, true);
 
     if (warp >= tc::MMA_WARP) {
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 40;\n");
+        RegisterSplit<64, 216>::release();
         if (warp == tc::MMA_WARP + 1) {
             if (lane == 0) {
                 const int brow = b * p.T + r * SEG * CH;
@@ -573,7 +574,7 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_seg_state_tc_kernel(const 
         return;
     }
 
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 232;\n");
+    RegisterSplit<64, 216>::acquire();
     const int rb = warp & 3;
     const int row = rb * 32 + lane;
     const int ch = warp >> 2;

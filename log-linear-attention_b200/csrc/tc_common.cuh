@@ -38,6 +38,18 @@ constexpr int LAM_LD = MAX_L + 2;   // row stride of the staged lambda tile: odd
 
 // CTA-wide barrier over the 8 element-wise warps and the MMA warp (the spare warps of the third
 // warpgroup exit at once and never take part)
+// Register hand-over between the third warpgroup (TMA producer, MMA issuer, two idle warps) and the two
+// element-wise warpgroups.  The kernel is launched with 168 registers per thread (384 threads); what the third
+// group gives up must cover what the other two take, otherwise setmaxnreg.inc waits for registers that never
+// become free.  The check is on the values themselves, so an unbalanced pair does not compile.
+template <int DEC, int INC>
+struct RegisterSplit {
+    static_assert(DEC % 8 == 0 && INC % 8 == 0 && DEC >= 24 && INC <= 256, "setmaxnreg takes multiples of 8 in [24, 256]");
+    static_assert(128 * (168 - DEC) >= 256 * (INC - 168), "the register pool does not cover this split");
+    __device__ static __forceinline__ void release() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;\n" ::"n"(DEC)); }
+    __device__ static __forceinline__ void acquire() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;\n" ::"n"(INC)); }
+};
+
 __device__ __forceinline__ void bar_work() { asm volatile("bar.sync 1, 288;\n" ::: "memory"); }
 
 // barrier over the 8 element-wise warps only

@@ -65,7 +65,94 @@ __global__ void __launch_bounds__(128, 1) umma_selftest_kernel(const bf16* __res
     if (warp == 0) umma::tmem_dealloc(tbase, 128);
 }
 
+// Issue-to-completion time of `reps` back-to-back products of one layout combination (operands already in
+// shared memory, accumulators in tensor memory): the per-instruction cost that the kernel designs assume.
+// issuers = 2: warps 0 and 1 each issue `reps` products into their own accumulator at the same time.
+__global__ void __launch_bounds__(128, 1) umma_cycles_kernel(int N, int kred, int mode, int reps, int issuers,
+                                                             long long* __restrict__ cycles, int* __restrict__ err) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    unsigned char* sA = smem;
+    unsigned char* sB = smem + 32768;
+    __shared__ uint64_t bar[2];
+    __shared__ uint32_t tmem_slot;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    for (int e = tid; e < 65536 / 4; e += 128) reinterpret_cast<uint32_t*>(smem)[e] = 0x3c003c00u;     // small finite bf16 pairs
+    if (warp == 0) umma::tmem_alloc(&tmem_slot, 256);
+    if (tid == 0) {
+        umma::mbar_init(&bar[0], 1);
+        umma::mbar_init(&bar[1], 1);
+        umma::fence_mbar_init();
+    }
+    umma::fence_async_smem();
+    umma::fence_before_sync();
+    __syncthreads();
+    umma::fence_after_sync();
+    const uint32_t tbase = tmem_slot + (warp == 1 ? 128 : 0);
+    const long long t0 = clock64();
+    if (lane == 0 && warp < (issuers % 10)) {
+        const uint32_t a = umma::smem_addr(sA), b = umma::smem_addr(sB);
+        const int a_rows = (mode == 2) ? kred : 128, b_rows = (mode == 0) ? N : kred;
+        // the compile-time shaped issue loops of the kernels where one exists for the combination
+        if (mode == 2 && N == 64 && kred == 64) {
+            // the second batch of the reverse-order backward pass: seven chains of different layouts and widths
+            // into different accumulators (36 instructions per repetition)
+            const uint32_t t = tmem_slot;
+            for (int r = 0; r < reps; ++r) {
+                umma::gemm_mm<128, 128, 128>(t + 0, a, b, umma::idesc_bf16(128, 64, true, true), false);
+                umma::gemm_km<128, 128, 128>(t + 64, b, a + 16384, umma::idesc_bf16(128, 64, false, true), false);
+                umma::gemm_kk<128, 128, 64>(t + 128, a, b, umma::idesc_bf16(128, 128, false, false), false);
+                umma::gemm_mm<128, 128, 64>(t + 0, b, a, umma::idesc_bf16(128, 64, true, true), false);
+                umma::gemm_mm<128, 128, 64>(t + 64, b + 8192, a + 8192, umma::idesc_bf16(128, 64, true, true), false);
+                umma::gemm_mm<128, 128, 128>(t + 128, a, b + 16384, umma::idesc_bf16(128, 64, true, true), false);
+            }
+        } else if (mode == 0 && N == 128 && kred == 128) {
+            for (int r = 0; r < reps; ++r) umma::gemm_kk<128, 128, 128>(tbase, a, b, umma::idesc_bf16(128, 128, false, false), r > 0);
+        } else if (mode == 0 && N == 128 && kred == 64) {
+            for (int r = 0; r < reps; ++r) umma::gemm_kk<128, 128, 64>(tbase, a, b, umma::idesc_bf16(128, 128, false, false), r > 0);
+        } else if (mode == 1 && N == 64 && kred == 128) {
+            for (int r = 0; r < reps; ++r) umma::gemm_km<128, 128, 128>(tbase, a, b, umma::idesc_bf16(128, 64, false, true), r > 0);
+        } else if (mode == 2 && N == 64 && kred == 128) {
+            for (int r = 0; r < reps; ++r) umma::gemm_mm<128, 128, 128>(tbase, a, b, umma::idesc_bf16(128, 64, true, true), r > 0);
+        } else if (mode == 2 && N == 128 && kred == 128) {
+            for (int r = 0; r < reps; ++r) umma::gemm_mm<128, 128, 128>(tbase, a, b, umma::idesc_bf16(128, 128, true, true), r > 0);
+        } else {
+            for (int r = 0; r < reps; ++r) {
+                if (mode == 0) umma::gemm_kk(tbase, a, a_rows, b, b_rows, kred, umma::idesc_bf16(128, N, false, false), r > 0);
+                if (mode == 1) umma::gemm_km(tbase, a, a_rows, b, b_rows, kred, umma::idesc_bf16(128, N, false, true), r > 0);
+                if (mode == 2) umma::gemm_mm(tbase, a, a_rows, b, b_rows, kred, umma::idesc_bf16(128, N, true, true), r > 0);
+            }
+        }
+        umma::commit(&bar[warp]);
+    }
+    // issuers >= 10: every thread of the CTA waits on the completion barrier while the products run
+    // (what the element-wise warps of the kernels do), instead of thread 0 alone
+    if (tid == 0 || issuers >= 10) {
+        bool ok = umma::mbar_wait(&bar[0], 0);
+        if ((issuers % 10) > 1) ok = umma::mbar_wait(&bar[1], 0) && ok;
+        const long long t1 = clock64();
+        if (tid == 0) *cycles = t1 - t0;
+        if (!ok) atomicExch(err, 1);
+    }
+    umma::fence_before_sync();
+    __syncthreads();
+    if (warp == 0) umma::tmem_dealloc(tmem_slot, 256);
+}
+
 }  // namespace llattn
+
+extern "C" int llattn_selftest_umma_cycles(int N, int kred, int mode, int reps, int issuers, long long* cycles, int* err_flag,
+                                           void* stream) {
+    if (!cycles || !err_flag) return LLATTN_ERR_NULL;
+    if (!(N == 64 || N == 128) || !(kred == 64 || kred == 128) || mode < 0 || mode > 2 || reps < 1 || reps > 4096 ||
+        !(issuers == 1 || issuers == 2 || issuers == 11 || issuers == 12))
+        return LLATTN_ERR_UNSUPPORTED_SHAPE;
+    const size_t sm = 65536 + 1024;
+    cudaError_t e = cudaFuncSetAttribute(llattn::umma_cycles_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
+    if (e != cudaSuccess) return (int)e;
+    llattn::umma_cycles_kernel<<<1, 128, sm, (cudaStream_t)stream>>>(N, kred, mode, reps, issuers, cycles, err_flag);
+    return (int)cudaGetLastError();
+}
 
 extern "C" int llattn_selftest_umma(const void* A, const void* B, float* D, int N, int kred, int mode, int* err_flag,
                                     void* stream) {

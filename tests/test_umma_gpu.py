@@ -27,3 +27,34 @@ def test_umma_tile_product(mode, N, kred):
     Af, Bf = A.float(), B.float()
     want = Af @ Bf.T if mode == 0 else (Af @ Bf if mode == 1 else Af.T @ Bf)
     assert torch.allclose(D, want, rtol=1e-3, atol=1e-2), (D - want).abs().max().item()
+
+
+@pytest.mark.parametrize("mode,N,kred,bound", [
+    (0, 128, 128, 72.0),    # K-major x K-major, N = 128: tensor-core bound, 64 cycles per K = 16 step
+    (2, 128, 128, 72.0),    # MN-major x MN-major, N = 128
+    (1, 64, 128, 64.0),     # N = 64: about 54 cycles per step (32 would be the arithmetic bound)
+    (2, 64, 128, 64.0),
+])
+def test_mma_issue_rate(mode, N, kred, bound):
+    """Cycles per tcgen05.mma (M = 128, K = 16) of the compile-time shaped issue loops that the kernels use,
+    from back-to-back products with resident operands (difference between 64 and 8 repetitions, so the
+    fixed issue-to-completion latency cancels).  Prints the figure; run with -s to see it."""
+    from hattention_b200 import _lib
+    lib = _lib.lib()
+    dev = torch.device("cuda:0")
+    cyc = torch.zeros(1, dtype=torch.int64, device=dev)
+    err = torch.zeros(1, dtype=torch.int32, device=dev)
+    total = {}
+    for reps in (8, 64):
+        best = None
+        for _ in range(3):
+            rc = lib.llattn_selftest_umma_cycles(N, kred, mode, reps, 1, cyc.data_ptr(), err.data_ptr(),
+                                                 torch.cuda.current_stream().cuda_stream)
+            assert rc == 0
+            torch.cuda.synchronize()
+            assert err.item() == 0
+            best = cyc.item() if best is None else min(best, cyc.item())
+        total[reps] = best
+    per_step = (total[64] - total[8]) / ((64 - 8) * (kred // 16))
+    print(f"mode {mode} N={N} kred={kred}: {per_step:.1f} cycles per K=16 step; 8 repetitions take {total[8]} cycles")
+    assert per_step <= bound
