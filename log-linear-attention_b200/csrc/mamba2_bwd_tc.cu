@@ -104,7 +104,7 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_fwdorder_tc_kernel(con
     constexpr uint32_t ID_MM64 = umma::idesc_bf16(128, 64, true, true);
 
     if (warp >= tc::MMA_WARP) {
-        RegisterSplit<80, 208>::release();
+        RegisterSplit<72, 216>::release();
         if (warp == tc::MMA_WARP + 1) {
             // ---- TMA producer
             if (lane == 0) {
@@ -188,7 +188,7 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_fwdorder_tc_kernel(con
     }
 
     // ================= warps 0..7 =================
-    RegisterSplit<80, 208>::acquire();
+    RegisterSplit<72, 216>::acquire();
     const int rb = warp & 3;
     const int row = rb * 32 + lane;
     const int ch = warp >> 2;
@@ -665,7 +665,7 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_revorder_tc_kernel(con
     constexpr uint32_t ID_MM64 = umma::idesc_bf16(128, 64, true, true);
 
     if (warp >= tc::MMA_WARP) {
-        RegisterSplit<80, 208>::release();
+        RegisterSplit<72, 216>::release();
         if (warp == tc::MMA_WARP + 1) {
             if (lane == 0) {
                 const int brow = b * p.T + r * SEGP * tc::PT;
@@ -741,7 +741,7 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_revorder_tc_kernel(con
     }
 
     // ================= warps 0..7 =================
-    RegisterSplit<80, 208>::acquire();
+    RegisterSplit<72, 216>::acquire();
     const int rb = warp & 3;
     const int row = rb * 32 + lane;
     const int ch = warp >> 2;

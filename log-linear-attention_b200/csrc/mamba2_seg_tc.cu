@@ -126,7 +126,7 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_hi_bwd_tc_kernel(const __g
     auto t_slot = [&](int i) -> uint32_t { return (uint32_t)(TM_DQ + (i % 3) * 64); };   // three adjacent 64-column slots
 
     if (warp >= tc::MMA_WARP) {
-        RegisterSplit<104, 200>::release();
+        RegisterSplit<120, 192>::release();
         if (warp == tc::MMA_WARP + 1) {
             if (lane == 0) {
                 // level states of the segment: rows of the (B*H*NS*LH*K, V) matrix
@@ -212,7 +212,7 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_hi_bwd_tc_kernel(const __g
     }
 
     // ================= warps 0..7 =================
-    RegisterSplit<104, 200>::acquire();
+    RegisterSplit<120, 192>::acquire();
     const int rb = warp & 3;
     const int row = rb * 32 + lane;
     const int ch = warp >> 2;
@@ -389,7 +389,7 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_hi_out_tc_kernel(const __g
     if (*abort_flag) return;
 
     if (warp >= tc::MMA_WARP) {
-        RegisterSplit<64, 216>::release();
+        RegisterSplit<56, 224>::release();
         if (warp == tc::MMA_WARP + 1) {
             if (lane == 0) {
                 tma::expect_tx(full_h, nl * tc::H_BYTES);
@@ -441,7 +441,7 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_hi_out_tc_kernel(const __g
         return;
     }
 
-    RegisterSplit<64, 216>::acquire();
+    RegisterSplit<56, 224>::acquire();
     const int rb = warp & 3;
     const int row = rb * 32 + lane;
     const int ch = warp >> 2;
