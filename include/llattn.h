@@ -191,7 +191,8 @@ int llattn_l2norm_bwd(const void* x, const float* dy, void* dx, long rows, int D
 /* Diagnostic: one 128 x N x kred bf16 tensor-core product (tcgen05.mma, accumulator in tensor
  * memory) per operand-layout combination used by the kernels: mode 0: D = A B^T with A [128][kred],
  * B [N][kred]; mode 1: D = A B with B [kred][N]; mode 2: D = A^T B with A [kred][128], B [kred][N].
- * D is [128][N] fp32.  *err_flag is set to 1 if the tensor core did not signal completion within
+ * D is [128][N] fp32.  Modes 10, 11, 12 are the same three products issued through the compile-time shaped
+ * loops that the kernels use.  *err_flag is set to 1 if the tensor core did not signal completion within
  * the kernel's bounded wait.  (No counterpart in the reference; used by the test-suite.) */
 int llattn_selftest_umma(const void* A, const void* B, float* D, int N, int kred, int mode, int* err_flag, void* stream);
 

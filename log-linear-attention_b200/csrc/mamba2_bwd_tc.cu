@@ -77,8 +77,11 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_fwdorder_tc_kernel(con
     uint64_t* full_vd = bars + 3;   // TMA: v and do tiles
     uint64_t* empty_qk = bars + 4;  // q / k tiles may be refilled
     uint64_t* empty_vd = bars + 5;  // v / do tiles may be refilled
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + SM::bar_off + 64);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + SM::bar_off + 72);
+    uint64_t* dq_ready = bars + 6;  // the dq tile of the pair is staged (fp32) for the store agent
+    uint64_t* dk_ready = bars + 7;  // ... the dk tile
+    uint64_t* stage_free = bars + 8;   // the store agent's reduce-adds have read both staging areas
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + SM::bar_off + 96);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + SM::bar_off + 104);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int h = blockIdx.x % p.H;
@@ -90,7 +93,7 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_fwdorder_tc_kernel(con
 
     if (tid == 0) {
 #pragma unroll
-        for (int i = 0; i < 6; ++i) umma::mbar_init(&bars[i], 1);
+        for (int i = 0; i < 9; ++i) umma::mbar_init(&bars[i], 1);
         umma::fence_mbar_init();
         *abort_flag = *p.err;
     }
@@ -104,7 +107,7 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_fwdorder_tc_kernel(con
     constexpr uint32_t ID_MM64 = umma::idesc_bf16(128, 64, true, true);
 
     if (warp >= tc::MMA_WARP) {
-        RegisterSplit<72, 216>::release();
+        RegisterSplit<56, 224>::release();
         if (warp == tc::MMA_WARP + 1) {
             // ---- TMA producer
             if (lane == 0) {
@@ -122,6 +125,29 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_fwdorder_tc_kernel(con
                     tma::load_panel(sK, &p.tm_k, 0, grp, row0, full_qk);
                     tma::load_panel(sK + tc::Q_BYTES / 2, &p.tm_k, 64, grp, row0, full_qk);
                 }
+            }
+            return;
+        }
+        if (warp == tc::MMA_WARP + 2) {
+            // ---- store agent: issues the fp32 TMA reduce-adds of the staged dq / dk tiles and is the one that
+            //      waits for them, so that no element-wise thread stalls on a bulk-group wait; when both staging
+            //      areas have been read it frees the q / k tile space (which doubles as the dk staging area)
+            if (lane == 0) {
+                for (int pl = 0; pl < npairs; ++pl) {
+                    const int grow = b * p.T + (r * SEGP + pl) * tc::PT;
+                    if (!umma::mbar_wait(dq_ready, pl & 1, abort_flag)) break;
+#pragma unroll
+                    for (int bx = 0; bx < 4; ++bx) tma::reduce_add_box(&p.tm_dq, bx * 32, grp, grow, sStage + bx * 16384);
+                    tma::commit_group();
+                    if (!umma::mbar_wait(dk_ready, pl & 1, abort_flag)) break;
+#pragma unroll
+                    for (int bx = 0; bx < 4; ++bx) tma::reduce_add_box(&p.tm_dk, bx * 32, grp, grow, sStage2 + bx * 16384);
+                    tma::commit_group();
+                    tma::wait_group_read0();
+                    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(umma::smem_addr(empty_qk)) : "memory");
+                    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(umma::smem_addr(stage_free)) : "memory");
+                }
+                tma::wait_group0();                  // every reduce-add has been performed before the CTA retires
             }
             return;
         }
@@ -177,7 +203,6 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_fwdorder_tc_kernel(con
             umma::fence_before_sync();
             bar_work();                              // barrier 3: end of the pair
             umma::fence_after_sync();
-            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(umma::smem_addr(empty_qk)) : "memory");
             if (*abort_flag) break;
         }
         if (*abort_flag && lane == 0) atomicExch(p.err, 1);
@@ -188,7 +213,7 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_fwdorder_tc_kernel(con
     }
 
     // ================= warps 0..7 =================
-    RegisterSplit<72, 216>::acquire();
+    RegisterSplit<56, 224>::acquire();
     const int rb = warp & 3;
     const int row = rb * 32 + lane;
     const int ch = warp >> 2;
@@ -285,6 +310,7 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_fwdorder_tc_kernel(con
         umma::mbar_wait(full_vd, pl & 1, abort_flag);
         umma::mbar_wait(full_qk, pl & 1, abort_flag);
         umma::mbar_wait(barA, pl & 1, abort_flag);
+        if (pl >= 1) umma::mbar_wait(stage_free, (pl - 1) & 1, abort_flag);   // dS / scaled-do space was the dq staging area
         umma::fence_after_sync();
 
         STAMP();   // 2 batch A complete
@@ -506,12 +532,7 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_fwdorder_tc_kernel(con
         STAMP();   // 9 dk read, dq staged
         umma::fence_async_smem();
         bar_compute();                               // dq staged; every thread is done with the k tile
-        if (tid == 0) {
-            const int grow = b * p.T + (int)t0;
-#pragma unroll
-            for (int bx = 0; bx < 4; ++bx) tma::reduce_add_box(&p.tm_dq, bx * 32, grp, grow, sStage + bx * 16384);
-            tma::commit_group();
-        }
+        if (tid == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(umma::smem_addr(dq_ready)) : "memory");
         // ---- dk tile -> fp32 staging in the q / k tile space -> TMA reduce-add
 #pragma unroll
         for (int hb = 0; hb < 2; ++hb) {
@@ -524,12 +545,7 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_fwdorder_tc_kernel(con
         STAMP();   // 10 dk staged
         umma::fence_async_smem();
         bar_compute();
-        if (tid == 0) {
-            const int grow = b * p.T + (int)t0;
-#pragma unroll
-            for (int bx = 0; bx < 4; ++bx) tma::reduce_add_box(&p.tm_dk, bx * 32, grp, grow, sStage2 + bx * 16384);
-            tma::commit_group();
-        }
+        if (tid == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(umma::smem_addr(dk_ready)) : "memory");
         if (ch == 0) {
             const float w = wq_row - (sWk[row] + sWk[128 + row]);
             red_add_f32(p.wq + ((long)b * p.T + t0 + row) * p.H + h, w);
@@ -571,7 +587,6 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_fwdorder_tc_kernel(con
         }
         STAMP();   // 12 states merged
         if (pl + 1 < npairs) store_lam();
-        if (tid == 0) tma::wait_group_read0();       // staging is rewritten by the next pair
         umma::fence_async_smem();
         umma::fence_before_sync();
         bar_work();                                  // barrier 3
@@ -579,7 +594,6 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_fwdorder_tc_kernel(con
         umma::fence_after_sync();
         if (*abort_flag) break;
     }
-    if (tid == 0) tma::wait_group0();                // all reduce-adds have been performed
     umma::fence_before_sync();
     bar_work();
 }
@@ -640,8 +654,10 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_revorder_tc_kernel(con
     uint64_t* full_vd = bars + 3;
     uint64_t* empty_qvd = bars + 4;    // the second batch is complete: q, v and do may be overwritten
     uint64_t* empty_k = bars + 5;      // ... and the compute warps have taken their k row sums
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + SM::bar_off + 64);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + SM::bar_off + 72);
+    uint64_t* dk_ready = bars + 6;     // the dk tile of the pair is staged (fp32) for the store agent
+    uint64_t* stage_free = bars + 7;   // the store agent's reduce-add has read the staging area
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + SM::bar_off + 96);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + SM::bar_off + 104);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int h = blockIdx.x % p.H;
@@ -653,7 +669,7 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_revorder_tc_kernel(con
 
     if (tid == 0) {
 #pragma unroll
-        for (int i = 0; i < 6; ++i) umma::mbar_init(&bars[i], 1);
+        for (int i = 0; i < 8; ++i) umma::mbar_init(&bars[i], 1);
         umma::fence_mbar_init();
         *abort_flag = *p.err;
     }
@@ -665,7 +681,7 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_revorder_tc_kernel(con
     constexpr uint32_t ID_MM64 = umma::idesc_bf16(128, 64, true, true);
 
     if (warp >= tc::MMA_WARP) {
-        RegisterSplit<72, 216>::release();
+        RegisterSplit<56, 224>::release();
         if (warp == tc::MMA_WARP + 1) {
             if (lane == 0) {
                 const int brow = b * p.T + r * SEGP * tc::PT;
@@ -684,6 +700,23 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_revorder_tc_kernel(con
                     tma::load_panel(sK, &p.tm_k, 0, grp, row0, full_qk);
                     tma::load_panel(sK + tc::Q_BYTES / 2, &p.tm_k, 64, grp, row0, full_qk);
                 }
+            }
+            return;
+        }
+        if (warp == tc::MMA_WARP + 2) {
+            // ---- store agent: issues the fp32 TMA reduce-add of the staged dk tile and waits for it, so that no
+            //      element-wise thread stalls on a bulk-group wait
+            if (lane == 0) {
+                for (int it = 0; it < npairs; ++it) {
+                    const int grow = b * p.T + (r * SEGP + (npairs - 1 - it)) * tc::PT;
+                    if (!umma::mbar_wait(dk_ready, it & 1, abort_flag)) break;
+#pragma unroll
+                    for (int bx = 0; bx < 4; ++bx) tma::reduce_add_box(&p.tm_dk, bx * 32, grp, grow, sStage + bx * 16384);
+                    tma::commit_group();
+                    tma::wait_group_read0();
+                    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(umma::smem_addr(stage_free)) : "memory");
+                }
+                tma::wait_group0();
             }
             return;
         }
@@ -741,7 +774,7 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_revorder_tc_kernel(con
     }
 
     // ================= warps 0..7 =================
-    RegisterSplit<72, 216>::acquire();
+    RegisterSplit<56, 224>::acquire();
     const int rb = warp & 3;
     const int row = rb * 32 + lane;
     const int ch = warp >> 2;
@@ -828,7 +861,6 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_revorder_tc_kernel(con
                 }
             }
         }
-        if (tid == 0) tma::wait_group_read0();       // the previous pair's staging tile (P / scaled do space) has been read
         umma::fence_before_sync();
         bar_work();                                  // barrier 1
         umma::fence_after_sync();
@@ -858,6 +890,7 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_revorder_tc_kernel(con
                     make_uint4(pk[c * 4], pk[c * 4 + 1], pk[c * 4 + 2], pk[c * 4 + 3]);
         }
         umma::mbar_wait(full_vd, it & 1, abort_flag);
+        if (it >= 1) umma::mbar_wait(stage_free, (it - 1) & 1, abort_flag);   // P / scaled-do space was the dk staging area
         // ---- Vs and the scaled copies of do for the reader insertions
         {
 #pragma unroll
@@ -1040,12 +1073,9 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_revorder_tc_kernel(con
         umma::fence_async_smem();
         bar_compute();
         if (tid == 0) {
-            // every compute thread has read its part of the k tile
+            // every compute thread has read its part of the k tile and staged its part of dk
             asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(umma::smem_addr(empty_k)) : "memory");
-            const int grow = b * p.T + (int)t0;
-#pragma unroll
-            for (int bx = 0; bx < 4; ++bx) tma::reduce_add_box(&p.tm_dk, bx * 32, grp, grow, sStage + bx * 16384);
-            tma::commit_group();
+            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(umma::smem_addr(dk_ready)) : "memory");
         }
         {
             bf16* gdv = p.dv + (((long)b * p.T + t0) * p.H + h) * tc::VD;
@@ -1073,7 +1103,6 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_revorder_tc_kernel(con
         umma::fence_after_sync();
         if (*abort_flag) break;
     }
-    if (tid == 0) tma::wait_group0();
     umma::fence_before_sync();
     bar_work();
 }

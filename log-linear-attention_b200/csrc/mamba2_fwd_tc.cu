@@ -81,7 +81,7 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_chunk_fwd_tc_kernel(const 
 
     if (warp >= tc::MMA_WARP) {
         // ================= third warpgroup: one warp issues the tensor-core work =================
-        RegisterSplit<40, 232>::release();
+        RegisterSplit<56, 224>::release();
         if (warp == tc::MMA_WARP + 1) {
             // ---- TMA producer: one lane streams the tiles of the segment through the stages
             if (lane == 0) {
@@ -154,7 +154,7 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_chunk_fwd_tc_kernel(const 
     }
 
     // ================= warps 0..7: loads, decay / mask / lambda, outputs, level states =================
-    RegisterSplit<40, 232>::acquire();
+    RegisterSplit<56, 224>::acquire();
     const int rb = warp & 3;                         // 32-row block of this thread's tensor-memory lane
     const int row = rb * 32 + lane;
     const int ch = warp >> 2;                        // column half handled by this thread

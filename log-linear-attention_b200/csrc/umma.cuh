@@ -30,18 +30,18 @@ __device__ __forceinline__ uint32_t tile_offset(int row, int col, int rows) {
 }
 
 // ---- shared memory matrix descriptors (SWIZZLE_128B, sm_100 version field = 1)
-__device__ __forceinline__ uint64_t desc_base() {
-    return (uint64_t(1) << 46) | (uint64_t(2) << 61);
-}
+// The upper 32 bits are the same for every operand of these kernels: stride offset 1024 bytes (8-row groups),
+// descriptor version 1 (bit 46), swizzle mode 128 B (bits 61..63 = 2).  Only the lower word differs: start
+// address >> 4 in bits 0..13 and the leading offset >> 4 in bits 16..29.  The issue loops therefore carry one
+// 32-bit register per operand and add compile-time offsets to it; the 64-bit descriptor is assembled inside
+// the instruction's asm block (fewer live registers in the issuing warp, one add per operand and step).
+constexpr uint32_t DESC_HI = (1024u >> 4) | (1u << 14) | (2u << 29);
 // K-major: 8-row groups are 1024 bytes apart; the leading-dimension field is unused with swizzle
-__device__ __forceinline__ uint64_t desc_kmajor(uint32_t saddr) {
-    return desc_base() | uint64_t((saddr >> 4) & 0x3FFF) | (uint64_t(1) << 16) | (uint64_t(1024 >> 4) << 32);
-}
+__device__ __forceinline__ uint32_t desc_lo_kmajor(uint32_t saddr) { return ((saddr >> 4) & 0x3FFFu) | (1u << 16); }
 // MN-major: consecutive 64-element blocks of the M/N index are `panel_bytes` apart (leading
 // offset), consecutive 8-row groups of the reduction index are 1024 bytes apart (stride offset)
-__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t saddr, uint32_t panel_bytes) {
-    return desc_base() | uint64_t((saddr >> 4) & 0x3FFF) | (uint64_t((panel_bytes >> 4) & 0x3FFF) << 16) |
-           (uint64_t(1024 >> 4) << 32);
+__device__ __forceinline__ uint32_t desc_lo_mnmajor(uint32_t saddr, uint32_t panel_bytes) {
+    return ((saddr >> 4) & 0x3FFFu) | (((panel_bytes >> 4) & 0x3FFFu) << 16);
 }
 
 // ---- instruction descriptor: bf16 x bf16 -> fp32, dense
@@ -50,19 +50,20 @@ __host__ __device__ constexpr uint32_t idesc_bf16(int M, int N, bool a_mn_major,
            (uint32_t(N >> 3) << 17) | (uint32_t(M >> 4) << 24);
 }
 
-__device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, bool accumulate) {
+__device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint32_t a_desc_lo, uint32_t b_desc_lo, uint32_t idesc, bool accumulate) {
     asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"((uint32_t)accumulate)
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "mov.b64 da, {%1, %5};\n\tmov.b64 db, {%2, %5};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, p;\n\t}\n"
+        ::"r"(d_tmem), "r"(a_desc_lo), "r"(b_desc_lo), "r"(idesc), "r"((uint32_t)accumulate), "r"(DESC_HI)
         : "memory");
 }
 // A operand from tensor memory (bf16 pairs packed in 32-bit columns), B from shared memory
-__device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, bool accumulate) {
+__device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_desc_lo, uint32_t idesc, bool accumulate) {
     asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}\n"
-        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"((uint32_t)accumulate)
+        "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\tsetp.ne.b32 p, %4, 0;\n\tmov.b64 db, {%2, %5};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %3, p;\n\t}\n"
+        ::"r"(d_tmem), "r"(a_tmem), "r"(b_desc_lo), "r"(idesc), "r"((uint32_t)accumulate), "r"(DESC_HI)
         : "memory");
 }
 
@@ -74,7 +75,7 @@ __device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_
 // D[128 x N] (+)= A[128 x KRED] * B[N x KRED]^T : both operands K-major tiles (rows = M / N index)
 template <int A_ROWS, int B_ROWS, int KRED>
 __device__ __forceinline__ void gemm_kk(uint32_t d_tmem, uint32_t a_saddr, uint32_t b_saddr, uint32_t idesc, bool accumulate) {
-    const uint64_t da = desc_kmajor(a_saddr), db = desc_kmajor(b_saddr);
+    const uint32_t da = desc_lo_kmajor(a_saddr), db = desc_lo_kmajor(b_saddr);
 #pragma unroll
     for (int kk = 0; kk < KRED; kk += 16) {
         const uint32_t ka = (kk >> 6) * A_ROWS * ROW_BYTES + (kk & 63) * 2;
@@ -85,7 +86,7 @@ __device__ __forceinline__ void gemm_kk(uint32_t d_tmem, uint32_t a_saddr, uint3
 // A K-major tile (rows = M index), B stored [KRED rows][N cols] (MN-major)
 template <int A_ROWS, int B_ROWS, int KRED>
 __device__ __forceinline__ void gemm_km(uint32_t d_tmem, uint32_t a_saddr, uint32_t b_saddr, uint32_t idesc, bool accumulate) {
-    const uint64_t da = desc_kmajor(a_saddr), db = desc_mnmajor(b_saddr, B_ROWS * ROW_BYTES);
+    const uint32_t da = desc_lo_kmajor(a_saddr), db = desc_lo_mnmajor(b_saddr, B_ROWS * ROW_BYTES);
 #pragma unroll
     for (int kk = 0; kk < KRED; kk += 16) {
         const uint32_t ka = (kk >> 6) * A_ROWS * ROW_BYTES + (kk & 63) * 2;
@@ -95,10 +96,54 @@ __device__ __forceinline__ void gemm_km(uint32_t d_tmem, uint32_t a_saddr, uint3
 // A stored [KRED rows][M cols], B stored [KRED rows][N cols] (both MN-major): D = A^T B
 template <int A_ROWS, int B_ROWS, int KRED>
 __device__ __forceinline__ void gemm_mm(uint32_t d_tmem, uint32_t a_saddr, uint32_t b_saddr, uint32_t idesc, bool accumulate) {
-    const uint64_t da = desc_mnmajor(a_saddr, A_ROWS * ROW_BYTES), db = desc_mnmajor(b_saddr, B_ROWS * ROW_BYTES);
+    const uint32_t da = desc_lo_mnmajor(a_saddr, A_ROWS * ROW_BYTES), db = desc_lo_mnmajor(b_saddr, B_ROWS * ROW_BYTES);
 #pragma unroll
     for (int kk = 0; kk < KRED; kk += 16) {
         mma_ss(d_tmem, da + ((kk * ROW_BYTES) >> 4), db + ((kk * ROW_BYTES) >> 4), idesc, accumulate || kk > 0);
+    }
+}
+// ---- 64-bit descriptor variants.  m2_hi_bwd_tc_kernel issues through these: with the 32-bit assembly above
+//      that kernel (and only that one) returned wrong reader gradients for the first 64 rows of a segment's
+//      first pair, deterministically, although the same loops pass the tile-product self-test at low and high
+//      shared-memory addresses; the cause has not been found, so the kernel stays on the form it is verified with.
+__device__ __forceinline__ uint64_t desc64_kmajor(uint32_t saddr) {
+    return (uint64_t(DESC_HI) << 32) | uint64_t(desc_lo_kmajor(saddr));
+}
+__device__ __forceinline__ uint64_t desc64_mnmajor(uint32_t saddr, uint32_t panel_bytes) {
+    return (uint64_t(DESC_HI) << 32) | uint64_t(desc_lo_mnmajor(saddr, panel_bytes));
+}
+__device__ __forceinline__ void mma_ss64(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, bool accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"((uint32_t)accumulate)
+        : "memory");
+}
+template <int A_ROWS, int B_ROWS, int KRED>
+__device__ __forceinline__ void gemm_kk64(uint32_t d_tmem, uint32_t a_saddr, uint32_t b_saddr, uint32_t idesc, bool accumulate) {
+    const uint64_t da = desc64_kmajor(a_saddr), db = desc64_kmajor(b_saddr);
+#pragma unroll
+    for (int kk = 0; kk < KRED; kk += 16) {
+        const uint32_t ka = (kk >> 6) * A_ROWS * ROW_BYTES + (kk & 63) * 2;
+        const uint32_t kb = (kk >> 6) * B_ROWS * ROW_BYTES + (kk & 63) * 2;
+        mma_ss64(d_tmem, da + (ka >> 4), db + (kb >> 4), idesc, accumulate || kk > 0);
+    }
+}
+template <int A_ROWS, int B_ROWS, int KRED>
+__device__ __forceinline__ void gemm_km64(uint32_t d_tmem, uint32_t a_saddr, uint32_t b_saddr, uint32_t idesc, bool accumulate) {
+    const uint64_t da = desc64_kmajor(a_saddr), db = desc64_mnmajor(b_saddr, B_ROWS * ROW_BYTES);
+#pragma unroll
+    for (int kk = 0; kk < KRED; kk += 16) {
+        const uint32_t ka = (kk >> 6) * A_ROWS * ROW_BYTES + (kk & 63) * 2;
+        mma_ss64(d_tmem, da + (ka >> 4), db + ((kk * ROW_BYTES) >> 4), idesc, accumulate || kk > 0);
+    }
+}
+template <int A_ROWS, int B_ROWS, int KRED>
+__device__ __forceinline__ void gemm_mm64(uint32_t d_tmem, uint32_t a_saddr, uint32_t b_saddr, uint32_t idesc, bool accumulate) {
+    const uint64_t da = desc64_mnmajor(a_saddr, A_ROWS * ROW_BYTES), db = desc64_mnmajor(b_saddr, B_ROWS * ROW_BYTES);
+#pragma unroll
+    for (int kk = 0; kk < KRED; kk += 16) {
+        mma_ss64(d_tmem, da + ((kk * ROW_BYTES) >> 4), db + ((kk * ROW_BYTES) >> 4), idesc, accumulate || kk > 0);
     }
 }
 // run-time sized variants (self-test)
@@ -107,22 +152,22 @@ __device__ __forceinline__ void gemm_kk(uint32_t d_tmem, uint32_t a_saddr, int a
     for (int kk = 0; kk < kred; kk += 16) {
         const uint32_t ka = (kk >> 6) * a_rows * ROW_BYTES + (kk & 63) * 2;
         const uint32_t kb = (kk >> 6) * b_rows * ROW_BYTES + (kk & 63) * 2;
-        mma_ss(d_tmem, desc_kmajor(a_saddr + ka), desc_kmajor(b_saddr + kb), idesc, accumulate || kk > 0);
+        mma_ss(d_tmem, desc_lo_kmajor(a_saddr + ka), desc_lo_kmajor(b_saddr + kb), idesc, accumulate || kk > 0);
     }
 }
 __device__ __forceinline__ void gemm_km(uint32_t d_tmem, uint32_t a_saddr, int a_rows, uint32_t b_saddr, int b_rows,
                                         int kred, uint32_t idesc, bool accumulate) {
     for (int kk = 0; kk < kred; kk += 16) {
         const uint32_t ka = (kk >> 6) * a_rows * ROW_BYTES + (kk & 63) * 2;
-        mma_ss(d_tmem, desc_kmajor(a_saddr + ka), desc_mnmajor(b_saddr + kk * ROW_BYTES, b_rows * ROW_BYTES), idesc,
+        mma_ss(d_tmem, desc_lo_kmajor(a_saddr + ka), desc_lo_mnmajor(b_saddr + kk * ROW_BYTES, b_rows * ROW_BYTES), idesc,
                accumulate || kk > 0);
     }
 }
 __device__ __forceinline__ void gemm_mm(uint32_t d_tmem, uint32_t a_saddr, int a_rows, uint32_t b_saddr, int b_rows,
                                         int kred, uint32_t idesc, bool accumulate) {
     for (int kk = 0; kk < kred; kk += 16) {
-        mma_ss(d_tmem, desc_mnmajor(a_saddr + kk * ROW_BYTES, a_rows * ROW_BYTES),
-               desc_mnmajor(b_saddr + kk * ROW_BYTES, b_rows * ROW_BYTES), idesc, accumulate || kk > 0);
+        mma_ss(d_tmem, desc_lo_mnmajor(a_saddr + kk * ROW_BYTES, a_rows * ROW_BYTES),
+               desc_lo_mnmajor(b_saddr + kk * ROW_BYTES, b_rows * ROW_BYTES), idesc, accumulate || kk > 0);
     }
 }
 

@@ -11,18 +11,21 @@ namespace llattn {
 // mode 1: A [128][kred], B [kred][N]      -> D = A B     (A K-major, B MN-major)
 // mode 2: A [kred][128], B [kred][N]      -> D = A^T B   (both MN-major)
 __global__ void __launch_bounds__(128, 1) umma_selftest_kernel(const bf16* __restrict__ A, const bf16* __restrict__ B,
-                                                               float* __restrict__ D, int N, int kred, int mode,
+                                                               float* __restrict__ D, int N, int kred, int tmode,
                                                                int* __restrict__ err) {
+    const int mode = tmode >= 10 ? tmode - 10 + 100 : tmode;      // 100.. : no run-time shaped issue below
+    const int lmode = tmode % 10;                                  // operand layout combination
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    unsigned char* sA = smem;                 // up to 128 x 128 bf16 = 32 KB
-    unsigned char* sB = smem + 32768;         // up to 128 x 128 bf16
+    // modes 10..12 place the tiles high in shared memory (the address range that the kernels' later tiles use)
+    unsigned char* sA = smem + (tmode >= 10 ? 131072 : 0);              // up to 128 x 128 bf16 = 32 KB
+    unsigned char* sB = smem + (tmode >= 10 ? 131072 + 49152 : 32768);  // up to 128 x 128 bf16
     __shared__ uint64_t bar;
     __shared__ uint32_t tmem_slot;
     const int tid = threadIdx.x, warp = tid >> 5;
 
-    const int a_rows = (mode == 2) ? kred : 128, a_cols = (mode == 2) ? 128 : kred;
-    const int b_rows = (mode == 0) ? N : kred, b_cols = (mode == 0) ? kred : N;
+    const int a_rows = (lmode == 2) ? kred : 128, a_cols = (lmode == 2) ? 128 : kred;
+    const int b_rows = (lmode == 0) ? N : kred, b_cols = (lmode == 0) ? kred : N;
     for (int e = tid; e < a_rows * a_cols; e += 128) {
         const int r = e / a_cols, c = e % a_cols;
         *reinterpret_cast<bf16*>(sA + umma::tile_offset(r, c, a_rows)) = A[e];
@@ -43,9 +46,21 @@ __global__ void __launch_bounds__(128, 1) umma_selftest_kernel(const bf16* __res
     const uint32_t tbase = tmem_slot;
     if (tid == 0) {
         const uint32_t a = umma::smem_addr(sA), b = umma::smem_addr(sB);
+        // mode + 10 selects the compile-time shaped issue loops that the kernels use
         if (mode == 0) umma::gemm_kk(tbase, a, a_rows, b, b_rows, kred, umma::idesc_bf16(128, N, false, false), false);
         if (mode == 1) umma::gemm_km(tbase, a, a_rows, b, b_rows, kred, umma::idesc_bf16(128, N, false, true), false);
         if (mode == 2) umma::gemm_mm(tbase, a, a_rows, b, b_rows, kred, umma::idesc_bf16(128, N, true, true), false);
+#define LLATTN_ST_CASE(NN, KK)                                                                                              \
+        if (N == NN && kred == KK) {                                                                                        \
+            if (tmode == 10) umma::gemm_kk<128, NN, KK>(tbase, a, b, umma::idesc_bf16(128, NN, false, false), false);       \
+            if (tmode == 11) umma::gemm_km<128, KK, KK>(tbase, a, b, umma::idesc_bf16(128, NN, false, true), false);        \
+            if (tmode == 12) umma::gemm_mm<KK, KK, KK>(tbase, a, b, umma::idesc_bf16(128, NN, true, true), false);          \
+        }
+        LLATTN_ST_CASE(64, 64)
+        LLATTN_ST_CASE(64, 128)
+        LLATTN_ST_CASE(128, 64)
+        LLATTN_ST_CASE(128, 128)
+#undef LLATTN_ST_CASE
         umma::commit(&bar);
     }
     const bool ok = umma::mbar_wait(&bar, 0);
@@ -157,8 +172,9 @@ extern "C" int llattn_selftest_umma_cycles(int N, int kred, int mode, int reps, 
 extern "C" int llattn_selftest_umma(const void* A, const void* B, float* D, int N, int kred, int mode, int* err_flag,
                                     void* stream) {
     if (!A || !B || !D || !err_flag) return LLATTN_ERR_NULL;
-    if (!(N == 64 || N == 128) || !(kred == 64 || kred == 128) || mode < 0 || mode > 2) return LLATTN_ERR_UNSUPPORTED_SHAPE;
-    const size_t sm = 65536 + 1024;
+    if (!(N == 64 || N == 128) || !(kred == 64 || kred == 128) || !((mode >= 0 && mode <= 2) || (mode >= 10 && mode <= 12)))
+        return LLATTN_ERR_UNSUPPORTED_SHAPE;
+    const size_t sm = (mode >= 10 ? 131072 + 49152 + 32768 : 65536) + 1024;
     cudaError_t e = cudaFuncSetAttribute(llattn::umma_selftest_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
     if (e != cudaSuccess) return (int)e;
     llattn::umma_selftest_kernel<<<1, 128, sm, (cudaStream_t)stream>>>((const llattn::bf16*)A, (const llattn::bf16*)B, D, N, kred,

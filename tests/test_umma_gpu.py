@@ -6,20 +6,21 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("mode", [0, 1, 2])
+@pytest.mark.parametrize("mode", [0, 1, 2, 10, 11, 12])
 @pytest.mark.parametrize("N,kred", [(128, 128), (64, 128), (128, 64), (64, 64)])
 def test_umma_tile_product(mode, N, kred):
     from hattention_b200 import _lib
     lib = _lib.lib()
     dev = torch.device("cuda:0")
     gen = torch.Generator().manual_seed(mode * 10 + N + kred)
+    issue_mode, mode = mode, mode % 10        # 10..12: the compile-time shaped issue loops of the kernels
     a_shape = (kred, 128) if mode == 2 else (128, kred)
     b_shape = (N, kred) if mode == 0 else (kred, N)
     A = torch.randn(a_shape, generator=gen).bfloat16().to(dev)
     B = torch.randn(b_shape, generator=gen).bfloat16().to(dev)
     D = torch.zeros(128, N, device=dev)
     err = torch.zeros(1, dtype=torch.int32, device=dev)
-    rc = lib.llattn_selftest_umma(A.data_ptr(), B.data_ptr(), D.data_ptr(), N, kred, mode, err.data_ptr(),
+    rc = lib.llattn_selftest_umma(A.data_ptr(), B.data_ptr(), D.data_ptr(), N, kred, issue_mode, err.data_ptr(),
                                   torch.cuda.current_stream().cuda_stream)
     assert rc == 0
     torch.cuda.synchronize()
