@@ -238,7 +238,7 @@ def run_gdn(args, rank, world, local):
         "n_gpus": 1, "steps": Kb, "warmup": W, "ms_per_step": ms_fb, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": f"log-linear Gated DeltaNet fwd+bwd, B={B} T=8192 H=16 Dk=Dv=128 chunk=64 L=14",
-                   "note": "l2norm / scale of q, k and their backward are torch elementwise ops around the CUDA kernels"},
+                   "note": "through chunk_h_gated_delta_rule: l2norm kernels, forward, backward; lambda / scale and dtype casts are torch ops"},
         "forward_only": {"ms": ms_fwd, "tokens_per_s": B * T / (ms_fwd * 1e-3)},
         "roofline": {"bound": "tensor", "achieved": flops_fwd / (ms_fwd * 1e-3) / 1e12, "peak": pk["tflops"], "unit": "TFLOP/s",
                      "frac": flops_fwd / (ms_fwd * 1e-3) / 1e12 / pk["tflops"], "traffic": None, "peak_source": pk["source"],
