@@ -179,6 +179,22 @@ int llattn_gdn_bwd(const void* q, const void* k, const void* v, const void* beta
                    float* dlambda, void* workspace, size_t workspace_bytes,
                    int B, int T, int H, int K, int V, int L, void* stream);
 
+/* The same forward and backward with the forward's intermediates kept between the two calls, so that
+ * the backward does not recompute them (the reference recomputes w, u and the level states in its
+ * backward, hattention/chunkwise_hgdn.py:820-870; keeping them trades memory for about a fifth of the
+ * step).  llattn_gdn_fwd_keep is llattn_gdn_fwd with a larger workspace that, on return, holds the
+ * chunk matrices and every chunk's level states; the caller leaves it untouched and hands it to
+ * llattn_gdn_bwd_kept as fwd_workspace.  Results are those of llattn_gdn_fwd / llattn_gdn_bwd. */
+size_t llattn_gdn_fwd_keep_workspace_bytes(int B, int T, int H, int K, int V, int L);
+int llattn_gdn_fwd_keep(const void* q, const void* k, const void* v, const void* beta, const float* g, const void* lambda,
+                        void* o, float* g_cum, void* Aw, void* Au, void* workspace, size_t workspace_bytes,
+                        int B, int T, int H, int K, int V, int L, void* stream);
+size_t llattn_gdn_bwd_kept_workspace_bytes(int B, int T, int H, int K, int V, int L);
+int llattn_gdn_bwd_kept(const void* q, const void* k, const void* v, const void* beta, const float* g_cum, const void* lambda,
+                        const void* Aw, const void* Au, const void* d_o, float* dq, float* dk, float* dv, float* dbeta,
+                        float* dg, float* dlambda, const void* fwd_workspace, size_t fwd_workspace_bytes, void* workspace,
+                        size_t workspace_bytes, int B, int T, int H, int K, int V, int L, void* stream);
+
 /* Row-wise L2 normalisation of q / k and its backward, as applied around the Gated DeltaNet drivers
  * when use_qk_l2norm_in_kernel is set.  Replace fla.modules.l2norm.l2norm_fwd / l2norm_bwd with the
  * scale folded in (hattention/kernel.py:20-29: l2norm_and_scale_fwd / l2norm_and_scale_bwd).

@@ -211,21 +211,24 @@ static int gdn_check(int B, int T, int H, int K, int V, int L) {
     return 0;
 }
 
-static size_t gdn_setup(llattn::GdnParams& p, void* ws, bool bwd = false) {
+// workspace parts: chunk matrices (kd, wd, qd, u), level states hs, adjoint level states dhs
+enum { GDN_WS_CHUNK = 1, GDN_WS_HS = 2, GDN_WS_DHS = 4 };
+static size_t gdn_setup(llattn::GdnParams& p, void* ws, int parts, size_t start = 0) {
     p.NT = p.T / 64;
     p.NLEV = ceil_log2i(p.NT);
     Carver c(ws);
+    c.off = start;
     const size_t n = (size_t)p.B * p.T * p.H;
-    p.kd = c.take<__nv_bfloat16>(n * p.K);
-    p.wd = c.take<__nv_bfloat16>(n * p.K);
-    p.qd = c.take<__nv_bfloat16>(n * p.K);
-    p.u = c.take<__nv_bfloat16>(n * p.V);
-    if (bwd) {
-        // level states and their adjoints: one K x 32 tile per (batch, head, 32-column slice, chunk, level)
-        const size_t tiles = (size_t)p.B * p.H * (p.V / llattn::GDN_VS) * p.NT * (p.NLEV > 0 ? p.NLEV : 1);
-        p.hs = c.take<__nv_bfloat16>(tiles * p.K * llattn::GDN_VS);
-        p.dhs = c.take<__nv_bfloat16>(tiles * p.K * llattn::GDN_VS);
+    if (parts & GDN_WS_CHUNK) {
+        p.kd = c.take<__nv_bfloat16>(n * p.K);
+        p.wd = c.take<__nv_bfloat16>(n * p.K);
+        p.qd = c.take<__nv_bfloat16>(n * p.K);
+        p.u = c.take<__nv_bfloat16>(n * p.V);
     }
+    // level states and their adjoints: one K x 32 tile per (batch, head, 32-column slice, chunk, level)
+    const size_t tiles = (size_t)p.B * p.H * (p.V / llattn::GDN_VS) * p.NT * (p.NLEV > 0 ? p.NLEV : 1);
+    if (parts & GDN_WS_HS) p.hs = c.take<__nv_bfloat16>(tiles * p.K * llattn::GDN_VS);
+    if (parts & GDN_WS_DHS) p.dhs = c.take<__nv_bfloat16>(tiles * p.K * llattn::GDN_VS);
     return c.off;
 }
 
@@ -233,31 +236,55 @@ size_t llattn_gdn_fwd_workspace_bytes(int B, int T, int H, int K, int V, int L) 
     if (gdn_check(B, T, H, K, V, L) != 0) return 0;
     llattn::GdnParams p = {};
     p.B = B; p.T = T; p.H = H; p.K = K; p.V = V; p.L = L;
-    return gdn_setup(p, nullptr);
+    return gdn_setup(p, nullptr, GDN_WS_CHUNK);
 }
+
+size_t llattn_gdn_fwd_keep_workspace_bytes(int B, int T, int H, int K, int V, int L) {
+    if (gdn_check(B, T, H, K, V, L) != 0) return 0;
+    llattn::GdnParams p = {};
+    p.B = B; p.T = T; p.H = H; p.K = K; p.V = V; p.L = L;
+    return gdn_setup(p, nullptr, GDN_WS_CHUNK | GDN_WS_HS);
+}
+
+static int gdn_fwd_impl(const void* q, const void* k, const void* v, const void* beta, const float* g, const void* lambda,
+                        void* o, float* g_cum, void* Aw, void* Au, void* workspace, size_t workspace_bytes,
+                        int B, int T, int H, int K, int V, int L, void* stream, bool keep);
 
 int llattn_gdn_fwd(const void* q, const void* k, const void* v, const void* beta, const float* g, const void* lambda,
                    void* o, float* g_cum, void* Aw, void* Au, void* workspace, size_t workspace_bytes,
                    int B, int T, int H, int K, int V, int L, void* stream) {
+    return gdn_fwd_impl(q, k, v, beta, g, lambda, o, g_cum, Aw, Au, workspace, workspace_bytes, B, T, H, K, V, L, stream, false);
+}
+
+int llattn_gdn_fwd_keep(const void* q, const void* k, const void* v, const void* beta, const float* g, const void* lambda,
+                        void* o, float* g_cum, void* Aw, void* Au, void* workspace, size_t workspace_bytes,
+                        int B, int T, int H, int K, int V, int L, void* stream) {
+    return gdn_fwd_impl(q, k, v, beta, g, lambda, o, g_cum, Aw, Au, workspace, workspace_bytes, B, T, H, K, V, L, stream, true);
+}
+
+static int gdn_fwd_impl(const void* q, const void* k, const void* v, const void* beta, const float* g, const void* lambda,
+                        void* o, float* g_cum, void* Aw, void* Au, void* workspace, size_t workspace_bytes,
+                        int B, int T, int H, int K, int V, int L, void* stream, bool keep) {
     int rc = gdn_check(B, T, H, K, V, L);
     if (rc != 0) return rc;
     if (!q || !k || !v || !beta || !g || !lambda || !o || !g_cum || !Aw || !Au) return LLATTN_ERR_NULL;
     llattn::GdnParams p = {};
     p.B = B; p.T = T; p.H = H; p.K = K; p.V = V; p.L = L;
-    const size_t need = gdn_setup(p, nullptr);
+    const int parts = keep ? (GDN_WS_CHUNK | GDN_WS_HS) : GDN_WS_CHUNK;
+    const size_t need = gdn_setup(p, nullptr, parts);
     if (!workspace || workspace_bytes < need || ((uintptr_t)workspace & 255)) return LLATTN_ERR_WORKSPACE;
-    gdn_setup(p, workspace);
+    gdn_setup(p, workspace, parts);
     p.q = (const __nv_bfloat16*)q; p.k = (const __nv_bfloat16*)k; p.v = (const __nv_bfloat16*)v;
     p.beta = (const __nv_bfloat16*)beta; p.g = g; p.l = (const __nv_bfloat16*)lambda;
     p.o = (__nv_bfloat16*)o; p.g_cum = g_cum; p.Aw = (__nv_bfloat16*)Aw; p.Au = (__nv_bfloat16*)Au;
-    return llattn::gdn_fwd_dispatch(p, (cudaStream_t)stream);
+    return keep ? llattn::gdn_fwd_keep_dispatch(p, (cudaStream_t)stream) : llattn::gdn_fwd_dispatch(p, (cudaStream_t)stream);
 }
 
 size_t llattn_gdn_bwd_levels_workspace_bytes(int B, int T, int H, int K, int V, int L) {
     if (gdn_check(B, T, H, K, V, L) != 0) return 0;
     llattn::GdnParams p = {};
     p.B = B; p.T = T; p.H = H; p.K = K; p.V = V; p.L = L;
-    return gdn_setup(p, nullptr, true);
+    return gdn_setup(p, nullptr, GDN_WS_CHUNK | GDN_WS_HS | GDN_WS_DHS);
 }
 
 int llattn_gdn_bwd_levels(const void* q, const void* k, const void* v, const void* beta, const float* g_cum, const void* lambda,
@@ -270,9 +297,9 @@ int llattn_gdn_bwd_levels(const void* q, const void* k, const void* v, const voi
         return LLATTN_ERR_NULL;
     llattn::GdnParams p = {};
     p.B = B; p.T = T; p.H = H; p.K = K; p.V = V; p.L = L;
-    const size_t need = gdn_setup(p, nullptr, true);
+    const size_t need = gdn_setup(p, nullptr, GDN_WS_CHUNK | GDN_WS_HS | GDN_WS_DHS);
     if (!workspace || workspace_bytes < need || ((uintptr_t)workspace & 255)) return LLATTN_ERR_WORKSPACE;
-    gdn_setup(p, workspace, true);
+    gdn_setup(p, workspace, GDN_WS_CHUNK | GDN_WS_HS | GDN_WS_DHS);
     p.q = (const __nv_bfloat16*)q; p.k = (const __nv_bfloat16*)k; p.v = (const __nv_bfloat16*)v;
     p.beta = (const __nv_bfloat16*)beta; p.g = nullptr; p.l = (const __nv_bfloat16*)lambda;
     p.g_cum = const_cast<float*>(g_cum);
@@ -285,8 +312,9 @@ int llattn_gdn_bwd_levels(const void* q, const void* k, const void* v, const voi
     return llattn::gdn_bwd_levels_dispatch(p, st);
 }
 
-static size_t gdn_bwd_setup(llattn::GdnParams& p, void* ws) {
-    const size_t base = gdn_setup(p, ws, true);
+static size_t gdn_bwd_setup(llattn::GdnParams& p, void* ws, bool kept = false) {
+    // with the forward call's workspace kept, only the adjoint states and the intermediate gradients are needed
+    const size_t base = gdn_setup(p, ws, kept ? GDN_WS_DHS : (GDN_WS_CHUNK | GDN_WS_HS | GDN_WS_DHS));
     Carver c(ws);
     c.off = base;
     const size_t n = (size_t)p.B * p.T * p.H;
@@ -305,19 +333,26 @@ size_t llattn_gdn_bwd_workspace_bytes(int B, int T, int H, int K, int V, int L) 
     return gdn_bwd_setup(p, nullptr);
 }
 
-int llattn_gdn_bwd(const void* q, const void* k, const void* v, const void* beta, const float* g_cum, const void* lambda,
-                   const void* Aw, const void* Au, const void* d_o, float* dq, float* dk, float* dv, float* dbeta, float* dg,
-                   float* dlambda, void* workspace, size_t workspace_bytes,
-                   int B, int T, int H, int K, int V, int L, void* stream) {
+static int gdn_bwd_impl(const void* q, const void* k, const void* v, const void* beta, const float* g_cum, const void* lambda,
+                        const void* Aw, const void* Au, const void* d_o, float* dq, float* dk, float* dv, float* dbeta, float* dg,
+                        float* dlambda, const void* fwd_workspace, size_t fwd_workspace_bytes, void* workspace,
+                        size_t workspace_bytes, int B, int T, int H, int K, int V, int L, void* stream) {
     int rc = gdn_check(B, T, H, K, V, L);
     if (rc != 0) return rc;
     if (!q || !k || !v || !beta || !g_cum || !lambda || !Aw || !Au || !d_o || !dq || !dk || !dv || !dbeta || !dg || !dlambda)
         return LLATTN_ERR_NULL;
     llattn::GdnParams p = {};
     p.B = B; p.T = T; p.H = H; p.K = K; p.V = V; p.L = L;
-    const size_t need = gdn_bwd_setup(p, nullptr);
+    const bool kept = fwd_workspace != nullptr;
+    if (kept) {
+        // chunk matrices and level states as llattn_gdn_fwd_keep left them
+        const size_t fneed = gdn_setup(p, nullptr, GDN_WS_CHUNK | GDN_WS_HS);
+        if (fwd_workspace_bytes < fneed || ((uintptr_t)fwd_workspace & 255)) return LLATTN_ERR_WORKSPACE;
+        gdn_setup(p, const_cast<void*>(fwd_workspace), GDN_WS_CHUNK | GDN_WS_HS);
+    }
+    const size_t need = gdn_bwd_setup(p, nullptr, kept);
     if (!workspace || workspace_bytes < need || ((uintptr_t)workspace & 255)) return LLATTN_ERR_WORKSPACE;
-    gdn_bwd_setup(p, workspace);
+    gdn_bwd_setup(p, workspace, kept);
     p.q = (const __nv_bfloat16*)q; p.k = (const __nv_bfloat16*)k; p.v = (const __nv_bfloat16*)v;
     p.beta = (const __nv_bfloat16*)beta; p.g = nullptr; p.l = (const __nv_bfloat16*)lambda;
     p.g_cum = const_cast<float*>(g_cum);
@@ -327,10 +362,34 @@ int llattn_gdn_bwd(const void* q, const void* k, const void* v, const void* beta
     cudaStream_t st = (cudaStream_t)stream;
     cudaError_t e = cudaMemsetAsync(dlambda, 0, (size_t)B * T * H * L * sizeof(float), st);
     if (e != cudaSuccess) return (int)e;
-    if ((rc = llattn::gdn_recompute_dispatch(p, st)) != 0) return rc;
+    if (!kept && (rc = llattn::gdn_recompute_dispatch(p, st)) != 0) return rc;
     if ((rc = llattn::gdn_bwd_scan_dispatch(p, st)) != 0) return rc;
     if ((rc = llattn::gdn_bwd_levels_dispatch(p, st)) != 0) return rc;
     return llattn::gdn_bwd_chunk_dispatch(p, st);
+}
+
+int llattn_gdn_bwd(const void* q, const void* k, const void* v, const void* beta, const float* g_cum, const void* lambda,
+                   const void* Aw, const void* Au, const void* d_o, float* dq, float* dk, float* dv, float* dbeta, float* dg,
+                   float* dlambda, void* workspace, size_t workspace_bytes,
+                   int B, int T, int H, int K, int V, int L, void* stream) {
+    return gdn_bwd_impl(q, k, v, beta, g_cum, lambda, Aw, Au, d_o, dq, dk, dv, dbeta, dg, dlambda, nullptr, 0, workspace,
+                        workspace_bytes, B, T, H, K, V, L, stream);
+}
+
+size_t llattn_gdn_bwd_kept_workspace_bytes(int B, int T, int H, int K, int V, int L) {
+    if (gdn_check(B, T, H, K, V, L) != 0) return 0;
+    llattn::GdnParams p = {};
+    p.B = B; p.T = T; p.H = H; p.K = K; p.V = V; p.L = L;
+    return gdn_bwd_setup(p, nullptr, true);
+}
+
+int llattn_gdn_bwd_kept(const void* q, const void* k, const void* v, const void* beta, const float* g_cum, const void* lambda,
+                        const void* Aw, const void* Au, const void* d_o, float* dq, float* dk, float* dv, float* dbeta,
+                        float* dg, float* dlambda, const void* fwd_workspace, size_t fwd_workspace_bytes, void* workspace,
+                        size_t workspace_bytes, int B, int T, int H, int K, int V, int L, void* stream) {
+    if (!fwd_workspace) return LLATTN_ERR_NULL;
+    return gdn_bwd_impl(q, k, v, beta, g_cum, lambda, Aw, Au, d_o, dq, dk, dv, dbeta, dg, dlambda, fwd_workspace,
+                        fwd_workspace_bytes, workspace, workspace_bytes, B, T, H, K, V, L, stream);
 }
 
 }  // extern "C"

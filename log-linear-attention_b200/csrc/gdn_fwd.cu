@@ -316,9 +316,10 @@ struct ScanSmem {
     static constexpr size_t total = gl_off + 16;
 };
 
-// SAVE = true (the backward's recomputation) also writes, for every chunk, the bf16 level states
-// that the chunk reads: hs[((b*H + h)*nvs + vs)*NT + c][level][KD][32].
-template <int KD, bool SAVE>
+// SAVE = true also writes, for every chunk, the bf16 level states that the chunk reads:
+// hs[((b*H + h)*nvs + vs)*NT + c][level][KD][32] (the backward's recomputation, or a forward whose caller
+// keeps the workspace for the backward); OUT = false skips the output (recomputation only).
+template <int KD, bool SAVE, bool OUT>
 __global__ void __launch_bounds__(256, 1) gdn_scan_kernel(const GdnParams p) {
     using SM = ScanSmem<KD>;
     constexpr int LDK = SM::LDK, LDS = SM::LDS;
@@ -415,7 +416,7 @@ __global__ void __launch_bounds__(256, 1) gdn_scan_kernel(const GdnParams p) {
         // the intra-chunk part of the output rows (written by the preparation kernel) is fetched before the
         // products so that its latency is off the chunk-to-chunk chain
         uint32_t o_in[4][2];
-        if (!SAVE && warp < 4) {
+        if (OUT && warp < 4) {
             const long rb = ((long)b * p.T + (long)c * CH) * p.H + h;
 #pragma unroll
             for (int nt = 0; nt < 4; ++nt)
@@ -472,7 +473,7 @@ __global__ void __launch_bounds__(256, 1) gdn_scan_kernel(const GdnParams p) {
                     *reinterpret_cast<uint32_t*>(sVh + i * LDS + nt * 8 + lc2) =
                         pack_bf16(__bfloat162float(x.x) - zsum[0][nt][hh * 2], __bfloat162float(x.y) - zsum[0][nt][hh * 2 + 1]);
                 }
-        } else if (!SAVE) {
+        } else if (OUT) {
             // output rows: add the intra-chunk part and store
             const long rowbase = ((long)b * p.T + (long)c * CH) * p.H + h;
 #pragma unroll
@@ -549,7 +550,7 @@ __global__ void __launch_bounds__(256, 1) gdn_scan_kernel(const GdnParams p) {
 // ------------------------------------------------------------------------------------------
 // host side
 // ------------------------------------------------------------------------------------------
-template <int KD, int VD, bool BWD>
+template <int KD, int VD, bool BWD, bool KEEP = false>
 static int launch_gdn_fwd(const GdnParams& p, cudaStream_t stream) {
     cudaError_t e;
     {
@@ -559,7 +560,7 @@ static int launch_gdn_fwd(const GdnParams& p, cudaStream_t stream) {
         kern<<<p.B * p.NT * p.H, 256, sm, stream>>>(p);
     }
     {
-        auto kern = gdn_scan_kernel<KD, BWD>;
+        auto kern = gdn_scan_kernel<KD, BWD || KEEP, !BWD>;
         const size_t sm = ScanSmem<KD>::total;
         if ((e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm)) != cudaSuccess) return (int)e;
         kern<<<p.B * p.H * (p.V / GDN_VS), 256, sm, stream>>>(p);
@@ -570,6 +571,13 @@ static int launch_gdn_fwd(const GdnParams& p, cudaStream_t stream) {
 int gdn_fwd_dispatch(const GdnParams& p, cudaStream_t stream) {
     if (p.K == 128 && p.V == 128) return launch_gdn_fwd<128, 128, false>(p, stream);
     if (p.K == 128 && p.V == 64) return launch_gdn_fwd<128, 64, false>(p, stream);
+    return LLATTN_ERR_UNSUPPORTED_SHAPE;
+}
+
+// forward that also leaves the level states (and the chunk matrices) in the workspace for the backward
+int gdn_fwd_keep_dispatch(const GdnParams& p, cudaStream_t stream) {
+    if (p.K == 128 && p.V == 128) return launch_gdn_fwd<128, 128, false, true>(p, stream);
+    if (p.K == 128 && p.V == 64) return launch_gdn_fwd<128, 64, false, true>(p, stream);
     return LLATTN_ERR_UNSUPPORTED_SHAPE;
 }
 

@@ -48,6 +48,7 @@ struct GdnParams {
 };
 
 int gdn_fwd_dispatch(const GdnParams& p, cudaStream_t stream);
+int gdn_fwd_keep_dispatch(const GdnParams& p, cudaStream_t stream);
 int gdn_recompute_dispatch(const GdnParams& p, cudaStream_t stream);
 int gdn_bwd_scan_dispatch(const GdnParams& p, cudaStream_t stream);      // adjoint level states, d_u
 int gdn_bwd_levels_dispatch(const GdnParams& p, cudaStream_t stream);    // d_qd, d_wd, d_kd, d_gl, dl (inter-chunk levels)

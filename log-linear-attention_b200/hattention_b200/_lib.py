@@ -71,6 +71,14 @@ def lib():
     L.llattn_gdn_bwd_workspace_bytes.argtypes = [ctypes.c_int] * 6
     L.llattn_gdn_bwd.restype = ctypes.c_int
     L.llattn_gdn_bwd.argtypes = [_P] * 15 + [_P, ctypes.c_size_t] + [ctypes.c_int] * 6 + [_P]
+    L.llattn_gdn_fwd_keep_workspace_bytes.restype = ctypes.c_size_t
+    L.llattn_gdn_fwd_keep_workspace_bytes.argtypes = [ctypes.c_int] * 6
+    L.llattn_gdn_fwd_keep.restype = ctypes.c_int
+    L.llattn_gdn_fwd_keep.argtypes = [_P] * 10 + [_P, ctypes.c_size_t] + [ctypes.c_int] * 6 + [_P]
+    L.llattn_gdn_bwd_kept_workspace_bytes.restype = ctypes.c_size_t
+    L.llattn_gdn_bwd_kept_workspace_bytes.argtypes = [ctypes.c_int] * 6
+    L.llattn_gdn_bwd_kept.restype = ctypes.c_int
+    L.llattn_gdn_bwd_kept.argtypes = [_P] * 15 + [_P, ctypes.c_size_t, _P, ctypes.c_size_t] + [ctypes.c_int] * 6 + [_P]
     L.llattn_selftest_umma_cycles.restype = ctypes.c_int
     L.llattn_selftest_umma_cycles.argtypes = [ctypes.c_int] * 5 + [_P, _P, _P]
     L.llattn_set_tensor_core_path.restype = None

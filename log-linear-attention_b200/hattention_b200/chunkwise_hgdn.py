@@ -85,8 +85,11 @@ def chunkwise_fwd(
     htype: HType,
     chunk_size: int,
     output_final_state: bool,
+    keep_workspace: Optional[list] = None,
 ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, Optional[torch.Tensor]]:
-    """Returns (g_cum, o, Aw, Au, None) like the reference driver (chunkwise_hgdn.py:566-788)."""
+    """Returns (g_cum, o, Aw, Au, None) like the reference driver (chunkwise_hgdn.py:566-788).
+    With a list as `keep_workspace` the call's workspace (chunk matrices and every chunk's level states)
+    is appended to it for `chunkwise_bwd(..., fwd_workspace=...)`, which then skips their recomputation."""
     if output_final_state:
         raise NotImplementedError("output_final_state=True (prefill hand-off) is not implemented")
     B, T, H, G, K, V, L = _check(q, k, v, b, g, l, head_first, level_base, htype, chunk_size)
@@ -101,11 +104,14 @@ def chunkwise_fwd(
         g_cum = torch.empty_like(g_)
         Aw = torch.empty(B, T, H, CHUNK, dtype=torch.bfloat16, device=q.device)
         Au = torch.empty_like(Aw)
-        n = lib.llattn_gdn_fwd_workspace_bytes(B, T, H, K, V, L)
+        keep = keep_workspace is not None
+        n = (lib.llattn_gdn_fwd_keep_workspace_bytes if keep else lib.llattn_gdn_fwd_workspace_bytes)(B, T, H, K, V, L)
         if n == 0:
             raise ValueError("unsupported GDN shape (K must be 128, V 64 or 128, T <= 16384)")
         ws = torch.empty(n, dtype=torch.uint8, device=q.device)
-        rc = lib.llattn_gdn_fwd(q_.data_ptr(), k_.data_ptr(), v_.data_ptr(), b_.data_ptr(), g_.data_ptr(), l_.data_ptr(),
+        if keep:
+            keep_workspace.append(ws)
+        rc = (lib.llattn_gdn_fwd_keep if keep else lib.llattn_gdn_fwd)(q_.data_ptr(), k_.data_ptr(), v_.data_ptr(), b_.data_ptr(), g_.data_ptr(), l_.data_ptr(),
                                 o.data_ptr(), g_cum.data_ptr(), Aw.data_ptr(), Au.data_ptr(), ws.data_ptr(), ws.numel(),
                                 B, T, H, K, V, L, torch.cuda.current_stream().cuda_stream)
         _lib.check(rc, "llattn_gdn_fwd")
@@ -206,11 +212,12 @@ def _gdn_prologue_torch(q, k, v, b, g, l):
     return qd, wd, kd, u, o, gl
 
 
-def chunkwise_bwd(q, k, v, b, g, l, Aw, Au, do, head_first, level_base, htype, chunk_size, **unused):
+def chunkwise_bwd(q, k, v, b, g, l, Aw, Au, do, head_first, level_base, htype, chunk_size, fwd_workspace=None, **unused):
     """Gradients (dq, dk, dv, db, dg, dl), fp32, of the driver for normalised q, k (signature of
     chunkwise_hgdn.py:799-817; `g` is the in-chunk cumulative sum returned by chunkwise_fwd).
-    One C-ABI call: recomputation of the chunk matrices and level states, reverse scan of the adjoint
-    states, state-dependent gradients, chunk-local gradients."""
+    One C-ABI call: recomputation of the chunk matrices and level states (skipped when `fwd_workspace`
+    is the workspace a `chunkwise_fwd(..., keep_workspace=[])` call on the same inputs left), reverse scan
+    of the adjoint states, state-dependent gradients, chunk-local gradients."""
     B, T, H, G_, K, V, L = _check(q, k, v, b, g, l, head_first, level_base, htype, chunk_size)
     if G_ != H:
         raise NotImplementedError("GDN backward expects one q/k per head")
@@ -223,15 +230,20 @@ def chunkwise_bwd(q, k, v, b, g, l, Aw, Au, do, head_first, level_base, htype, c
         dv = torch.empty(B, T, H, V, **f32)
         db, dg = torch.empty(B, T, H, **f32), torch.empty(B, T, H, **f32)
         dl = torch.empty(B, T, H, L, **f32)
-        n = lib.llattn_gdn_bwd_workspace_bytes(B, T, H, K, V, L)
+        kept = fwd_workspace is not None
+        n = (lib.llattn_gdn_bwd_kept_workspace_bytes if kept else lib.llattn_gdn_bwd_workspace_bytes)(B, T, H, K, V, L)
         if n == 0:
             raise ValueError("unsupported GDN shape (K must be 128, V 64 or 128, T <= 16384)")
         ws = torch.empty(n, dtype=torch.uint8, device=q.device)
-        rc = lib.llattn_gdn_bwd(q_.data_ptr(), k_.data_ptr(), v_.data_ptr(), b_.data_ptr(), gc_.data_ptr(), l_.data_ptr(),
-                                Aw_.data_ptr(), Au_.data_ptr(), do_.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
-                                db.data_ptr(), dg.data_ptr(), dl.data_ptr(), ws.data_ptr(), ws.numel(),
-                                B, T, H, K, V, L, torch.cuda.current_stream().cuda_stream)
-        _lib.check(rc, "llattn_gdn_bwd")
+        head = (q_.data_ptr(), k_.data_ptr(), v_.data_ptr(), b_.data_ptr(), gc_.data_ptr(), l_.data_ptr(),
+                Aw_.data_ptr(), Au_.data_ptr(), do_.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
+                db.data_ptr(), dg.data_ptr(), dl.data_ptr())
+        tail = (ws.data_ptr(), ws.numel(), B, T, H, K, V, L, torch.cuda.current_stream().cuda_stream)
+        if kept:
+            rc = lib.llattn_gdn_bwd_kept(*head, fwd_workspace.data_ptr(), fwd_workspace.numel(), *tail)
+        else:
+            rc = lib.llattn_gdn_bwd(*head, *tail)
+        _lib.check(rc, "llattn_gdn_bwd_kept" if kept else "llattn_gdn_bwd")
     return dq, dk, dv, db, dg, dl
 
 
@@ -284,24 +296,44 @@ def _chunkwise_bwd_autograd(q, k, v, b, g, l, do):
     return tuple(grads)
 
 
-def gdn_forward(q, k, v, b, g, l, scale, head_first, level_base, htype, chunk_size):
-    """l2norm(q) * scale, l2norm(k), then the driver (hattention/kernel.py:109-120)."""
+# Largest forward workspace (chunk matrices + level states, bytes) that gdn_forward keeps for the backward
+# when asked to; above it the backward recomputes, which is the reference's memory behaviour.
+KEEP_WORKSPACE_MAX_BYTES = 8 << 30
+
+
+def gdn_forward(q, k, v, b, g, l, scale, head_first, level_base, htype, chunk_size, keep: Optional[list] = None):
+    """l2norm(q) * scale, l2norm(k), then the driver (hattention/kernel.py:109-120).  With a list as
+    `keep`, the normalised q, k and the driver's workspace are appended to it for gdn_backward."""
     qn = l2norm_fwd(q, scale)
     kn = l2norm_fwd(k)
-    g_cum, o, Aw, Au, _ = chunkwise_fwd(qn, kn, v, b, g, l, head_first, level_base, htype, chunk_size, False)
+    kept = None
+    if keep is not None and q.shape[2] == v.shape[2]:
+        B, T, H = v.shape[:3]
+        n = _lib.lib().llattn_gdn_fwd_keep_workspace_bytes(B, T, H, q.shape[-1], v.shape[-1], l.shape[-1])
+        if 0 < n <= KEEP_WORKSPACE_MAX_BYTES:
+            kept = []
+    g_cum, o, Aw, Au, _ = chunkwise_fwd(qn, kn, v, b, g, l, head_first, level_base, htype, chunk_size, False,
+                                        keep_workspace=kept)
+    if kept:
+        keep.extend([qn, kn, kept[0]])
     return g_cum, o, Aw, Au
 
 
-def gdn_backward(q, k, v, b, g_cum, l, Aw, Au, do, scale, head_first, level_base, htype, chunk_size):
+def gdn_backward(q, k, v, b, g_cum, l, Aw, Au, do, scale, head_first, level_base, htype, chunk_size, kept=None):
     """Backward of gdn_forward w.r.t. the raw q, k (through l2norm / scale), v, b, g, l
-    (hattention/kernel.py:198-225)."""
-    qn = l2norm_fwd(q, scale)
-    kn = l2norm_fwd(k)
+    (hattention/kernel.py:198-225).  `kept` is the list gdn_forward filled, or None / empty."""
+    if kept:
+        qn, kn, fwd_ws = kept
+    else:
+        qn = l2norm_fwd(q, scale)
+        kn = l2norm_fwd(k)
+        fwd_ws = None
     H = v.shape[2]
     G = k.shape[2]
     if G != H:
         raise NotImplementedError("GDN backward expects one q/k per head")
-    dq, dk, dv, db, dg, dl = chunkwise_bwd(qn, kn, v, b, g_cum, l, Aw, Au, do, head_first, level_base, htype, chunk_size)
+    dq, dk, dv, db, dg, dl = chunkwise_bwd(qn, kn, v, b, g_cum, l, Aw, Au, do, head_first, level_base, htype, chunk_size,
+                                           fwd_workspace=fwd_ws)
     dq = l2norm_bwd(q, dq, scale)
     dk = l2norm_bwd(k, dk)
     return dq, dk, dv, db, dg, dl

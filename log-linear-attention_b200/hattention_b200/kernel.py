@@ -9,9 +9,11 @@ from . import _lib
 from .chunkwise import chunkwise_bwd, chunkwise_fwd, final_states
 
 
-# Keep the Mamba-2 forward call's scratch (segment-level states, about 0.2 GB at B=2, T=16384, H=32)
-# alive until the backward, which then skips their recomputation.  The reference keeps only the inputs
-# (kernel.py:125); set to False for that memory behaviour.
+# Keep the forward call's scratch alive until the backward, which then skips its recomputation: the
+# Mamba-2 segment-level states (about 0.2 GB at B=2, T=16384, H=32), and for Gated DeltaNet the chunk
+# matrices and every chunk's level states (2.4 GB at B=4, T=8192, H=16, 128 x 128 heads; not kept above
+# chunkwise_hgdn.KEEP_WORKSPACE_MAX_BYTES).  The reference keeps only the inputs (kernel.py:125); set to
+# False for that memory behaviour.
 KEEP_FORWARD_STATES = True
 
 
@@ -48,8 +50,10 @@ class HAttentionFunction(torch.autograd.Function):
                 raise NotImplementedError
             if scale is None:
                 raise NotImplementedError
+            kept = [] if KEEP_FORWARD_STATES and any(ctx.needs_input_grad[:6]) else None
             g_cum, o, Aw, Au = gdn_forward(q, k, v, b.contiguous(), g, l, scale, head_first, level_base, htype,
-                                           chunk_sizes[0])
+                                           chunk_sizes[0], keep=kept)
+            ctx.fwd_workspace = kept if kept else None
         else:
             raise NotImplementedError
         ctx.save_for_backward(q, k, v, b, g_cum, l, Aw, Au)
@@ -75,7 +79,9 @@ class HAttentionFunction(torch.autograd.Function):
         else:
             from .chunkwise_hgdn import gdn_backward
             dq, dk, dv, db, dg, dl = gdn_backward(q, k, v, b, g_cum, l, Aw, Au, do, ctx.scale, ctx.head_first,
-                                                  ctx.level_base, ctx.htype, ctx.chunk_sizes[0])
+                                                  ctx.level_base, ctx.htype, ctx.chunk_sizes[0],
+                                                  kept=ctx.fwd_workspace)
+            ctx.fwd_workspace = None
         return (dq.to(q), dk.to(k), dv.to(v), db.to(b) if b is not None else None, dg.to(ctx.dtype), dl.to(l),
                 None, None, None, None, None, None, None, None)
 

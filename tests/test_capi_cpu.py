@@ -98,6 +98,13 @@ def test_gdn_entry_points_reject_bad_arguments(lib):
     assert lib.llattn_gdn_bwd(*([null] * 15), null, 0, 1, 1024, 2, 64, 64, 11, null) == -1
     assert lib.llattn_gdn_bwd(*([null] * 15), null, 0, 1, 1024, 2, 128, 64, 11, null) == -6
     assert lib.llattn_gdn_bwd_levels(*([null] * 15), null, 0, 1, 1024, 2, 128, 64, 11, null) == -6
+    # forward that keeps its intermediates / backward that reads them
+    keep = lib.llattn_gdn_fwd_keep_workspace_bytes(1, 1024, 2, 128, 128, 11)
+    bkept = lib.llattn_gdn_bwd_kept_workspace_bytes(1, 1024, 2, 128, 128, 11)
+    assert keep > fwd and 0 < bkept < bwd and keep + bkept >= bwd
+    assert lib.llattn_gdn_fwd_keep_workspace_bytes(1, 1024, 2, 96, 64, 12) == 0
+    assert lib.llattn_gdn_fwd_keep(*([null] * 10), null, 0, 1, 1024, 2, 128, 64, 11, null) == -6
+    assert lib.llattn_gdn_bwd_kept(*([null] * 15), null, 0, null, 0, 1, 1024, 2, 128, 64, 11, null) == -6
 
 
 def test_elementwise_entry_points_reject_bad_arguments(lib):

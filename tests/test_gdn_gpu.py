@@ -133,6 +133,53 @@ def test_backward_stages_match_whole_path_autograd(B, T, H, Dv, L):
         assert_close(a, w_, key, atol=8e-3)
 
 
+@pytest.mark.parametrize("B,T,H,Dv,L", [(1, 1408, 2, 128, 12), (2, 1024, 1, 64, 11), (1, 64, 2, 128, 7)])
+def test_backward_with_forward_states_kept(B, T, H, Dv, L):
+    """The forward that leaves its chunk matrices and level states in the workspace returns the same
+    output, and the backward that reads them returns the gradients of the recomputing backward (same
+    kernels on the same bf16 values; only the order of the atomic adds into dl differs)."""
+    from hattention_b200 import chunkwise_hgdn as hg
+    from hattention_b200.base import HType
+    dev = torch.device("cuda:0")
+    Dk = 128
+    q, k, v, b, g, l = orc.make_gdn_inputs(B, T, H, Dk, Dv, L, seed=T + 1)
+    scale = Dk ** -0.5
+    qn, kn = orc.gdn_layer_inputs(q, k, scale)
+    qn, kn, v, b, l = (x.bfloat16().to(dev) for x in (qn, kn, v, b, l / scale))
+    g = g.float().to(dev)
+    do = torch.randn(B, T, H, Dv, generator=torch.Generator().manual_seed(4)).bfloat16().to(dev)
+    g_cum, o, Aw, Au, _ = hg.chunkwise_fwd(qn, kn, v, b, g, l, False, 2, HType.WEAK, 64, False)
+    kept = []
+    g_cum2, o2, Aw2, Au2, _ = hg.chunkwise_fwd(qn, kn, v, b, g, l, False, 2, HType.WEAK, 64, False, keep_workspace=kept)
+    assert len(kept) == 1
+    for a, w_ in ((g_cum2, g_cum), (o2, o), (Aw2, Aw), (Au2, Au)):
+        assert torch.equal(a, w_)
+    want = hg.chunkwise_bwd(qn, kn, v, b, g_cum, l, Aw, Au, do, False, 2, HType.WEAK, 64)
+    got = hg.chunkwise_bwd(qn, kn, v, b, g_cum2, l, Aw2, Au2, do, False, 2, HType.WEAK, 64, fwd_workspace=kept[0])
+    torch.cuda.synchronize()
+    for a, w_, key in zip(got, want, ("dq", "dk", "dv", "db", "dg", "dl")):
+        assert torch.isfinite(a).all(), key
+        torch.testing.assert_close(a, w_, rtol=1e-4, atol=1e-5 * max(1.0, w_.abs().max().item()), msg=key)
+
+
+def test_autograd_function_keeps_and_releases_forward_states():
+    """hattention_kernel keeps the forward workspace on the autograd context and drops it in backward;
+    with the switch off the gradients are the same."""
+    from hattention_b200 import kernel as hk
+    B, T, H, Dk, Dv, L = 1, 512, 2, 128, 64, 11
+    q, k, v, b, g, l = orc.make_gdn_inputs(B, T, H, Dk, Dv, L, seed=78)
+    do = torch.randn(B, T, H, Dv, generator=torch.Generator().manual_seed(6))
+    assert hk.KEEP_FORWARD_STATES
+    _, kept_grads = run_cuda_grads(q, k, v, b, g, l, do)
+    hk.KEEP_FORWARD_STATES = False
+    try:
+        _, plain_grads = run_cuda_grads(q, k, v, b, g, l, do)
+    finally:
+        hk.KEEP_FORWARD_STATES = True
+    for a, w_, key in zip(kept_grads, plain_grads, ("dq", "dk", "dv", "db", "dg", "dl")):
+        torch.testing.assert_close(a.float(), w_.float(), rtol=2e-2, atol=1e-2 * max(1.0, w_.float().abs().max().item()), msg=key)
+
+
 @pytest.mark.parametrize("D", [64, 128, 256])
 def test_l2norm_kernels(D):
     """l2norm forward (with the reference's two bf16 rounding points) and backward against torch."""
