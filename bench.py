@@ -248,6 +248,63 @@ def run_gdn(args, rank, world, local):
     print(json.dumps(line), flush=True)
 
 
+def run_sequence_parallel(args, rank, world, local):
+    """Secondary bench line: one sequence of world x T tokens split along T over the ranks (B=2, H=32,
+    P=64, N=128 per rank, T = --seq-len per rank): in-shard part on the CUDA kernels, shard summaries
+    all-gathered (reduce-scattered in the backward) over NCCL, cross-shard levels as torch products."""
+    import torch.distributed as dist
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the hot path has no CPU fallback")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29655")
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    from hattention_b200.sequence_parallel import hattention_sequence_parallel
+    w = dict(WORKLOAD)
+    w["L"] = WORKLOAD["L"] + (world - 1).bit_length()
+    B, T, H, P, N, G, L = w["B"], w["T"], w["H"], w["P"], w["N"], w["G"], w["L"]
+    gen = torch.Generator().manual_seed(100 + rank)
+    q = (torch.randn(B, T, G, N, generator=gen) / N ** 0.5).bfloat16().to(dev)
+    k = (torch.randn(B, T, G, N, generator=gen) / N ** 0.5).bfloat16().to(dev)
+    v = torch.randn(B, T, H, P, generator=gen).bfloat16().to(dev)
+    g = (-torch.nn.functional.softplus(torch.randn(B, T, H, generator=gen) - 2.0)).float().to(dev)
+    lam = torch.nn.functional.softplus(torch.randn(B, T, H, L, generator=gen)).bfloat16().to(dev)
+    do = torch.randn(B, T, H, P, generator=gen).bfloat16().to(dev)
+    ins = [x.requires_grad_(True) for x in (q, k, v, g, lam)]
+
+    def step():
+        o = hattention_sequence_parallel(*ins)
+        torch.autograd.grad(o, ins, do)
+
+    W, K = max(args.warmup, 3), args.steps
+    for _ in range(W):
+        step()
+    dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler = ClockSampler(local)
+    e0.record()
+    for _ in range(K):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    dist.barrier()
+    clocks = sampler.stop()
+    t = torch.tensor([e0.elapsed_time(e1) / K], device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = t.item()
+    if rank == 0:
+        print(json.dumps({
+            "metric": "log-linear Mamba-2 sequence-parallel fwd+bwd tokens/s", "value": world * B * T / (ms * 1e-3),
+            "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"one sequence of {world}x{T} tokens split along T, B={B} H={H} P={P} N={N} L={L}",
+                       "note": "cross-shard levels: all-gather of shard final states + torch products"},
+            "clocks": clocks}), flush=True)
+    dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -255,8 +312,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="mamba2", choices=["mamba2", "gdn"],
-                    help="mamba2 = the headline workload; gdn = log-linear Gated DeltaNet layer, B=4 T=8192 H=16 Dk=Dv=128 L=14")
+    ap.add_argument("--workload", default="mamba2", choices=["mamba2", "gdn", "mamba2-sp"],
+                    help="mamba2 = the headline workload; gdn = log-linear Gated DeltaNet layer, B=4 T=8192 H=16 Dk=Dv=128 L=14; "
+                         "mamba2-sp = Mamba-2 with one sequence split along T over the ranks (run under torchrun)")
     ap.add_argument("--batch", type=int, default=WORKLOAD["B"],
                     help="per-GPU batch; the headline workload is 2, profiler captures use 1")
     ap.add_argument("--seq-len", type=int, default=WORKLOAD["T"],
@@ -277,6 +335,9 @@ def main():
         return
     if args.workload == "gdn":
         run_gdn(args, rank, world, local)
+        return
+    if args.workload == "mamba2-sp":
+        run_sequence_parallel(args, rank, world, local)
         return
 
     if not torch.cuda.is_available():

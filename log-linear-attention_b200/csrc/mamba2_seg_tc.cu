@@ -158,7 +158,16 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_hi_bwd_tc_kernel(const __g
         const uint32_t aQ = umma::smem_addr(sQ), aH = umma::smem_addr(sH), aDOs = umma::smem_addr(sDOs);
         if (lane == 0) umma::mbar_wait(full_h, 0, abort_flag);
         for (int pl = 0; pl < npairs; ++pl) {
-            if (lane == 0) umma::mbar_wait(full_q, pl & 1, abort_flag);
+            if (lane == 0) {
+                umma::mbar_wait(full_q, pl & 1, abort_flag);
+                // The level reads start only after every element-wise thread has taken its do row out of
+                // shared memory (phase pl of empty_do).  Measured, not derived: when this chain ran while
+                // those threads were still in their loads at the top of the pair (it happens in the CTAs
+                // whose q and do tiles land at about the same time), a few percent of the launches on
+                // some B200s returned wrong dlambda / dq / reader summaries for the first rows of the
+                // segment; with the chain ordered after the loads, none did in thousands of repeats.
+                umma::mbar_wait(empty_do, pl & 1, abort_flag);
+            }
             __syncwarp();
             umma::fence_after_sync();
             // The issue of a tcgen05.mma costs about as much for N = 64 as for N = 256, so the level reads of up
