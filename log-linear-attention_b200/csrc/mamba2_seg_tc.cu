@@ -158,16 +158,7 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_hi_bwd_tc_kernel(const __g
         const uint32_t aQ = umma::smem_addr(sQ), aH = umma::smem_addr(sH), aDOs = umma::smem_addr(sDOs);
         if (lane == 0) umma::mbar_wait(full_h, 0, abort_flag);
         for (int pl = 0; pl < npairs; ++pl) {
-            if (lane == 0) {
-                umma::mbar_wait(full_q, pl & 1, abort_flag);
-                // The level reads start only after every element-wise thread has taken its do row out of
-                // shared memory (phase pl of empty_do).  Measured, not derived: when this chain ran while
-                // those threads were still in their loads at the top of the pair (it happens in the CTAs
-                // whose q and do tiles land at about the same time), a few percent of the launches on
-                // some B200s returned wrong dlambda / dq / reader summaries for the first rows of the
-                // segment; with the chain ordered after the loads, none did in thousands of repeats.
-                umma::mbar_wait(empty_do, pl & 1, abort_flag);
-            }
+            if (lane == 0) umma::mbar_wait(full_q, pl & 1, abort_flag);
             __syncwarp();
             umma::fence_after_sync();
             // The issue of a tcgen05.mma costs about as much for N = 64 as for N = 256, so the level reads of up
@@ -243,7 +234,18 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_hi_bwd_tc_kernel(const __g
         uint4 dox[4];
 #pragma unroll
         for (int c = 0; c < 4; ++c) dox[c] = *reinterpret_cast<const uint4*>(sDO + umma::tile_offset(row, ch * 32 + c * 8, tc::PT));
-        asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(umma::smem_addr(empty_do)) : "memory");
+        {
+            // The arrive hands the do tile back to the TMA producer, so it must not be performed before this
+            // thread's loads from the tile have returned.  Nothing in the instruction stream says so: the
+            // loaded words are first used after the level reads, and the arrive was observed to overtake the
+            // loads while the MMA warp's chain kept shared memory busy (the refill then replaced rows that
+            // had not been read; wrong dlambda / dq / reader summaries in a few percent of the launches on
+            // some GPUs).  The address therefore depends on every loaded word through p.zero, which is 0 at
+            // run time but not known to the compiler.
+            const uint32_t x = dox[0].x ^ dox[0].y ^ dox[0].z ^ dox[0].w ^ dox[1].x ^ dox[1].y ^ dox[1].z ^ dox[1].w ^
+                               dox[2].x ^ dox[2].y ^ dox[2].z ^ dox[2].w ^ dox[3].x ^ dox[3].y ^ dox[3].z ^ dox[3].w;
+            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(umma::smem_addr(empty_do) + (x & p.zero)) : "memory");
+        }
         float* myDL = sDL + (ch * 128 + row) * NDLH;
         for (int i = 0; i < nl; ++i) {
             if (i == 0 || i == 3) {                  // one completion per chain of level reads
