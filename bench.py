@@ -243,7 +243,9 @@ def run_gdn(args, rank, world, local):
         "roofline": {"bound": "tensor", "achieved": flops_fwd / (ms_fwd * 1e-3) / 1e12, "peak": pk["tflops"], "unit": "TFLOP/s",
                      "frac": flops_fwd / (ms_fwd * 1e-3) / 1e12 / pk["tflops"], "traffic": None, "peak_source": pk["source"],
                      "kernel": "GDN forward launch chain (chunk preparation + state scan), reference-formulation flops"},
-        "gpu_launches": 7 * Kb, "clocks": clocks,
+        # kernels of this library per forward + backward with the forward states kept: l2norm forward x2, chunk
+        # preparation, state scan; reverse scan, level gradients, chunk-local gradients, l2norm backward x2
+        "gpu_launches": 9 * Kb, "clocks": clocks,
     }
     print(json.dumps(line), flush=True)
 
