@@ -167,7 +167,7 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_hi_bwd_tc_kernel(const __g
             {
                 const int n0 = nl < 3 ? nl : 3;
                 if (lane == 0) {
-                    umma::gemm_km64<tc::PT, tc::KD, tc::KD>(tbase + TM_DQ, aQ, aH, umma::idesc_bf16(128, 64 * n0, false, true), false);
+                    umma::gemm_km<tc::PT, tc::KD, tc::KD>(tbase + TM_DQ, aQ, aH, umma::idesc_bf16(128, 64 * n0, false, true), false);
                     umma::commit(&barT[0]);
                 }
                 __syncwarp();
@@ -175,7 +175,7 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_hi_bwd_tc_kernel(const __g
                     bar_work();                      // the three slots have been read by the compute warps
                     umma::fence_after_sync();
                     if (lane == 0) {
-                        umma::gemm_km64<tc::PT, tc::KD, tc::KD>(tbase + TM_DQ, aQ, aH + 3 * tc::H_BYTES,
+                        umma::gemm_km<tc::PT, tc::KD, tc::KD>(tbase + TM_DQ, aQ, aH + 3 * tc::H_BYTES,
                                                               umma::idesc_bf16(128, 64 * (nl - 3), false, true), false);
                         umma::commit(&barT[1]);
                     }
@@ -188,11 +188,11 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_hi_bwd_tc_kernel(const __g
             if (lane == 0) {
                 // reader summaries of up to four levels per chain (N = 256), then dq over all levels
                 const int n0 = nl < 4 ? nl : 4;
-                umma::gemm_mm64<tc::PT, tc::PT, tc::PT>(tbase + TM_DF, aQ, aDOs, umma::idesc_bf16(128, 64 * n0, true, true), pl > 0);
+                umma::gemm_mm<tc::PT, tc::PT, tc::PT>(tbase + TM_DF, aQ, aDOs, umma::idesc_bf16(128, 64 * n0, true, true), pl > 0);
                 if (nl > 4)
-                    umma::gemm_mm64<tc::PT, tc::PT, tc::PT>(tbase + TM_DF + 4 * 64, aQ, aDOs + 4 * tc::V_BYTES, ID_MM64, pl > 0);
+                    umma::gemm_mm<tc::PT, tc::PT, tc::PT>(tbase + TM_DF + 4 * 64, aQ, aDOs + 4 * tc::V_BYTES, ID_MM64, pl > 0);
                 for (int i = 0; i < nl; ++i)
-                    umma::gemm_kk64<tc::PT, tc::KD, tc::VD>(tbase + TM_DQ, aDOs + i * tc::V_BYTES, aH + i * tc::H_BYTES, ID_KK128, i > 0);
+                    umma::gemm_kk<tc::PT, tc::KD, tc::VD>(tbase + TM_DQ, aDOs + i * tc::V_BYTES, aH + i * tc::H_BYTES, ID_KK128, i > 0);
                 umma::commit(barB);
                 // q is free as soon as the batch is done: let the producer refill it while dq is read out
                 umma::mbar_wait(barB, pl & 1, abort_flag);

@@ -102,10 +102,10 @@ __device__ __forceinline__ void gemm_mm(uint32_t d_tmem, uint32_t a_saddr, uint3
         mma_ss(d_tmem, da + ((kk * ROW_BYTES) >> 4), db + ((kk * ROW_BYTES) >> 4), idesc, accumulate || kk > 0);
     }
 }
-// ---- 64-bit descriptor variants.  m2_hi_bwd_tc_kernel issues through these: with the 32-bit assembly above
-//      that kernel (and only that one) returned wrong reader gradients for the first 64 rows of a segment's
-//      first pair, deterministically, although the same loops pass the tile-product self-test at low and high
-//      shared-memory addresses; the cause has not been found, so the kernel stays on the form it is verified with.
+// ---- 64-bit descriptor variants (the whole descriptor kept in one register pair; a few more instructions
+//      per MMA than the 32-bit form above).  No kernel issues through them any more: m2_hi_bwd_tc_kernel did
+//      while it returned wrong reader gradients with the faster 32-bit form, which turned out to be its do-tile
+//      release overtaking the loads (see that kernel), not the descriptors.  Kept for A/B checks.
 __device__ __forceinline__ uint64_t desc64_kmajor(uint32_t saddr) {
     return (uint64_t(DESC_HI) << 32) | uint64_t(desc_lo_kmajor(saddr));
 }
