@@ -9,9 +9,15 @@
  * Tensor layouts (all contiguous, "sequence first", as the reference passes them with
  * head_first=False): q,k (B,T,G,K) bf16; v,o,do,dv (B,T,H,V) bf16; g,dg (B,T,H) fp32;
  * lambda (B,T,H,L) bf16; dlambda (B,T,H,L) fp32; dq,dk (B,T,G,K) bf16.  Head h uses q/k group
- * h / (H/G).  Constraints: T % 64 == 0, K in {64,128}, V == 64, H % G == 0,
- * L >= 7 + ceil(log2(T/64)), L <= 32 (the reference's checks: hattention/chunkwise.py:1140-1153,
- * 1211-1214).
+ * h / (H/G).  Constraints: T % 64 == 0, T <= 524288 (the scans over 512-token segments hold ten segment
+ * levels), K in {64,128}, V == 64, H % G == 0, L >= 7 + ceil(log2(T/64)), L <= 32 (the reference's
+ * checks: hattention/chunkwise.py:1140-1153, 1211-1214).
+ *
+ * Status word.  The first 4 bytes of every workspace are a status word that the call clears and that a
+ * kernel sets to 1 if one of its bounded waits (on a TMA transfer or on the tensor core) ran out; the
+ * outputs of such a call are not valid.  A launch cannot report this through its return value (nothing
+ * waits for the GPU), so callers that want to know read the word after synchronising:
+ * llattn_workspace_status, or llattn_static_scratch_status for llattn_mamba2_fwd_static.
  */
 #ifndef LLATTN_H_
 #define LLATTN_H_
@@ -29,16 +35,20 @@ extern "C" {
 #define LLATTN_ERR_WORKSPACE (-5)           /* workspace NULL, misaligned or too small       */
 #define LLATTN_ERR_NULL (-6)                /* a required pointer is NULL                    */
 #define LLATTN_ERR_STATIC_SCRATCH (-7)      /* problem needs more than LLATTN_STATIC_SCRATCH_BYTES */
+#define LLATTN_ERR_TENSOR_MAP (-8)          /* the driver refused a TMA tensor map for these pointers */
 
 /* Size of the built-in scratch array used by llattn_mamba2_fwd_static (16 MiB). */
 #define LLATTN_STATIC_SCRATCH_BYTES (16u << 20)
 
 /* Library / ABI version, for the loader's sanity check. */
 int llattn_version(void);
-/* Process-wide switch between the tcgen05 (tensor memory) chunk kernels (1, default) and the
- * warp-level mma.sync kernels (0) where both exist; for A/B comparison.  The first word of every
- * workspace is a status word: kernels set it to 1 if a bounded wait on the tensor core gave up. */
-void llattn_set_tensor_core_path(int enabled);
+/* Number of kernels this library has launched in the process so far (all entry points, all threads). */
+unsigned long long llattn_kernel_launches(void);
+/* Copies the status word of `workspace` (a workspace that an earlier call on `stream` used) to *status_host
+ * and returns after the stream has drained: unlike the compute entry points this one synchronises.
+ * 0 = every wait completed, 1 = a kernel gave up and the call's outputs must be discarded.  (No counterpart
+ * in the reference, whose Triton kernels have no bounded waits.) */
+int llattn_workspace_status(const void* workspace, int* status_host, void* stream);
 /* Chunk length the kernels are built for (64, as hattention/kernel.py:355-356 fixes it). */
 int llattn_chunk(void);
 
@@ -63,15 +73,21 @@ int llattn_mamba2_fwd(const void* q, const void* k, const void* v, const float* 
  * array compiled into the library (LLATTN_STATIC_SCRATCH_BYTES = 16 MiB of device memory on every
  * GPU that loads the library, held until the process exits).  The call allocates and frees
  * nothing.  Shapes whose scratch need (llattn_mamba2_fwd_workspace_bytes) exceeds the array are
- * rejected with LLATTN_ERR_STATIC_SCRATCH; e.g. B*H = 8 at T = 4096, K = 128, V = 64 needs 5.0 MiB.
+ * rejected with LLATTN_ERR_STATIC_SCRATCH; at T = 4096, K = 128, V = 64 the need is 1.125 MiB per
+ * (batch, head), so the array serves B*H <= 14 there.
  *
  * The first call on each device looks up the array's device address (cudaGetSymbolAddress) for
  * the device that is current at that moment and caches it; make that first call with the right
  * device current and before starting any stream capture.  All calls on one device share the one
  * array, and it keeps whatever the previous call left in it (the kernels overwrite every element
  * before reading it, so no clearing is needed): two calls whose kernels can overlap on the GPU
- * - different streams, or different host threads - race on it and must be serialised by the caller. */
+ * - different streams, or different host threads - race on it and must be serialised by the caller.
+ * (Two host threads that make the FIRST call on a device at the same time both store the same looked-up
+ * address into the cache; that is harmless, the race on the array itself is not.)
+ * llattn_static_scratch_status reads the status word of the array on the current device (see "Status
+ * word" above) after synchronising `stream`. */
 size_t llattn_static_scratch_bytes(void);
+int llattn_static_scratch_status(int* status_host, void* stream);
 int llattn_mamba2_fwd_static(const void* q, const void* k, const void* v, const float* g, const void* lambda,
                              void* o, float* g_cum, int B, int T, int H, int G, int K, int V, int L, void* stream);
 

@@ -3,6 +3,11 @@
 
 #include "llattn_gdn.h"
 #include "llattn_mamba2.h"
+#include "llattn_testing.h"
+
+namespace llattn {
+std::atomic<unsigned long long> g_kernel_launches{0};
+}
 
 namespace {
 
@@ -33,6 +38,9 @@ int check_shape(int B, int T, int H, int G, int K, int V, int L) {
     if (!((K == 64 || K == 128) && V == 64)) return LLATTN_ERR_UNSUPPORTED_SHAPE;
     if (L > 32) return LLATTN_ERR_UNSUPPORTED_SHAPE;
     if (L < 7 + ceil_log2i(T / 64)) return LLATTN_ERR_TOO_FEW_LEVELS;
+    // the per-level scans over segments hold at most M2_MAX_LH segment levels: T <= 512 * 2^10 tokens
+    const int seg = 1 << llattn::M2_MLOW;
+    if (ceil_log2i((T / 64 + seg - 1) / seg) > llattn::M2_MAX_LH) return LLATTN_ERR_UNSUPPORTED_SHAPE;
     return 0;
 }
 
@@ -79,8 +87,16 @@ static void* g_static_scratch_addr[64] = {nullptr};
 
 extern "C" {
 
-int llattn_version(void) { return 1; }
-void llattn_set_tensor_core_path(int enabled) { llattn::g_use_tensor_core_path = enabled ? 1 : 0; }
+int llattn_version(void) { return 2; }
+void llattn_testing_use_tensor_core_path(int enabled) { llattn::g_use_tensor_core_path.store(enabled ? 1 : 0); }
+unsigned long long llattn_kernel_launches(void) { return llattn::g_kernel_launches.load(); }
+
+int llattn_workspace_status(const void* workspace, int* status_host, void* stream) {
+    if (!workspace || !status_host) return LLATTN_ERR_NULL;
+    cudaError_t e = cudaMemcpyAsync(status_host, workspace, sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream);
+    if (e != cudaSuccess) return (int)e;
+    return (int)cudaStreamSynchronize((cudaStream_t)stream);
+}
 int llattn_chunk(void) { return 64; }
 
 size_t llattn_mamba2_fwd_workspace_bytes(int B, int T, int H, int G, int K, int V, int L) {
@@ -110,6 +126,19 @@ int llattn_mamba2_fwd(const void* q, const void* k, const void* v, const float* 
 }
 
 size_t llattn_static_scratch_bytes(void) { return LLATTN_STATIC_SCRATCH_BYTES; }
+
+int llattn_static_scratch_status(int* status_host, void* stream) {
+    if (!status_host) return LLATTN_ERR_NULL;
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= 64) return LLATTN_ERR_UNSUPPORTED_SHAPE;
+    if (g_static_scratch_addr[dev] == nullptr) {   // no call has used the array on this device yet
+        *status_host = 0;
+        return 0;
+    }
+    return llattn_workspace_status(g_static_scratch_addr[dev], status_host, stream);
+}
 
 int llattn_mamba2_fwd_static(const void* q, const void* k, const void* v, const float* g, const void* lambda,
                              void* o, float* g_cum, int B, int T, int H, int G, int K, int V, int L, void* stream) {
@@ -193,7 +222,7 @@ int llattn_mamba2_bwd_saved(const void* q, const void* k, const void* v, const f
     llattn::mamba2_uncumsum(g_cum, const_cast<float*>(p.g), (long)B * T, H, st);
     rc = llattn::mamba2_bwd_dispatch(p, st);
     if (rc != 0) return rc;
-    llattn::mamba2_dg(p, dg, st);
+    if ((rc = llattn::mamba2_dg(p, dg, st)) != 0) return rc;
     llattn::cast_f32_to_bf16(p.dq_acc, dq, (long)nqk, st);
     llattn::cast_f32_to_bf16(p.dk_acc, dk, (long)nqk, st);
     return (int)cudaGetLastError();

@@ -466,7 +466,7 @@ int gdn_bwd_scan_dispatch(const GdnParams& p, cudaStream_t stream) {
     const size_t sm = ScanBwdSmem<128>::total;
     cudaError_t e;
     if ((e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm)) != cudaSuccess) return (int)e;
-    kern<<<p.B * p.H * (p.V / GDN_VS), 256, sm, stream>>>(p);
+    kern<<<p.B * p.H * (p.V / GDN_VS), 256, sm, stream>>>(p); LLATTN_LAUNCHED();
     return (int)cudaGetLastError();
 }
 
@@ -476,7 +476,7 @@ static int launch_levels(const GdnParams& p, cudaStream_t stream) {
     const size_t sm = LevSmem<KD, VD>::total;
     cudaError_t e;
     if ((e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm)) != cudaSuccess) return (int)e;
-    kern<<<p.B * p.NT * p.H, 256, sm, stream>>>(p);
+    kern<<<p.B * p.NT * p.H, 256, sm, stream>>>(p); LLATTN_LAUNCHED();
     return (int)cudaGetLastError();
 }
 

@@ -506,7 +506,7 @@ static int launch_chunk(const GdnParams& p, cudaStream_t stream) {
     const size_t sm = ChunkBwdSmem<KD, VD>::total;
     cudaError_t e;
     if ((e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm)) != cudaSuccess) return (int)e;
-    kern<<<p.B * p.NT * p.H, 256, sm, stream>>>(p);
+    kern<<<p.B * p.NT * p.H, 256, sm, stream>>>(p); LLATTN_LAUNCHED();
     return (int)cudaGetLastError();
 }
 

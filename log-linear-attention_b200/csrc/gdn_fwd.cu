@@ -557,13 +557,13 @@ static int launch_gdn_fwd(const GdnParams& p, cudaStream_t stream) {
         auto kern = gdn_chunk_prep_kernel<KD, VD, BWD>;
         const size_t sm = PrepSmem<KD, VD>::total;
         if ((e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm)) != cudaSuccess) return (int)e;
-        kern<<<p.B * p.NT * p.H, 256, sm, stream>>>(p);
+        kern<<<p.B * p.NT * p.H, 256, sm, stream>>>(p); LLATTN_LAUNCHED();
     }
     {
         auto kern = gdn_scan_kernel<KD, BWD || KEEP, !BWD>;
         const size_t sm = ScanSmem<KD>::total;
         if ((e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm)) != cudaSuccess) return (int)e;
-        kern<<<p.B * p.H * (p.V / GDN_VS), 256, sm, stream>>>(p);
+        kern<<<p.B * p.H * (p.V / GDN_VS), 256, sm, stream>>>(p); LLATTN_LAUNCHED();
     }
     return (int)cudaGetLastError();
 }

@@ -9,6 +9,7 @@
 #include <cuda_runtime.h>
 
 #include "../../include/llattn.h"
+#include "launch_count.h"
 
 namespace llattn {
 
@@ -106,9 +107,9 @@ int llattn_l2norm_fwd(const void* x, void* y, long rows, int D, float scale, voi
     __nv_bfloat16* yo = (__nv_bfloat16*)y;
     const int lpr = D <= 64 ? 8 : (D <= 128 ? 16 : 32);
     const long blocks = (rows * lpr + 255) / 256;
-    if (lpr == 8) llattn::l2norm_fwd_kernel<8><<<(unsigned)blocks, 256, 0, st>>>(xi, yo, rows, D, scale, 1e-6f);
-    else if (lpr == 16) llattn::l2norm_fwd_kernel<16><<<(unsigned)blocks, 256, 0, st>>>(xi, yo, rows, D, scale, 1e-6f);
-    else llattn::l2norm_fwd_kernel<32><<<(unsigned)blocks, 256, 0, st>>>(xi, yo, rows, D, scale, 1e-6f);
+    if (lpr == 8) { llattn::l2norm_fwd_kernel<8><<<(unsigned)blocks, 256, 0, st>>>(xi, yo, rows, D, scale, 1e-6f); LLATTN_LAUNCHED(); }
+    else if (lpr == 16) { llattn::l2norm_fwd_kernel<16><<<(unsigned)blocks, 256, 0, st>>>(xi, yo, rows, D, scale, 1e-6f); LLATTN_LAUNCHED(); }
+    else { llattn::l2norm_fwd_kernel<32><<<(unsigned)blocks, 256, 0, st>>>(xi, yo, rows, D, scale, 1e-6f); LLATTN_LAUNCHED(); }
     return (int)cudaGetLastError();
 }
 
@@ -121,9 +122,9 @@ int llattn_l2norm_bwd(const void* x, const float* dy, void* dx, long rows, int D
     __nv_bfloat16* o = (__nv_bfloat16*)dx;
     const int lpr = D <= 64 ? 8 : (D <= 128 ? 16 : 32);
     const long blocks = (rows * lpr + 255) / 256;
-    if (lpr == 8) llattn::l2norm_bwd_kernel<8><<<(unsigned)blocks, 256, 0, st>>>(xi, dy, o, rows, D, scale, 1e-6f);
-    else if (lpr == 16) llattn::l2norm_bwd_kernel<16><<<(unsigned)blocks, 256, 0, st>>>(xi, dy, o, rows, D, scale, 1e-6f);
-    else llattn::l2norm_bwd_kernel<32><<<(unsigned)blocks, 256, 0, st>>>(xi, dy, o, rows, D, scale, 1e-6f);
+    if (lpr == 8) { llattn::l2norm_bwd_kernel<8><<<(unsigned)blocks, 256, 0, st>>>(xi, dy, o, rows, D, scale, 1e-6f); LLATTN_LAUNCHED(); }
+    else if (lpr == 16) { llattn::l2norm_bwd_kernel<16><<<(unsigned)blocks, 256, 0, st>>>(xi, dy, o, rows, D, scale, 1e-6f); LLATTN_LAUNCHED(); }
+    else { llattn::l2norm_bwd_kernel<32><<<(unsigned)blocks, 256, 0, st>>>(xi, dy, o, rows, D, scale, 1e-6f); LLATTN_LAUNCHED(); }
     return (int)cudaGetLastError();
 }
 

@@ -13,6 +13,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "launch_count.h"
+
 namespace llattn {
 
 constexpr int CH = 64;        // chunk length (the reference fixes 64, hattention/kernel.py:355-356)

@@ -4,11 +4,14 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
+#include <atomic>
+
 #include "../../include/llattn.h"
 
 namespace llattn {
 
 constexpr int M2_MLOW = 3;   // a segment is 2^M2_MLOW chunks (512 tokens)
+constexpr int M2_MAX_LH = 10;   // segment levels held by the per-level scans over segments (T <= 512 * 2^10)
 
 struct Mamba2Params {
     // tensor maps (64-column panels, 128 rows) for the tcgen05 kernels; valid only when those run
@@ -63,9 +66,9 @@ int mamba2_bwd2_tc_launch(const Mamba2Params& p, cudaStream_t stream);
 int mamba2_hi_bwd_tc_launch(const Mamba2Params& p, cudaStream_t stream);
 int mamba2_seg_state_tc_launch(const Mamba2Params& p, cudaStream_t stream);
 int mamba2_hi_out_tc_launch(const Mamba2Params& p, cudaStream_t stream);
-extern int g_use_tensor_core_path;
+extern std::atomic<int> g_use_tensor_core_path;   // test hook, see llattn_testing.h
 void mamba2_uncumsum(const float* gc, float* g, long BT, int H, cudaStream_t stream);
-void mamba2_dg(const Mamba2Params& p, float* dg, cudaStream_t stream);
+int mamba2_dg(const Mamba2Params& p, float* dg, cudaStream_t stream);
 void cast_f32_to_bf16(const float* src, void* dst, long n, cudaStream_t stream);
 
 }  // namespace llattn

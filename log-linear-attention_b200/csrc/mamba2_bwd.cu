@@ -1074,7 +1074,7 @@ static int launch_bwd(Mamba2Params p, cudaStream_t stream) {
         // forward high-level states: recomputed unless the caller kept the forward call's workspace
         int rc = p.reuse_states ? 0 : mamba2_fwd_states_dispatch(p, stream);
         if (rc != 0) return rc;
-        const bool hi_tc = (KD == 128 && VD == 64 && (p.NT % 2) == 0 && p.L <= 20 && p.LH <= 10 && g_use_tensor_core_path);
+        const bool hi_tc = (KD == 128 && VD == 64 && (p.NT % 2) == 0 && p.L <= 20 && p.LH <= 10 && g_use_tensor_core_path.load());
         if (hi_tc) {
             rc = mamba2_hi_bwd_tc_launch(p, stream);
             if (rc != 0) return rc;
@@ -1082,29 +1082,29 @@ static int launch_bwd(Mamba2Params p, cudaStream_t stream) {
             {
                 auto kern = m2_hi_bwd_q_kernel<KD, VD, MLOW>;
                 if ((e = set_smem(kern, HiBwdSmem<KD, VD>::total)) != cudaSuccess) return (int)e;
-                kern<<<p.B * p.H * (p.NT - SEG), 256, HiBwdSmem<KD, VD>::total, stream>>>(p);
+                kern<<<p.B * p.H * (p.NT - SEG), 256, HiBwdSmem<KD, VD>::total, stream>>>(p); LLATTN_LAUNCHED();
             }
             {
                 auto kern = m2_seg_dstate_kernel<KD, VD, MLOW>;
                 if ((e = set_smem(kern, SegDSmem<KD, VD, MLOW>::total)) != cudaSuccess) return (int)e;
                 dim3 grid(p.B * p.H * (p.NS - 1), p.LH);
-                kern<<<grid, 256, SegDSmem<KD, VD, MLOW>::total, stream>>>(p);
+                kern<<<grid, 256, SegDSmem<KD, VD, MLOW>::total, stream>>>(p); LLATTN_LAUNCHED();
             }
         }
         {
             dim3 grid((KV / 4 + 255) / 256, p.B * p.H);
-            if (p.LH <= 5) m2_seg_dscan_kernel<5><<<grid, 256, 0, stream>>>(p, KV);
-            else m2_seg_dscan_kernel<MAX_LH_B><<<grid, 256, 0, stream>>>(p, KV);
+            if (p.LH <= 5) { m2_seg_dscan_kernel<5><<<grid, 256, 0, stream>>>(p, KV); LLATTN_LAUNCHED(); }
+            else { m2_seg_dscan_kernel<MAX_LH_B><<<grid, 256, 0, stream>>>(p, KV); LLATTN_LAUNCHED(); }
         }
     }
-    const bool use_tc = (KD == 128 && VD == 64 && (p.NT % 2) == 0 && p.L <= 20 && g_use_tensor_core_path);
+    const bool use_tc = (KD == 128 && VD == 64 && (p.NT % 2) == 0 && p.L <= 20 && g_use_tensor_core_path.load());
     if (use_tc) {
         int rc = mamba2_bwd1_tc_launch(p, stream);
         if (rc != 0) return rc;
     } else {
         auto kern = m2_bwd_fwdorder_kernel<KD, VD, MLOW>;
         if ((e = set_smem(kern, Bwd1Smem<KD, VD, MLOW>::total)) != cudaSuccess) return (int)e;
-        kern<<<p.B * p.H * p.NS, 256, Bwd1Smem<KD, VD, MLOW>::total, stream>>>(p);
+        kern<<<p.B * p.H * p.NS, 256, Bwd1Smem<KD, VD, MLOW>::total, stream>>>(p); LLATTN_LAUNCHED();
     }
     if (use_tc) {
         int rc = mamba2_bwd2_tc_launch(p, stream);
@@ -1112,7 +1112,7 @@ static int launch_bwd(Mamba2Params p, cudaStream_t stream) {
     } else {
         auto kern = m2_bwd_revorder_kernel<KD, VD, MLOW>;
         if ((e = set_smem(kern, Bwd2Smem<KD, VD, MLOW>::total)) != cudaSuccess) return (int)e;
-        kern<<<p.B * p.H * p.NS, 256, Bwd2Smem<KD, VD, MLOW>::total, stream>>>(p);
+        kern<<<p.B * p.H * p.NS, 256, Bwd2Smem<KD, VD, MLOW>::total, stream>>>(p); LLATTN_LAUNCHED();
     }
     return (int)cudaGetLastError();
 }
@@ -1125,19 +1125,23 @@ int mamba2_bwd_dispatch(Mamba2Params p, cudaStream_t stream) {
 
 void mamba2_uncumsum(const float* gc, float* g, long BT, int H, cudaStream_t stream) {
     const long n = BT * H;
-    m2_uncumsum_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(gc, g, BT, H);
+    m2_uncumsum_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(gc, g, BT, H); LLATTN_LAUNCHED();
 }
 
-void mamba2_dg(const Mamba2Params& p, float* dg, cudaStream_t stream) {
+int mamba2_dg(const Mamba2Params& p, float* dg, cudaStream_t stream) {
     dim3 grid(p.B * p.H, (p.NT + 63) / 64);
     const size_t smem = (size_t)(p.NT + p.NS + p.NT * p.LZ + p.NT * (M2_MLOW + 1) + p.NS * (p.LH > 0 ? p.LH : 1) + (size_t)p.LZ * p.NT) * sizeof(float);
-    if (smem > 48 * 1024) cudaFuncSetAttribute(m2_dg_kernel<M2_MLOW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    m2_dg_kernel<M2_MLOW><<<grid, 256, smem, stream>>>(p, dg);
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(m2_dg_kernel<M2_MLOW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+    }
+    m2_dg_kernel<M2_MLOW><<<grid, 256, smem, stream>>>(p, dg); LLATTN_LAUNCHED();
+    return (int)cudaGetLastError();
 }
 
 void cast_f32_to_bf16(const float* src, void* dst, long n, cudaStream_t stream) {
     const long thr = (n + 3) / 4;
-    m2_cast_bf16_kernel<<<(unsigned)((thr + 255) / 256), 256, 0, stream>>>(src, reinterpret_cast<bf16*>(dst), n);
+    m2_cast_bf16_kernel<<<(unsigned)((thr + 255) / 256), 256, 0, stream>>>(src, reinterpret_cast<bf16*>(dst), n); LLATTN_LAUNCHED();
 }
 
 }  // namespace llattn

@@ -1120,7 +1120,7 @@ int mamba2_bwd2_tc_launch(const Mamba2Params& p_in, cudaStream_t stream) {
     const size_t sm = Bwd2TcSmem<M2_MLOW>::total;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
     if (e != cudaSuccess) return (int)e;
-    kern<<<p.B * p.H * p.NS, tc::NTHREADS, sm, stream>>>(p);
+    kern<<<p.B * p.H * p.NS, tc::NTHREADS, sm, stream>>>(p); LLATTN_LAUNCHED();
     return (int)cudaGetLastError();
 }
 
@@ -1138,7 +1138,7 @@ int mamba2_bwd1_tc_launch(const Mamba2Params& p_in, cudaStream_t stream) {
     const size_t sm = Bwd1TcSmem<M2_MLOW>::total;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
     if (e != cudaSuccess) return (int)e;
-    kern<<<p.B * p.H * p.NS, tc::NTHREADS, sm, stream>>>(p);
+    kern<<<p.B * p.H * p.NS, tc::NTHREADS, sm, stream>>>(p); LLATTN_LAUNCHED();
     return (int)cudaGetLastError();
 }
 

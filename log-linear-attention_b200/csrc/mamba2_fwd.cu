@@ -559,25 +559,25 @@ __global__ void __launch_bounds__(256, 1) m2_hi_out_kernel(const Mamba2Params p)
 template <int KD, int VD, int MLOW>
 static int launch_states(Mamba2Params p, cudaStream_t stream) {
     cudaError_t e;
-    if (KD == 128 && VD == 64 && g_use_tensor_core_path) {
+    if (KD == 128 && VD == 64 && g_use_tensor_core_path.load()) {
         int rc = mamba2_seg_state_tc_launch(p, stream);
         if (rc != 0) return rc;
     } else {
         auto kern = m2_seg_state_kernel<KD, VD, MLOW>;
         size_t sm = SegSmem<KD, VD, MLOW>::total;
         if ((e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm)) != cudaSuccess) return (int)e;
-        kern<<<p.B * p.H * (p.NS - 1), 256, sm, stream>>>(p);
+        kern<<<p.B * p.H * (p.NS - 1), 256, sm, stream>>>(p); LLATTN_LAUNCHED();
     }
     const int KV = KD * VD;
     dim3 grid((KV / 4 + 255) / 256, p.B * p.H);
-    m2_seg_scan_kernel<<<grid, 256, 0, stream>>>(p, KV);
+    m2_seg_scan_kernel<<<grid, 256, 0, stream>>>(p, KV); LLATTN_LAUNCHED();
     return (int)cudaGetLastError();
 }
 
 template <int KD, int VD, int MLOW>
 static int launch_fwd(Mamba2Params p, cudaStream_t stream) {
     cudaError_t e;
-    const bool use_tc = (KD == 128 && VD == 64 && (p.NT % 2) == 0 && p.L <= 20 && g_use_tensor_core_path);
+    const bool use_tc = (KD == 128 && VD == 64 && (p.NT % 2) == 0 && p.L <= 20 && g_use_tensor_core_path.load());
     if (p.NS > 1) {
         p.o_has_high = use_tc ? 2 : 1;      // 2: partial output goes to the column-chunk-major scratch
         int rc = launch_states<KD, VD, MLOW>(p, stream);
@@ -589,7 +589,7 @@ static int launch_fwd(Mamba2Params p, cudaStream_t stream) {
             auto kern = m2_hi_out_kernel<KD, VD, MLOW>;
             size_t sm = HiSmem<KD, VD>::total;
             if ((e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm)) != cudaSuccess) return (int)e;
-            kern<<<p.B * p.H * (p.NT - (1 << MLOW)), 256, sm, stream>>>(p);
+            kern<<<p.B * p.H * (p.NT - (1 << MLOW)), 256, sm, stream>>>(p); LLATTN_LAUNCHED();
         }
     }
     if (use_tc) {
@@ -599,12 +599,12 @@ static int launch_fwd(Mamba2Params p, cudaStream_t stream) {
         auto kern = m2_chunk_fwd_kernel<KD, VD, MLOW>;
         size_t sm = FwdSmem<KD, VD, MLOW>::total;
         if ((e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm)) != cudaSuccess) return (int)e;
-        kern<<<p.B * p.H * p.NS, 256, sm, stream>>>(p);
+        kern<<<p.B * p.H * p.NS, 256, sm, stream>>>(p); LLATTN_LAUNCHED();
     }
     return (int)cudaGetLastError();
 }
 
-int g_use_tensor_core_path = 1;
+std::atomic<int> g_use_tensor_core_path{1};
 
 int mamba2_fwd_dispatch(Mamba2Params p, cudaStream_t stream) {
     if (p.K == 128 && p.V == 64) return launch_fwd<128, 64, M2_MLOW>(p, stream);

@@ -476,7 +476,7 @@ int mamba2_fwd_tc_launch(const Mamba2Params& p_in, cudaStream_t stream) {
     const size_t sm = FwdTcSmem<M2_MLOW>::total;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
     if (e != cudaSuccess) return (int)e;
-    kern<<<p.B * p.H * p.NS, tc::NTHREADS, sm, stream>>>(p);
+    kern<<<p.B * p.H * p.NS, tc::NTHREADS, sm, stream>>>(p); LLATTN_LAUNCHED();
     return (int)cudaGetLastError();
 }
 

@@ -644,7 +644,7 @@ int mamba2_seg_state_tc_launch(const Mamba2Params& p_in, cudaStream_t stream) {
     const size_t sm = SegStateTcSmem<M2_MLOW>::total;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
     if (e != cudaSuccess) return (int)e;
-    kern<<<p.B * p.H * (p.NS - 1), tc::NTHREADS, sm, stream>>>(p);
+    kern<<<p.B * p.H * (p.NS - 1), tc::NTHREADS, sm, stream>>>(p); LLATTN_LAUNCHED();
     return (int)cudaGetLastError();
 }
 
@@ -660,13 +660,13 @@ int mamba2_hi_out_tc_launch(const Mamba2Params& p_in, cudaStream_t stream) {
         const size_t sm = HiOutTcSmem<M2_MLOW, 5>::total;
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
         if (e != cudaSuccess) return (int)e;
-        kern<<<p.B * p.H * (p.NS - 1), tc::NTHREADS, sm, stream>>>(p);
+        kern<<<p.B * p.H * (p.NS - 1), tc::NTHREADS, sm, stream>>>(p); LLATTN_LAUNCHED();
     } else {
         auto kern = m2_hi_out_tc_kernel<M2_MLOW, 8>;
         const size_t sm = HiOutTcSmem<M2_MLOW, 8>::total;
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
         if (e != cudaSuccess) return (int)e;
-        kern<<<p.B * p.H * (p.NS - 1), tc::NTHREADS, sm, stream>>>(p);
+        kern<<<p.B * p.H * (p.NS - 1), tc::NTHREADS, sm, stream>>>(p); LLATTN_LAUNCHED();
     }
     return (int)cudaGetLastError();
 }
@@ -686,7 +686,7 @@ int mamba2_hi_bwd_tc_launch(const Mamba2Params& p_in, cudaStream_t stream) {
     // one launch per window of five segment levels (a single one up to T = 16384); dq, the q.dq totals and
     // the per-level outputs of different windows add up or are disjoint
     for (p.lev_lo = 0; p.lev_lo < p.LH; p.lev_lo += tcs::MAXLH)
-        kern<<<p.B * p.H * (p.NS - 1), tc::NTHREADS, sm, stream>>>(p);
+        kern<<<p.B * p.H * (p.NS - 1), tc::NTHREADS, sm, stream>>>(p); LLATTN_LAUNCHED();
     return (int)cudaGetLastError();
 }
 

@@ -12,6 +12,7 @@
 #include <cuda_runtime.h>
 
 #include "../../include/llattn.h"
+#include "launch_count.h"
 
 namespace llattn {
 
@@ -216,6 +217,7 @@ int llattn_mamba2_prep_fwd(const void* x, const void* dt_raw, const float* dt_bi
     else if (lpr == 16) LLATTN_PREP_DISPATCH(llattn::m2_prep_fwd_kernel, 16, lambda_mode, ARGS_F);
     else LLATTN_PREP_DISPATCH(llattn::m2_prep_fwd_kernel, 32, lambda_mode, ARGS_F);
 #undef ARGS_F
+    LLATTN_LAUNCHED();
     return (int)cudaGetLastError();
 }
 
@@ -241,6 +243,7 @@ int llattn_mamba2_prep_bwd(const void* x, const void* dt_raw, const float* dt_bi
     else if (lpr == 16) LLATTN_PREP_DISPATCH(llattn::m2_prep_bwd_kernel, 16, lambda_mode, ARGS_B);
     else LLATTN_PREP_DISPATCH(llattn::m2_prep_bwd_kernel, 32, lambda_mode, ARGS_B);
 #undef ARGS_B
+    LLATTN_LAUNCHED();
     return (int)cudaGetLastError();
 }
 
@@ -262,6 +265,7 @@ int llattn_mamba2_residual(const void* o, const void* x, const float* D, void* y
     else if (lpr == 16) RES(16);
     else RES(32);
 #undef RES
+    LLATTN_LAUNCHED();
     return (int)cudaGetLastError();
 }
 

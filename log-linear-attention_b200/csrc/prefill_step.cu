@@ -200,8 +200,8 @@ int llattn_mamba2_final_state(const void* k, const void* v, const float* g, floa
     using bf = __nv_bfloat16;
     dim3 grid(B * H, L);
     cudaStream_t st = (cudaStream_t)stream;
-    if (K == 128) llattn::mamba2_final_state_kernel<128, 64><<<grid, 256, 0, st>>>((const bf*)k, (const bf*)v, g, states, B, T, H, G, L);
-    else llattn::mamba2_final_state_kernel<64, 64><<<grid, 256, 0, st>>>((const bf*)k, (const bf*)v, g, states, B, T, H, G, L);
+    if (K == 128) { llattn::mamba2_final_state_kernel<128, 64><<<grid, 256, 0, st>>>((const bf*)k, (const bf*)v, g, states, B, T, H, G, L); LLATTN_LAUNCHED(); }
+    else { llattn::mamba2_final_state_kernel<64, 64><<<grid, 256, 0, st>>>((const bf*)k, (const bf*)v, g, states, B, T, H, G, L); LLATTN_LAUNCHED(); }
     return (int)cudaGetLastError();
 }
 
@@ -218,6 +218,7 @@ int llattn_mamba2_step(float* states, const void* q, const void* k, const void* 
         llattn::mamba2_step_kernel<16><<<B * H, 256, sm, st>>>(states, (const bf*)q, (const bf*)k, (const bf*)v, g, (const bf*)lambda, (bf*)o, H, G, K, V, L, carry_level);
     else
         llattn::mamba2_step_kernel<32><<<B * H, 256, sm, st>>>(states, (const bf*)q, (const bf*)k, (const bf*)v, g, (const bf*)lambda, (bf*)o, H, G, K, V, L, carry_level);
+    LLATTN_LAUNCHED();
     return (int)cudaGetLastError();
 }
 

@@ -8,6 +8,8 @@
 namespace llattn {
 namespace tma {
 
+constexpr int ERR_TENSOR_MAP = -8;   // LLATTN_ERR_TENSOR_MAP of the public header: the driver refused a tensor map
+
 // A (BT, NH, C) bf16 tensor (C contiguous) seen as a rank-3 map; a box is 64 columns x 1 head x
 // `box_rows` rows, 128-byte swizzled: exactly one 64-column panel of a shared-memory operand tile.
 inline int make_panel_map(CUtensorMap* out, const void* base, long BT, int NH, int C, int box_rows) {
@@ -19,7 +21,7 @@ inline int make_panel_map(CUtensorMap* out, const void* base, long BT, int NH, i
         void* ptr = nullptr;
         cudaDriverEntryPointQueryResult qres;
         cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres);
-        if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || !ptr) return 999;
+        if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || !ptr) return ERR_TENSOR_MAP;
         fn = reinterpret_cast<EncodeFn>(ptr);
     }
     const cuuint64_t dims[3] = {(cuuint64_t)C, (cuuint64_t)NH, (cuuint64_t)BT};
@@ -29,7 +31,7 @@ inline int make_panel_map(CUtensorMap* out, const void* base, long BT, int NH, i
     CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS ? 0 : 1000 + (int)r;
+    return r == CUDA_SUCCESS ? 0 : ERR_TENSOR_MAP;
 }
 
 // A (BT, NH, C) fp32 tensor; a box is 32 columns (128 bytes) x 1 head x `box_rows` rows, 128-byte
@@ -43,7 +45,7 @@ inline int make_f32_box_map(CUtensorMap* out, const void* base, long BT, int NH,
         void* ptr = nullptr;
         cudaDriverEntryPointQueryResult qres;
         cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres);
-        if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || !ptr) return 999;
+        if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || !ptr) return ERR_TENSOR_MAP;
         fn = reinterpret_cast<EncodeFn>(ptr);
     }
     const cuuint64_t dims[3] = {(cuuint64_t)C, (cuuint64_t)NH, (cuuint64_t)BT};
@@ -53,7 +55,7 @@ inline int make_f32_box_map(CUtensorMap* out, const void* base, long BT, int NH,
     CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void*>(base), dims, strides, box, estr,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS ? 0 : 1000 + (int)r;
+    return r == CUDA_SUCCESS ? 0 : ERR_TENSOR_MAP;
 }
 
 #ifdef __CUDACC__

@@ -102,50 +102,6 @@ __device__ __forceinline__ void gemm_mm(uint32_t d_tmem, uint32_t a_saddr, uint3
         mma_ss(d_tmem, da + ((kk * ROW_BYTES) >> 4), db + ((kk * ROW_BYTES) >> 4), idesc, accumulate || kk > 0);
     }
 }
-// ---- 64-bit descriptor variants (the whole descriptor kept in one register pair; a few more instructions
-//      per MMA than the 32-bit form above).  No kernel issues through them any more: m2_hi_bwd_tc_kernel did
-//      while it returned wrong reader gradients with the faster 32-bit form, which turned out to be its do-tile
-//      release overtaking the loads (see that kernel), not the descriptors.  Kept for A/B checks.
-__device__ __forceinline__ uint64_t desc64_kmajor(uint32_t saddr) {
-    return (uint64_t(DESC_HI) << 32) | uint64_t(desc_lo_kmajor(saddr));
-}
-__device__ __forceinline__ uint64_t desc64_mnmajor(uint32_t saddr, uint32_t panel_bytes) {
-    return (uint64_t(DESC_HI) << 32) | uint64_t(desc_lo_mnmajor(saddr, panel_bytes));
-}
-__device__ __forceinline__ void mma_ss64(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, bool accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"((uint32_t)accumulate)
-        : "memory");
-}
-template <int A_ROWS, int B_ROWS, int KRED>
-__device__ __forceinline__ void gemm_kk64(uint32_t d_tmem, uint32_t a_saddr, uint32_t b_saddr, uint32_t idesc, bool accumulate) {
-    const uint64_t da = desc64_kmajor(a_saddr), db = desc64_kmajor(b_saddr);
-#pragma unroll
-    for (int kk = 0; kk < KRED; kk += 16) {
-        const uint32_t ka = (kk >> 6) * A_ROWS * ROW_BYTES + (kk & 63) * 2;
-        const uint32_t kb = (kk >> 6) * B_ROWS * ROW_BYTES + (kk & 63) * 2;
-        mma_ss64(d_tmem, da + (ka >> 4), db + (kb >> 4), idesc, accumulate || kk > 0);
-    }
-}
-template <int A_ROWS, int B_ROWS, int KRED>
-__device__ __forceinline__ void gemm_km64(uint32_t d_tmem, uint32_t a_saddr, uint32_t b_saddr, uint32_t idesc, bool accumulate) {
-    const uint64_t da = desc64_kmajor(a_saddr), db = desc64_mnmajor(b_saddr, B_ROWS * ROW_BYTES);
-#pragma unroll
-    for (int kk = 0; kk < KRED; kk += 16) {
-        const uint32_t ka = (kk >> 6) * A_ROWS * ROW_BYTES + (kk & 63) * 2;
-        mma_ss64(d_tmem, da + (ka >> 4), db + ((kk * ROW_BYTES) >> 4), idesc, accumulate || kk > 0);
-    }
-}
-template <int A_ROWS, int B_ROWS, int KRED>
-__device__ __forceinline__ void gemm_mm64(uint32_t d_tmem, uint32_t a_saddr, uint32_t b_saddr, uint32_t idesc, bool accumulate) {
-    const uint64_t da = desc64_mnmajor(a_saddr, A_ROWS * ROW_BYTES), db = desc64_mnmajor(b_saddr, B_ROWS * ROW_BYTES);
-#pragma unroll
-    for (int kk = 0; kk < KRED; kk += 16) {
-        mma_ss64(d_tmem, da + ((kk * ROW_BYTES) >> 4), db + ((kk * ROW_BYTES) >> 4), idesc, accumulate || kk > 0);
-    }
-}
 // run-time sized variants (self-test)
 __device__ __forceinline__ void gemm_kk(uint32_t d_tmem, uint32_t a_saddr, int a_rows, uint32_t b_saddr, int b_rows,
                                         int kred, uint32_t idesc, bool accumulate) {
@@ -197,9 +153,9 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     *abort = 1;
     return false;
 }
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t limit = SPIN_LIMIT) {
     const uint32_t a = smem_addr(bar);
-    for (uint32_t it = 0; it < SPIN_LIMIT; ++it) {
+    for (uint32_t it = 0; it < limit; ++it) {
         uint32_t done;
         asm volatile(
             "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"

@@ -4,6 +4,7 @@
 #include "llattn_common.cuh"
 #include "umma.cuh"
 #include "../../include/llattn.h"
+#include "llattn_testing.h"
 
 namespace llattn {
 
@@ -156,6 +157,19 @@ __global__ void __launch_bounds__(128, 1) umma_cycles_kernel(int N, int kred, in
 
 }  // namespace llattn
 
+namespace llattn {
+// waits on a barrier that never completes; gives up after `limit` polls and reports like the production kernels
+__global__ void wait_timeout_kernel(uint32_t limit, int* status) {
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) {
+        umma::mbar_init(&bar, 1);
+        umma::fence_mbar_init();
+    }
+    __syncthreads();
+    if (threadIdx.x == 0 && !umma::mbar_wait(&bar, 0, limit)) atomicExch(status, 1);
+}
+}  // namespace llattn
+
 extern "C" int llattn_selftest_umma_cycles(int N, int kred, int mode, int reps, int issuers, long long* cycles, int* err_flag,
                                            void* stream) {
     if (!cycles || !err_flag) return LLATTN_ERR_NULL;
@@ -165,7 +179,7 @@ extern "C" int llattn_selftest_umma_cycles(int N, int kred, int mode, int reps, 
     const size_t sm = 65536 + 1024;
     cudaError_t e = cudaFuncSetAttribute(llattn::umma_cycles_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
     if (e != cudaSuccess) return (int)e;
-    llattn::umma_cycles_kernel<<<1, 128, sm, (cudaStream_t)stream>>>(N, kred, mode, reps, issuers, cycles, err_flag);
+    llattn::umma_cycles_kernel<<<1, 128, sm, (cudaStream_t)stream>>>(N, kred, mode, reps, issuers, cycles, err_flag); LLATTN_LAUNCHED();
     return (int)cudaGetLastError();
 }
 
@@ -178,6 +192,13 @@ extern "C" int llattn_selftest_umma(const void* A, const void* B, float* D, int 
     cudaError_t e = cudaFuncSetAttribute(llattn::umma_selftest_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
     if (e != cudaSuccess) return (int)e;
     llattn::umma_selftest_kernel<<<1, 128, sm, (cudaStream_t)stream>>>((const llattn::bf16*)A, (const llattn::bf16*)B, D, N, kred,
-                                                                        mode, err_flag);
+                                                                        mode, err_flag); LLATTN_LAUNCHED();
+    return (int)cudaGetLastError();
+}
+
+extern "C" int llattn_selftest_wait_timeout(int spin_limit, int* status_dev, void* stream) {
+    if (!status_dev) return LLATTN_ERR_NULL;
+    const unsigned limit = spin_limit < 1 ? 1u : (spin_limit > (1 << 20) ? (1u << 20) : (unsigned)spin_limit);
+    llattn::wait_timeout_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(limit, status_dev); LLATTN_LAUNCHED();
     return (int)cudaGetLastError();
 }

@@ -14,6 +14,7 @@ ERRORS = {
     -5: "workspace missing, misaligned or too small",
     -6: "null pointer",
     -7: "problem needs more scratch than the built-in static array holds",
+    -8: "the driver refused a TMA tensor map for these pointers",
 }
 
 _SHAPE = [ctypes.c_int] * 7
@@ -81,12 +82,40 @@ def lib():
     L.llattn_gdn_bwd_kept.argtypes = [_P] * 15 + [_P, ctypes.c_size_t, _P, ctypes.c_size_t] + [ctypes.c_int] * 6 + [_P]
     L.llattn_selftest_umma_cycles.restype = ctypes.c_int
     L.llattn_selftest_umma_cycles.argtypes = [ctypes.c_int] * 5 + [_P, _P, _P]
-    L.llattn_set_tensor_core_path.restype = None
-    L.llattn_set_tensor_core_path.argtypes = [ctypes.c_int]
+    L.llattn_testing_use_tensor_core_path.restype = None        # test-only symbol (csrc/llattn_testing.h)
+    L.llattn_testing_use_tensor_core_path.argtypes = [ctypes.c_int]
+    L.llattn_selftest_wait_timeout.restype = ctypes.c_int       # test-only symbol
+    L.llattn_selftest_wait_timeout.argtypes = [ctypes.c_int, _P, _P]
+    L.llattn_kernel_launches.restype = ctypes.c_ulonglong
+    L.llattn_kernel_launches.argtypes = []
+    L.llattn_workspace_status.restype = ctypes.c_int
+    L.llattn_workspace_status.argtypes = [_P, _P, _P]
+    L.llattn_static_scratch_status.restype = ctypes.c_int
+    L.llattn_static_scratch_status.argtypes = [_P, _P]
     L.llattn_selftest_umma.restype = ctypes.c_int
     L.llattn_selftest_umma.argtypes = [_P, _P, _P, ctypes.c_int, ctypes.c_int, ctypes.c_int, _P, _P]
     _lib = L
     return L
+
+
+# When set, every Mamba-2 driver call reads its workspace's status word after the launch (one stream
+# synchronisation per call) and raises if a kernel gave up on a bounded wait.  Off by default: the
+# drivers then never synchronise, like the reference's.  The test-suite, the smoke check and the
+# benchmark switch it on or read the word themselves.
+CHECK_STATUS = os.environ.get("LLATTN_CHECK_STATUS", "0") not in ("", "0")
+
+
+def workspace_status(ws, stream) -> int:
+    """Status word of a workspace tensor that a call on `stream` used (synchronises the stream)."""
+    out = ctypes.c_int(-1)
+    rc = lib().llattn_workspace_status(ws.data_ptr(), ctypes.byref(out), stream)
+    check(rc, "llattn_workspace_status")
+    return out.value
+
+
+def raise_on_status(ws, stream, what: str):
+    if workspace_status(ws, stream) != 0:
+        raise RuntimeError(f"{what}: a kernel gave up on a bounded wait (status word set); the outputs are not valid")
 
 
 def check(rc: int, what: str):

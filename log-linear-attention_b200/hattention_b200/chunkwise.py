@@ -25,6 +25,12 @@ def _check(q, k, v, g, l, head_first, level_base, htype, chunk_size):
         raise NotImplementedError("chunk_size must be 64")
     if not (q.is_cuda and k.is_cuda and v.is_cuda and g.is_cuda and l.is_cuda):
         raise RuntimeError("log-linear attention kernels need CUDA tensors (there is no CPU path)")
+    if not (q.dtype == k.dtype == v.dtype == torch.bfloat16):
+        # the reference computes in the dtype it is given (hattention/kernel.py:127-135: fp32 inputs reach its
+        # dots as fp32); these kernels take bf16 operands with fp32 accumulation only, and rounding other
+        # dtypes silently would not be the same function
+        raise NotImplementedError(f"q / k / v must be bfloat16 (got {q.dtype}, {k.dtype}, {v.dtype}): the kernels compute with "
+                                  "bf16 operands and fp32 accumulation; the reference's fp32 mode is not implemented")
     B, T, G, K = k.shape
     _, _, H, V = v.shape
     L = l.shape[-1]
@@ -85,6 +91,8 @@ def chunkwise_fwd(
                                    o.data_ptr(), g_cum.data_ptr(), ws.data_ptr(), ws.numel(),
                                    B, T, H, G, K, V, L, _stream())
         _lib.check(rc, "llattn_mamba2_fwd")
+        if _lib.CHECK_STATUS:
+            _lib.raise_on_status(ws, _stream(), "llattn_mamba2_fwd")
         if keep_workspace is not None:
             keep_workspace.append(ws)
         ht = final_states(k_, v_, g_, L) if output_final_state else None
@@ -143,4 +151,6 @@ def chunkwise_bwd(
                                          fws.data_ptr() if fws is not None else None, fws.numel() if fws is not None else 0,
                                          B, T, H, G, K, V, L, _stream())
         _lib.check(rc, "llattn_mamba2_bwd_saved")
+        if _lib.CHECK_STATUS:
+            _lib.raise_on_status(ws, _stream(), "llattn_mamba2_bwd_saved")
     return dq, dk, dv, dg, dl

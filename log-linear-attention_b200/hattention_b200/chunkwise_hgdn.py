@@ -118,100 +118,6 @@ def chunkwise_fwd(
     return g_cum, o, Aw, Au, None
 
 
-def _levels_matrix(n: int, device) -> torch.Tensor:
-    idx = torch.arange(n, device=device)
-    x = idx[:, None] ^ idx[None, :]
-    lev = torch.zeros_like(x)
-    nz = x > 0
-    lev[nz] = torch.floor(torch.log2(x[nz].float())).long() + 1
-    return lev
-
-
-def _gdn_chunkwise_torch(q, k, v, b, g, l):
-    """Differentiable fp32 restatement of the chunkwise GDN forward in batched torch ops on the
-    GPU (q, k already normalised / scaled; one q/k per head).  Test infrastructure for
-    `_chunkwise_bwd_autograd`; the product path is the CUDA kernels.
-    Same formulas as csrc/gdn_fwd.cu; levels are scanned per level (chunkwise_hgdn.py:718-788)."""
-    B, T, H, K = q.shape
-    V = v.shape[-1]
-    L = l.shape[-1]
-    C = CHUNK
-    NT = T // C
-    dev = q.device
-    f = lambda x: x.reshape(B, NT, C, H, -1).permute(0, 3, 1, 2, 4)        # (B,H,NT,C,*)
-    qc, kc, vc, lc = f(q), f(k), f(v), f(l)
-    bc = b.reshape(B, NT, C, H).permute(0, 3, 1, 2)                         # (B,H,NT,C)
-    G = torch.cumsum(g.reshape(B, NT, C, H).permute(0, 3, 1, 2), dim=-1)
-    gl = G[..., -1]
-    tril = torch.tril(torch.ones(C, C, dtype=torch.bool, device=dev))
-    stril = torch.tril(torch.ones(C, C, dtype=torch.bool, device=dev), -1)
-    diff = (G[..., :, None] - G[..., None, :]).masked_fill(~tril, float("-inf"))
-    Gam = torch.exp(diff)
-    A = (bc[..., :, None] * (kc @ kc.transpose(-1, -2))).masked_fill(~stril, 0.0)
-    eye = torch.eye(C, device=dev, dtype=q.dtype).expand(B, H, NT, C, C)
-    Aw = torch.linalg.solve_triangular(eye + A, eye, upper=False)
-    Au = torch.linalg.solve_triangular(eye + A * Gam, eye, upper=False)
-    w = Aw @ (bc[..., None] * kc)
-    u = Au @ (bc[..., None] * vc)
-    kd = kc * torch.exp(gl[..., None] - G)[..., None]
-    wd = w * torch.exp(G)[..., None]
-    QK = (qc @ kc.transpose(-1, -2)).masked_fill(~tril, 0.0)
-    qd = torch.exp(G)[..., None] * (qc - QK @ w)
-    lev = _levels_matrix(C, dev)
-    lam = torch.gather(lc, 4, lev[None, None, None].expand(B, H, NT, C, C))
-    o = ((QK @ Aw) * Gam * bc[..., None, :] * lam) @ vc                      # (B,H,NT,C,V)
-    ell_h0 = get_num_levels(C, 2)
-    Lc = ceil_log(NT, 2) if NT > 1 else 0
-    outs = [o[:, :, c] for c in range(NT)]
-    if Lc > 0:
-        lv = torch.arange(Lc, device=dev)
-        S = torch.zeros(B, H, Lc, K, V, device=dev, dtype=q.dtype)
-        for c in range(NT):
-            bit = ((c >> lv) & 1).to(q.dtype)                                # (Lc,)
-            reset = (((c + 1) % (2 << lv)) == 0).to(q.dtype)
-            lam_c = lc[:, :, c, :, ell_h0:ell_h0 + Lc] * bit                  # (B,H,C,Lc)
-            R = qd[:, :, c, None] @ S                                        # (B,H,Lc,C,V)
-            outs[c] = outs[c] + (lam_c.permute(0, 1, 3, 2)[..., None] * R).sum(2)
-            if c + 1 < NT:
-                Z = wd[:, :, c, None] @ S
-                Vh = u[:, :, c, None] * (1 - bit)[None, None, :, None, None] - Z
-                S = (torch.exp(gl[:, :, c])[..., None, None, None] * S + kd[:, :, c, None].transpose(-1, -2) @ Vh) \
-                    * (1 - reset)[None, None, :, None, None]
-    o = torch.stack(outs, dim=2)                                             # (B,H,NT,C,V)
-    return o.permute(0, 2, 3, 1, 4).reshape(B, T, H, V)
-
-
-def _gdn_prologue_torch(q, k, v, b, g, l):
-    """Chunk-local part of the forward (everything before the scan over chunks) as batched fp32
-    torch ops: returns qd, wd, kd, u, the intra-chunk output and the chunk totals of g, all
-    (B,H,NT,C,*).  Test infrastructure: differentiated by autograd in `_chunkwise_bwd_staged`."""
-    B, T, H, K = q.shape
-    C = CHUNK
-    NT = T // C
-    dev = q.device
-    f = lambda x: x.reshape(B, NT, C, H, -1).permute(0, 3, 1, 2, 4)
-    qc, kc, vc, lc = f(q), f(k), f(v), f(l)
-    bc = b.reshape(B, NT, C, H).permute(0, 3, 1, 2)
-    G = torch.cumsum(g.reshape(B, NT, C, H).permute(0, 3, 1, 2), dim=-1)
-    gl = G[..., -1]
-    tril = torch.tril(torch.ones(C, C, dtype=torch.bool, device=dev))
-    stril = torch.tril(torch.ones(C, C, dtype=torch.bool, device=dev), -1)
-    Gam = torch.exp((G[..., :, None] - G[..., None, :]).masked_fill(~tril, float("-inf")))
-    A = (bc[..., :, None] * (kc @ kc.transpose(-1, -2))).masked_fill(~stril, 0.0)
-    eye = torch.eye(C, device=dev, dtype=q.dtype).expand(B, H, NT, C, C)
-    Aw = torch.linalg.solve_triangular(eye + A, eye, upper=False)
-    Au = torch.linalg.solve_triangular(eye + A * Gam, eye, upper=False)
-    w = Aw @ (bc[..., None] * kc)
-    u = Au @ (bc[..., None] * vc)
-    kd = kc * torch.exp(gl[..., None] - G)[..., None]
-    wd = w * torch.exp(G)[..., None]
-    QK = (qc @ kc.transpose(-1, -2)).masked_fill(~tril, 0.0)
-    qd = torch.exp(G)[..., None] * (qc - QK @ w)
-    lam = torch.gather(lc, 4, _levels_matrix(C, dev)[None, None, None].expand(B, H, NT, C, C))
-    o = ((QK @ Aw) * Gam * bc[..., None, :] * lam) @ vc
-    return qd, wd, kd, u, o, gl
-
-
 def chunkwise_bwd(q, k, v, b, g, l, Aw, Au, do, head_first, level_base, htype, chunk_size, fwd_workspace=None, **unused):
     """Gradients (dq, dk, dv, db, dg, dl), fp32, of the driver for normalised q, k (signature of
     chunkwise_hgdn.py:799-817; `g` is the in-chunk cumulative sum returned by chunkwise_fwd).
@@ -245,55 +151,6 @@ def chunkwise_bwd(q, k, v, b, g, l, Aw, Au, do, head_first, level_base, htype, c
             rc = lib.llattn_gdn_bwd(*head, *tail)
         _lib.check(rc, "llattn_gdn_bwd_kept" if kept else "llattn_gdn_bwd")
     return dq, dk, dv, db, dg, dl
-
-
-def _chunkwise_bwd_staged(q, k, v, b, g, l, Aw, Au, do):
-    """Cross-check used by the test-suite: the CUDA level stage (`llattn_gdn_bwd_levels`) followed by
-    autograd through the batched torch restatement of the chunk-local part."""
-    B, T, H, K = q.shape
-    V, L = v.shape[-1], l.shape[-1]
-    lib = _lib.lib()
-    NT = T // CHUNK
-    with torch.cuda.device(q.device):
-        q_, k_, v_, b_, l_, do_, Aw_, Au_ = (x.to(torch.bfloat16).contiguous() for x in (q, k, v, b, l, do, Aw, Au))
-        gc_ = g.to(torch.float32).contiguous()
-        d_qd = torch.empty(B, T, H, K, dtype=torch.float32, device=q.device)
-        d_wd = torch.empty_like(d_qd)
-        d_kd = torch.empty_like(d_qd)
-        d_u = torch.empty(B, T, H, V, dtype=torch.bfloat16, device=q.device)
-        d_gl = torch.empty(B, NT, H, dtype=torch.float32, device=q.device)
-        dl = torch.zeros(B, T, H, L, dtype=torch.float32, device=q.device)
-        ws = torch.empty(lib.llattn_gdn_bwd_levels_workspace_bytes(B, T, H, K, V, L), dtype=torch.uint8, device=q.device)
-        rc = lib.llattn_gdn_bwd_levels(q_.data_ptr(), k_.data_ptr(), v_.data_ptr(), b_.data_ptr(), gc_.data_ptr(), l_.data_ptr(),
-                                       Aw_.data_ptr(), Au_.data_ptr(), do_.data_ptr(), d_qd.data_ptr(), d_wd.data_ptr(),
-                                       d_kd.data_ptr(), d_u.data_ptr(), d_gl.data_ptr(), dl.data_ptr(), ws.data_ptr(), ws.numel(),
-                                       B, T, H, K, V, L, torch.cuda.current_stream().cuda_stream)
-        _lib.check(rc, "llattn_gdn_bwd_levels")
-        del ws
-        graw = gc_.clone()
-        gv = graw.view(B, NT, CHUNK, H)
-        gv[:, :, 1:] = gv[:, :, 1:] - gc_.view(B, NT, CHUNK, H)[:, :, :-1]
-        f = lambda x: x.reshape(B, NT, CHUNK, H, -1).permute(0, 3, 1, 2, 4).float()
-        with torch.enable_grad():
-            ins = [x.detach().float().requires_grad_(True) for x in (q_, k_, v_, b_, graw, l_)]
-            outs = _gdn_prologue_torch(*ins)
-            grads = torch.autograd.grad(outs, ins, [f(d_qd), f(d_wd), f(d_kd), f(d_u), f(do_), d_gl.permute(0, 2, 1)])
-        dq, dk, dv, db, dg, dl_low = grads
-        return dq, dk, dv, db, dg, dl + dl_low
-
-
-def _chunkwise_bwd_autograd(q, k, v, b, g, l, do):
-    """Whole-path autograd through `_gdn_chunkwise_torch` (fp32, a Python loop over chunks): the
-    slow cross-check that the test-suite compares `chunkwise_bwd` with."""
-    B, T, H = g.shape
-    graw = g.float().clone()
-    gv = graw.view(B, T // CHUNK, CHUNK, H)
-    gv[:, :, 1:] = gv[:, :, 1:] - g.float().view(B, T // CHUNK, CHUNK, H)[:, :, :-1]
-    with torch.enable_grad():
-        ins = [x.detach().float().requires_grad_(True) for x in (q, k, v, b, graw, l)]
-        o = _gdn_chunkwise_torch(*ins)
-        grads = torch.autograd.grad(o, ins, do.float())
-    return tuple(grads)
 
 
 # Largest forward workspace (chunk matrices + level states, bytes) that gdn_forward keeps for the backward

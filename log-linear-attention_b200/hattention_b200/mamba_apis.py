@@ -165,7 +165,7 @@ def hmamba_chunk_scan_combined(
     if dt_bias is not None:
         dt = dt + dt_bias[None, None, :]
     dt = torch.nn.functional.softplus(dt)
-    x = x * dt[..., None]
+    x = (x * dt[..., None]).to(x.dtype)      # an fp32 dt must not promote the kernel's v operand (bf16 only)
     g = A[None, None, :] * dt
     lam = compute_lambda(L[None, None], dl, lambda_mode)
     y = hattention_kernel(q=C, k=B, v=x, b=None, g=g, l=lam, scale=None, head_first=False,

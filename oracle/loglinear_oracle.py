@@ -152,6 +152,65 @@ def mamba2_chunkwise(q, k, v, g, l, chunk: int = 64) -> torch.Tensor:
     return torch.stack(outs, dim=1).reshape(B, T, H, V)
 
 
+def mamba2_chunkwise_blocked(q, k, v, g, l, chunk: int = 64) -> torch.Tensor:
+    """The same chunkwise function as `mamba2_chunkwise`, with every inter-chunk level evaluated
+    for all chunks at once instead of by a scan over chunks, so that sequences of 16K-64K tokens
+    finish in seconds.  It uses the closed form of the state a reader chunk sees
+    (chunkwise.py:110-280: contributor chunks are the first half of the block of 2^(l+1) chunks
+    that contains the reader, decayed by the chunk totals in between):
+
+        H_l[c] = sum_{c' in [b, b + 2^l)} exp(GL[c-1] - GL[c']) KV_c',   b = (c >> (l+1)) << (l+1)
+
+    with GL the running sum of the chunk totals of g.  Checked against `mamba2_chunkwise` and the
+    reference-generated fixtures in tests/test_oracle_golden.py."""
+    B, T, H, V = v.shape
+    K = q.shape[-1]
+    L = l.shape[-1]
+    C = chunk
+    assert T % C == 0
+    NT = T // C
+    qh = _expand_groups(q, H).reshape(B, NT, C, H, K)
+    kh = _expand_groups(k, H).reshape(B, NT, C, H, K)
+    vc = v.reshape(B, NT, C, H, V)
+    lc = l.reshape(B, NT, C, H, L)
+    Gc = torch.cumsum(g.reshape(B, NT, C, H), dim=2)
+    lev = torch.from_numpy(levels_matrix(C))
+    tril = lev >= 0
+    diff = (Gc[:, :, :, None, :] - Gc[:, :, None, :, :]).masked_fill(~tril[None, None, :, :, None], float("-inf"))
+    lam = torch.gather(lc.permute(0, 1, 3, 2, 4), 4,
+                       lev.clamp(min=0)[None, None, None].expand(B, NT, H, C, C))
+    P = torch.einsum("bcihk,bcjhk->bchij", qh, kh) * lam * torch.exp(diff).permute(0, 1, 4, 2, 3)
+    o = torch.einsum("bchij,bcjhv->bcihv", P, vc)
+
+    ell_h0 = get_num_levels(C)
+    Lc = ceil_log2(NT) if NT > 1 else 0
+    if ell_h0 + Lc > L:
+        raise ValueError("not enough lambda levels")
+    glast = Gc[:, :, -1, :]                                         # (B,NT,H)
+    kv = torch.einsum("bcjhk,bcjh,bcjhv->bchkv", kh, torch.exp(glast[:, :, None, :] - Gc), vc)
+    qs = qh * torch.exp(Gc)[..., None]                              # q_i exp(G_i)
+    for ell in range(Lc):
+        half = 1 << ell
+        period = 2 * half
+        nblk = -(-NT // period)
+        pad = nblk * period - NT
+
+        def blocks(x):
+            if pad:
+                x = torch.cat([x, x.new_zeros((B, pad) + tuple(x.shape[2:]))], dim=1)
+            return x.reshape((B, nblk, period) + tuple(x.shape[2:]))
+
+        GL = torch.cumsum(blocks(glast), dim=2)                     # running chunk totals inside each block
+        mid = GL[:, :, half - 1:half]                               # total up to the last contributor
+        F = torch.einsum("bjch,bjchkv->bjhkv", torch.exp(mid - GL[:, :, :half]), blocks(kv)[:, :, :half])
+        dec = torch.exp(GL[:, :, half - 1:period - 1] - mid)        # reader m sees exp(GL[c-1] - GL[mid-1])
+        w = blocks(lc[..., ell_h0 + ell])[:, :, half:] * dec[:, :, :, None, :]          # (B,nblk,half,C,H)
+        add = torch.einsum("bjmihk,bjhkv,bjmih->bjmihv", blocks(qs)[:, :, half:], F, w)
+        add = torch.cat([add.new_zeros(add.shape), add], dim=2).reshape(B, nblk * period, C, H, V)
+        o = o + add[:, :NT]
+    return o.reshape(B, T, H, V)
+
+
 class FenwickState:
     """Out-of-place restatement of `HState` (recurrent.py:9-131): one (B,H,K,V) state and
     one token count per level; `cascade` merges level i into i+1 when it is full."""
@@ -243,6 +302,83 @@ def gdn_materialized(q, k, v, b, g, l) -> torch.Tensor:
         S = sum(l[:, t, :, int(lev[t, s])][:, :, None, None] * contrib[s] for s in range(t + 1))
         outs.append(torch.einsum("bhk,bhkv->bhv", q[:, t], S))
     return torch.stack(outs, dim=1)
+
+
+def gdn_chunkwise(q, k, v, b, g, l, chunk: int = 64) -> torch.Tensor:
+    """Chunkwise form of the delta-rule structure for normalised q, k (one per head), as the
+    reference's driver organises it (chunkwise_hgdn.py:566-788 with the chunk matrices of
+    fla_future/chunk_scaled_dot_kkt.py, solve_tril.py, wy_fast.py, chunk_delta_h.py):
+
+      per chunk  Gam[i,j] = exp(G_i - G_j) [j <= i] ; A = strict_tril(beta_i k_i.k_j)
+                 Aw = (I + A)^-1 ; Au = (I + A * Gam)^-1 ; w = Aw (beta k) ; u = Au (beta v)
+                 kd = k exp(G_last - G) ; wd = w exp(G) ; qd = exp(G) (q - tril(q k^T) w)
+      intra      o = ((tril(q k^T) Aw) * Gam * beta_j * l[t, bit_length(i^j)]) v
+      level      readers (bit l of c set) add l[t,lh] qd.S ; then, unless c ends a period of the level
+                 (state zeroed), S <- exp(G_last) S + kd^T ((bit clear ? u : 0) - wd S).
+
+    All levels advance together through one loop over chunks.  Differentiable; evaluates in the
+    dtype of its inputs on their device (fp64 on the CPU as the checker of the CUDA kernels).
+    Checked against the reference-generated fixture and the token recurrence in
+    tests/test_oracle_golden.py."""
+    B, T, H, K = q.shape
+    V = v.shape[-1]
+    L = l.shape[-1]
+    C = chunk
+    NT = T // C
+    dev = q.device
+    f = lambda x: x.reshape(B, NT, C, H, -1).permute(0, 3, 1, 2, 4)        # (B,H,NT,C,*)
+    qc, kc, vc, lc = f(q), f(k), f(v), f(l)
+    bc = b.reshape(B, NT, C, H).permute(0, 3, 1, 2)                         # (B,H,NT,C)
+    G = torch.cumsum(g.reshape(B, NT, C, H).permute(0, 3, 1, 2), dim=-1)
+    gl = G[..., -1]
+    tril = torch.tril(torch.ones(C, C, dtype=torch.bool, device=dev))
+    stril = torch.tril(torch.ones(C, C, dtype=torch.bool, device=dev), -1)
+    Gam = torch.exp((G[..., :, None] - G[..., None, :]).masked_fill(~tril, float("-inf")))
+    A = (bc[..., :, None] * (kc @ kc.transpose(-1, -2))).masked_fill(~stril, 0.0)
+    eye = torch.eye(C, device=dev, dtype=q.dtype).expand(B, H, NT, C, C)
+    Aw = torch.linalg.solve_triangular(eye + A, eye, upper=False)
+    Au = torch.linalg.solve_triangular(eye + A * Gam, eye, upper=False)
+    w = Aw @ (bc[..., None] * kc)
+    u = Au @ (bc[..., None] * vc)
+    kd = kc * torch.exp(gl[..., None] - G)[..., None]
+    wd = w * torch.exp(G)[..., None]
+    QK = (qc @ kc.transpose(-1, -2)).masked_fill(~tril, 0.0)
+    qd = torch.exp(G)[..., None] * (qc - QK @ w)
+    lev = torch.from_numpy(levels_matrix(C)).clamp(min=0).to(dev)
+    lam = torch.gather(lc, 4, lev[None, None, None].expand(B, H, NT, C, C))
+    o = ((QK @ Aw) * Gam * bc[..., None, :] * lam) @ vc                      # (B,H,NT,C,V)
+    ell_h0 = get_num_levels(C)
+    Lc = ceil_log2(NT) if NT > 1 else 0
+    if ell_h0 + Lc > L:
+        raise ValueError("not enough lambda levels")
+    outs = [o[:, :, c] for c in range(NT)]
+    if Lc > 0:
+        lv = torch.arange(Lc, device=dev)
+        S = torch.zeros(B, H, Lc, K, V, device=dev, dtype=q.dtype)
+        for c in range(NT):
+            bit = ((c >> lv) & 1).to(q.dtype)                                # (Lc,)
+            reset = (((c + 1) % (2 << lv)) == 0).to(q.dtype)
+            lam_c = lc[:, :, c, :, ell_h0:ell_h0 + Lc] * bit                  # (B,H,C,Lc)
+            R = qd[:, :, c, None] @ S                                        # (B,H,Lc,C,V)
+            outs[c] = outs[c] + (lam_c.permute(0, 1, 3, 2)[..., None] * R).sum(2)
+            if c + 1 < NT:
+                Z = wd[:, :, c, None] @ S
+                Vh = u[:, :, c, None] * (1 - bit)[None, None, :, None, None] - Z
+                S = (torch.exp(gl[:, :, c])[..., None, None, None] * S + kd[:, :, c, None].transpose(-1, -2) @ Vh) \
+                    * (1 - reset)[None, None, :, None, None]
+    o = torch.stack(outs, dim=2)                                             # (B,H,NT,C,V)
+    return o.permute(0, 2, 3, 1, 4).reshape(B, T, H, V)
+
+
+def gdn_chunkwise_grads(q, k, v, b, g, l, do, scale: float):
+    """Gradients of sum(o * do) w.r.t. the RAW (q, k, v, b, g, l) of the GDN op through the
+    l2norm / scale preparation and `gdn_chunkwise`, in float64 (l is the lambda the kernels see,
+    i.e. already divided by scale)."""
+    ins = [x.detach().double().requires_grad_(True) for x in (q, k, v, b, g, l)]
+    qn, kn = gdn_layer_inputs(ins[0], ins[1], scale)
+    o = gdn_chunkwise(qn, kn, ins[2], ins[3], ins[4], ins[5])
+    grads = torch.autograd.grad((o * do.double()).sum(), ins)
+    return o.detach(), grads
 
 
 def gdn_layer_inputs(q, k, scale: float):

@@ -17,3 +17,14 @@ def pytest_configure(config):
 @pytest.fixture(scope="session")
 def golden_dir():
     return os.path.join(ROOT, "tests", "golden")
+
+
+@pytest.fixture(autouse=True)
+def _read_status_words():
+    """Every Mamba-2 driver call made by a test reads its workspace's status word and raises if a kernel gave
+    up on a bounded wait (the drivers do not synchronise by default)."""
+    from hattention_b200 import _lib
+    old = _lib.CHECK_STATUS
+    _lib.CHECK_STATUS = True
+    yield
+    _lib.CHECK_STATUS = old

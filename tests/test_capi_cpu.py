@@ -31,8 +31,46 @@ def test_header_symbols_are_exported(lib):
 
 
 def test_version_and_chunk(lib):
-    assert lib.llattn_version() >= 1
+    assert lib.llattn_version() >= 2
     assert lib.llattn_chunk() == 64
+    assert lib.llattn_kernel_launches() >= 0
+
+
+def test_static_scratch_capacity_stated_in_the_header(lib):
+    """include/llattn.h and INTEGRATION.md say: 1.125 MiB per (batch, head) at T = 4096, K = 128, V = 64, so the
+    16 MiB array serves B*H <= 14 there."""
+    cap = lib.llattn_static_scratch_bytes()
+    assert cap == 16 << 20
+    need = lambda bh: lib.llattn_mamba2_fwd_workspace_bytes(1, 4096, bh, 1, 128, 64, 13)
+    assert abs((need(2) - need(1)) / 2 ** 20 - 1.125) < 1e-3
+    assert need(14) <= cap < need(15)
+    null = ctypes.c_void_p(0)
+    # a size beyond the array is refused before anything touches a device or a pointer; so is a missing pointer
+    dummy = ctypes.c_void_p(256)
+    assert lib.llattn_mamba2_fwd_static(*([dummy] * 7), 1, 4096, 15, 1, 128, 64, 13, null) == -7
+    assert lib.llattn_mamba2_fwd_static(*([null] * 7), 1, 4096, 14, 1, 128, 64, 13, null) == -6
+
+
+def test_longest_supported_sequence(lib):
+    """The scans over segments hold ten segment levels: T = 512 * 1024 is the longest sequence; longer ones are
+    refused instead of reading levels that were never written."""
+    assert lib.llattn_mamba2_fwd_workspace_bytes(1, 524288, 1, 1, 128, 64, 20) > 0
+    assert lib.llattn_mamba2_fwd_workspace_bytes(1, 524288 + 512, 1, 1, 128, 64, 21) == 0
+    null = ctypes.c_void_p(0)
+    assert lib.llattn_mamba2_fwd(*([null] * 8), 0, 1, 1048576, 1, 1, 128, 64, 21, null) == -1
+
+
+def test_bf16_only(lib):
+    """fp32 q / k / v never reach a kernel: the Python driver refuses them (no fp32 mode; no CPU path either)."""
+    import torch
+    from hattention_b200.base import HType
+    from hattention_b200.chunkwise import _check
+    q = torch.zeros(1, 64, 1, 128)
+    v = torch.zeros(1, 64, 2, 64)
+    g = torch.zeros(1, 64, 2)
+    l = torch.zeros(1, 64, 2, 7)
+    with pytest.raises((NotImplementedError, RuntimeError)):
+        _check(q, q, v, g, l, False, 2, HType.WEAK, 64)
 
 
 def test_workspace_sizes(lib):

@@ -74,8 +74,8 @@ def run_cuda_grads(q, k, v, b, g, l, do):
 
 
 def test_gradients_match_reference_golden(golden_dir):
-    """Gradients w.r.t. the raw q, k, v, beta, g, lambda against the reference's autograd through
-    hgdn_minimal (interim backward: autograd through a torch restatement on the GPU)."""
+    """Gradients w.r.t. the raw q, k, v, beta, g, lambda from the CUDA backward against the reference's
+    autograd through hgdn_minimal (fixture)."""
     z = np.load(os.path.join(golden_dir, "gdn_c64.npz"))
     d = {k: torch.from_numpy(z[k]) for k in z.files if z[k].ndim > 0}
     o, grads = run_cuda_grads(d["q"], d["k"], d["v"], d["b"], d["g"], d["l"], d["do"])
@@ -118,8 +118,9 @@ def test_backward_stages_match_whole_path_autograd(B, T, H, Dv, L):
     do = torch.randn(B, T, H, Dv, generator=torch.Generator().manual_seed(3)).bfloat16().to(dev)
     g_cum, o, Aw, Au, _ = hg.chunkwise_fwd(qn, kn, v, b, g, l, False, 2, HType.WEAK, 64, False)
     got = hg.chunkwise_bwd(qn, kn, v, b, g_cum, l, Aw, Au, do, False, 2, HType.WEAK, 64)
-    staged = hg._chunkwise_bwd_staged(qn, kn, v, b, g_cum, l, Aw, Au, do)
-    want = hg._chunkwise_bwd_autograd(qn, kn, v, b, g_cum, l, do)
+    import gdn_torch_stages as gts
+    staged = gts.chunkwise_bwd_staged(qn, kn, v, b, g_cum, l, Aw, Au, do)
+    want = gts.chunkwise_bwd_autograd(qn, kn, v, b, g_cum, l, do)
     torch.cuda.synchronize()
     for a, w_, key in zip(staged, want, ("dq", "dk", "dv", "db", "dg", "dl")):
         rel = ((a.double() - w_.double()).norm() / w_.double().norm()).item()

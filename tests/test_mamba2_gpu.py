@@ -62,11 +62,13 @@ def test_golden_fixture_from_reference(golden_dir):
     (1, 704, 2, 64, 128, 2, 11),      # 11 chunks: ragged last segment, two q/k groups
     (1, 4096, 2, 64, 128, 1, 13),     # eight segments: three high levels
     (1, 2048, 2, 64, 64, 2, 15),      # K = 64, spare lambda levels
+    (1, 1024, 4, 64, 128, 2, 11),     # two q/k groups with an even chunk count: group indexing of the TMA loads / reduce-adds
+    (1, 16384, 2, 64, 128, 1, 15),    # 32 segments: five high levels
 ])
 def test_forward_and_backward_match_oracle(B, T, H, P, N, G, L):
     q, k, v, g, l, do = rounded_inputs(B, T, H, P, N, G, L, seed=T + H)
     o, grads = run_cuda(q, k, v, g, l, do)
-    o_ref, g_ref = orc.mamba2_grads(q, k, v, g, l, do, fn=lambda *a: orc.mamba2_chunkwise(*a, chunk=64))
+    o_ref, g_ref = orc.mamba2_grads(q, k, v, g, l, do, fn=orc.mamba2_chunkwise_blocked if T > 4096 else orc.mamba2_chunkwise)
     assert_close(o, o_ref, "o")
     for got, want, key in zip(grads, g_ref, ("dq", "dk", "dv", "dg", "dl")):
         assert_close(got, want, key)
@@ -134,12 +136,12 @@ def test_tensor_core_and_warp_mma_forward_agree():
     args = (q.bfloat16().to(dev), k.bfloat16().to(dev), v.bfloat16().to(dev), g.to(dev), l.bfloat16().to(dev),
             False, 2, HType.WEAK, 64, False)
     try:
-        lib.llattn_set_tensor_core_path(0)
+        lib.llattn_testing_use_tensor_core_path(0)
         o_warp, gc_warp, _ = chunkwise_fwd(*args)
-        lib.llattn_set_tensor_core_path(1)
+        lib.llattn_testing_use_tensor_core_path(1)
         o_tc, gc_tc, _ = chunkwise_fwd(*args)
     finally:
-        lib.llattn_set_tensor_core_path(1)
+        lib.llattn_testing_use_tensor_core_path(1)
     torch.cuda.synchronize()
     assert torch.allclose(gc_warp, gc_tc, rtol=1e-5, atol=1e-6)
     o_ref = orc.mamba2_chunkwise(q.double(), k.double(), v.double(), g.double(), l.double())

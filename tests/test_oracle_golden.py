@@ -39,6 +39,33 @@ def test_mamba2_forward_forms_match_reference(golden_dir, name):
         assert torch.allclose(o_chk, d[ref], rtol=1e-4, atol=2e-6), ref
 
 
+@pytest.mark.parametrize("name", ["mamba2_c1.npz", "mamba2_c64.npz"])
+def test_mamba2_blocked_form_matches_reference(golden_dir, name):
+    """The all-chunks-at-once form used as the checker at 16K-64K tokens: reference fixtures (outputs and
+    autograd gradients) and the per-level scan form on ragged / grouped shapes."""
+    d = load(golden_dir, name)
+    q, k, v, g, l = (d[x] for x in "qkvgl")
+    C = int(d["chunk"])
+    o = orc.mamba2_chunkwise_blocked(q, k, v, g, l, chunk=C)
+    for ref in ("o_chunk", "o_recurrent", "o_materialized"):
+        assert torch.allclose(o, d[ref], rtol=1e-4, atol=2e-6), ref
+    _, grads = orc.mamba2_grads(q, k, v, g, l, d["do"], fn=lambda *a: orc.mamba2_chunkwise_blocked(*a, chunk=C))
+    for got, key in zip(grads, ("dq", "dk", "dv", "dg", "dl")):
+        want = d[key].double()
+        assert torch.allclose(got, want, rtol=1e-3, atol=1e-5 * max(1.0, want.abs().max().item())), key
+
+
+@pytest.mark.parametrize("B,T,H,G,L,C", [(1, 704, 2, 2, 11, 64), (2, 1024, 4, 1, 12, 64), (1, 64, 2, 1, 7, 64), (1, 208, 2, 1, 9, 16)])
+def test_mamba2_blocked_form_matches_scan_form(B, T, H, G, L, C):
+    q, k, v, g, l = orc.make_mamba2_inputs(B, T, H, 16, 32, G, L, seed=T, dtype=torch.float64)
+    do = torch.randn(B, T, H, 16, dtype=torch.float64, generator=torch.Generator().manual_seed(1))
+    o1, g1 = orc.mamba2_grads(q, k, v, g, l, do, fn=lambda *a: orc.mamba2_chunkwise(*a, chunk=C))
+    o2, g2 = orc.mamba2_grads(q, k, v, g, l, do, fn=lambda *a: orc.mamba2_chunkwise_blocked(*a, chunk=C))
+    assert torch.allclose(o1, o2, rtol=1e-10, atol=1e-12)
+    for a, b_ in zip(g1, g2):
+        assert torch.allclose(a, b_, rtol=1e-9, atol=1e-11)
+
+
 def test_mamba2_recurrence_matches_reference(golden_dir):
     d = load(golden_dir, "mamba2_c1.npz")
     q, k, v, g, l = (d[x] for x in "qkvgl")
@@ -71,6 +98,31 @@ def test_gdn_recurrence_and_gradients_match_reference(golden_dir, name):
     for got, key in zip(grads, ("dq", "dk", "dv", "db", "dg", "dl")):
         want = d[key].double()
         assert torch.allclose(got, want, rtol=2e-3, atol=2e-5 * max(1.0, want.abs().max().item())), key
+
+
+def test_gdn_chunkwise_form_matches_reference(golden_dir):
+    """The chunkwise delta-rule form used as the gradient checker at long sequences: the reference fixture
+    (chunk 64: hgdn_minimal outputs, recurrence outputs, autograd gradients) and the token recurrence."""
+    d = load(golden_dir, "gdn_c64.npz")
+    q, k, v, b, g, l = (d[x] for x in "qkvbgl")
+    scale = float(d["scale"])
+    o, grads = orc.gdn_chunkwise_grads(q, k, v, b, g, l.double() / scale, d["do"], scale)
+    grads = list(grads)
+    grads[5] = grads[5] / scale
+    assert torch.allclose(o.float(), d["o_chunk"], rtol=1e-4, atol=5e-6)
+    assert torch.allclose(o.float(), d["o_recurrent"], rtol=1e-4, atol=5e-6)
+    for got, key in zip(grads, ("dq", "dk", "dv", "db", "dg", "dl")):
+        want = d[key].double()
+        assert torch.allclose(got, want, rtol=2e-3, atol=2e-5 * max(1.0, want.abs().max().item())), key
+
+
+@pytest.mark.parametrize("T,L", [(192, 9), (704, 11)])
+def test_gdn_chunkwise_form_matches_recurrence(T, L):
+    q, k, v, b, g, l = orc.make_gdn_inputs(1, T, 2, 16, 8, L, seed=T, dtype=torch.float64)
+    qn, kn = orc.gdn_layer_inputs(q, k, 0.25)
+    o1 = orc.gdn_chunkwise(qn, kn, v, b, g.double(), l)
+    o2, _ = orc.recurrent(qn, kn, v, g.double(), l, b=b)
+    assert torch.allclose(o1, o2, rtol=1e-8, atol=1e-10)
 
 
 def test_gdn_materialized_matches_recurrence():

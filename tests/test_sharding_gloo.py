@@ -24,13 +24,25 @@ def test_plan_batch_first_then_heads():
     assert all(s.qk_allreduce_group == 1 for s in p)
     with pytest.raises(ValueError):
         sharding.plan(3, 32, 1, 2)
+    # head ranges that straddle q/k groups are refused (their dq / dk would miss other ranks' parts)
+    with pytest.raises(ValueError):
+        sharding.plan(1, 12, 2, 3)            # 4 heads per rank, groups of 6
+    with pytest.raises(ValueError):
+        sharding.plan(1, 12, 4, 3)            # 4 heads per rank, groups of 3
+    p = sharding.plan(1, 12, 2, 2)            # 6 heads per rank = one whole group each
+    assert all(s.qk_allreduce_group == 1 for s in p)
+    p = sharding.plan(1, 12, 2, 6)            # 2 heads per rank, three ranks share a group
+    assert all(s.qk_allreduce_group == 3 for s in p)
 
 
 def _worker(rank, world, port, split_heads, ret):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
-    B, T, H, P, N, G, L = (1, 128, 4, 8, 8, 1, 8) if split_heads else (2, 128, 2, 8, 8, 1, 8)
+    if world == 4:
+        B, T, H, P, N, G, L = 2, 128, 4, 8, 8, 1, 8         # two batch items x two head halves: two subgroups of two ranks
+    else:
+        B, T, H, P, N, G, L = (1, 128, 4, 8, 8, 1, 8) if split_heads else (2, 128, 2, 8, 8, 1, 8)
     q, k, v, g, l = orc.make_mamba2_inputs(B, T, H, P, N, G, L, seed=3, dtype=torch.float64)
     do = torch.randn(B, T, H, P, generator=torch.Generator().manual_seed(4), dtype=torch.float64)
     g = g.double()
@@ -40,6 +52,9 @@ def _worker(rank, world, port, split_heads, ret):
     dos = do[shard.b0:shard.b1, :, shard.h0:shard.h1]
     o_s, gr = orc.mamba2_grads(qs, ks, vs, gs, ls, dos, fn=lambda *a: orc.mamba2_chunkwise(*a, chunk=16))
     dq, dk = sharding.reduce_qk_grads(gr[0].clone(), gr[1].clone(), shard, rank)
+    if world == 4:
+        # a second step through the cached subgroups: both ranks of a subgroup hold the sum, so halves add up to it again
+        dq, dk = sharding.reduce_qk_grads(dq / 2, dk / 2, shard, rank)
     ok = torch.allclose(o_s, o_full[shard.b0:shard.b1, :, shard.h0:shard.h1], atol=1e-12)
     ok &= torch.allclose(gr[2], grads_full[2][shard.b0:shard.b1, :, shard.h0:shard.h1], atol=1e-10)
     ok &= torch.allclose(dq, grads_full[0][shard.b0:shard.b1], atol=1e-10)
@@ -58,6 +73,20 @@ def test_two_rank_gloo_sharding_matches_unsharded(split_heads):
     ret = ctx.Queue()
     port = 29611 + (1 if split_heads else 0)
     procs = [ctx.Process(target=_worker, args=(r, 2, port, split_heads, ret)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=300)
+        assert p.exitcode == 0
+    assert ret.get(timeout=10) == 1
+
+
+def test_four_rank_gloo_two_subgroups():
+    """World larger than the q/k group: two batch items, each split over two ranks by heads, so two disjoint
+    subgroups of two ranks reduce dq / dk; the subgroups are created once, collectively, and reused."""
+    ctx = mp.get_context("spawn")
+    ret = ctx.Queue()
+    procs = [ctx.Process(target=_worker, args=(r, 4, 29617, True, ret)) for r in range(4)]
     for p in procs:
         p.start()
     for p in procs:

@@ -59,3 +59,25 @@ def test_mma_issue_rate(mode, N, kred, bound):
     per_step = (total[64] - total[8]) / ((64 - 8) * (kred // 16))
     print(f"mode {mode} N={N} kred={kred}: {per_step:.1f} cycles per K=16 step; 8 repetitions take {total[8]} cycles")
     assert per_step <= bound
+
+
+def test_wait_that_runs_out_sets_the_status_word():
+    """A bounded wait that nothing completes: the kernel gives up after its poll limit, sets the status word and
+    returns; the host reads the word through the C ABI and the context stays usable."""
+    import ctypes
+    from hattention_b200 import _lib
+    DEV = torch.device("cuda:0")
+    lib = _lib.lib()
+    ws = torch.zeros(64, dtype=torch.int32, device=DEV)
+    stream = torch.cuda.current_stream().cuda_stream
+    out = ctypes.c_int(-1)
+    assert lib.llattn_workspace_status(ws.data_ptr(), ctypes.byref(out), stream) == 0 and out.value == 0
+    before = lib.llattn_kernel_launches()
+    assert lib.llattn_selftest_wait_timeout(2000, ws.data_ptr(), stream) == 0
+    assert lib.llattn_kernel_launches() == before + 1
+    assert lib.llattn_workspace_status(ws.data_ptr(), ctypes.byref(out), stream) == 0
+    assert out.value == 1
+    with pytest.raises(RuntimeError):
+        _lib.raise_on_status(ws, stream, "self-test")
+    # the device still answers
+    assert torch.ones(4, device=DEV).sum().item() == 4.0
