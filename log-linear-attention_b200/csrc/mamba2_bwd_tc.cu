@@ -9,6 +9,8 @@
 // tensor operation per 128 x 32 box instead of per-thread red.global).  The gradient w.r.t. the
 // in-chunk cumulative decay uses q_i.dq_i = sum_levels lambda[i,lev] dlambda[i,lev] (o is linear in
 // lambda), so only k_j.dk_j needs a pass over a tile.
+#include <stdlib.h>
+
 #include "tc_common.cuh"
 
 namespace llattn {
@@ -84,8 +86,8 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_fwdorder_tc_kernel(con
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + SM::bar_off + 104);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int h = blockIdx.x % p.H;
-    const int r = (blockIdx.x / p.H) % p.NS;
+    const int h = p.order ? (blockIdx.x / p.NS) % p.H : blockIdx.x % p.H;
+    const int r = p.order ? blockIdx.x % p.NS : (blockIdx.x / p.H) % p.NS;
     const int b = blockIdx.x / (p.H * p.NS);
     const int grp = h / (p.H / p.G);
     const int L = p.L;
@@ -660,8 +662,8 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_revorder_tc_kernel(con
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + SM::bar_off + 104);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int h = blockIdx.x % p.H;
-    const int r = (blockIdx.x / p.H) % p.NS;
+    const int h = p.order ? (blockIdx.x / p.NS) % p.H : blockIdx.x % p.H;
+    const int r = p.order ? blockIdx.x % p.NS : (blockIdx.x / p.H) % p.NS;
     const int b = blockIdx.x / (p.H * p.NS);
     const int grp = h / (p.H / p.G);
     const int L = p.L;
@@ -830,6 +832,11 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_revorder_tc_kernel(con
     const uint32_t tbase = *tmem_slot;
 
     for (int it = 0; it < npairs; ++it) {
+#ifdef LLATTN_STAMPS
+        int nstamp = 0;
+        const int stamp_slot = (blockIdx.x == 300 && it == 2) ? (tid == 0 ? 0 : (tid == 200 ? 1 : (tid == 96 ? 2 : -1))) : -1;
+#endif
+        STAMPR();   // 0 top
         const int pl = npairs - 1 - it;
         const long t0 = (long)(r * SEGP + pl) * tc::PT;
         float gq[4];
@@ -864,6 +871,7 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_revorder_tc_kernel(con
         umma::fence_before_sync();
         bar_work();                                  // barrier 1
         umma::fence_after_sync();
+        STAMPR();   // 1 after barrier 1
         const float Gi = sGp[row];
         const float glp = sGp[tc::PT - 1];
         float lam[NLAM];
@@ -889,6 +897,7 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_revorder_tc_kernel(con
                 *reinterpret_cast<uint4*>(sDKV + umma::tile_offset(row, ch * 32 + c * 8, tc::KD)) =
                     make_uint4(pk[c * 4], pk[c * 4 + 1], pk[c * 4 + 2], pk[c * 4 + 3]);
         }
+        STAMPR();   // 2 dKV tile written
         umma::mbar_wait(full_vd, it & 1, abort_flag);
         if (it >= 1) umma::mbar_wait(stage_free, (it - 1) & 1, abort_flag);   // P / scaled-do space was the dk staging area
         // ---- Vs and the scaled copies of do for the reader insertions
@@ -931,9 +940,11 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_revorder_tc_kernel(con
                     ++slot;
                 }
         }
+        STAMPR();   // 3 Vs / scaled do written
         // ---- S -> P (bf16 tile)
         umma::mbar_wait(barA, it & 1, abort_flag);
         umma::fence_after_sync();
+        STAMPR();   // 4 S complete
 #pragma unroll
         for (int jb = 0; jb < 4; ++jb) {
             const int j0 = jb * 32 + ch * 16;
@@ -982,6 +993,7 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_revorder_tc_kernel(con
                 *reinterpret_cast<uint4*>(sP + umma::tile_offset(row, j0 + c * 8, tc::PT)) =
                     make_uint4(packed[c * 4], packed[c * 4 + 1], packed[c * 4 + 2], packed[c * 4 + 3]);
         }
+        STAMPR();   // 5 P written
         umma::fence_async_smem();
         umma::fence_before_sync();
         bar_work();                                  // barrier 2
@@ -989,6 +1001,7 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_revorder_tc_kernel(con
 
         umma::mbar_wait(barB, it & 1, abort_flag);
         umma::fence_after_sync();
+        STAMPR();   // 6 batch B complete
         // ---- dv = P^T do + decay_j (k dKV) : stage bf16 rows, coalesced copy-out
         {
             float ta[32], tb[32];
@@ -1005,6 +1018,7 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_revorder_tc_kernel(con
                 *reinterpret_cast<uint4*>(sVs + umma::tile_offset(row, ch * 32 + c * 8, tc::PT)) = x;   // Vs is free: second batch done
             }
         }
+        STAMPR();   // 7 dv staged
         // ---- level part of dk: k_j . dk_j, fp32 staging
         float wk_part = 0.f;
 #pragma unroll
@@ -1027,6 +1041,7 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_revorder_tc_kernel(con
                 *reinterpret_cast<float4*>(box + box_offset(row, c * 4)) = make_float4(t[c * 4], t[c * 4 + 1], t[c * 4 + 2], t[c * 4 + 3]);
         }
         sMisc[ch * 128 + row] = wk_part;
+        STAMPR();   // 8 dk staged
         // ---- contributor totals Y = <KV of each chunk of the pair, adjoint state> and the state update
         {
             float kva[32], kvb[32];
@@ -1070,6 +1085,7 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_revorder_tc_kernel(con
                 }
             }
         }
+        STAMPR();   // 9 states updated
         umma::fence_async_smem();
         bar_compute();
         if (tid == 0) {
@@ -1096,10 +1112,12 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_revorder_tc_kernel(con
             const long cidx = ((long)b * p.H + h) * p.NT + (r * SEGP + pl) * 2 + cpart;
             p.Yc[cidx * (MLOW + 1) + (lv == MP ? MLOW : lv + 1)] = y;
         }
+        STAMPR();   // 10 dv out
         if (it + 1 < npairs) store_lam();
         umma::fence_async_smem();
         umma::fence_before_sync();
         bar_work();                                  // barrier 3
+        STAMPR();   // 11 after barrier 3
         umma::fence_after_sync();
         if (*abort_flag) break;
     }
@@ -1109,6 +1127,7 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_revorder_tc_kernel(con
 
 int mamba2_bwd2_tc_launch(const Mamba2Params& p_in, cudaStream_t stream) {
     Mamba2Params p = p_in;
+    p.order = getenv("LLATTN_EXPERIMENT_ORDER") ? atoi(getenv("LLATTN_EXPERIMENT_ORDER")) : 0;
     int rc;
     const long BT = (long)p.B * p.T;
     if ((rc = tma::make_panel_map(&p.tm_q, p.q, BT, p.G, p.K, tc::PT)) != 0) return rc;
@@ -1126,6 +1145,7 @@ int mamba2_bwd2_tc_launch(const Mamba2Params& p_in, cudaStream_t stream) {
 
 int mamba2_bwd1_tc_launch(const Mamba2Params& p_in, cudaStream_t stream) {
     Mamba2Params p = p_in;
+    p.order = getenv("LLATTN_EXPERIMENT_ORDER") ? atoi(getenv("LLATTN_EXPERIMENT_ORDER")) : 0;
     int rc;
     const long BT = (long)p.B * p.T;
     if ((rc = tma::make_panel_map(&p.tm_q, p.q, BT, p.G, p.K, tc::PT)) != 0) return rc;

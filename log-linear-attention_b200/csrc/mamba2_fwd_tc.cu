@@ -11,6 +11,8 @@
 //     the masks / decays / lambda weights are applied on the way from tensor memory to the bf16
 //     P tile; level-state masters stay in registers in the tensor-memory readout layout (one
 //     state row per thread), their bf16 copies are written once as MN-major operands.
+#include <stdlib.h>
+
 #include "tc_common.cuh"
 
 namespace llattn {
@@ -58,8 +60,8 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_chunk_fwd_tc_kernel(const 
     static_assert(MP <= 2, "two tensor-memory slots for level reads");
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int h = blockIdx.x % p.H;
-    const int r = (blockIdx.x / p.H) % p.NS;
+    const int h = p.order ? (blockIdx.x / p.NS) % p.H : blockIdx.x % p.H;
+    const int r = p.order ? blockIdx.x % p.NS : (blockIdx.x / p.H) % p.NS;
     const int b = blockIdx.x / (p.H * p.NS);
     const int grp = h / (p.H / p.G);
     const int L = p.L;
@@ -468,6 +470,7 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_chunk_fwd_tc_kernel(const 
 
 int mamba2_fwd_tc_launch(const Mamba2Params& p_in, cudaStream_t stream) {
     Mamba2Params p = p_in;
+    p.order = getenv("LLATTN_EXPERIMENT_ORDER") ? atoi(getenv("LLATTN_EXPERIMENT_ORDER")) : 0;
     int rc;
     if ((rc = tma::make_panel_map(&p.tm_q, p.q, (long)p.B * p.T, p.G, p.K, tc::PT)) != 0) return rc;
     if ((rc = tma::make_panel_map(&p.tm_k, p.k, (long)p.B * p.T, p.G, p.K, tc::PT)) != 0) return rc;

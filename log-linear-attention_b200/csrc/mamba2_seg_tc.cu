@@ -8,6 +8,8 @@
 //   seg_dstate : dF[r][j] = sum_pairs q^T (do * lambda_j exp(G))                     (fp32 K x V per set level)
 //   hi_bwd_q   : dlambda_j = exp(G) (do . (q H0_j)) ; dq += (do * lambda_j exp(G)) H0_j^T   (TMA reduce-add)
 // G is the cumulative log decay from the start of the segment (inclusive).
+#include <stdlib.h>
+
 #include "tc_common.cuh"
 
 namespace llattn {
@@ -96,8 +98,8 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_hi_bwd_tc_kernel(const __g
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + SM::bar_off + 104);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int h = blockIdx.x % p.H;
-    const int r = 1 + (blockIdx.x / p.H) % (p.NS - 1);
+    const int h = p.order ? (blockIdx.x / (p.NS - 1)) % p.H : blockIdx.x % p.H;
+    const int r = 1 + (p.order ? blockIdx.x % (p.NS - 1) : (blockIdx.x / p.H) % (p.NS - 1));
     const int b = blockIdx.x / (p.H * (p.NS - 1));
     const int grp = h / (p.H / p.G);
     const int nchunks = min(SEG, p.NT - r * SEG);
@@ -379,8 +381,8 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_hi_out_tc_kernel(const __g
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + SM::bar_off + 72);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int h = blockIdx.x % p.H;
-    const int r = 1 + (blockIdx.x / p.H) % (p.NS - 1);
+    const int h = p.order ? (blockIdx.x / (p.NS - 1)) % p.H : blockIdx.x % p.H;
+    const int r = 1 + (p.order ? blockIdx.x % (p.NS - 1) : (blockIdx.x / p.H) % (p.NS - 1));
     const int b = blockIdx.x / (p.H * (p.NS - 1));
     const int grp = h / (p.H / p.G);
     const int nchunks = min(SEG, p.NT - r * SEG);
@@ -636,6 +638,7 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_seg_state_tc_kernel(const 
 
 int mamba2_seg_state_tc_launch(const Mamba2Params& p_in, cudaStream_t stream) {
     Mamba2Params p = p_in;
+    p.order = getenv("LLATTN_EXPERIMENT_ORDER") ? atoi(getenv("LLATTN_EXPERIMENT_ORDER")) : 0;
     int rc;
     const long BT = (long)p.B * p.T;
     if ((rc = tma::make_panel_map(&p.tm_k, p.k, BT, p.G, p.K, tc::PT)) != 0) return rc;
@@ -650,6 +653,7 @@ int mamba2_seg_state_tc_launch(const Mamba2Params& p_in, cudaStream_t stream) {
 
 int mamba2_hi_out_tc_launch(const Mamba2Params& p_in, cudaStream_t stream) {
     Mamba2Params p = p_in;
+    p.order = getenv("LLATTN_EXPERIMENT_ORDER") ? atoi(getenv("LLATTN_EXPERIMENT_ORDER")) : 0;
     int rc;
     const long BT = (long)p.B * p.T;
     if ((rc = tma::make_panel_map(&p.tm_q, p.q, BT, p.G, p.K, tc::PT)) != 0) return rc;
@@ -673,6 +677,7 @@ int mamba2_hi_out_tc_launch(const Mamba2Params& p_in, cudaStream_t stream) {
 
 int mamba2_hi_bwd_tc_launch(const Mamba2Params& p_in, cudaStream_t stream) {
     Mamba2Params p = p_in;
+    p.order = getenv("LLATTN_EXPERIMENT_ORDER") ? atoi(getenv("LLATTN_EXPERIMENT_ORDER")) : 0;
     int rc;
     const long BT = (long)p.B * p.T;
     if ((rc = tma::make_panel_map(&p.tm_q, p.q, BT, p.G, p.K, tc::PT)) != 0) return rc;
@@ -685,8 +690,10 @@ int mamba2_hi_bwd_tc_launch(const Mamba2Params& p_in, cudaStream_t stream) {
     if (e != cudaSuccess) return (int)e;
     // one launch per window of five segment levels (a single one up to T = 16384); dq, the q.dq totals and
     // the per-level outputs of different windows add up or are disjoint
-    for (p.lev_lo = 0; p.lev_lo < p.LH; p.lev_lo += tcs::MAXLH)
-        kern<<<p.B * p.H * (p.NS - 1), tc::NTHREADS, sm, stream>>>(p); LLATTN_LAUNCHED();
+    for (p.lev_lo = 0; p.lev_lo < p.LH; p.lev_lo += tcs::MAXLH) {
+        kern<<<p.B * p.H * (p.NS - 1), tc::NTHREADS, sm, stream>>>(p);
+        LLATTN_LAUNCHED();
+    }
     return (int)cudaGetLastError();
 }
 

@@ -16,8 +16,13 @@ static __device__ long long g_stamps[3][32];
     do {                                                                    \
         if (stamp_slot >= 0 && nstamp < 32) g_stamps[stamp_slot][nstamp++] = clock64(); \
     } while (0)
+#define STAMPR()                                                            \
+    do {                                                                    \
+        if (stamp_slot >= 0 && nstamp < 16) g_stamps[stamp_slot][16 + nstamp++] = clock64(); \
+    } while (0)
 #else
 #define STAMP() do { } while (0)
+#define STAMPR() do { } while (0)
 #endif
 
 namespace tc {

@@ -3,7 +3,7 @@
 Mirrors the module layout of the reference package for the one path it replaces:
 `base` (level arithmetic, enums), `chunkwise` (Mamba-2 drivers), `chunkwise_hgdn` (Gated DeltaNet
 drivers, l2norm), `kernel` (autograd boundary, prefill / decode step), `mamba_apis` and
-`gated_delta_rule_apis` (layer-level APIs), `sharding` (batch x head partition across GPUs).  The CUDA
+`gated_delta_rule_apis` (layer-level APIs), `recurrent` (decode state), `sharding` (batch x head partition across GPUs).  The CUDA
 kernels live in libllattn.so (C ABI, built from ../csrc) and are reached through ctypes; there is no CPU
 or Triton fallback.
 """
@@ -23,7 +23,7 @@ def install_as_hattention():
         pkg = types.ModuleType("hattention")
         pkg.__path__ = []
         sys.modules["hattention"] = pkg
-    for name in ("base", "chunkwise", "kernel", "mamba_apis", "chunkwise_hgdn", "gated_delta_rule_apis"):
+    for name in ("base", "recurrent", "chunkwise", "kernel", "mamba_apis", "chunkwise_hgdn", "gated_delta_rule_apis"):
         try:
             mod = importlib.import_module(f"{__name__}.{name}")
         except ImportError:

@@ -7,6 +7,7 @@ import torch
 from .base import HStruct, HType
 from . import _lib
 from .chunkwise import chunkwise_bwd, chunkwise_fwd, final_states
+from .recurrent import HState  # noqa: F401  (re-exported: the reference imports it from both modules)
 
 
 # Keep the forward call's scratch alive until the backward, which then skips its recomputation: the
@@ -107,51 +108,6 @@ def hattention_kernel(
         chunk_sizes = (64, 64)
     return HAttentionFunction.apply(q, k, v, b, g, l, scale, head_first, level_base, htype, hstruct, chunk_sizes,
                                     chunkwise, use_qk_l2norm_in_kernel)
-
-
-class HState:
-    """Level states of one layer for decoding, with the fields of the reference's `HState`
-    (hattention/recurrent.py:9-131): `states` (B,H,K,V,L) in `dtype` and one token count per level.
-    The counts are identical for every sequence and are kept on the host, so that the cascade
-    (recurrent.py:42-54) costs no device synchronisation."""
-
-    def __init__(self, base: int, htype: HType, hstruct: HStruct, shape, dtype: torch.dtype, device) -> None:
-        if base != 2 or htype != HType.WEAK:
-            raise NotImplementedError
-        self.base, self.htype, self.hstruct = base, htype, hstruct
-        self.shape, self.dtype, self.device = tuple(shape), dtype, device
-        self.max_num_levels = self.shape[-1]
-        self.states = torch.zeros(self.shape, dtype=dtype, device=device)
-        self.counts = [0] * self.max_num_levels
-
-    def cascade_counts(self) -> int:
-        """Runs the cascade on the counts; returns the level that receives the merged levels."""
-        for level in range(self.max_num_levels):
-            cap = 1 << level
-            if self.counts[level] == cap:
-                if level + 1 >= self.max_num_levels:
-                    raise ValueError("more tokens than the levels can hold")
-                self.counts[level + 1] += self.counts[level]
-                self.counts[level] = 0
-            elif self.counts[level] < cap:
-                return level
-            else:
-                raise ValueError
-        return self.max_num_levels - 1
-
-    def set_counts_after(self, T: int) -> None:
-        """Counts after T tokens: level 0 holds the last token, level j+1 holds 2^j tokens for each set
-        bit j of T-1 (the bookkeeping at the end of kernel.py:452-463)."""
-        self.counts = [0] * self.max_num_levels
-        if T <= 0:
-            return
-        self.counts[0] = 1
-        m = T - 1
-        for j in range(m.bit_length()):
-            if (m >> j) & 1:
-                if j + 1 >= self.max_num_levels:
-                    raise ValueError("more tokens than the levels can hold")
-                self.counts[j + 1] = 1 << j
 
 
 @torch.no_grad()

@@ -8,7 +8,13 @@ import torch
 from . import _lib
 from .base import HStruct, HType
 from .chunkwise import chunkwise_bwd, chunkwise_fwd
-from .kernel import KEEP_FORWARD_STATES, hattention_kernel
+from .kernel import KEEP_FORWARD_STATES, hattention_kernel, hattention_prefill, hattention_step
+from .recurrent import HState
+
+try:
+    from torchtune.modules import RotaryPositionalEmbeddings
+except ImportError:          # the reference tolerates a missing torchtune the same way (mamba_apis.py:26-29)
+    RotaryPositionalEmbeddings = None
 
 _LAMBDA_MODES = {"positive": 0, "bounded": 1, None: 2}
 # bf16 CUDA activations take the fused element-wise kernels; False keeps the reference's sequence of
@@ -89,6 +95,50 @@ class HMambaCombinedFunction(torch.autograd.Function):
                 dD.to(D_dt) if D_ is not None else None, dbias.to(b_dt) if bias_ is not None else None, None, None, None)
 
 
+class LambdaLevelMLP(torch.nn.Module):
+    """Per-level lambda inputs from `dim` features: a rotary position embedding whose position is the level
+    index, then one linear unit, for each of the two operands (mamba_apis.py:32-67 in the reference).  Only the
+    non-fixed lambda mode uses it; it needs torchtune's RotaryPositionalEmbeddings like the reference's."""
+
+    def __init__(self, dim: int, max_num_levels: int, **kwargs) -> None:
+        super().__init__()
+        if RotaryPositionalEmbeddings is None:
+            raise ImportError("LambdaLevelMLP needs torchtune (RotaryPositionalEmbeddings)")
+        self.dim = dim
+        self.max_num_levels = max_num_levels
+        self.mlp0 = torch.nn.Linear(in_features=dim, out_features=1)
+        self.mlp1 = torch.nn.Linear(in_features=dim, out_features=1)
+        self.rope = RotaryPositionalEmbeddings(dim=dim, max_seq_len=max_num_levels)
+
+    def forward(self, x0: torch.Tensor, x1: torch.Tensor, num_levels: int) -> Tuple[torch.Tensor, torch.Tensor]:
+        if x0.ndim != 4 or x1.ndim != 4:
+            raise ValueError
+        if num_levels > self.max_num_levels:
+            raise ValueError
+        y0s, y1s = [], []
+        for level in range(num_levels):
+            pos0 = torch.full((x0.shape[1],), level, dtype=torch.int32, device=x0.device)
+            pos1 = torch.full((x1.shape[1],), level, dtype=torch.int32, device=x1.device)
+            y0s.append(self.mlp0(self.rope(x0, input_pos=pos0)))
+            y1s.append(self.mlp1(self.rope(x1, input_pos=pos1)))
+        return torch.concat(y0s, dim=-1), torch.concat(y1s, dim=-1)
+
+
+def compute_lambda_maybe_fixed(L: torch.Tensor, dl: torch.Tensor, lambda_mode: Optional[str], lambda_level_max: int,
+                               lambda_level_fixed: bool, lambda_level_module) -> torch.Tensor:
+    """mamba_apis.py:88-113: fixed levels use L and dl as they are; otherwise the level module expands
+    `dim` features into `lambda_level_max` levels first."""
+    if lambda_level_fixed:
+        if not (L.ndim in (3, 4) and dl.ndim in (3, 4) and L.shape[-1] == lambda_level_max and dl.shape[-1] == lambda_level_max):
+            raise ValueError
+        return compute_lambda(L=L, dl=dl, lambda_mode=lambda_mode)
+    if not (L.ndim in (3, 4) and dl.ndim in (3, 4) and L.shape[-1] == lambda_level_module.dim
+            and dl.shape[-1] == lambda_level_module.dim):
+        raise ValueError
+    L_new, dl_new = lambda_level_module(L, dl, num_levels=lambda_level_max)
+    return compute_lambda(L=L_new, dl=dl_new, lambda_mode=lambda_mode)
+
+
 def compute_lambda(L: torch.Tensor, dl: torch.Tensor, lambda_mode: Optional[str]) -> torch.Tensor:
     """mamba_apis.py:70-85."""
     if lambda_mode == "positive":
@@ -141,8 +191,6 @@ def hmamba_chunk_scan_combined(
         raise NotImplementedError
     if return_varlen_states is not False:
         raise NotImplementedError
-    if return_final_states:
-        raise NotImplementedError("prefill hand-off (return_final_states=True) is not implemented")
     if B.shape != C.shape:
         raise ValueError("B and C must have the same shape")
     if lambda_level_max is None or lambda_level_base is None or lambda_htype is None or lambda_hstruct is None \
@@ -154,6 +202,21 @@ def hmamba_chunk_scan_combined(
         raise ValueError
     if D is not None and D.dim() != 1:
         raise ValueError
+    if return_final_states:
+        # inference: outputs for the prompt and the level states to decode from (mamba_apis.py:381-399)
+        if D is not None:
+            D_residual = x * D[None, None, :, None]
+        if dt_bias is not None:
+            dt = dt + dt_bias[None, None, :]
+        dt = torch.nn.functional.softplus(dt.float())
+        v = (x * dt[..., None]).to(C.dtype)
+        lam = compute_lambda(L[None, None].to(dl.dtype), dl, lambda_mode)
+        y, state = hattention_prefill(q=C, k=B, v=v, b=None, g=A[None, None, :].float() * dt, l=lam.to(C.dtype), scale=None,
+                                      head_first=False, level_base=lambda_level_base, htype=lambda_htype,
+                                      hstruct=lambda_hstruct)
+        if D is not None:
+            y = y + D_residual
+        return y, state
     bf16_cuda = all(t.is_cuda and t.dtype == torch.bfloat16 for t in (x, dt, B, C, dl))
     if (FUSED_PREP and bf16_cuda and lambda_hstruct == HStruct.MAMBA2 and lambda_htype == HType.WEAK and lambda_level_base == 2
             and lambda_mode in _LAMBDA_MODES and x.shape[-1] % 8 == 0 and x.shape[-1] <= 256 and L.dim() == 2):
@@ -173,6 +236,75 @@ def hmamba_chunk_scan_combined(
     if D is not None:
         y = y + D_residual
     return y, None
+
+
+def hselective_state_update(
+    state: HState,
+    x: torch.Tensor,
+    dt: torch.Tensor,
+    A: torch.Tensor,
+    B: torch.Tensor,
+    C: torch.Tensor,
+    dl: torch.Tensor,
+    L: torch.Tensor,
+    D: Optional[torch.Tensor] = None,
+    z: Optional[torch.Tensor] = None,
+    dt_bias: Optional[torch.Tensor] = None,
+    dt_softplus: bool = False,
+    state_batch_indices: Optional[torch.Tensor] = None,
+    lambda_mode: Optional[str] = None,
+    lambda_level_max: Optional[int] = None,
+    lambda_level_base: Optional[int] = None,
+    lambda_htype: Optional[HType] = None,
+    lambda_hstruct: Optional[HStruct] = None,
+    lambda_level_fixed: Optional[bool] = None,
+    lambda_level_module=None,
+) -> Tuple[torch.Tensor, HState]:
+    """One decode step of the layer: x (B,H,P), dt (B,H), A (H), B/C (B,G,N), dl (B,H,L), L (H,L) ->
+    (out (B,H,P), state).  Signature, checks and preparation of the reference's function of this name
+    (mamba_apis.py:407-566); the state update and read-out (its `step_state` / `step_output`) are one CUDA
+    kernel here (`hattention_step`), which takes the log decay A*dt where the reference passes exp(A*dt)."""
+    if state_batch_indices is not None:
+        raise NotImplementedError
+    if z is not None:
+        raise NotImplementedError
+    if x.dim() != 3 or dt.dim() != 2 or A.dim() != 1 or B.dim() != 3 or C.dim() != 3 or dl.dim() != 3 or L.dim() != 2:
+        raise ValueError
+    if D is not None and D.dim() != 1:
+        raise ValueError
+    if dt_bias is not None and dt_bias.dim() != 1:
+        raise ValueError
+    batch, nheads, headdim = x.shape
+    _, ngroups, dstate = B.shape
+    dlambda = L.shape[-1]
+    if dt.shape != x.shape[:2] or A.shape != (nheads,) or nheads % ngroups != 0 or B.shape != (batch, ngroups, dstate) \
+            or C.shape != B.shape or dl.shape != (batch, nheads, dlambda) or L.shape != (nheads, dlambda):
+        raise ValueError
+    if D is not None and D.shape != (nheads,):
+        raise ValueError
+    if lambda_level_max is None or lambda_level_base is None or lambda_htype is None or lambda_hstruct is None \
+            or lambda_level_fixed is None:
+        raise ValueError
+    if D is not None:
+        D_residual = x * D[None, :, None]
+    if dt_bias is not None:
+        if dt_bias.shape != (nheads,):
+            raise ValueError
+        dt = dt + dt_bias
+    if dt_softplus:
+        dt = torch.nn.functional.softplus(dt)
+    g = (A[None, :].float() * dt.float())
+    v = (x * dt[..., None]).to(C.dtype)
+    lam = compute_lambda_maybe_fixed(L=L[None].to(dl.dtype), dl=dl, lambda_mode=lambda_mode, lambda_level_max=lambda_level_max,
+                                     lambda_level_fixed=lambda_level_fixed, lambda_level_module=lambda_level_module)
+    if not (C.dtype == B.dtype and state.base == lambda_level_base and state.htype == lambda_htype
+            and state.hstruct == lambda_hstruct):
+        raise TypeError
+    out, state = hattention_step(state, q=C, k=B, v=v, b=None, g=g.to(state.dtype), l=lam.to(C.dtype), scale=None,
+                                 level_base=lambda_level_base, htype=lambda_htype, hstruct=lambda_hstruct)
+    if D is not None:
+        out = out + D_residual
+    return out, state
 
 
 def _causal_conv1d_silu(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor]) -> torch.Tensor:

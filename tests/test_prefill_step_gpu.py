@@ -59,3 +59,49 @@ def test_decode_from_empty_state():
         ot, hs = hattention_step(hs, dq[:, t], dk[:, t], dv[:, t], None, dg[:, t], dl[:, t], None, 2, HType.WEAK, HStruct.MAMBA2)
         assert_close(ot, want[:, t], f"step {t}")
     assert hs.counts == list(st.counts)
+
+
+def test_layer_api_prefill_states_then_layer_decode_step():
+    """The calls the reference's mixer makes at inference (modeling_hattention.py:467-490, 342-362):
+    hmamba_chunk_scan_combined(..., return_final_states=True) for the prompt, then hselective_state_update per
+    token, against the oracle's recurrence on the prepared tensors; and return_final_states=False gives the same
+    prompt outputs with no state."""
+    from hattention_b200.base import HStruct, HType
+    from hattention_b200.mamba_apis import hmamba_chunk_scan_combined, hselective_state_update
+    from hattention_b200.recurrent import HState
+    torch.manual_seed(1)
+    B, T, H, P, N, L, NDEC = 2, 200, 2, 64, 128, 12, 4
+    TT = T + NDEC
+    x = torch.randn(B, TT, H, P).bfloat16()
+    dt = (torch.randn(B, TT, H) - 2).bfloat16()
+    A = -torch.exp(torch.rand(H) * 2.7)
+    Bm = (torch.randn(B, TT, 1, N) / N ** 0.5).bfloat16()
+    Cm = (torch.randn(B, TT, 1, N) / N ** 0.5).bfloat16()
+    dl = torch.randn(B, TT, H, L).bfloat16()
+    Lp = torch.ones(H, L)
+    D = torch.randn(H)
+    bias = torch.randn(H) * 0.1
+    kw = dict(dt_softplus=True, lambda_mode="positive", lambda_level_max=L, lambda_level_base=2, lambda_htype=HType.WEAK,
+              lambda_hstruct=HStruct.MAMBA2, lambda_level_fixed=True)
+    d = lambda t: t.to(DEV)
+    y, state = hmamba_chunk_scan_combined(d(x[:, :T]), d(dt[:, :T]), d(A), d(Bm[:, :T]), d(Cm[:, :T]), d(dl[:, :T]), d(Lp), 64,
+                                          D=d(D), dt_bias=d(bias), return_final_states=True, **kw)
+    assert isinstance(state, HState) and state.states.shape == (B, H, N, P, L) and sum(state.counts) == T
+    y0, none = hmamba_chunk_scan_combined(d(x[:, :T - 8]), d(dt[:, :T - 8]), d(A), d(Bm[:, :T - 8]), d(Cm[:, :T - 8]),
+                                          d(dl[:, :T - 8]), d(Lp), 64, D=d(D), dt_bias=d(bias), return_final_states=False, **kw)
+    assert none is None
+    # oracle on the prepared tensors
+    dts = torch.nn.functional.softplus(dt.float() + bias[None, None])
+    v = (x.float() * dts[..., None]).bfloat16().double()
+    g = (A[None, None] * dts).double()
+    lam = torch.nn.functional.softplus(Lp[None, None] * dl.float()).bfloat16().double()
+    want, st = orc.recurrent(Cm.double(), Bm.double(), v, g, lam)
+    want = want + x.double() * D[None, None, :, None].double()
+    assert_close(y, want[:, :T], "prompt outputs with final states")
+    assert_close(y0, want[:, :T - 8], "prompt outputs without final states")
+    for t in range(T, TT):
+        out, state = hselective_state_update(state, d(x[:, t]), d(dt[:, t]), d(A), d(Bm[:, t]), d(Cm[:, t]), d(dl[:, t]), d(Lp),
+                                             D=d(D), dt_bias=d(bias), **kw)
+        assert_close(out, want[:, t], f"layer decode step {t}")
+    torch.cuda.synchronize()
+    assert state.counts == list(st.counts)
