@@ -15,9 +15,8 @@ shims below bridge the drift without touching the reference's kernels:
      int64 table (levels[t, s] = bit_length(t ^ s) for s <= t, `default` above the diagonal, optional
      clamp) with vectorised torch ops on the requested device; equality with the reference's loop is
      checked for T = 256 in tests/test_reference_compat.py.
-  3. Triton's `Autotuner` grew constructor arguments since the reference's `hattention/autotune.py`
-     was written; if constructing it the reference's way fails, the same call is retried with the
-     keyword names of the installed Triton.
+The reference's pure-PyTorch forms (`hssd_minimal.py`, `recurrent.py`) import through the same two shims
+and run on the CPU; bench.py times them as the reference arm on host cores.
 """
 import functools
 import importlib
@@ -60,8 +59,9 @@ def _install_safe_exp():
     op.safe_exp = safe_exp
 
 
-def load_reference():
-    """Returns the reference's modules {base, chunkwise, kernel?}; raises with the first failing import."""
+def load_reference(triton_path: bool = True, torch_forms: bool = False):
+    """Returns the reference's modules by name: `base`, plus `chunkwise` (the Triton drivers) and / or
+    `hssd_minimal`, `recurrent` (the pure-PyTorch forms).  Raises with the first failing import."""
     if not os.path.isdir(os.path.join(REF_ROOT, "hattention")):
         raise RuntimeError("baseline/_ref/hattention is missing: run `python baseline/make_ref.py <reference checkout>`")
     if REF_ROOT not in sys.path:
@@ -72,6 +72,14 @@ def load_reference():
     base = importlib.import_module("hattention.base")
     cached = functools.lru_cache(maxsize=4)(levels_matrix_closed_form)
     base.make_levels_matrix = cached
-    chunkwise = importlib.import_module("hattention.chunkwise")
-    chunkwise.make_levels_matrix = cached
-    return {"base": base, "chunkwise": chunkwise}
+    out = {"base": base}
+    if triton_path:
+        chunkwise = importlib.import_module("hattention.chunkwise")
+        chunkwise.make_levels_matrix = cached
+        out["chunkwise"] = chunkwise
+    if torch_forms:
+        hm = importlib.import_module("hattention.hssd_minimal")
+        hm.make_levels_matrix = cached
+        out["hssd_minimal"] = hm
+        out["recurrent"] = importlib.import_module("hattention.recurrent")
+    return out

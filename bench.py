@@ -1,7 +1,7 @@
 """Benchmark of the log-linear Mamba-2 chunkwise forward+backward hot path.
 
     python bench.py --gpus N --steps K --warmup W            # CUDA path (this repository)
-    python bench.py --impl reference --gpus N --steps K ...  # reference algorithm on host cores
+    python bench.py --impl reference --gpus N --steps K ...  # the reference's CPU implementation on host cores
 
 Workload at every N (weak scaling, one process per GPU, batch sharded, no data-path collective):
 the configuration the headline metric is quoted on, per GPU: B=2, T=16384, H=32, P=64, N=128,
@@ -9,11 +9,17 @@ G=1, chunk 64, L=15, bf16 inputs with fp32 accumulation, synthetic seeded inputs
 distributions of that configuration.  A step is one forward plus one backward of the operator
 (drivers `chunkwise_fwd` + `chunkwise_bwd`, the functions the reference's autograd boundary calls).
 
-Printed: one JSON line (rank 0).  `value` is tokens/s with inputs resident in HBM; `e2e` is the
-same metric with every step's inputs copied from pinned host memory and every output copied back.
+Printed: one JSON line (rank 0).  `value` is tokens/s with inputs resident in HBM, from the median of
+R back-to-back blocks of K steps (R chosen so that about a second is timed; every block is bracketed by
+CUDA events; `repeats` gives the spread); `e2e` is the same metric with every step's inputs copied from
+pinned host memory and every output copied back.  At N=1 the line also carries `cpu_baseline` (the
+reference's own PyTorch chunkwise form on host cores), `cpu_baseline_recurrent` (its token recurrence,
+forward only), `triton_reference` (the reference's Triton kernels on the same GPU, same inputs) and
+`secondary` (other configurations on the same kernels).
 """
 import argparse
 import json
+import math
 import os
 import statistics
 import subprocess
@@ -29,11 +35,16 @@ for _p in (ROOT, PKG):
 import torch  # noqa: E402
 
 WORKLOAD = dict(B=2, T=16384, H=32, P=64, N=128, G=1, L=15, chunk=64)
-NAME = "log-linear Mamba-2 chunkwise fwd+bwd, B=2 T=16384 H=32 P=64 N=128 G=1 chunk=64 L=15 (per GPU)"
 METRIC = "log-linear Mamba-2 chunkwise fwd+bwd tokens/s at T=16K"
 
 
-def fmin_flops(B, T, H, P, N, C=64):
+def workload_name(w=None):
+    w = w or WORKLOAD
+    return (f"log-linear Mamba-2 chunkwise fwd+bwd, B={w['B']} T={w['T']} H={w['H']} P={w['P']} N={w['N']} G={w['G']} "
+            f"chunk=64 L={w['L']} (per GPU)")
+
+
+def fmin_flops(B, T, H, P, N, C=64, backward=True):
     """Necessary tensor flops of the chunkwise Fenwick-merge algorithm, dense per 64x64 tile:
     fwd = CK + CV + (1 + Lc/2) S ; bwd = 3 CK + 2 CV + (3 + Lc) S per (batch, head, chunk)."""
     NT = T // C
@@ -41,7 +52,7 @@ def fmin_flops(B, T, H, P, N, C=64):
     CK, CV, S = 2 * C * C * N, 2 * C * C * P, 2 * C * N * P
     fwd = CK + CV + (1 + Lc / 2) * S
     bwd = 3 * CK + 2 * CV + (3 + Lc) * S
-    return (fwd + bwd) * B * H * NT
+    return (fwd + (bwd if backward else 0)) * B * H * NT
 
 
 def algorithmic_bytes(B, T, H, P, N, G, L):
@@ -54,8 +65,25 @@ def peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
         d = json.load(open(path))
-        return dict(tflops=d.get("bf16_tflops_sustained", d.get("bf16_tflops")), hbm=d.get("hbm_gbs"), source="measured")
-    return dict(tflops=1400.0, hbm=6650.0, source="fallback")
+        return dict(tflops=d.get("bf16_tflops_sustained", d.get("bf16_tflops")), tflops_burst=d.get("bf16_tflops"),
+                    hbm=d.get("hbm_gbs"), source="measured")
+    return dict(tflops=1400.0, tflops_burst=1590.0, hbm=6650.0, source="fallback")
+
+
+def measured_traffic(w):
+    """DRAM read + write bytes per launch of the dominant kernel, from the counter file that the ncu recipe in
+    profiles/ writes (captured at batch 1; every CTA handles one (batch, head, segment), so traffic is
+    proportional to the batch).  None when there is no capture for this shape."""
+    path = os.path.join(ROOT, "profiles", "tc_counters_B1.json")
+    if not os.path.exists(path):
+        return None, None
+    d = json.load(open(path))
+    shape = d.get("shape", {})
+    if (shape.get("T"), shape.get("H"), shape.get("P"), shape.get("N")) != (w["T"], w["H"], w["P"], w["N"]):
+        return None, None
+    k = d["kernels"][d["dominant"]]
+    per_b = k["dram_read_bytes"] + k["dram_write_bytes"]
+    return per_b * w["B"] / shape.get("B", 1), d["dominant"]
 
 
 class ClockSampler:
@@ -101,12 +129,11 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def make_inputs(seed, pin):
+def make_inputs(seed, pin, w=None):
     """Seeded synthetic tensors with the value distributions of the configuration: X~N(0,1);
     B,C~N(0,1)/sqrt(N); dt=softplus(N(0,1)-2); A=-exp(U(0,ln16)) per head; lambda=softplus(N(0,1));
     dY~N(0,1).  Kernel-level inputs: q=C, k=B, v=X*dt, g=A*dt."""
-    import math
-    w = WORKLOAD
+    w = w or WORKLOAD
     B, T, H, P, N, G, L = (w[x] for x in ("B", "T", "H", "P", "N", "G", "L"))
     gen = torch.Generator().manual_seed(seed)
     X = torch.randn(B, T, H, P, generator=gen)
@@ -121,74 +148,164 @@ def make_inputs(seed, pin):
     return [t.pin_memory() for t in ts] if pin else ts
 
 
-def cpu_baseline_sample(threads, T=4096, H=32, steps=3):
-    """The reference's CPU-runnable chunkwise algorithm (oracle port, fp32): forward + autograd
-    backward on a bounded sample of the workload; plus the token recurrence, forward only."""
+# ----------------------------------------------------------------------------------------------
+# the reference's CPU implementation of the path (reference arm, cpu_baseline)
+# ----------------------------------------------------------------------------------------------
+CPU_SLICE = dict(B=1, T=4096)       # one step of the CPU arm: this slice of the workload (cost is linear in B and ~T log T)
+
+
+def _cpu_forms():
+    """(kind, chunkwise fwd+bwd step function factory, recurrent forward function or None).  The reference's own
+    hssd_minimal_discrete / hattention_recurrent when the copy made by baseline/make_ref.py is present, else
+    the oracle's port of the same algorithms."""
+    from oracle import loglinear_oracle as orc
+    try:
+        from baseline import ref_compat
+        m = ref_compat.load_reference(triton_path=False, torch_forms=True)
+        hm, rec, base = m["hssd_minimal"], m["recurrent"], m["base"]
+
+        def chunk_fwd(q, k, v, g, l):
+            H = v.shape[2]
+            return hm.hssd_minimal_discrete(v, g, k.expand(-1, -1, H, -1), q.expand(-1, -1, H, -1), l, 2, base.HType.WEAK, 64)
+
+        def recurrent_fwd(q, k, v, g, l):
+            H = v.shape[2]
+            return rec.hattention_recurrent(q.expand(-1, -1, H, -1).contiguous(), k.expand(-1, -1, H, -1).contiguous(), v,
+                                            torch.exp(g), None, l, 2, base.HType.WEAK, base.HStruct.MAMBA2)[0]
+        return "reference", chunk_fwd, recurrent_fwd
+    except Exception:                       # no copy of the reference on this machine
+        return "port", (lambda q, k, v, g, l: orc.mamba2_chunkwise(q, k, v, g, l, chunk=64)), \
+            (lambda q, k, v, g, l: orc.recurrent(q, k, v, g, l)[0])
+
+
+def cpu_chunkwise_steps(threads, steps, warmup, T=None):
+    """fp32 chunkwise forward + autograd backward of the reference's PyTorch form on a slice of the workload."""
     from oracle import loglinear_oracle as orc
     torch.set_num_threads(threads)
     w = WORKLOAD
-    q, k, v, g, l = orc.make_mamba2_inputs(1, T, H, w["P"], w["N"], w["G"], w["L"], seed=0)
-    do = torch.randn(1, T, H, w["P"], generator=torch.Generator().manual_seed(1))
-    best = None
-    for _ in range(steps):
-        ins = [x.clone().requires_grad_(True) for x in (q, k, v, g, l)]
-        t0 = time.perf_counter()
-        o = orc.mamba2_chunkwise(*ins, chunk=64)
-        torch.autograd.grad((o * do).sum(), ins)
-        dt = time.perf_counter() - t0
-        best = dt if best is None else min(best, dt)
-    return T / best, f"B=1 T={T} H={H} P=64 N=128 L=15 fp32, chunkwise fwd + autograd bwd, best of {steps}"
-
-
-def run_reference(args, rank, world):
-    """Reference arm: the reference's own CPU algorithm for the path (oracle port), all host threads."""
-    if rank != 0:
-        return
-    threads = os.cpu_count() or 1
-    T, H = 4096, WORKLOAD["H"]
-    from oracle import loglinear_oracle as orc
-    torch.set_num_threads(threads)
-    w = WORKLOAD
-    q, k, v, g, l = orc.make_mamba2_inputs(1, T, H, w["P"], w["N"], w["G"], w["L"], seed=0)
-    do = torch.randn(1, T, H, w["P"], generator=torch.Generator().manual_seed(1))
+    T = T or min(CPU_SLICE["T"], w["T"])
+    kind, chunk_fwd, _ = _cpu_forms()
+    q, k, v, g, l = orc.make_mamba2_inputs(CPU_SLICE["B"], T, w["H"], w["P"], w["N"], w["G"], w["L"], seed=0)
+    do = torch.randn(CPU_SLICE["B"], T, w["H"], w["P"], generator=torch.Generator().manual_seed(1))
 
     def step():
         ins = [x.clone().requires_grad_(True) for x in (q, k, v, g, l)]
-        o = orc.mamba2_chunkwise(*ins, chunk=64)
+        o = chunk_fwd(*ins)
         torch.autograd.grad((o * do).sum(), ins)
 
-    for _ in range(min(args.warmup, 2)):
+    for _ in range(warmup):
         step()
-    steps = max(1, min(args.steps, 10))
-    t0 = time.perf_counter()
+    times = []
     for _ in range(steps):
+        t0 = time.perf_counter()
         step()
-    dt = (time.perf_counter() - t0) / steps
-    val = T / dt
-    sample = f"each step = B=1 T={T} H={H} P=64 N=128 L=15 slice of the workload, fp32, chunkwise fwd + autograd bwd"
+        times.append(time.perf_counter() - t0)
+    what = "hssd_minimal_discrete" if kind == "reference" else "oracle port of hssd_minimal_discrete"
+    sample = (f"each step = B={CPU_SLICE['B']} T={T} H={w['H']} P={w['P']} N={w['N']} L={w['L']} slice of the workload, fp32, "
+              f"{what} forward + autograd backward")
+    return kind, T, times, sample
+
+
+def cpu_recurrent_sample(threads, T=256):
+    """The reference's token recurrence (forward only; it has no backward), truncated to T tokens."""
+    from oracle import loglinear_oracle as orc
+    torch.set_num_threads(threads)
+    w = WORKLOAD
+    kind, _, rec_fwd = _cpu_forms()
+    q, k, v, g, l = orc.make_mamba2_inputs(1, T, w["H"], w["P"], w["N"], w["G"], w["L"], seed=0)
+    with torch.no_grad():
+        rec_fwd(q[:, :32], k[:, :32], v[:, :32], g[:, :32], l[:, :32])
+        t0 = time.perf_counter()
+        rec_fwd(q, k, v, g, l)
+        dt = time.perf_counter() - t0
+    what = "hattention_recurrent" if kind == "reference" else "oracle port of hattention_recurrent"
+    return {"value": T / dt, "unit": "tokens/s", "cores": threads, "kind": kind,
+            "sample": f"{what}, forward only, B=1 truncated to T={T} (cost is linear in T), H={w['H']} P={w['P']} N={w['N']} L={w['L']}, fp32"}
+
+
+def run_reference(args, rank, world):
+    """Reference arm: the reference's own CPU implementation of the path, all host threads, rank 0 only."""
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    warm = min(args.warmup, 2)
+    steps = max(1, min(args.steps, 10))
+    kind, T, times, sample = cpu_chunkwise_steps(threads, steps, warm)
+    dt = sum(times) / len(times)
+    val = CPU_SLICE["B"] * T / dt
     line = {
         "impl": "reference", "metric": METRIC, "value": val, "unit": "tokens/s", "n_gpus": args.gpus, "steps": steps,
-        "warmup": min(args.warmup, 2), "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
+        "warmup": warm, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": NAME, "timed_on": "host cores"},
-        "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample},
+        "config": {"workload": f"B={CPU_SLICE['B']} T={T} slice of: {workload_name()}", "timed_on": "host cores",
+                   "note": "tokens/s of the slice; the algorithm's cost per token grows with log2(T) only"},
+        "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": threads, "kind": kind, "sample": sample},
         "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
 
 
-def run_gdn(args, rank, world, local):
-    """Secondary bench line: log-linear Gated DeltaNet, B=4 T=8192 H=16 Dk=Dv=128 chunk=64 L=14 per GPU.
-    Forward and backward are both the CUDA kernels; the forward is also timed on its own."""
-    import math
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device: the hot path has no CPU fallback")
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
+# ----------------------------------------------------------------------------------------------
+# CUDA-event timing helpers
+# ----------------------------------------------------------------------------------------------
+def time_blocks(step, K, barrier, min_total_ms=1000.0, max_blocks=40):
+    """Times blocks of exactly K steps, each bracketed by CUDA events on the current stream and a barrier +
+    synchronise on both sides; repeats until about `min_total_ms` have been timed.  Returns the block times (ms)."""
+    times = []
+    total = 0.0
+    while True:
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(K):
+            step()
+        e1.record()
+        barrier()
+        t = e0.elapsed_time(e1)
+        times.append(t)
+        total += t
+        if total >= min_total_ms or len(times) >= max_blocks:
+            return times
+
+
+def launches():
+    from hattention_b200 import _lib
+    return _lib.lib().llattn_kernel_launches()
+
+
+# ----------------------------------------------------------------------------------------------
+# secondary measurements (N = 1): other configurations on the same kernels
+# ----------------------------------------------------------------------------------------------
+def secondary_mamba2(dev, B, T, H, backward, steps, label):
+    from hattention_b200.base import HType
+    from hattention_b200.chunkwise import chunkwise_bwd, chunkwise_fwd
+    w = dict(WORKLOAD, B=B, T=T, H=H, L=7 + max(0, (T // 64 - 1).bit_length()))
+    q, k, v, g, l, do = [t.to(dev) for t in make_inputs(7, False, w)]
+
+    def step():
+        kept = [] if backward else None
+        o, g_cum, _ = chunkwise_fwd(q, k, v, g, l, False, 2, HType.WEAK, 64, False, keep_workspace=kept)
+        if backward:
+            chunkwise_bwd(q, k, v, g_cum, l, do, False, 2, HType.WEAK, 64, fwd_workspace=kept[0])
+
+    for _ in range(3):
+        step()
+    n0 = launches()
+    times = time_blocks(step, steps, torch.cuda.synchronize, min_total_ms=300.0, max_blocks=10)
+    nl = (launches() - n0) // len(times)
+    ms = statistics.median(times) / steps
+    flops = fmin_flops(B, T, H, w["P"], w["N"], backward=backward)
+    pk = peaks()
+    return {"workload": label, "ms_per_step": ms, "tokens_per_s": B * T / (ms * 1e-3), "steps": steps, "blocks": len(times),
+            "algorithmic_tflops": flops / (ms * 1e-3) / 1e12, "frac_of_sustained_bf16_peak": flops / (ms * 1e-3) / 1e12 / pk["tflops"],
+            "gpu_launches": nl}
+
+
+def secondary_gdn(dev, steps):
     from hattention_b200.gated_delta_rule_apis import chunk_h_gated_delta_rule
-    B, T, H, Dk, Dv, L = (args.batch if args.batch_given else 4), 8192, 16, 128, 128, 14
-    gen = torch.Generator().manual_seed(rank)
+    B, T, H, Dk, Dv, L = 4, 8192, 16, 128, 128, 14
+    gen = torch.Generator().manual_seed(11)
     q = torch.randn(B, T, H, Dk, generator=gen).bfloat16().to(dev)
     k = torch.randn(B, T, H, Dk, generator=gen).bfloat16().to(dev)
     v = torch.randn(B, T, H, Dv, generator=gen).bfloat16().to(dev)
@@ -196,58 +313,103 @@ def run_gdn(args, rank, world, local):
     g = torch.nn.functional.logsigmoid(torch.randn(B, T, H, generator=gen) + 3.0).float().to(dev)
     lam = torch.nn.functional.softplus(torch.randn(B, T, H, L, generator=gen)).bfloat16().to(dev)
     do = torch.randn(B, T, H, Dv, generator=gen).bfloat16().to(dev)
-
-    def fwd():
-        return chunk_h_gated_delta_rule(q, k, v, g, lam, beta, use_qk_l2norm_in_kernel=True)[0]
-
-    W, K = max(args.warmup, 3), args.steps
-    for _ in range(W):
-        fwd()
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    sampler = ClockSampler(local)
-    e0.record()
-    for _ in range(K):
-        fwd()
-    e1.record()
-    torch.cuda.synchronize()
-    ms_fwd = e0.elapsed_time(e1) / K
-    clocks = sampler.stop()
     ins = [x.clone().requires_grad_(True) for x in (q, k, v, g, lam, beta)]
 
+    def fwd():
+        with torch.no_grad():
+            chunk_h_gated_delta_rule(q, k, v, g, lam, beta, use_qk_l2norm_in_kernel=True)
+
     def fwdbwd():
-        o = chunk_h_gated_delta_rule(ins[0], ins[1], ins[2], ins[3], ins[4], ins[5], use_qk_l2norm_in_kernel=True)[0]
+        o = chunk_h_gated_delta_rule(*ins, use_qk_l2norm_in_kernel=True)[0]
         torch.autograd.grad(o, ins, do)
 
-    fwdbwd()
-    torch.cuda.synchronize()
-    Kb = K
-    e0.record()
-    for _ in range(Kb):
-        fwdbwd()
-    e1.record()
-    torch.cuda.synchronize()
-    ms_fb = e0.elapsed_time(e1) / Kb
+    out = {}
+    for name, fn in (("forward", fwd), ("forward+backward", fwdbwd)):
+        for _ in range(2):
+            fn()
+        n0 = launches()
+        times = time_blocks(fn, steps, torch.cuda.synchronize, min_total_ms=300.0, max_blocks=10)
+        out[name] = (statistics.median(times) / steps, (launches() - n0) // len(times))
     C, NT = 64, T // 64
     Lc = (NT - 1).bit_length()
     CK, CV, S = 2 * C * C * Dk, 2 * C * C * Dv, 2 * C * Dk * Dv
-    flops_fwd = (5 * CK + 2 * CV + 2 * C ** 3 + Lc * 2.5 * S) * B * H * NT     # reference-formulation count
-    pk = peaks()
-    line = {
-        "metric": "log-linear Gated DeltaNet chunkwise tokens/s at T=8K", "value": B * T / (ms_fb * 1e-3), "unit": "tokens/s",
-        "n_gpus": 1, "steps": Kb, "warmup": W, "ms_per_step": ms_fb, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": f"log-linear Gated DeltaNet fwd+bwd, B={B} T=8192 H=16 Dk=Dv=128 chunk=64 L=14",
-                   "note": "through chunk_h_gated_delta_rule: l2norm kernels, forward, backward; lambda / scale and dtype casts are torch ops"},
-        "forward_only": {"ms": ms_fwd, "tokens_per_s": B * T / (ms_fwd * 1e-3)},
-        "roofline": {"bound": "tensor", "achieved": flops_fwd / (ms_fwd * 1e-3) / 1e12, "peak": pk["tflops"], "unit": "TFLOP/s",
-                     "frac": flops_fwd / (ms_fwd * 1e-3) / 1e12 / pk["tflops"], "traffic": None, "peak_source": pk["source"],
-                     "kernel": "GDN forward launch chain (chunk preparation + state scan), reference-formulation flops"},
-        # kernels of this library per forward + backward with the forward states kept: l2norm forward x2, chunk
-        # preparation, state scan; reverse scan, level gradients, chunk-local gradients, l2norm backward x2
-        "gpu_launches": 9 * Kb, "clocks": clocks,
-    }
-    print(json.dumps(line), flush=True)
+    flops_fwd = (5 * CK + 2 * CV + 2 * C ** 3 + Lc * 2.5 * S) * B * H * NT     # count of the reference's formulation
+    ms_fb, nl = out["forward+backward"]
+    return {"workload": f"log-linear Gated DeltaNet fwd+bwd through chunk_h_gated_delta_rule, B={B} T={T} H={H} Dk=Dv=128 chunk=64 L={L}",
+            "ms_per_step": ms_fb, "tokens_per_s": B * T / (ms_fb * 1e-3), "steps": steps, "gpu_launches": nl,
+            "forward_only_ms": out["forward"][0],
+            "forward_tflops_reference_formulation": flops_fwd / (out["forward"][0] * 1e-3) / 1e12}
+
+
+# ----------------------------------------------------------------------------------------------
+# the reference's Triton kernels on this GPU (N = 1), run in a child process
+# ----------------------------------------------------------------------------------------------
+def triton_arm_child(args):
+    """Child process: times the reference's own chunkwise_fwd + chunkwise_bwd (Triton) on the headline inputs
+    after its autotune warm-up, and compares this repository's outputs with them.  Prints one JSON line."""
+    os.environ.setdefault("TRITON_CACHE_DIR", os.path.join(ROOT, "baseline", "_ref", "triton_cache"))
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    try:
+        from baseline import ref_compat
+        m = ref_compat.load_reference()
+        cw, HT = m["chunkwise"], m["base"].HType
+        q, k, v, g, l, do = [t.to(dev) for t in make_inputs(0, False)]
+
+        def ref_step():
+            o, gc, _ = cw.chunkwise_fwd(q=q, k=k, v=v, g=g, l=l, head_first=False, level_base=2, htype=HT.WEAK, chunk_size=64,
+                                        output_final_state=False)
+            return (o,) + tuple(cw.chunkwise_bwd(q=q, k=k, v=v, g=gc, l=l, do=do, head_first=False, level_base=2, htype=HT.WEAK,
+                                                 chunk_size=64))
+        t0 = time.perf_counter()
+        ref = ref_step()                       # compiles and autotunes
+        torch.cuda.synchronize()
+        compile_s = time.perf_counter() - t0
+        for _ in range(max(args.warmup, 3)):
+            ref_step()
+        K = max(3, min(args.steps, 10))
+        times = time_blocks(ref_step, K, torch.cuda.synchronize, min_total_ms=500.0, max_blocks=5)
+        ms = statistics.median(times) / K
+        from hattention_b200.base import HType
+        from hattention_b200.chunkwise import chunkwise_bwd, chunkwise_fwd
+        kept = []
+        o, g_cum, _ = chunkwise_fwd(q, k, v, g, l, False, 2, HType.WEAK, 64, False, keep_workspace=kept)
+        ours = (o,) + tuple(chunkwise_bwd(q, k, v, g_cum, l, do, False, 2, HType.WEAK, 64, fwd_workspace=kept[0]))
+        torch.cuda.synchronize()
+        err = {}
+        for name, a, b in zip(("o", "dq", "dk", "dv", "dg", "dl"), ours, ref):
+            a, b = a.float(), b.float()
+            err[name] = {"max_abs": (a - b).abs().max().item(), "max_abs_triton": b.abs().max().item(),
+                         "rel_frobenius": ((a - b).norm() / b.norm()).item()}
+        w = WORKLOAD
+        print(json.dumps({"status": "ok", "ms_per_step": ms, "tokens_per_s": w["B"] * w["T"] / (ms * 1e-3), "steps": K,
+                          "blocks": len(times), "first_call_s": compile_s, "max_err_vs_triton": err,
+                          "what": "hattention.chunkwise.chunkwise_fwd + chunkwise_bwd (Triton, autotuned), same inputs, same GPU"}),
+              flush=True)
+    except Exception as e:      # noqa: BLE001  (the first line of the error is the result)
+        msg = (str(e).strip().splitlines() or [type(e).__name__])[0]
+        print(json.dumps({"status": "unavailable", "error": f"{type(e).__name__}: {msg}"[:400]}), flush=True)
+
+
+def triton_reference(args, timeout_s):
+    if not os.path.isdir(os.path.join(ROOT, "baseline", "_ref", "hattention")):
+        return {"status": "unavailable", "error": "baseline/_ref/hattention missing (python baseline/make_ref.py <reference checkout>)"}
+    cmd = [sys.executable, os.path.abspath(__file__), "--triton-arm-child", "--steps", str(args.steps), "--warmup", str(args.warmup)]
+    env = dict(os.environ)
+    for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK"):
+        env.pop(k, None)
+    try:
+        r = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout_s, env=env)
+    except subprocess.TimeoutExpired:
+        return {"status": "unavailable", "error": f"no result within {timeout_s} s (Triton compile + autotune of the reference kernels)"}
+    for line in reversed(r.stdout.strip().splitlines()):
+        if line.startswith("{"):
+            try:
+                return json.loads(line)
+            except ValueError:
+                continue
+    tail = (r.stderr.strip().splitlines() or ["no output"])[-1]
+    return {"status": "unavailable", "error": f"child exited {r.returncode}: {tail}"[:400]}
 
 
 def run_sequence_parallel(args, rank, world, local):
@@ -279,21 +441,18 @@ def run_sequence_parallel(args, rank, world, local):
         o = hattention_sequence_parallel(*ins)
         torch.autograd.grad(o, ins, do)
 
+    def barrier():
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+
     W, K = max(args.warmup, 3), args.steps
     for _ in range(W):
         step()
-    dist.barrier()
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     sampler = ClockSampler(local)
-    e0.record()
-    for _ in range(K):
-        step()
-    e1.record()
-    torch.cuda.synchronize()
-    dist.barrier()
+    times = time_blocks(step, K, barrier, min_total_ms=500.0, max_blocks=10)
     clocks = sampler.stop()
-    t = torch.tensor([e0.elapsed_time(e1) / K], device=dev, dtype=torch.float64)
+    t = torch.tensor([statistics.median(times) / K], device=dev, dtype=torch.float64)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms = t.item()
     if rank == 0:
@@ -314,16 +473,22 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="only the headline measurement: no secondary configurations, no Triton reference, no CPU baselines")
+    ap.add_argument("--triton-timeout", type=int, default=420, help="seconds allowed for the reference Triton measurement")
+    ap.add_argument("--triton-arm-child", action="store_true", help=argparse.SUPPRESS)
+    ap.add_argument("--timed-ms", type=float, default=1000.0,
+                    help="blocks of K steps are repeated until this much device time has been measured (0: one block, "
+                         "for profiler captures)")
     ap.add_argument("--workload", default="mamba2", choices=["mamba2", "gdn", "mamba2-sp"],
-                    help="mamba2 = the headline workload; gdn = log-linear Gated DeltaNet layer, B=4 T=8192 H=16 Dk=Dv=128 L=14; "
-                         "mamba2-sp = Mamba-2 with one sequence split along T over the ranks (run under torchrun)")
+                    help="mamba2 = the headline workload (other configurations ride along under `secondary`); "
+                         "gdn = only the Gated DeltaNet secondary measurement (B=4 T=8192 H=16 Dk=Dv=128 L=14); mamba2-sp = Mamba-2 with one sequence split along T over the ranks (run under torchrun)")
     ap.add_argument("--batch", type=int, default=WORKLOAD["B"],
                     help="per-GPU batch; the headline workload is 2, profiler captures use 1")
     ap.add_argument("--seq-len", type=int, default=WORKLOAD["T"],
                     help="sequence length; the headline workload is 16384 (65536 with --batch 1 is one GPU's share of the "
                          "multi-GPU scaling configuration); L follows as 7 + ceil(log2(T/64))")
     args = ap.parse_args()
-    args.batch_given = any(a == "--batch" or a.startswith("--batch=") for a in sys.argv[1:])
     WORKLOAD["B"] = args.batch
     if args.seq_len != WORKLOAD["T"]:
         WORKLOAD["T"] = args.seq_len
@@ -332,14 +497,20 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
 
+    if args.triton_arm_child:
+        triton_arm_child(args)
+        return
     if args.impl == "reference":
         run_reference(args, rank, world)
         return
-    if args.workload == "gdn":
-        run_gdn(args, rank, world, local)
-        return
     if args.workload == "mamba2-sp":
         run_sequence_parallel(args, rank, world, local)
+        return
+    if args.workload == "gdn":
+        if not torch.cuda.is_available():
+            raise SystemExit("bench.py needs a CUDA device: the hot path has no CPU fallback")
+        torch.cuda.set_device(local)
+        print(json.dumps(secondary_gdn(torch.device("cuda", local), args.steps)), flush=True)
         return
 
     if not torch.cuda.is_available():
@@ -351,17 +522,20 @@ def main():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
 
+    from hattention_b200 import _lib
     from hattention_b200.base import HType
     from hattention_b200.chunkwise import chunkwise_bwd, chunkwise_fwd
 
     w = WORKLOAD
     host = make_inputs(seed=rank, pin=True)
     q, k, v, g, l, do = [t.to(dev) for t in host]
+    last_ws = []
 
-    def step(q, k, v, g, l, do):
+    def step(q=q, k=k, v=v, g=g, l=l, do=do):
         kept = []      # the forward's scratch stays alive until the backward, as the autograd function does
         o, g_cum, _ = chunkwise_fwd(q, k, v, g, l, False, 2, HType.WEAK, 64, False, keep_workspace=kept)
         grads = chunkwise_bwd(q, k, v, g_cum, l, do, False, 2, HType.WEAK, 64, fwd_workspace=kept[0])
+        last_ws[:] = kept
         return (o,) + tuple(grads)
 
     def barrier():
@@ -373,20 +547,21 @@ def main():
     W = max(args.warmup, 3)
     K = args.steps
     for _ in range(W):
-        outs = step(q, k, v, g, l, do)
+        outs = step()
     barrier()
-    # ---- device-resident timing
+    # ---- device-resident timing: R blocks of exactly K steps
     sampler = ClockSampler(local) if rank == 0 else None
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(K):
-        outs = step(q, k, v, g, l, do)
-    e1.record()
-    barrier()
-    ms = e0.elapsed_time(e1)
+    n0 = launches()
+    times = time_blocks(step, K, barrier, min_total_ms=args.timed_ms)
+    launches_per_block = (launches() - n0) // len(times)
     clocks = sampler.stop() if sampler else None
+    status = _lib.workspace_status(last_ws[0], torch.cuda.current_stream().cuda_stream)
+    if status != 0:
+        raise SystemExit("a kernel gave up on a bounded wait during the timed region (status word set): no valid measurement")
+    ms_block = statistics.median(times)
 
     # ---- end to end: host buffers in, host buffers out, every step
+    outs = step()
     host_out = [torch.empty(t.shape, dtype=t.dtype).pin_memory() for t in outs]
     h2d = sum(t.numel() * t.element_size() for t in host)
     d2h = sum(t.numel() * t.element_size() for t in host_out)
@@ -430,49 +605,65 @@ def main():
     barrier()
     ms_e2e = f0.elapsed_time(f1)
 
-    t_dev = torch.tensor([ms, ms_e2e], device=dev, dtype=torch.float64)
+    t_dev = torch.tensor([ms_block, ms_e2e, min(times), max(times)], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t_dev, op=dist.ReduceOp.MAX)
-    ms, ms_e2e = t_dev.tolist()
+    ms_block, ms_e2e, t_min, t_max = t_dev.tolist()
 
     if rank == 0:
         tokens = w["B"] * w["T"] * world
-        per_step = ms / K
+        per_step = ms_block / K
         value = tokens / (per_step * 1e-3)
         e2e_val = tokens / (ms_e2e / Ke * 1e-3)
         pk = peaks()
         flops = fmin_flops(w["B"], w["T"], w["H"], w["P"], w["N"])
         achieved = flops / (per_step * 1e-3) / 1e12
-        NT = w["T"] // 64
-        NS = (NT + 7) // 8
-        # forward: segment summaries, segment scan, high-level output, chunk kernel; backward: un-cumsum,
-        # high-level backward, reverse segment scan (segment states are those of the forward call),
-        # two chunk passes, dg, two casts
-        launches_per_step = (4 if NS > 1 else 1) + 1 + (2 if NS > 1 else 0) + 2 + 1 + 2
+        traffic, traffic_kernel = measured_traffic(w)
         line = {
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
             "ms_per_step": per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": NAME.replace("B=2", f"B={w['B']}").replace("T=16384", f"T={w['T']}").replace("L=15", f"L={w['L']}"), "l2": "inputs_exceed_l2 (about 320 MB of inputs per step vs 126 MB L2)",
+            "config": {"workload": workload_name(), "l2": "inputs_exceed_l2 (about 320 MB of inputs per step vs 126 MB L2)",
                        "sharding": f"batch x {world}, no collective"},
+            "repeats": {"blocks": len(times), "steps_per_block": K, "ms_per_step_median": per_step,
+                        "ms_per_step_min": t_min / K, "ms_per_step_max": t_max / K, "timed_ms_total": sum(times)},
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": pk["tflops"], "unit": "TFLOP/s",
-                         "frac": achieved / pk["tflops"],
-                         # DRAM read + write of the dominant kernel (forward-order backward pass) from an ncu
-                         # capture at B=1 (227.9 MB per launch), proportional to the batch
-                         "traffic": 227.9e6 * w["B"] if (w["T"], w["H"]) == (16384, 32) else None,
+                         "frac": achieved / pk["tflops"], "frac_of_burst_peak": achieved / pk["tflops_burst"],
+                         "traffic": traffic, "traffic_kernel": traffic_kernel,
+                         "traffic_source": "profiles/tc_counters_B1.json (ncu, batch 1, scaled by the batch)" if traffic else None,
                          "peak_source": pk["source"],
                          "kernel": "whole fwd+bwd launch chain of one step (algorithmic flops F_min / step time)",
                          "algorithmic_flops_per_step": flops,
                          "algorithmic_bytes_per_step": algorithmic_bytes(w["B"], w["T"], w["H"], w["P"], w["N"], w["G"], w["L"])},
             "e2e": {"value": e2e_val, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "steps": Ke},
-            "gpu_launches": launches_per_step * K,
+            "gpu_launches": launches_per_block,
             "clocks": clocks,
         }
-        if not args.no_cpu_baseline:
+        extras = world == 1 and not args.no_extras
+        if extras and not args.no_cpu_baseline:
             threads = os.cpu_count() or 1
-            val, sample = cpu_baseline_sample(threads)
-            line["cpu_baseline"] = {"value": val, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample}
+            kind, T, ctimes, sample = cpu_chunkwise_steps(threads, steps=3, warmup=1)
+            line["cpu_baseline"] = {"value": CPU_SLICE["B"] * T / min(ctimes), "unit": "tokens/s", "cores": threads, "kind": kind,
+                                    "sample": sample + ", best of 3"}
+            line["cpu_baseline_recurrent"] = cpu_recurrent_sample(threads)
+        if extras:
+            torch.cuda.empty_cache()
+            sec = []
+            for fn, a in ((secondary_mamba2, (dev, 8, 4096, 24, False, 10, "log-linear Mamba-2 forward, B=8 T=4096 H=24 P=64 N=128 G=1 L=13")),
+                          (secondary_mamba2, (dev, 1, 65536, 32, True, 5, "log-linear Mamba-2 fwd+bwd, B=1 T=65536 H=32 P=64 N=128 G=1 L=17 "
+                                                                           "(one GPU's share of the long-context configuration)")),
+                          (secondary_gdn, (dev, 5))):
+                try:
+                    sec.append(fn(*a))
+                except Exception as e:      # noqa: BLE001
+                    sec.append({"workload": a[-1] if isinstance(a[-1], str) else "log-linear Gated DeltaNet", "error": str(e)[:200]})
+                torch.cuda.empty_cache()
+            line["secondary"] = sec
+            tr = triton_reference(args, args.triton_timeout)
+            if tr.get("status") == "ok":
+                tr["speedup"] = tr["ms_per_step"] / per_step
+            line["triton_reference"] = tr
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
