@@ -163,6 +163,29 @@ int llattn_gdn_fwd(const void* q, const void* k, const void* v, const void* beta
                    void* o, float* g_cum, void* Aw, void* Au, void* workspace, size_t workspace_bytes,
                    int B, int T, int H, int K, int V, int L, void* stream);
 
+/* Prompt pass of the log-linear Gated DeltaNet layer: llattn_gdn_fwd plus the level states a decoder continues
+ * from.  `states` is fp32 (B,H,K,V,L), level innermost (the layout of the reference's HState,
+ * hattention/recurrent.py:9-40); it is cleared and then, for every set bit j of NT - 1 (NT = T / 64), level
+ * 7 + j receives the state of the block of 2^j chunks that the LAST chunk reads, i.e. the states as they stand
+ * before the last 64 tokens.  The caller feeds those 64 tokens (and any tokens beyond T) through
+ * llattn_gdn_step, which builds the levels inside the chunk.  Together the two replace hattention_prefill with
+ * hstruct = GDELTA (hattention/kernel.py:469-560: chunkwise_fwd with output_final_state=True, then
+ * postprocess_prefill_hstate_, :378-466).  Other arguments and constraints as llattn_gdn_fwd. */
+int llattn_gdn_prefill(const void* q, const void* k, const void* v, const void* beta, const float* g, const void* lambda,
+                       void* o, float* g_cum, void* Aw, void* Au, float* states, void* workspace, size_t workspace_bytes,
+                       int B, int T, int H, int K, int V, int L, void* stream);
+
+/* One decode step of the log-linear Gated DeltaNet layer for every (batch, head).  Replaces hattention_step with
+ * hstruct = GDELTA (hattention/kernel.py:563-633) after its l2norm / scale of q and k, i.e. HState.cascade_weak /
+ * insert with the delta-rule gate and step_output (hattention/recurrent.py:42-54, 79-98, 134-166): levels
+ * 0..carry_level are summed into level carry_level (the caller runs the cascade on the token counts), every
+ * level becomes exp(g) (S - beta k (k^T S)), level 0 becomes beta k v^T, and o = q . sum_l lambda_l S_l.
+ * states fp32 (B,H,K,V,L) updated in place, one pass over HBM; q, k (B,H,K) already normalised (q also scaled),
+ * v (B,H,V), beta (B,H), lambda (B,H,L), o (B,H,V) bf16; g (B,H) fp32 log decay.
+ * K % 32 == 0, K <= 256, V % 8 == 0, L <= 32 (K / 32 in {1,2,3,4,6,8}; {2,4} when L > 16). */
+int llattn_gdn_step(float* states, const void* q, const void* k, const void* v, const void* beta, const float* g,
+                    const void* lambda, void* o, int B, int H, int K, int V, int L, int carry_level, void* stream);
+
 /* Log-linear Gated DeltaNet backward, first stage: everything that involves the inter-chunk level
  * states.  Replaces, inside hattention.chunkwise_hgdn.chunkwise_bwd (hattention/chunkwise_hgdn.py:
  * 799-1010), the per-level loop over chunk_gated_delta_rule_fwd_h (state recomputation),

@@ -277,7 +277,18 @@ size_t llattn_gdn_fwd_keep_workspace_bytes(int B, int T, int H, int K, int V, in
 
 static int gdn_fwd_impl(const void* q, const void* k, const void* v, const void* beta, const float* g, const void* lambda,
                         void* o, float* g_cum, void* Aw, void* Au, void* workspace, size_t workspace_bytes,
-                        int B, int T, int H, int K, int V, int L, void* stream, bool keep);
+                        int B, int T, int H, int K, int V, int L, void* stream, bool keep, float* final_states = nullptr);
+
+int llattn_gdn_prefill(const void* q, const void* k, const void* v, const void* beta, const float* g, const void* lambda,
+                       void* o, float* g_cum, void* Aw, void* Au, float* states, void* workspace, size_t workspace_bytes,
+                       int B, int T, int H, int K, int V, int L, void* stream) {
+    if (!states) return LLATTN_ERR_NULL;
+    int rc = gdn_check(B, T, H, K, V, L);
+    if (rc != 0) return rc;
+    cudaError_t e = cudaMemsetAsync(states, 0, (size_t)B * H * K * V * L * sizeof(float), (cudaStream_t)stream);
+    if (e != cudaSuccess) return (int)e;
+    return gdn_fwd_impl(q, k, v, beta, g, lambda, o, g_cum, Aw, Au, workspace, workspace_bytes, B, T, H, K, V, L, stream, false, states);
+}
 
 int llattn_gdn_fwd(const void* q, const void* k, const void* v, const void* beta, const float* g, const void* lambda,
                    void* o, float* g_cum, void* Aw, void* Au, void* workspace, size_t workspace_bytes,
@@ -293,7 +304,7 @@ int llattn_gdn_fwd_keep(const void* q, const void* k, const void* v, const void*
 
 static int gdn_fwd_impl(const void* q, const void* k, const void* v, const void* beta, const float* g, const void* lambda,
                         void* o, float* g_cum, void* Aw, void* Au, void* workspace, size_t workspace_bytes,
-                        int B, int T, int H, int K, int V, int L, void* stream, bool keep) {
+                        int B, int T, int H, int K, int V, int L, void* stream, bool keep, float* final_states) {
     int rc = gdn_check(B, T, H, K, V, L);
     if (rc != 0) return rc;
     if (!q || !k || !v || !beta || !g || !lambda || !o || !g_cum || !Aw || !Au) return LLATTN_ERR_NULL;
@@ -306,6 +317,7 @@ static int gdn_fwd_impl(const void* q, const void* k, const void* v, const void*
     p.q = (const __nv_bfloat16*)q; p.k = (const __nv_bfloat16*)k; p.v = (const __nv_bfloat16*)v;
     p.beta = (const __nv_bfloat16*)beta; p.g = g; p.l = (const __nv_bfloat16*)lambda;
     p.o = (__nv_bfloat16*)o; p.g_cum = g_cum; p.Aw = (__nv_bfloat16*)Aw; p.Au = (__nv_bfloat16*)Au;
+    p.final_states = final_states;
     return keep ? llattn::gdn_fwd_keep_dispatch(p, (cudaStream_t)stream) : llattn::gdn_fwd_dispatch(p, (cudaStream_t)stream);
 }
 

@@ -406,6 +406,27 @@ __global__ void __launch_bounds__(256, 1) gdn_scan_kernel(const GdnParams p) {
                 }
             }
         }
+        if (OUT && c == p.NT - 1 && p.final_states != nullptr) {
+            // prefill hand-off: the level states every token of the last chunk starts from.  Level 7 + lv holds the block
+            // of 2^lv chunks for each set bit lv of c (the binary-indexed tree as it stands before this chunk); the
+            // caller steps the last chunk's tokens through the decode kernel, which fills levels 0..6.
+            float* dst = p.final_states + ((long)b * p.H + h) * KD * p.V * p.L;
+#pragma unroll
+            for (int lv = 0; lv < GDN_MAXLEV; ++lv) {
+                if (lv < nlev && ((c >> lv) & 1)) {
+#pragma unroll
+                    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                        for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const int row = warp * 16 * MT + mt * 16 + lr + (e >> 1) * 8;
+                                const int col = vs * GDN_VS + nt * 8 + lc2 + (e & 1);
+                                dst[((long)row * p.V + col) * p.L + INTRA_LEVELS + lv] = M[lv][mt][nt][e];
+                            }
+                }
+            }
+        }
         const bf16* cQW = sQW;
         const bf16* cKd = sKd + st * CH * LDK;
         const bf16* cU = sU + st * CH * LDS;

@@ -21,6 +21,7 @@ struct GdnParams {
     // outputs
     __nv_bfloat16* o;            // (B,T,H,V)
     float* g_cum;                // (B,T,H)
+    float* final_states;         // optional (B,H,K,V,L) fp32: level states as of the start of the last chunk (prefill hand-off)
     __nv_bfloat16* Aw;           // (B,T,H,64)  (I + A)^-1 rows, saved for the backward
     __nv_bfloat16* Au;           // (B,T,H,64)  (I + A*Gamma)^-1 rows
     // scratch written by the chunk preparation, read by the scan

@@ -50,10 +50,7 @@ struct Mamba2Params {
     int NT, NS, LH;
     int o_has_high;
     int lev_lo;                  // first segment level handled by one launch of the tensor-core high-level backward
-    int order;                   // EXPERIMENT: 0 = heads fastest in the grid, 1 = segments fastest
     int reuse_states;            // backward: seg_D / seg_H0 come from the forward call, do not recompute them
-    unsigned int zero;           // always 0 (every Mamba2Params is value-initialised); a run-time zero that the
-                                 // compiler cannot fold, used to tie the release of a tile to the loads from it
 };
 
 int mamba2_fwd_dispatch(Mamba2Params p, cudaStream_t stream);

@@ -9,8 +9,6 @@
 // tensor operation per 128 x 32 box instead of per-thread red.global).  The gradient w.r.t. the
 // in-chunk cumulative decay uses q_i.dq_i = sum_levels lambda[i,lev] dlambda[i,lev] (o is linear in
 // lambda), so only k_j.dk_j needs a pass over a tile.
-#include <stdlib.h>
-
 #include "tc_common.cuh"
 
 namespace llattn {
@@ -86,8 +84,8 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_fwdorder_tc_kernel(con
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + SM::bar_off + 104);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int h = p.order ? (blockIdx.x / p.NS) % p.H : blockIdx.x % p.H;
-    const int r = p.order ? blockIdx.x % p.NS : (blockIdx.x / p.H) % p.NS;
+    const int h = blockIdx.x % p.H;
+    const int r = (blockIdx.x / p.H) % p.NS;
     const int b = blockIdx.x / (p.H * p.NS);
     const int grp = h / (p.H / p.G);
     const int L = p.L;
@@ -321,71 +319,83 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_fwdorder_tc_kernel(con
         float wq_tile = 0.f;                         // sum_j bf16(dS_ij) S_ij: q_i.dq_i of the tile product, same rounding as dk
 #pragma unroll
         for (int i = 0; i < 8; ++i) bins[i] = 0.f;
+        // blocks above the diagonal: zeros
+#pragma unroll 1
+        for (int jb = rb + 1; jb < 4; ++jb) {
+            const int j0 = jb * 32 + ch * 16;
 #pragma unroll
-        for (int jb = 0; jb < 4; ++jb) {
+            for (int c = 0; c < 2; ++c)
+                *reinterpret_cast<uint4*>(sDS + umma::tile_offset(row, j0 + c * 8, tc::PT)) = make_uint4(0u, 0u, 0u, 0u);
+        }
+        // blocks below the diagonal: one level per block, decay factorised through the block end.  A run-time loop
+        // (one copy of the body): the fully unrolled form made the loop body larger than the instruction cache.
+#pragma unroll 1
+        for (int jb = 0; jb < rb; ++jb) {
             const int j0 = jb * 32 + ch * 16;
             uint32_t packed[8];
-            if (jb > rb) {
+            float s[16], dp[16];
+            umma::tmem_ld16x2(umma::tmem_addr(tbase + tcb::TB_S, warp, j0), s, umma::tmem_addr(tbase + tcb::TB_DP, warp, j0), dp);
+            const bool lev6 = ((rb ^ jb) == 1);
+            const float lm = lev6 ? lam[6] : lam[7];
+            const float rf = fexp(Gi - sGp[jb * 32 + 31]);
+            float bsum = 0.f;
 #pragma unroll
-                for (int e = 0; e < 8; ++e) packed[e] = 0u;
-            } else {
-                float s[16], dp[16];
-                umma::tmem_ld16(umma::tmem_addr(tbase + tcb::TB_S, warp, j0), s);
-                umma::tmem_ld16(umma::tmem_addr(tbase + tcb::TB_DP, warp, j0), dp);
-                if (jb < rb) {
-                    const bool lev6 = ((rb ^ jb) == 1);
-                    const float lm = lev6 ? lam[6] : lam[7];
-                    const float rf = fexp(Gi - sGp[jb * 32 + 31]);
-                    float bsum = 0.f;
+            for (int e = 0; e < 16; e += 4) {
+                const float4 cf = *reinterpret_cast<const float4*>(sCf + j0 + e);
+                const float cfv[4] = {cf.x, cf.y, cf.z, cf.w};
 #pragma unroll
-                    for (int e = 0; e < 16; e += 4) {
-                        const float4 cf = *reinterpret_cast<const float4*>(sCf + j0 + e);
-                        const float cfv[4] = {cf.x, cf.y, cf.z, cf.w};
-#pragma unroll
-                        for (int u = 0; u < 4; ++u) {
-                            const float ed = dp[e + u] * rf * cfv[u];
-                            bsum += ed * s[e + u];
-                            const float dsv = ed * lm;
-                            wq_tile += __bfloat162float(__float2bfloat16(dsv)) * s[e + u];
-                            s[e + u] = dsv;
-                        }
-                        packed[e >> 1] = pack_bf16(s[e], s[e + 1]);
-                        packed[(e >> 1) + 1] = pack_bf16(s[e + 2], s[e + 3]);
-                    }
-                    if (lev6) bins[6] += bsum; else bins[7] += bsum;
-                } else {
-                    const int li = lane;
-#pragma unroll
-                    for (int e = 0; e < 16; e += 4) {
-                        const float4 gj = *reinterpret_cast<const float4*>(sGp + j0 + e);
-                        const float gjv[4] = {gj.x, gj.y, gj.z, gj.w};
-#pragma unroll
-                        for (int u = 0; u < 4; ++u) {
-                            const int jj = ch * 16 + e + u;
-                            const int x = li ^ jj;
-                            const float d = (jj <= li) ? (Gi - gjv[u]) : -INFINITY;
-                            const float ed = dp[e + u] * fexp(d);
-                            const float es = ed * s[e + u];
-                            float lm = lam[0];
-                            lm = (x >= 1) ? lam[1] : lm;
-                            lm = (x >= 2) ? lam[2] : lm;
-                            lm = (x >= 4) ? lam[3] : lm;
-                            lm = (x >= 8) ? lam[4] : lm;
-                            lm = (x >= 16) ? lam[5] : lm;
-                            bins[0] += (x == 0) ? es : 0.f;
-                            bins[1] += (x == 1) ? es : 0.f;
-                            bins[2] += (x >= 2 && x < 4) ? es : 0.f;
-                            bins[3] += (x >= 4 && x < 8) ? es : 0.f;
-                            bins[4] += (x >= 8 && x < 16) ? es : 0.f;
-                            bins[5] += (x >= 16) ? es : 0.f;
-                            const float dsv = ed * lm;
-                            wq_tile += __bfloat162float(__float2bfloat16(dsv)) * s[e + u];
-                            s[e + u] = dsv;
-                        }
-                        packed[e >> 1] = pack_bf16(s[e], s[e + 1]);
-                        packed[(e >> 1) + 1] = pack_bf16(s[e + 2], s[e + 3]);
-                    }
+                for (int u = 0; u < 4; ++u) {
+                    const float ed = dp[e + u] * rf * cfv[u];
+                    bsum += ed * s[e + u];
+                    const float dsv = ed * lm;
+                    wq_tile += __bfloat162float(__float2bfloat16(dsv)) * s[e + u];
+                    s[e + u] = dsv;
                 }
+                packed[e >> 1] = pack_bf16(s[e], s[e + 1]);
+                packed[(e >> 1) + 1] = pack_bf16(s[e + 2], s[e + 3]);
+            }
+            if (lev6) bins[6] += bsum; else bins[7] += bsum;
+#pragma unroll
+            for (int c = 0; c < 2; ++c)
+                *reinterpret_cast<uint4*>(sDS + umma::tile_offset(row, j0 + c * 8, tc::PT)) =
+                    make_uint4(packed[c * 4], packed[c * 4 + 1], packed[c * 4 + 2], packed[c * 4 + 3]);
+        }
+        // diagonal block: levels 0..5, causal mask folded into the exponent
+        {
+            const int j0 = rb * 32 + ch * 16;
+            uint32_t packed[8];
+            float s[16], dp[16];
+            umma::tmem_ld16x2(umma::tmem_addr(tbase + tcb::TB_S, warp, j0), s, umma::tmem_addr(tbase + tcb::TB_DP, warp, j0), dp);
+            const int li = lane;
+#pragma unroll
+            for (int e = 0; e < 16; e += 4) {
+                const float4 gj = *reinterpret_cast<const float4*>(sGp + j0 + e);
+                const float gjv[4] = {gj.x, gj.y, gj.z, gj.w};
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int jj = ch * 16 + e + u;
+                    const int x = li ^ jj;
+                    const float d = (jj <= li) ? (Gi - gjv[u]) : -INFINITY;
+                    const float ed = dp[e + u] * fexp(d);
+                    const float es = ed * s[e + u];
+                    float lm = lam[0];
+                    lm = (x >= 1) ? lam[1] : lm;
+                    lm = (x >= 2) ? lam[2] : lm;
+                    lm = (x >= 4) ? lam[3] : lm;
+                    lm = (x >= 8) ? lam[4] : lm;
+                    lm = (x >= 16) ? lam[5] : lm;
+                    bins[0] += (x == 0) ? es : 0.f;
+                    bins[1] += (x == 1) ? es : 0.f;
+                    bins[2] += (x >= 2 && x < 4) ? es : 0.f;
+                    bins[3] += (x >= 4 && x < 8) ? es : 0.f;
+                    bins[4] += (x >= 8 && x < 16) ? es : 0.f;
+                    bins[5] += (x >= 16) ? es : 0.f;
+                    const float dsv = ed * lm;
+                    wq_tile += __bfloat162float(__float2bfloat16(dsv)) * s[e + u];
+                    s[e + u] = dsv;
+                }
+                packed[e >> 1] = pack_bf16(s[e], s[e + 1]);
+                packed[(e >> 1) + 1] = pack_bf16(s[e + 2], s[e + 3]);
             }
 #pragma unroll
             for (int c = 0; c < 2; ++c)
@@ -662,8 +672,8 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_revorder_tc_kernel(con
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + SM::bar_off + 104);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int h = p.order ? (blockIdx.x / p.NS) % p.H : blockIdx.x % p.H;
-    const int r = p.order ? blockIdx.x % p.NS : (blockIdx.x / p.H) % p.NS;
+    const int h = blockIdx.x % p.H;
+    const int r = (blockIdx.x / p.H) % p.NS;
     const int b = blockIdx.x / (p.H * p.NS);
     const int grp = h / (p.H / p.G);
     const int L = p.L;
@@ -945,48 +955,61 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_revorder_tc_kernel(con
         umma::mbar_wait(barA, it & 1, abort_flag);
         umma::fence_after_sync();
         STAMPR();   // 4 S complete
+        // blocks above the diagonal: zeros
+#pragma unroll 1
+        for (int jb = rb + 1; jb < 4; ++jb) {
+            const int j0 = jb * 32 + ch * 16;
 #pragma unroll
-        for (int jb = 0; jb < 4; ++jb) {
+            for (int c = 0; c < 2; ++c)
+                *reinterpret_cast<uint4*>(sP + umma::tile_offset(row, j0 + c * 8, tc::PT)) = make_uint4(0u, 0u, 0u, 0u);
+        }
+        // blocks below the diagonal (run-time loop: one copy of the body keeps the loop inside the instruction cache)
+#pragma unroll 1
+        for (int jb = 0; jb < rb; ++jb) {
             const int j0 = jb * 32 + ch * 16;
             uint32_t packed[8];
-            if (jb > rb) {
+            float s[16];
+            umma::tmem_ld16(umma::tmem_addr(tbase + tcr::TR_S, warp, j0), s);
+            // one level per block, decay factorised through the block end
+            const float lm = ((rb ^ jb) == 1) ? lam[6] : lam[7];
+            const float rf = lm * fexp(Gi - sGp[jb * 32 + 31]);
 #pragma unroll
-                for (int e = 0; e < 8; ++e) packed[e] = 0u;
-            } else {
-                float s[16];
-                umma::tmem_ld16(umma::tmem_addr(tbase + tcr::TR_S, warp, j0), s);
-                if (jb < rb) {
-                    const float lm = ((rb ^ jb) == 1) ? lam[6] : lam[7];
-                    const float rf = lm * fexp(Gi - sGp[jb * 32 + 31]);
+            for (int e = 0; e < 16; e += 4) {
+                const float4 cf = *reinterpret_cast<const float4*>(sCf + j0 + e);
+                packed[e >> 1] = pack_bf16(s[e] * rf * cf.x, s[e + 1] * rf * cf.y);
+                packed[(e >> 1) + 1] = pack_bf16(s[e + 2] * rf * cf.z, s[e + 3] * rf * cf.w);
+            }
 #pragma unroll
-                    for (int e = 0; e < 16; e += 4) {
-                        const float4 cf = *reinterpret_cast<const float4*>(sCf + j0 + e);
-                        packed[e >> 1] = pack_bf16(s[e] * rf * cf.x, s[e + 1] * rf * cf.y);
-                        packed[(e >> 1) + 1] = pack_bf16(s[e + 2] * rf * cf.z, s[e + 3] * rf * cf.w);
-                    }
-                } else {
-                    const int li = lane;
+            for (int c = 0; c < 2; ++c)
+                *reinterpret_cast<uint4*>(sP + umma::tile_offset(row, j0 + c * 8, tc::PT)) =
+                    make_uint4(packed[c * 4], packed[c * 4 + 1], packed[c * 4 + 2], packed[c * 4 + 3]);
+        }
+        // diagonal block: levels 0..5, causal mask folded into the exponent
+        {
+            const int j0 = rb * 32 + ch * 16;
+            uint32_t packed[8];
+            float s[16];
+            umma::tmem_ld16(umma::tmem_addr(tbase + tcr::TR_S, warp, j0), s);
+            const int li = lane;
 #pragma unroll
-                    for (int e = 0; e < 16; e += 4) {
-                        const float4 gj = *reinterpret_cast<const float4*>(sGp + j0 + e);
-                        const float gjv[4] = {gj.x, gj.y, gj.z, gj.w};
+            for (int e = 0; e < 16; e += 4) {
+                const float4 gj = *reinterpret_cast<const float4*>(sGp + j0 + e);
+                const float gjv[4] = {gj.x, gj.y, gj.z, gj.w};
 #pragma unroll
-                        for (int u = 0; u < 4; ++u) {
-                            const int jj = ch * 16 + e + u;
-                            const int x = li ^ jj;
-                            float lm = lam[0];
-                            lm = (x >= 1) ? lam[1] : lm;
-                            lm = (x >= 2) ? lam[2] : lm;
-                            lm = (x >= 4) ? lam[3] : lm;
-                            lm = (x >= 8) ? lam[4] : lm;
-                            lm = (x >= 16) ? lam[5] : lm;
-                            const float d = (jj <= li) ? (Gi - gjv[u]) : -INFINITY;
-                            s[e + u] = s[e + u] * fexp(d) * lm;
-                        }
-                        packed[e >> 1] = pack_bf16(s[e], s[e + 1]);
-                        packed[(e >> 1) + 1] = pack_bf16(s[e + 2], s[e + 3]);
-                    }
+                for (int u = 0; u < 4; ++u) {
+                    const int jj = ch * 16 + e + u;
+                    const int x = li ^ jj;
+                    float lm = lam[0];
+                    lm = (x >= 1) ? lam[1] : lm;
+                    lm = (x >= 2) ? lam[2] : lm;
+                    lm = (x >= 4) ? lam[3] : lm;
+                    lm = (x >= 8) ? lam[4] : lm;
+                    lm = (x >= 16) ? lam[5] : lm;
+                    const float d = (jj <= li) ? (Gi - gjv[u]) : -INFINITY;
+                    s[e + u] = s[e + u] * fexp(d) * lm;
                 }
+                packed[e >> 1] = pack_bf16(s[e], s[e + 1]);
+                packed[(e >> 1) + 1] = pack_bf16(s[e + 2], s[e + 3]);
             }
 #pragma unroll
             for (int c = 0; c < 2; ++c)
@@ -1127,7 +1150,6 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_revorder_tc_kernel(con
 
 int mamba2_bwd2_tc_launch(const Mamba2Params& p_in, cudaStream_t stream) {
     Mamba2Params p = p_in;
-    p.order = getenv("LLATTN_EXPERIMENT_ORDER") ? atoi(getenv("LLATTN_EXPERIMENT_ORDER")) : 0;
     int rc;
     const long BT = (long)p.B * p.T;
     if ((rc = tma::make_panel_map(&p.tm_q, p.q, BT, p.G, p.K, tc::PT)) != 0) return rc;
@@ -1145,7 +1167,6 @@ int mamba2_bwd2_tc_launch(const Mamba2Params& p_in, cudaStream_t stream) {
 
 int mamba2_bwd1_tc_launch(const Mamba2Params& p_in, cudaStream_t stream) {
     Mamba2Params p = p_in;
-    p.order = getenv("LLATTN_EXPERIMENT_ORDER") ? atoi(getenv("LLATTN_EXPERIMENT_ORDER")) : 0;
     int rc;
     const long BT = (long)p.B * p.T;
     if ((rc = tma::make_panel_map(&p.tm_q, p.q, BT, p.G, p.K, tc::PT)) != 0) return rc;

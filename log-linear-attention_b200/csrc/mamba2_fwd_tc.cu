@@ -11,8 +11,6 @@
 //     the masks / decays / lambda weights are applied on the way from tensor memory to the bf16
 //     P tile; level-state masters stay in registers in the tensor-memory readout layout (one
 //     state row per thread), their bf16 copies are written once as MN-major operands.
-#include <stdlib.h>
-
 #include "tc_common.cuh"
 
 namespace llattn {
@@ -60,8 +58,8 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_chunk_fwd_tc_kernel(const 
     static_assert(MP <= 2, "two tensor-memory slots for level reads");
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int h = p.order ? (blockIdx.x / p.NS) % p.H : blockIdx.x % p.H;
-    const int r = p.order ? blockIdx.x % p.NS : (blockIdx.x / p.H) % p.NS;
+    const int h = blockIdx.x % p.H;
+    const int r = (blockIdx.x / p.H) % p.NS;
     const int b = blockIdx.x / (p.H * p.NS);
     const int grp = h / (p.H / p.G);
     const int L = p.L;
@@ -303,50 +301,61 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_chunk_fwd_tc_kernel(const 
         STAMP();                                     // 6
         // ---- S -> P (bf16, K-major A operand of P v).  This thread: row `row`, and in every 32-column
         //      block jb <= rb the 16 columns [jb*32 + ch*16, +16)
+        // blocks above the diagonal: zeros
+#pragma unroll 1
+        for (int jb = rb + 1; jb < 4; ++jb) {
+            const int j0 = jb * 32 + ch * 16;
 #pragma unroll
-        for (int jb = 0; jb < 4; ++jb) {
+            for (int c = 0; c < 2; ++c)
+                *reinterpret_cast<uint4*>(sP + umma::tile_offset(row, j0 + c * 8, tc::PT)) = make_uint4(0u, 0u, 0u, 0u);
+        }
+        // blocks below the diagonal (run-time loop: one copy of the body keeps the loop inside the instruction cache)
+#pragma unroll 1
+        for (int jb = 0; jb < rb; ++jb) {
             const int j0 = jb * 32 + ch * 16;
             uint32_t packed[8];
-            if (jb > rb) {
+            float s[16];
+            umma::tmem_ld16(umma::tmem_addr(tbase + tc::TM_S, warp, j0), s);
+            // one level per block, decay factorised through the block end
+            const float lm = ((rb ^ jb) == 1) ? lam[6] : lam[7];
+            const float rf = lm * fexp(Gi - sGp[jb * 32 + 31]);
 #pragma unroll
-                for (int e = 0; e < 8; ++e) packed[e] = 0u;
-            } else {
-                float s[16];
-                umma::tmem_ld16(umma::tmem_addr(tbase + tc::TM_S, warp, j0), s);
-                if (jb < rb) {
-                    // block below the diagonal: one level, decay factorised through the block end
-                    const float lm = ((rb ^ jb) == 1) ? lam[6] : lam[7];
-                    const float rf = lm * fexp(Gi - sGp[jb * 32 + 31]);
+            for (int e = 0; e < 16; e += 4) {
+                const float4 cf = *reinterpret_cast<const float4*>(sCf + j0 + e);
+                packed[e >> 1] = pack_bf16(s[e] * rf * cf.x, s[e + 1] * rf * cf.y);
+                packed[(e >> 1) + 1] = pack_bf16(s[e + 2] * rf * cf.z, s[e + 3] * rf * cf.w);
+            }
 #pragma unroll
-                    for (int e = 0; e < 16; e += 4) {
-                        const float4 cf = *reinterpret_cast<const float4*>(sCf + j0 + e);
-                        packed[e >> 1] = pack_bf16(s[e] * rf * cf.x, s[e + 1] * rf * cf.y);
-                        packed[(e >> 1) + 1] = pack_bf16(s[e + 2] * rf * cf.z, s[e + 3] * rf * cf.w);
-                    }
-                } else {
-                    // diagonal block: levels 0..5, causal mask folded into the exponent
-                    const int li = lane;             // row - jb*32
+            for (int c = 0; c < 2; ++c)
+                *reinterpret_cast<uint4*>(sP + umma::tile_offset(row, j0 + c * 8, tc::PT)) =
+                    make_uint4(packed[c * 4], packed[c * 4 + 1], packed[c * 4 + 2], packed[c * 4 + 3]);
+        }
+        // diagonal block: levels 0..5, causal mask folded into the exponent
+        {
+            const int j0 = rb * 32 + ch * 16;
+            uint32_t packed[8];
+            float s[16];
+            umma::tmem_ld16(umma::tmem_addr(tbase + tc::TM_S, warp, j0), s);
+            const int li = lane;
 #pragma unroll
-                    for (int e = 0; e < 16; e += 4) {
-                        const float4 gj = *reinterpret_cast<const float4*>(sGp + j0 + e);
-                        const float gjv[4] = {gj.x, gj.y, gj.z, gj.w};
+            for (int e = 0; e < 16; e += 4) {
+                const float4 gj = *reinterpret_cast<const float4*>(sGp + j0 + e);
+                const float gjv[4] = {gj.x, gj.y, gj.z, gj.w};
 #pragma unroll
-                        for (int u = 0; u < 4; ++u) {
-                            const int jj = ch * 16 + e + u;      // column inside the block
-                            const int x = li ^ jj;
-                            float lm = lam[0];
-                            lm = (x >= 1) ? lam[1] : lm;
-                            lm = (x >= 2) ? lam[2] : lm;
-                            lm = (x >= 4) ? lam[3] : lm;
-                            lm = (x >= 8) ? lam[4] : lm;
-                            lm = (x >= 16) ? lam[5] : lm;
-                            const float d = (jj <= li) ? (Gi - gjv[u]) : -INFINITY;
-                            s[e + u] = s[e + u] * fexp(d) * lm;
-                        }
-                        packed[e >> 1] = pack_bf16(s[e], s[e + 1]);
-                        packed[(e >> 1) + 1] = pack_bf16(s[e + 2], s[e + 3]);
-                    }
+                for (int u = 0; u < 4; ++u) {
+                    const int jj = ch * 16 + e + u;
+                    const int x = li ^ jj;
+                    float lm = lam[0];
+                    lm = (x >= 1) ? lam[1] : lm;
+                    lm = (x >= 2) ? lam[2] : lm;
+                    lm = (x >= 4) ? lam[3] : lm;
+                    lm = (x >= 8) ? lam[4] : lm;
+                    lm = (x >= 16) ? lam[5] : lm;
+                    const float d = (jj <= li) ? (Gi - gjv[u]) : -INFINITY;
+                    s[e + u] = s[e + u] * fexp(d) * lm;
                 }
+                packed[e >> 1] = pack_bf16(s[e], s[e + 1]);
+                packed[(e >> 1) + 1] = pack_bf16(s[e + 2], s[e + 3]);
             }
 #pragma unroll
             for (int c = 0; c < 2; ++c)
@@ -470,7 +479,6 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_chunk_fwd_tc_kernel(const 
 
 int mamba2_fwd_tc_launch(const Mamba2Params& p_in, cudaStream_t stream) {
     Mamba2Params p = p_in;
-    p.order = getenv("LLATTN_EXPERIMENT_ORDER") ? atoi(getenv("LLATTN_EXPERIMENT_ORDER")) : 0;
     int rc;
     if ((rc = tma::make_panel_map(&p.tm_q, p.q, (long)p.B * p.T, p.G, p.K, tc::PT)) != 0) return rc;
     if ((rc = tma::make_panel_map(&p.tm_k, p.k, (long)p.B * p.T, p.G, p.K, tc::PT)) != 0) return rc;

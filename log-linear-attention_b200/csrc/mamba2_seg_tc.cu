@@ -8,8 +8,6 @@
 //   seg_dstate : dF[r][j] = sum_pairs q^T (do * lambda_j exp(G))                     (fp32 K x V per set level)
 //   hi_bwd_q   : dlambda_j = exp(G) (do . (q H0_j)) ; dq += (do * lambda_j exp(G)) H0_j^T   (TMA reduce-add)
 // G is the cumulative log decay from the start of the segment (inclusive).
-#include <stdlib.h>
-
 #include "tc_common.cuh"
 
 namespace llattn {
@@ -65,7 +63,8 @@ struct HiBwdTcSmem {
     static constexpr uint32_t gs_off = dos_off + tcs::MAXLH * tc::V_BYTES; // float [SEG*64] + [SEG+1]
     static constexpr uint32_t misc_off = gs_off + (SEG * 64 + SEG + 32) * 4;  // float [2][128][MAXLH+1] dlambda halves
     static constexpr uint32_t bar_off = misc_off + 2 * 128 * (tcs::MAXLH + 1) * 4;
-    static constexpr uint32_t total = bar_off + 128 + 1024;
+    static constexpr uint32_t sink_off = bar_off + 128;                    // uint32 [256], written only (tile release)
+    static constexpr uint32_t total = sink_off + 256 * 4 + 1024;
 };
 
 template <int MLOW>
@@ -96,10 +95,11 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_hi_bwd_tc_kernel(const __g
     uint64_t* empty_do = bars + 8;   // every compute thread holds its do row in registers (256 arrivals)
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + SM::bar_off + 96);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + SM::bar_off + 104);
+    uint32_t* sink = reinterpret_cast<uint32_t*>(smem + SM::sink_off);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int h = p.order ? (blockIdx.x / (p.NS - 1)) % p.H : blockIdx.x % p.H;
-    const int r = 1 + (p.order ? blockIdx.x % (p.NS - 1) : (blockIdx.x / p.H) % (p.NS - 1));
+    const int h = blockIdx.x % p.H;
+    const int r = 1 + (blockIdx.x / p.H) % (p.NS - 1);
     const int b = blockIdx.x / (p.H * (p.NS - 1));
     const int grp = h / (p.H / p.G);
     const int nchunks = min(SEG, p.NT - r * SEG);
@@ -237,16 +237,11 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_hi_bwd_tc_kernel(const __g
 #pragma unroll
         for (int c = 0; c < 4; ++c) dox[c] = *reinterpret_cast<const uint4*>(sDO + umma::tile_offset(row, ch * 32 + c * 8, tc::PT));
         {
-            // The arrive hands the do tile back to the TMA producer, so it must not be performed before this
-            // thread's loads from the tile have returned.  Nothing in the instruction stream says so: the
-            // loaded words are first used after the level reads, and the arrive was observed to overtake the
-            // loads while the MMA warp's chain kept shared memory busy (the refill then replaced rows that
-            // had not been read; wrong dlambda / dq / reader summaries in a few percent of the launches on
-            // some GPUs).  The address therefore depends on every loaded word through p.zero, which is 0 at
-            // run time but not known to the compiler.
+            // every thread holds its do row in registers: hand the tile back to the producer (the release must
+            // follow the loads, see release_tile_after_loads)
             const uint32_t x = dox[0].x ^ dox[0].y ^ dox[0].z ^ dox[0].w ^ dox[1].x ^ dox[1].y ^ dox[1].z ^ dox[1].w ^
                                dox[2].x ^ dox[2].y ^ dox[2].z ^ dox[2].w ^ dox[3].x ^ dox[3].y ^ dox[3].z ^ dox[3].w;
-            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(umma::smem_addr(empty_do) + (x & p.zero)) : "memory");
+            release_tile_after_loads(empty_do, sink + tid, x);
         }
         float* myDL = sDL + (ch * 128 + row) * NDLH;
         for (int i = 0; i < nl; ++i) {
@@ -381,8 +376,8 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_hi_out_tc_kernel(const __g
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + SM::bar_off + 72);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int h = p.order ? (blockIdx.x / (p.NS - 1)) % p.H : blockIdx.x % p.H;
-    const int r = 1 + (p.order ? blockIdx.x % (p.NS - 1) : (blockIdx.x / p.H) % (p.NS - 1));
+    const int h = blockIdx.x % p.H;
+    const int r = 1 + (blockIdx.x / p.H) % (p.NS - 1);
     const int b = blockIdx.x / (p.H * (p.NS - 1));
     const int grp = h / (p.H / p.G);
     const int nchunks = min(SEG, p.NT - r * SEG);
@@ -638,7 +633,6 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_seg_state_tc_kernel(const 
 
 int mamba2_seg_state_tc_launch(const Mamba2Params& p_in, cudaStream_t stream) {
     Mamba2Params p = p_in;
-    p.order = getenv("LLATTN_EXPERIMENT_ORDER") ? atoi(getenv("LLATTN_EXPERIMENT_ORDER")) : 0;
     int rc;
     const long BT = (long)p.B * p.T;
     if ((rc = tma::make_panel_map(&p.tm_k, p.k, BT, p.G, p.K, tc::PT)) != 0) return rc;
@@ -653,7 +647,6 @@ int mamba2_seg_state_tc_launch(const Mamba2Params& p_in, cudaStream_t stream) {
 
 int mamba2_hi_out_tc_launch(const Mamba2Params& p_in, cudaStream_t stream) {
     Mamba2Params p = p_in;
-    p.order = getenv("LLATTN_EXPERIMENT_ORDER") ? atoi(getenv("LLATTN_EXPERIMENT_ORDER")) : 0;
     int rc;
     const long BT = (long)p.B * p.T;
     if ((rc = tma::make_panel_map(&p.tm_q, p.q, BT, p.G, p.K, tc::PT)) != 0) return rc;
@@ -677,7 +670,6 @@ int mamba2_hi_out_tc_launch(const Mamba2Params& p_in, cudaStream_t stream) {
 
 int mamba2_hi_bwd_tc_launch(const Mamba2Params& p_in, cudaStream_t stream) {
     Mamba2Params p = p_in;
-    p.order = getenv("LLATTN_EXPERIMENT_ORDER") ? atoi(getenv("LLATTN_EXPERIMENT_ORDER")) : 0;
     int rc;
     const long BT = (long)p.B * p.T;
     if ((rc = tma::make_panel_map(&p.tm_q, p.q, BT, p.G, p.K, tc::PT)) != 0) return rc;

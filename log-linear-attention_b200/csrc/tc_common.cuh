@@ -55,6 +55,19 @@ struct RegisterSplit {
     __device__ static __forceinline__ void acquire() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;\n" ::"n"(INC)); }
 };
 
+// Hands a TMA-filled tile back to the producer from a thread that has read it with ld.shared.  The arrive must
+// not be performed before those loads have returned (the producer would refill the tile under them), and
+// nothing orders a plain arrive after earlier loads whose results are not used yet.  So the release is preceded,
+// in program order and in the same asm block, by a shared-memory store whose VALUE is computed from every loaded
+// word: the store cannot issue before the loads have delivered their data, and the arrive issues after it.
+// `sink` is any 4-byte shared-memory word that nothing reads (one per thread or shared by all).
+__device__ __forceinline__ void release_tile_after_loads(uint64_t* bar, uint32_t* sink, uint32_t digest_of_loaded_words) {
+    asm volatile(
+        "st.shared.u32 [%0], %1;\n\tmbarrier.arrive.shared::cta.b64 _, [%2];\n"
+        ::"r"(umma::smem_addr(sink)), "r"(digest_of_loaded_words), "r"(umma::smem_addr(bar))
+        : "memory");
+}
+
 __device__ __forceinline__ void bar_work() { asm volatile("bar.sync 1, 288;\n" ::: "memory"); }
 
 // barrier over the 8 element-wise warps only

@@ -64,6 +64,10 @@ def lib():
     L.llattn_mamba2_final_state.argtypes = [_P] * 4 + [ctypes.c_int] * 7 + [_P]
     L.llattn_mamba2_step.restype = ctypes.c_int
     L.llattn_mamba2_step.argtypes = [_P] * 7 + [ctypes.c_int] * 7 + [_P]
+    L.llattn_gdn_prefill.restype = ctypes.c_int
+    L.llattn_gdn_prefill.argtypes = [_P] * 11 + [_P, ctypes.c_size_t] + [ctypes.c_int] * 6 + [_P]
+    L.llattn_gdn_step.restype = ctypes.c_int
+    L.llattn_gdn_step.argtypes = [_P] * 8 + [ctypes.c_int] * 6 + [_P]
     L.llattn_l2norm_fwd.restype = ctypes.c_int
     L.llattn_l2norm_fwd.argtypes = [_P, _P, ctypes.c_long, ctypes.c_int, ctypes.c_float, _P]
     L.llattn_l2norm_bwd.restype = ctypes.c_int

@@ -87,12 +87,16 @@ def chunkwise_fwd(
     output_final_state: bool,
     keep_workspace: Optional[list] = None,
 ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, Optional[torch.Tensor]]:
-    """Returns (g_cum, o, Aw, Au, None) like the reference driver (chunkwise_hgdn.py:566-788).
+    """Returns (g_cum, o, Aw, Au, ht) like the reference driver (chunkwise_hgdn.py:566-788).
     With a list as `keep_workspace` the call's workspace (chunk matrices and every chunk's level states)
-    is appended to it for `chunkwise_bwd(..., fwd_workspace=...)`, which then skips their recomputation."""
-    if output_final_state:
-        raise NotImplementedError("output_final_state=True (prefill hand-off) is not implemented")
+    is appended to it for `chunkwise_bwd(..., fwd_workspace=...)`, which then skips their recomputation.
+    `output_final_state=True`: ht is (B,H,K,V,L) fp32 with the inter-chunk level states AS OF THE START OF THE LAST
+    CHUNK (level 7 + j holds the block of 2^j chunks for each set bit j of NT - 1; levels 0..6 are zero); the prefill
+    path steps the last chunk's tokens from there (the reference returns the states after the last chunk and
+    rebuilds the levels inside it afterwards, kernel.py:378-466)."""
     B, T, H, G, K, V, L = _check(q, k, v, b, g, l, head_first, level_base, htype, chunk_size)
+    if output_final_state and keep_workspace is not None:
+        raise NotImplementedError("final states and a kept workspace in the same call")
     lib = _lib.lib()
     with torch.cuda.device(q.device):
         if G != H:   # one q/k per head, as the reference expands them (chunkwise_hgdn.py:613-620)
@@ -111,11 +115,19 @@ def chunkwise_fwd(
         ws = torch.empty(n, dtype=torch.uint8, device=q.device)
         if keep:
             keep_workspace.append(ws)
-        rc = (lib.llattn_gdn_fwd_keep if keep else lib.llattn_gdn_fwd)(q_.data_ptr(), k_.data_ptr(), v_.data_ptr(), b_.data_ptr(), g_.data_ptr(), l_.data_ptr(),
-                                o.data_ptr(), g_cum.data_ptr(), Aw.data_ptr(), Au.data_ptr(), ws.data_ptr(), ws.numel(),
-                                B, T, H, K, V, L, torch.cuda.current_stream().cuda_stream)
-        _lib.check(rc, "llattn_gdn_fwd")
-    return g_cum, o, Aw, Au, None
+        ht = None
+        if output_final_state:
+            ht = torch.empty(B, H, K, V, L, dtype=torch.float32, device=q.device)
+            rc = lib.llattn_gdn_prefill(q_.data_ptr(), k_.data_ptr(), v_.data_ptr(), b_.data_ptr(), g_.data_ptr(), l_.data_ptr(),
+                                        o.data_ptr(), g_cum.data_ptr(), Aw.data_ptr(), Au.data_ptr(), ht.data_ptr(), ws.data_ptr(),
+                                        ws.numel(), B, T, H, K, V, L, torch.cuda.current_stream().cuda_stream)
+            _lib.check(rc, "llattn_gdn_prefill")
+        else:
+            rc = (lib.llattn_gdn_fwd_keep if keep else lib.llattn_gdn_fwd)(q_.data_ptr(), k_.data_ptr(), v_.data_ptr(), b_.data_ptr(), g_.data_ptr(), l_.data_ptr(),
+                                    o.data_ptr(), g_cum.data_ptr(), Aw.data_ptr(), Au.data_ptr(), ws.data_ptr(), ws.numel(),
+                                    B, T, H, K, V, L, torch.cuda.current_stream().cuda_stream)
+            _lib.check(rc, "llattn_gdn_fwd")
+    return g_cum, o, Aw, Au, ht
 
 
 def chunkwise_bwd(q, k, v, b, g, l, Aw, Au, do, head_first, level_base, htype, chunk_size, fwd_workspace=None, **unused):

@@ -6,7 +6,7 @@ from typing import Optional
 import torch
 
 from .base import HStruct, HType
-from .kernel import hattention_kernel
+from .kernel import hattention_kernel, hattention_prefill, hattention_step
 
 SCALE_LAMBDA = True
 
@@ -26,9 +26,11 @@ def chunk_h_gated_delta_rule(
     head_first: bool = False,
     use_qk_l2norm_in_kernel: bool = False,
 ):
-    """q,k (B,T,H,K), v (B,T,H,V), g (B,T,H) log decay, l (B,T,H,L), beta (B,T,H) -> (o, None).
-    Same checks as the reference (gated_delta_rule_apis.py:35-70): bf16 only, no varlen, l2norm
-    in the kernel is mandatory, scale defaults to K^-1/2 and lambda is divided by it."""
+    """q,k (B,T,H,K), v (B,T,H,V), g (B,T,H) log decay, l (B,T,H,L), beta (B,T,H) -> (o, final_state).
+    Same checks and dispatch as the reference (gated_delta_rule_apis.py:35-132): bf16 only, no varlen, l2norm
+    in the kernel is mandatory, scale defaults to K^-1/2 and lambda is divided by it; training call without
+    states, prompt call with `output_final_state=True` (-> `hattention_prefill`), and one-token call with an
+    `initial_state` (-> `hattention_step`)."""
     assert q.dtype == k.dtype == v.dtype
     assert q.dtype != torch.float32, "ChunkGatedDeltaRuleFunction does not support float32. Please use bfloat16."
     assert len(beta.shape) == 3, "beta must be of shape [B, T, H] if head_first=False, or [B, H, T] otherwise."
@@ -42,8 +44,18 @@ def chunk_h_gated_delta_rule(
         scale = k.shape[-1] ** -0.5
     if SCALE_LAMBDA:
         l = l / scale
-    if output_final_state or initial_state is not None:
-        raise NotImplementedError("prefill / decode hand-off is not implemented")
-    o = hattention_kernel(q=q, k=k, v=v, b=beta, g=g, l=l, scale=scale, head_first=False, level_base=2,
-                          htype=HType.WEAK, hstruct=HStruct.GDELTA, use_qk_l2norm_in_kernel=use_qk_l2norm_in_kernel)
-    return o, None
+    common = dict(scale=scale, level_base=2, htype=HType.WEAK, hstruct=HStruct.GDELTA,
+                  use_qk_l2norm_in_kernel=use_qk_l2norm_in_kernel)
+    if output_final_state is False:
+        if initial_state is not None:
+            raise NotImplementedError
+        o = hattention_kernel(q=q, k=k, v=v, b=beta, g=g, l=l, head_first=False, **common)
+        return o, None
+    if initial_state is None:
+        return hattention_prefill(q=q, k=k, v=v, b=beta, g=g, l=l, head_first=False, **common)
+    if not (q.ndim == 4 and k.ndim == 4 and v.ndim == 4 and beta.ndim == 3 and g.ndim == 3 and l.ndim == 4
+            and q.shape[1] == k.shape[1] == v.shape[1] == beta.shape[1] == g.shape[1] == l.shape[1] == 1):
+        raise ValueError
+    o, final_state = hattention_step(hstate=initial_state, q=q.squeeze(1), k=k.squeeze(1), v=v.squeeze(1), b=beta.squeeze(1),
+                                     g=g.squeeze(1), l=l.squeeze(1), **common)
+    return o.unsqueeze(1), final_state

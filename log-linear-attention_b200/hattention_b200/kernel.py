@@ -114,31 +114,52 @@ def hattention_kernel(
 def hattention_step(hstate: HState, q, k, v, b, g, l, scale, level_base, htype, hstruct,
                     use_qk_l2norm_in_kernel: bool = False):
     """One decoding step, signature of the reference's `hattention_step` (kernel.py:563-633):
-    q, k (B,G,K), v (B,H,V), g (B,H), l (B,H,L) -> (o (B,H,V), hstate).  Mamba-2 structure only."""
+    q, k (B,G,K), v (B,H,V), g (B,H), l (B,H,L)[, b (B,H)] -> (o (B,H,V), hstate).  One CUDA kernel per step for
+    either structure (`llattn_mamba2_step`, `llattn_gdn_step`); for the delta-rule structure q and k are
+    L2-normalised (q also scaled) first, as the reference does when `use_qk_l2norm_in_kernel` is set."""
     if not (q.ndim == 3 and k.ndim == 3 and v.ndim == 3 and g.ndim == 2 and l.ndim == 3
             and (b is None or b.ndim == 2) and g.dtype == hstate.dtype and q.dtype == k.dtype == v.dtype == l.dtype
             and hstate.base == level_base and hstate.htype == htype and hstate.hstruct == hstruct):
         raise TypeError
-    if hstruct != HStruct.MAMBA2 or b is not None:
-        raise NotImplementedError("the decode step is implemented for the Mamba-2 structure")
-    if use_qk_l2norm_in_kernel or scale is not None:
-        raise NotImplementedError
     if hstate.dtype != torch.float32:
         raise NotImplementedError("level states are kept in fp32")
     B, G, K = k.shape
     _, H, V = v.shape
     L = l.shape[-1]
+    lib = _lib.lib()
+    if hstruct == HStruct.MAMBA2:
+        if b is not None:
+            raise ValueError
+        if use_qk_l2norm_in_kernel or scale is not None:
+            raise NotImplementedError
+    else:
+        if b is None:
+            raise ValueError
+        if use_qk_l2norm_in_kernel:
+            if scale is None:
+                raise NotImplementedError
+            from .chunkwise_hgdn import l2norm_fwd
+            q, k = l2norm_fwd(q, scale), l2norm_fwd(k)
+        elif scale is not None:
+            raise NotImplementedError
+        if G != H:
+            q, k = q.repeat_interleave(H // G, dim=1), k.repeat_interleave(H // G, dim=1)
     carry = hstate.cascade_counts()
     hstate.counts[0] += 1
-    lib = _lib.lib()
     with torch.cuda.device(v.device):
         q_, k_, v_, l_ = (x.to(torch.bfloat16).contiguous() for x in (q, k, v, l))
         g_ = g.to(torch.float32).contiguous()
         o = torch.empty(B, H, V, dtype=torch.bfloat16, device=v.device)
-        rc = lib.llattn_mamba2_step(hstate.states.data_ptr(), q_.data_ptr(), k_.data_ptr(), v_.data_ptr(), g_.data_ptr(),
-                                    l_.data_ptr(), o.data_ptr(), B, H, G, K, V, L, carry,
-                                    torch.cuda.current_stream().cuda_stream)
-        _lib.check(rc, "llattn_mamba2_step")
+        stream = torch.cuda.current_stream().cuda_stream
+        if hstruct == HStruct.MAMBA2:
+            rc = lib.llattn_mamba2_step(hstate.states.data_ptr(), q_.data_ptr(), k_.data_ptr(), v_.data_ptr(), g_.data_ptr(),
+                                        l_.data_ptr(), o.data_ptr(), B, H, G, K, V, L, carry, stream)
+            _lib.check(rc, "llattn_mamba2_step")
+        else:
+            b_ = b.to(torch.bfloat16).contiguous()
+            rc = lib.llattn_gdn_step(hstate.states.data_ptr(), q_.data_ptr(), k_.data_ptr(), v_.data_ptr(), b_.data_ptr(),
+                                     g_.data_ptr(), l_.data_ptr(), o.data_ptr(), B, H, K, V, L, carry, stream)
+            _lib.check(rc, "llattn_gdn_step")
     return o.to(v.dtype), hstate
 
 
@@ -146,16 +167,14 @@ def hattention_step(hstate: HState, q, k, v, b, g, l, scale, level_base, htype, 
 def hattention_prefill(q, k, v, b, g, l, scale, head_first, level_base, htype, hstruct,
                        chunk_size: Optional[int] = None, use_qk_l2norm_in_kernel: bool = False):
     """Outputs for a prompt and the level states to continue from, signature of the reference's
-    `hattention_prefill` (kernel.py:469-560).  The largest multiple of the chunk size goes through the
-    chunkwise kernels, its level states come from one kernel (`final_states`), the remaining tokens are
-    stepped.  Mamba-2 structure only."""
+    `hattention_prefill` (kernel.py:469-560).  Mamba-2 structure: the largest multiple of the chunk size goes
+    through the chunkwise kernels, its level states come from one kernel (`final_states`), the remaining tokens
+    are stepped.  Delta-rule structure: the chunkwise kernels produce the outputs of the full chunks and the
+    inter-chunk level states as of the start of the last full chunk; that chunk's tokens and the remaining ones
+    are stepped through the decode kernel, which builds the levels inside the chunk."""
     if chunk_size is None:
         chunk_size = 64
     if head_first:
-        raise NotImplementedError
-    if hstruct != HStruct.MAMBA2 or b is not None:
-        raise NotImplementedError("prefill is implemented for the Mamba-2 structure")
-    if use_qk_l2norm_in_kernel or scale is not None:
         raise NotImplementedError
     B, T, G, K = k.shape
     _, _, H, V = v.shape
@@ -163,13 +182,36 @@ def hattention_prefill(q, k, v, b, g, l, scale, head_first, level_base, htype, h
     T0 = T - (T % chunk_size)
     o = torch.zeros_like(v)
     hstate = HState(base=level_base, htype=htype, hstruct=hstruct, shape=(B, H, K, V, L), dtype=torch.float32, device=g.device)
-    if T0 != 0:
-        o0, _, ht = chunkwise_fwd(q[:, :T0], k[:, :T0], v[:, :T0], g[:, :T0], l[:, :T0], head_first, level_base, htype,
-                                  chunk_size, True)
-        o[:, :T0] = o0.to(v.dtype)
-        hstate.states = ht
-        hstate.set_counts_after(T0)
-    for t in range(T0, T):
-        o[:, t], hstate = hattention_step(hstate, q[:, t], k[:, t], v[:, t], None, g[:, t].float(), l[:, t], None,
-                                          level_base, htype, hstruct)
+    if hstruct == HStruct.MAMBA2:
+        if b is not None:
+            raise ValueError
+        if use_qk_l2norm_in_kernel or scale is not None:
+            raise NotImplementedError
+        if T0 != 0:
+            o0, _, ht = chunkwise_fwd(q[:, :T0], k[:, :T0], v[:, :T0], g[:, :T0], l[:, :T0], head_first, level_base, htype,
+                                      chunk_size, True)
+            o[:, :T0] = o0.to(v.dtype)
+            hstate.states = ht
+            hstate.set_counts_after(T0)
+        first_step = T0
+    else:
+        from .chunkwise_hgdn import chunkwise_fwd as chunkwise_fwd_hgdn, l2norm_fwd
+        if b is None:
+            raise ValueError
+        if not use_qk_l2norm_in_kernel or scale is None:
+            raise NotImplementedError
+        first_step = 0
+        if T0 != 0:
+            qn, kn = l2norm_fwd(q[:, :T0], scale), l2norm_fwd(k[:, :T0])
+            _, o0, _, _, ht = chunkwise_fwd_hgdn(qn, kn, v[:, :T0], b[:, :T0], g[:, :T0], l[:, :T0], head_first, level_base,
+                                                 htype, chunk_size, True)
+            o[:, :T0] = o0.to(v.dtype)
+            hstate.states = ht
+            first_step = T0 - chunk_size
+            hstate.set_counts_before(first_step)
+    for t in range(first_step, T):
+        ot, hstate = hattention_step(hstate, q[:, t], k[:, t], v[:, t], b[:, t] if b is not None else None, g[:, t].float(),
+                                     l[:, t], scale, level_base, htype, hstruct, use_qk_l2norm_in_kernel)
+        if t >= T0:
+            o[:, t] = ot
     return o, hstate

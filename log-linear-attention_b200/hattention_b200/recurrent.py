@@ -50,6 +50,16 @@ class HState:
                     raise ValueError("more tokens than the levels can hold")
                 self.counts[j + 1] = 1 << j
 
+    def set_counts_before(self, t: int) -> None:
+        """Counts as the cascade leaves them just before token t (0-based) is inserted: level 0 empty, level j+1
+        holds 2^j tokens for each set bit j of t."""
+        self.counts = [0] * self.max_num_levels
+        for j in range(max(t, 0).bit_length()):
+            if (t >> j) & 1:
+                if j + 1 >= self.max_num_levels:
+                    raise ValueError("more tokens than the levels can hold")
+                self.counts[j + 1] = 1 << j
+
     def reset_states(self) -> None:
         """recurrent.py:102-103; the token counts restart with the states."""
         self.states = torch.zeros_like(self.states)

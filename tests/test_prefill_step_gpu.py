@@ -105,3 +105,34 @@ def test_layer_api_prefill_states_then_layer_decode_step():
         assert_close(out, want[:, t], f"layer decode step {t}")
     torch.cuda.synchronize()
     assert state.counts == list(st.counts)
+
+
+@pytest.mark.parametrize("T,Dv", [(200, 64), (64, 128), (333, 128), (1024, 128), (40, 64)])
+def test_gdn_prefill_then_decode_matches_recurrence(T, Dv):
+    """Delta-rule structure through the layer API: prompt call with output_final_state=True (chunkwise kernels for the
+    full chunks, level states exported before the last one, its tokens stepped), then one-token calls with the
+    returned state, against the fp64 token recurrence on the prepared tensors."""
+    from hattention_b200.gated_delta_rule_apis import chunk_h_gated_delta_rule
+    B, H, Dk, L, NDEC = 2, 2, 128, 12, 5
+    q, k, v, b, g, l = orc.make_gdn_inputs(B, T + NDEC, H, Dk, Dv, L, seed=T)
+    q, k, v, b, l = (x.bfloat16().float() for x in (q, k, v, b, l))
+    scale = Dk ** -0.5
+    qn, kn = orc.gdn_layer_inputs(q.double(), k.double(), scale)
+    want, st = orc.recurrent(qn, kn, v.double(), g.double(), l.double() / scale, b=b.double())
+    d = lambda x: x.bfloat16().to(DEV)
+    dq, dk, dv, db, dl = d(q), d(k), d(v), d(b), d(l)
+    dg = g.float().to(DEV)
+    o, hs = chunk_h_gated_delta_rule(dq[:, :T], dk[:, :T], dv[:, :T], dg[:, :T], dl[:, :T], db[:, :T],
+                                     output_final_state=True, use_qk_l2norm_in_kernel=True)
+    torch.cuda.synchronize()
+    assert_close(o, want[:, :T], "prompt outputs", atol=4e-3)
+    want_T, st_T = orc.recurrent(qn[:, :T], kn[:, :T], v.double()[:, :T], g.double()[:, :T], (l.double() / scale)[:, :T], b=b.double()[:, :T])
+    assert hs.counts == list(st_T.counts)
+    assert_close(hs.states, torch.stack(st_T.states, dim=-1), "level states after the prompt", atol=4e-3)
+    for t in range(T, T + NDEC):
+        ot, hs = chunk_h_gated_delta_rule(dq[:, t:t + 1], dk[:, t:t + 1], dv[:, t:t + 1], dg[:, t:t + 1], dl[:, t:t + 1],
+                                          db[:, t:t + 1], initial_state=hs, output_final_state=True, use_qk_l2norm_in_kernel=True)
+        assert_close(ot[:, 0], want[:, t], f"decode step {t}", atol=4e-3)
+    torch.cuda.synchronize()
+    assert hs.counts == list(st.counts)
+    assert_close(hs.states, torch.stack(st.states, dim=-1), "level states after decoding", atol=4e-3)
