@@ -81,3 +81,39 @@ def test_wait_that_runs_out_sets_the_status_word():
         _lib.raise_on_status(ws, stream, "self-test")
     # the device still answers
     assert torch.ones(4, device=DEV).sum().item() == 4.0
+
+
+def test_phase_clock_stamps_of_one_pair():
+    """Only in a library built with `make -C log-linear-attention_b200/csrc clean all EXTRA=-DLLATTN_STAMPS`: prints the
+    clock64() stamps that three threads of one CTA take at fixed points of one chunk pair of the forward and the
+    forward-order / reverse-order backward kernels (run with -s).  Skipped for the normal build."""
+    import ctypes
+    from hattention_b200 import _lib
+    from hattention_b200.base import HType
+    from hattention_b200.chunkwise import chunkwise_bwd, chunkwise_fwd
+    from oracle import loglinear_oracle as orc
+    lib = _lib.lib()
+    if not hasattr(lib, "llattn_debug_read_stamps"):
+        pytest.skip("library built without -DLLATTN_STAMPS")
+    dev = torch.device("cuda:0")
+    q, k, v, g, l = orc.make_mamba2_inputs(1, 16384, 32, 64, 128, 1, 15, seed=0)
+    q, k, v, l = (x.bfloat16().to(dev) for x in (q, k, v, l))
+    g = g.float().to(dev)
+    do = torch.randn_like(v)
+    for _ in range(3):
+        kept = []
+        o, gc, _ = chunkwise_fwd(q, k, v, g, l, False, 2, HType.WEAK, 64, False, keep_workspace=kept)
+        chunkwise_bwd(q, k, v, gc, l, do, False, 2, HType.WEAK, 64, fwd_workspace=kept[0])
+    torch.cuda.synchronize()
+    for name, fn in (("forward", "llattn_debug_read_stamps"), ("backward", "llattn_debug_read_stamps_bwd")):
+        buf = (ctypes.c_longlong * 96)()
+        f = getattr(lib, fn)
+        f.argtypes = [ctypes.c_void_p]
+        assert f(buf) == 0
+        d = list(buf)
+        for half, lo in (("forward-order / forward pass", 0), ("reverse-order pass", 16)):
+            if not d[lo]:
+                continue
+            for s_, who in enumerate(("thread 0", "thread 200", "thread 96")):
+                row = d[32 * s_ + lo: 32 * s_ + lo + 16]
+                print(name, half, who, [x - d[lo] if x else None for x in row])
