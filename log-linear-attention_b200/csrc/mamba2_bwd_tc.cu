@@ -129,22 +129,24 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_fwdorder_tc_kernel(con
             return;
         }
         if (warp == tc::MMA_WARP + 2) {
-            // ---- store agent: issues the fp32 TMA reduce-adds of the staged dq / dk tiles and is the one that
-            //      waits for them, so that no element-wise thread stalls on a bulk-group wait; when both staging
-            //      areas have been read it frees the q / k tile space (which doubles as the dk staging area)
+            // ---- store agent: issues the fp32 TMA reduce-adds of the staged dk / dq tiles and is the one that
+            //      waits for them, so that no element-wise thread stalls on a bulk-group wait; the q / k tile space
+            //      (which doubles as the dk staging area) is freed as soon as the dk reduce-add has read it
             if (lane == 0) {
                 for (int pl = 0; pl < npairs; ++pl) {
                     const int grow = b * p.T + (r * SEGP + pl) * tc::PT;
-                    if (!umma::mbar_wait(dq_ready, pl & 1, abort_flag)) break;
-#pragma unroll
-                    for (int bx = 0; bx < 4; ++bx) tma::reduce_add_box(&p.tm_dq, bx * 32, grp, grow, sStage + bx * 16384);
-                    tma::commit_group();
+                    // dk first: its staging area is the q / k tile space, which the next pair's loads wait for
                     if (!umma::mbar_wait(dk_ready, pl & 1, abort_flag)) break;
 #pragma unroll
                     for (int bx = 0; bx < 4; ++bx) tma::reduce_add_box(&p.tm_dk, bx * 32, grp, grow, sStage2 + bx * 16384);
                     tma::commit_group();
                     tma::wait_group_read0();
                     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(umma::smem_addr(empty_qk)) : "memory");
+                    if (!umma::mbar_wait(dq_ready, pl & 1, abort_flag)) break;
+#pragma unroll
+                    for (int bx = 0; bx < 4; ++bx) tma::reduce_add_box(&p.tm_dq, bx * 32, grp, grow, sStage + bx * 16384);
+                    tma::commit_group();
+                    tma::wait_group_read0();
                     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(umma::smem_addr(stage_free)) : "memory");
                 }
                 tma::wait_group0();                  // every reduce-add has been performed before the CTA retires
@@ -161,8 +163,7 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_fwdorder_tc_kernel(con
         const uint32_t aQ = umma::smem_addr(sQ), aK = umma::smem_addr(sK), aV = umma::smem_addr(sV), aDO = umma::smem_addr(sDO);
         const uint32_t aDS = umma::smem_addr(sDS), aDOs = umma::smem_addr(sDOs), aVs = umma::smem_addr(sVs);
         for (int pl = 0; pl < npairs; ++pl) {
-            bar_work();                              // barrier 1: decay tables in place, previous pair fully retired
-            umma::fence_after_sync();
+            // (no barrier here: the end-of-pair barrier of the previous pair is all the tensor core needs)
             if (lane == 0) {
                 umma::mbar_wait(full_qk, pl & 1, abort_flag);
                 umma::mbar_wait(full_vd, pl & 1, abort_flag);
@@ -234,12 +235,44 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_fwdorder_tc_kernel(con
 #pragma unroll
         for (int i = 0; i < LAMR; ++i)
             if (lam_rc[i] != 0xffffffffu) lam_r[i] = lp[(long)(lam_rc[i] >> 8) * p.H * L + (lam_rc[i] & 255)];
-        if (warp < 2) {
-            const float* gp = p.g + ((long)b * p.T + t0 + 4 * lane) * p.H + h;
+    };
+    // raw g of a pair: one warp (the one that builds the decay tables), four consecutive tokens per lane
+    auto fetch_g = [&](int pl) {
+        const long t0 = (long)(r * SEGP + pl) * tc::PT;
+        const float* gp = p.g + ((long)b * p.T + t0 + 4 * lane) * p.H + h;
 #pragma unroll
-            for (int i = 0; i < 4; ++i) g_n[i] = gp[(long)i * p.H];
+        for (int i = 0; i < 4; ++i) g_n[i] = gp[(long)i * p.H];
+    };
+    // Decay tables of a pair from the g values in g_n, by one full warp: G (pair-wide inclusive cumulative sum),
+    // Cf = exp(G[end of 32-block] - G[j]), Vf = exp(G[127] - G[j]).  Built ahead of the pair that reads them, so that
+    // a pair starts without a barrier of its own.
+    auto decay_tables = [&](float* tG) {
+        float gq[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) gq[i] = g_n[i];
+        gq[1] += gq[0];
+        gq[2] += gq[1];
+        gq[3] += gq[2];
+        float tot = gq[3];
+#pragma unroll
+        for (int d = 1; d < 16; d <<= 1) {
+            const float t = __shfl_up_sync(0xffffffffu, tot, d);
+            if ((lane & 15) >= d) tot += t;
+        }
+        const float gla = __shfl_sync(0xffffffffu, tot, 15);
+        const float glb = __shfl_sync(0xffffffffu, tot, 31);
+        const float glp = gla + glb;
+        const float pbase = tot - gq[3] + (lane >= 16 ? gla : 0.f);
+        const float gend = __shfl_sync(0xffffffffu, tot, (lane & ~7) + 7) + (lane >= 16 ? gla : 0.f);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float G = pbase + gq[i];
+            tG[4 * lane + i] = G;
+            tG[128 + 4 * lane + i] = fexp(gend - G);
+            tG[256 + 4 * lane + i] = fexp(glp - G);
         }
     };
+    constexpr int TABLE_WARP = 4;                    // lane quarter 0, column half 1: the warp with the most slack
     auto store_lam = [&]() {
 #pragma unroll
         for (int i = 0; i < LAMR; ++i)
@@ -248,6 +281,10 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_fwdorder_tc_kernel(con
     };
     fetch_small(0);
     store_lam();
+    if (warp == TABLE_WARP) {
+        fetch_g(0);
+        decay_tables(sGp);
+    }
     umma::fence_before_sync();
     bar_work();
     umma::fence_after_sync();
@@ -265,39 +302,11 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_fwdorder_tc_kernel(con
 #endif
         STAMP();   // 0 top
         const long t0 = (long)(r * SEGP + pl) * tc::PT;
-        float gq[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) gq[i] = g_n[i];
-        if (pl + 1 < npairs) fetch_small(pl + 1);
-        if (warp < 2) {
-            gq[1] += gq[0];
-            gq[2] += gq[1];
-            gq[3] += gq[2];
-            float tot = gq[3];
-#pragma unroll
-            for (int d = 1; d < 16; d <<= 1) {
-                const float t = __shfl_up_sync(0xffffffffu, tot, d);
-                if ((lane & 15) >= d) tot += t;
-            }
-            const float gla = __shfl_sync(0xffffffffu, tot, 15);
-            const float glb = __shfl_sync(0xffffffffu, tot, 31);
-            const float glp = gla + glb;
-            const float pbase = tot - gq[3] + (lane >= 16 ? gla : 0.f);
-            const float gend = __shfl_sync(0xffffffffu, tot, (lane & ~7) + 7) + (lane >= 16 ? gla : 0.f);
-            if ((lane >> 4) == warp) {
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const float G = pbase + gq[i];
-                    sGp[4 * lane + i] = G;
-                    sCf[4 * lane + i] = fexp(gend - G);
-                    sVf[4 * lane + i] = fexp(glp - G);
-                }
-            }
+        if (pl + 1 < npairs) {
+            fetch_small(pl + 1);
+            if (warp == TABLE_WARP) fetch_g(pl + 1);
         }
-        umma::fence_before_sync();
-        bar_work();                                  // barrier 1
-        umma::fence_after_sync();
-        STAMP();   // 1 after barrier 1
+        STAMP();   // 1 small fetches issued
         int nread = 0;
 #pragma unroll
         for (int lv = 0; lv < MP; ++lv) nread += (pl >> lv) & 1;
@@ -327,8 +336,9 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_fwdorder_tc_kernel(con
             for (int c = 0; c < 2; ++c)
                 *reinterpret_cast<uint4*>(sDS + umma::tile_offset(row, j0 + c * 8, tc::PT)) = make_uint4(0u, 0u, 0u, 0u);
         }
-        // blocks below the diagonal: one level per block, decay factorised through the block end.  A run-time loop
-        // (one copy of the body): the fully unrolled form made the loop body larger than the instruction cache.
+        // blocks below the diagonal: one level per block, decay factorised through the block end.  A run-time loop with
+        // one copy of the body (measured 3 % faster per step than four unrolled copies; finer-grained loops with more
+        // tensor-memory loads were slower in the backward kernels).
 #pragma unroll 1
         for (int jb = 0; jb < rb; ++jb) {
             const int j0 = jb * 32 + ch * 16;
@@ -467,6 +477,9 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_fwdorder_tc_kernel(con
         bar_work();                                  // barrier 2 (also: dlambda halves of every row are in shared memory)
         umma::fence_after_sync();
         STAMP();   // 6 after barrier 2
+        // every read of this pair's decay tables is behind barrier 2 (what follows uses Gi / glp from registers):
+        // one warp rebuilds them for the next pair while the second batch runs
+        if (warp == TABLE_WARP && pl + 1 < npairs) decay_tables(sGp);
         // ---- while the second batch runs: dlambda out (coalesced), q.dq row sums, reader totals Z per chunk
         {
             float* gdl = p.dl + (((long)b * p.T + t0) * p.H + h) * L;
@@ -531,6 +544,21 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_fwdorder_tc_kernel(con
             }
         }
         sWk[ch * 128 + row] = wk_part;
+        bar_compute();                               // every thread is done with the k tile
+        // ---- dk tile -> fp32 staging in the q / k tile space -> TMA reduce-add (first, so that the tile space is
+        //      handed back to the producer as early as possible)
+#pragma unroll
+        for (int hb = 0; hb < 2; ++hb) {
+            unsigned char* box = sStage2 + (ch * 2 + hb) * 16384;
+#pragma unroll
+            for (int c = 0; c < 8; ++c)
+                *reinterpret_cast<float4*>(box + box_offset(row, c * 4)) =
+                    make_float4(dkv[hb][c * 4], dkv[hb][c * 4 + 1], dkv[hb][c * 4 + 2], dkv[hb][c * 4 + 3]);
+        }
+        STAMP();   // 9 dk staged
+        umma::fence_async_smem();
+        bar_compute();
+        if (tid == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(umma::smem_addr(dk_ready)) : "memory");
         // ---- dq tile -> fp32 staging (dS + scaled do space) -> TMA reduce-add
 #pragma unroll
         for (int hb = 0; hb < 2; ++hb) {
@@ -541,23 +569,10 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_fwdorder_tc_kernel(con
             for (int c = 0; c < 8; ++c)
                 *reinterpret_cast<float4*>(box + box_offset(row, c * 4)) = make_float4(t[c * 4], t[c * 4 + 1], t[c * 4 + 2], t[c * 4 + 3]);
         }
-        STAMP();   // 9 dk read, dq staged
-        umma::fence_async_smem();
-        bar_compute();                               // dq staged; every thread is done with the k tile
-        if (tid == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(umma::smem_addr(dq_ready)) : "memory");
-        // ---- dk tile -> fp32 staging in the q / k tile space -> TMA reduce-add
-#pragma unroll
-        for (int hb = 0; hb < 2; ++hb) {
-            unsigned char* box = sStage2 + (ch * 2 + hb) * 16384;
-#pragma unroll
-            for (int c = 0; c < 8; ++c)
-                *reinterpret_cast<float4*>(box + box_offset(row, c * 4)) =
-                    make_float4(dkv[hb][c * 4], dkv[hb][c * 4 + 1], dkv[hb][c * 4 + 2], dkv[hb][c * 4 + 3]);
-        }
-        STAMP();   // 10 dk staged
+        STAMP();   // 10 dq staged
         umma::fence_async_smem();
         bar_compute();
-        if (tid == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(umma::smem_addr(dk_ready)) : "memory");
+        if (tid == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(umma::smem_addr(dq_ready)) : "memory");
         if (ch == 0) {
             const float w = wq_row - (sWk[row] + sWk[128 + row]);
             red_add_f32(p.wq + ((long)b * p.T + t0 + row) * p.H + h, w);
@@ -629,8 +644,8 @@ struct Bwd2TcSmem {
     static constexpr uint32_t dos_off = p_off + tc::PT * tc::PT * 2;       // ... + 2 scaled do tiles: also the 64 KB fp32 staging
     static constexpr uint32_t vs_off = dos_off + 2 * tc::V_BYTES;
     static constexpr uint32_t dkv_off = vs_off + tc::V_BYTES;              // bf16 [128 features][64]
-    static constexpr uint32_t gp_off = dkv_off + tc::H_BYTES;              // float [3][128]
-    static constexpr uint32_t lam_off = gp_off + 3 * 128 * 4;
+    static constexpr uint32_t gp_off = dkv_off + tc::H_BYTES;              // float [2][3][128]: decay tables of this pair and the next
+    static constexpr uint32_t lam_off = gp_off + 2 * 3 * 128 * 4;
     static constexpr uint32_t misc_off = lam_off + 128 * tc::LAM_LD * 2;   // float [512]
     static constexpr uint32_t bar_off = misc_off + 2048;
     static constexpr uint32_t total = bar_off + 128 + 1024;
@@ -654,9 +669,7 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_revorder_tc_kernel(con
     unsigned char* sStage = smem + SM::p_off;
     unsigned char* sVs = smem + SM::vs_off;
     unsigned char* sDKV = smem + SM::dkv_off;
-    float* sGp = reinterpret_cast<float*>(smem + SM::gp_off);
-    float* sCf = sGp + 128;
-    float* sVf = sGp + 256;
+    float* sTab = reinterpret_cast<float*>(smem + SM::gp_off);           // [2][3][128]: per pair G | Cf | Vf
     bf16* sLam = reinterpret_cast<bf16*>(smem + SM::lam_off);
     float* sMisc = reinterpret_cast<float*>(smem + SM::misc_off);        // [2][128] k.dk halves ; [8][8] Y partials at +256
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SM::bar_off);
@@ -742,8 +755,7 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_revorder_tc_kernel(con
         const uint32_t aP = umma::smem_addr(sP), aDOs = umma::smem_addr(sDOs), aVs = umma::smem_addr(sVs), aDKV = umma::smem_addr(sDKV);
         for (int it = 0; it < npairs; ++it) {
             const int pl = npairs - 1 - it;
-            bar_work();                              // barrier 1
-            umma::fence_after_sync();
+            // (no barrier here: the end-of-pair barrier of the previous pair is all the tensor core needs)
             if (lane == 0) {
                 umma::mbar_wait(full_qk, it & 1, abort_flag);
                 umma::gemm_kk<tc::PT, tc::PT, tc::KD>(tbase + tcr::TR_S, aQ, aK, ID_KK128, false);
@@ -807,12 +819,44 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_revorder_tc_kernel(con
 #pragma unroll
         for (int i = 0; i < LAMR; ++i)
             if (lam_rc[i] != 0xffffffffu) lam_r[i] = lp[(long)(lam_rc[i] >> 8) * p.H * L + (lam_rc[i] & 255)];
-        if (warp < 2) {
-            const float* gp = p.g + ((long)b * p.T + t0 + 4 * lane) * p.H + h;
+    };
+    // raw g of a pair: one warp (the one that builds the decay tables), four consecutive tokens per lane
+    auto fetch_g = [&](int pl) {
+        const long t0 = (long)(r * SEGP + pl) * tc::PT;
+        const float* gp = p.g + ((long)b * p.T + t0 + 4 * lane) * p.H + h;
 #pragma unroll
-            for (int i = 0; i < 4; ++i) g_n[i] = gp[(long)i * p.H];
+        for (int i = 0; i < 4; ++i) g_n[i] = gp[(long)i * p.H];
+    };
+    // Decay tables of a pair from the g values in g_n, by one full warp: G (pair-wide inclusive cumulative sum),
+    // Cf = exp(G[end of 32-block] - G[j]), Vf = exp(G[127] - G[j]).  Built ahead of the pair that reads them, so that
+    // a pair starts without a barrier of its own.
+    auto decay_tables = [&](float* tG) {
+        float gq[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) gq[i] = g_n[i];
+        gq[1] += gq[0];
+        gq[2] += gq[1];
+        gq[3] += gq[2];
+        float tot = gq[3];
+#pragma unroll
+        for (int d = 1; d < 16; d <<= 1) {
+            const float t = __shfl_up_sync(0xffffffffu, tot, d);
+            if ((lane & 15) >= d) tot += t;
+        }
+        const float gla = __shfl_sync(0xffffffffu, tot, 15);
+        const float glb = __shfl_sync(0xffffffffu, tot, 31);
+        const float glp = gla + glb;
+        const float pbase = tot - gq[3] + (lane >= 16 ? gla : 0.f);
+        const float gend = __shfl_sync(0xffffffffu, tot, (lane & ~7) + 7) + (lane >= 16 ? gla : 0.f);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float G = pbase + gq[i];
+            tG[4 * lane + i] = G;
+            tG[128 + 4 * lane + i] = fexp(gend - G);
+            tG[256 + 4 * lane + i] = fexp(glp - G);
         }
     };
+    constexpr int TABLE_WARP = 4;                    // lane quarter 0, column half 1: the warp with the most slack
     auto store_lam = [&]() {
 #pragma unroll
         for (int i = 0; i < LAMR; ++i)
@@ -821,6 +865,11 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_revorder_tc_kernel(con
     };
     fetch_small(npairs - 1);
     store_lam();
+    if (warp == TABLE_WARP) {
+        fetch_g(npairs - 1);
+        decay_tables(sTab);
+        if (npairs > 1) fetch_g(npairs - 2);
+    }
 
     // adjoint states: thread = state row `row`, 32 columns; index MP = adjoint of the segment summary
     float RM[MP + 1][32];
@@ -849,39 +898,11 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_revorder_tc_kernel(con
         STAMPR();   // 0 top
         const int pl = npairs - 1 - it;
         const long t0 = (long)(r * SEGP + pl) * tc::PT;
-        float gq[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) gq[i] = g_n[i];
+        const float* sGp = sTab + (it & 1) * 384;    // tables of this pair (written while the previous one ran)
+        const float* sCf = sGp + 128;
+        const float* sVf = sGp + 256;
         if (it + 1 < npairs) fetch_small(pl - 1);
-        if (warp < 2) {
-            gq[1] += gq[0];
-            gq[2] += gq[1];
-            gq[3] += gq[2];
-            float tot = gq[3];
-#pragma unroll
-            for (int d = 1; d < 16; d <<= 1) {
-                const float t = __shfl_up_sync(0xffffffffu, tot, d);
-                if ((lane & 15) >= d) tot += t;
-            }
-            const float gla = __shfl_sync(0xffffffffu, tot, 15);
-            const float glb = __shfl_sync(0xffffffffu, tot, 31);
-            const float glp = gla + glb;
-            const float pbase = tot - gq[3] + (lane >= 16 ? gla : 0.f);
-            const float gend = __shfl_sync(0xffffffffu, tot, (lane & ~7) + 7) + (lane >= 16 ? gla : 0.f);
-            if ((lane >> 4) == warp) {
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const float G = pbase + gq[i];
-                    sGp[4 * lane + i] = G;
-                    sCf[4 * lane + i] = fexp(gend - G);
-                    sVf[4 * lane + i] = fexp(glp - G);
-                }
-            }
-        }
-        umma::fence_before_sync();
-        bar_work();                                  // barrier 1
-        umma::fence_after_sync();
-        STAMPR();   // 1 after barrier 1
+        STAMPR();   // 1 small fetches issued
         const float Gi = sGp[row];
         const float glp = sGp[tc::PT - 1];
         float lam[NLAM];
@@ -963,7 +984,7 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_revorder_tc_kernel(con
             for (int c = 0; c < 2; ++c)
                 *reinterpret_cast<uint4*>(sP + umma::tile_offset(row, j0 + c * 8, tc::PT)) = make_uint4(0u, 0u, 0u, 0u);
         }
-        // blocks below the diagonal (run-time loop: one copy of the body keeps the loop inside the instruction cache)
+        // blocks below the diagonal (run-time loop: one copy of the body)
 #pragma unroll 1
         for (int jb = 0; jb < rb; ++jb) {
             const int j0 = jb * 32 + ch * 16;
@@ -1017,6 +1038,10 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_revorder_tc_kernel(con
                     make_uint4(packed[c * 4], packed[c * 4 + 1], packed[c * 4 + 2], packed[c * 4 + 3]);
         }
         STAMPR();   // 5 P written
+        if (warp == TABLE_WARP && it + 1 < npairs) {
+            decay_tables(sTab + ((it + 1) & 1) * 384);
+            if (it + 2 < npairs) fetch_g(pl - 2);
+        }
         umma::fence_async_smem();
         umma::fence_before_sync();
         bar_work();                                  // barrier 2

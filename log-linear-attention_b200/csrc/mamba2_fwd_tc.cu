@@ -24,8 +24,8 @@ struct FwdTcSmem {
     static constexpr uint32_t p_off = k_off + 2 * tc::Q_BYTES;
     static constexpr uint32_t vs_off = p_off + tc::PT * tc::PT * 2;
     static constexpr uint32_t h_off = vs_off + tc::V_BYTES;
-    static constexpr uint32_t gp_off = h_off + (MP > 0 ? MP : 1) * tc::H_BYTES;   // float [3][128]
-    static constexpr uint32_t lam_off = gp_off + 3 * 128 * 4;          // bf16 [128][L <= 32]
+    static constexpr uint32_t gp_off = h_off + (MP > 0 ? MP : 1) * tc::H_BYTES;   // float [2][3][128]: decay tables of this pair and the next
+    static constexpr uint32_t lam_off = gp_off + 2 * 3 * 128 * 4;      // bf16 [128][L <= 32]
     static constexpr uint32_t bar_off = lam_off + 128 * (MAX_L + 2) * 2;   // 10 mbarriers + tmem slot + abort flag     // 4 mbarriers + tmem slot + abort flag
     static constexpr uint32_t total = bar_off + 128 + 1024;             // + slack for 1024-byte alignment
 };
@@ -44,9 +44,7 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_chunk_fwd_tc_kernel(const 
     unsigned char* sP = smem + SM::p_off;
     unsigned char* sVs = smem + SM::vs_off;
     unsigned char* sH = smem + SM::h_off;
-    float* sGp = reinterpret_cast<float*>(smem + SM::gp_off);      // pair-wide inclusive cumsum of g
-    float* sCf = sGp + 128;                                        // exp(G[end of 32-block] - G[j])
-    float* sVf = sGp + 256;                                        // exp(G[127] - G[j])
+    float* sTab = reinterpret_cast<float*>(smem + SM::gp_off);     // [2][3][128]: per pair, G | Cf | Vf (see decay_tables)
     bf16* sLam = reinterpret_cast<bf16*>(smem + SM::lam_off);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SM::bar_off);     // MMA completion: S, T, O, KV
     uint64_t* full_q = bars + 4;                     // TMA completion: q tile
@@ -111,8 +109,8 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_chunk_fwd_tc_kernel(const 
             const int st = pl & 1;
             const uint32_t aQ = umma::smem_addr(sQ), aK = umma::smem_addr(sK + st * tc::Q_BYTES);
             const uint32_t aV = umma::smem_addr(sV + st * tc::V_BYTES);
-            bar_work();                              // barrier 1: tiles and decay tables of this pair are in place
-            umma::fence_after_sync();
+            // (no barrier here: the end-of-pair barrier of the previous pair is all the tensor core needs; the decay
+            //  tables of this pair were written one pair ahead)
             if (lane == 0) {
                 umma::mbar_wait(full_q, pl & 1, abort_flag);
                 umma::mbar_wait(&full_kv[st], (pl >> 1) & 1, abort_flag);
@@ -177,12 +175,49 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_chunk_fwd_tc_kernel(const 
 #pragma unroll
         for (int i = 0; i < LAMR; ++i)
             if (lam_rc[i] != 0xffffffffu) lam_r[i] = lp[(long)(lam_rc[i] >> 8) * p.H * L + (lam_rc[i] & 255)];
-        if (warp < 2) {
-            const float* gp = p.g + ((long)b * p.T + t0 + 4 * lane) * p.H + h;
+    };
+    // raw g of a pair: one warp (the one that builds the decay tables), four consecutive tokens per lane
+    auto fetch_g = [&](int pl) {
+        const long t0 = (long)(r * SEGP + pl) * tc::PT;
+        const float* gp = p.g + ((long)b * p.T + t0 + 4 * lane) * p.H + h;
 #pragma unroll
-            for (int i = 0; i < 4; ++i) g_n[i] = gp[(long)i * p.H];
+        for (int i = 0; i < 4; ++i) g_n[i] = gp[(long)i * p.H];
+    };
+    // Decay tables of pair `pl` from the g values in g_n, by one full warp: G (pair-wide inclusive cumulative sum),
+    // Cf = exp(G[end of 32-block] - G[j]), Vf = exp(G[127] - G[j]); also the in-chunk cumulative sum to global memory.
+    // Built one pair ahead into the other half of sTab, so that a pair starts without a barrier of its own.
+    auto decay_tables = [&](int pl) {
+        float* tG = sTab + (pl & 1) * 384;
+        const long t0 = (long)(r * SEGP + pl) * tc::PT;
+        float gq[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) gq[i] = g_n[i];
+        gq[1] += gq[0];
+        gq[2] += gq[1];
+        gq[3] += gq[2];
+        float tot = gq[3];                           // inclusive scan of lane totals inside each chunk (16 lanes)
+#pragma unroll
+        for (int d = 1; d < 16; d <<= 1) {
+            const float t = __shfl_up_sync(0xffffffffu, tot, d);
+            if ((lane & 15) >= d) tot += t;
+        }
+        const float gla = __shfl_sync(0xffffffffu, tot, 15);        // end of the first chunk
+        const float glb = __shfl_sync(0xffffffffu, tot, 31);        // end of the second chunk (in-chunk)
+        const float glp = gla + glb;
+        const float cbase = tot - gq[3];                            // in-chunk exclusive prefix of this lane
+        const float pbase = cbase + (lane >= 16 ? gla : 0.f);       // pair-wide
+        const float gend = __shfl_sync(0xffffffffu, tot, (lane & ~7) + 7) + (lane >= 16 ? gla : 0.f);
+        float* gc = p.g_cum + ((long)b * p.T + t0 + 4 * lane) * p.H + h;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float G = pbase + gq[i];
+            tG[4 * lane + i] = G;
+            tG[128 + 4 * lane + i] = fexp(gend - G);
+            tG[256 + 4 * lane + i] = fexp(glp - G);
+            gc[(long)i * p.H] = cbase + gq[i];
         }
     };
+    constexpr int TABLE_WARP = 4;                    // lane quarter 0 (one 32 x 32 block of the S tile): the warp with slack
     auto store_lam = [&]() {
 #pragma unroll
         for (int i = 0; i < LAMR; ++i)
@@ -191,6 +226,11 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_chunk_fwd_tc_kernel(const 
     };
     fetch_small(0);
     store_lam();
+    if (warp == TABLE_WARP) {
+        fetch_g(0);
+        decay_tables(0);
+        if (npairs > 1) fetch_g(1);
+    }
     umma::fence_before_sync();
     bar_work();
     umma::fence_after_sync();
@@ -210,9 +250,9 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_chunk_fwd_tc_kernel(const 
         STAMP();                                     // 0: top of the pair
         const int st = pl & 1;
         const long t0 = (long)(r * SEGP + pl) * tc::PT;
-        float gq[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) gq[i] = g_n[i];
+        const float* sGp = sTab + (pl & 1) * 384;    // tables of this pair (written while the previous pair ran)
+        const float* sCf = sGp + 128;
+        const float* sVf = sGp + 256;
         if (pl + 1 < npairs) fetch_small(pl + 1);
         // partial output of the high levels for this thread's row / column half (issued early, used late)
         uint4 ohi[4];
@@ -223,43 +263,9 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_chunk_fwd_tc_kernel(const 
             for (int c = 0; c < 4; ++c) ohi[c] = *reinterpret_cast<const uint4*>(gh + c * tc::PT * 8);
         }
         STAMP();                                     // 1: small fetches issued
-        umma::mbar_wait(full_q, pl & 1, abort_flag);
-        umma::mbar_wait(&full_kv[st], (pl >> 1) & 1, abort_flag);
+        umma::mbar_wait(&full_kv[st], (pl >> 1) & 1, abort_flag);      // the v tile (read below with generic loads)
         STAMP();                                     // 2: tiles landed
-        // cumulative sums of g: both warps scan the pair, each publishes one chunk
-        if (warp < 2) {
-            gq[1] += gq[0];
-            gq[2] += gq[1];
-            gq[3] += gq[2];
-            float tot = gq[3];                       // inclusive scan of lane totals inside each chunk (16 lanes)
-#pragma unroll
-            for (int d = 1; d < 16; d <<= 1) {
-                const float t = __shfl_up_sync(0xffffffffu, tot, d);
-                if ((lane & 15) >= d) tot += t;
-            }
-            const float gla = __shfl_sync(0xffffffffu, tot, 15);        // end of the first chunk
-            const float glb = __shfl_sync(0xffffffffu, tot, 31);        // end of the second chunk (in-chunk)
-            const float glp = gla + glb;
-            const float cbase = tot - gq[3];                            // in-chunk exclusive prefix of this lane
-            const float pbase = cbase + (lane >= 16 ? gla : 0.f);       // pair-wide
-            const float gend = __shfl_sync(0xffffffffu, tot, (lane & ~7) + 7) + (lane >= 16 ? gla : 0.f);
-            if ((lane >> 4) == warp) {
-                float* gc = p.g_cum + ((long)b * p.T + t0 + 4 * lane) * p.H + h;
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const float G = pbase + gq[i];
-                    sGp[4 * lane + i] = G;
-                    sCf[4 * lane + i] = fexp(gend - G);
-                    sVf[4 * lane + i] = fexp(glp - G);
-                    gc[(long)i * p.H] = cbase + gq[i];
-                }
-            }
-        }
-        umma::fence_async_smem();
-        umma::fence_before_sync();
-        bar_work();                                  // barrier 1
-        umma::fence_after_sync();
-        STAMP();                                     // 3: after barrier 1
+        STAMP();                                     // 3
         int nread = 0;
 #pragma unroll
         for (int lv = 0; lv < MP; ++lv) nread += (pl >> lv) & 1;
@@ -309,60 +315,52 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_chunk_fwd_tc_kernel(const 
             for (int c = 0; c < 2; ++c)
                 *reinterpret_cast<uint4*>(sP + umma::tile_offset(row, j0 + c * 8, tc::PT)) = make_uint4(0u, 0u, 0u, 0u);
         }
-        // blocks below the diagonal (run-time loop: one copy of the body keeps the loop inside the instruction cache)
+        // Blocks below the diagonal, four columns at a time in run-time loops (one short copy of the body instead of
+        // four unrolled 16-column copies: measured faster in this kernel, where the phase has a single accumulator).
 #pragma unroll 1
         for (int jb = 0; jb < rb; ++jb) {
-            const int j0 = jb * 32 + ch * 16;
-            uint32_t packed[8];
-            float s[16];
-            umma::tmem_ld16(umma::tmem_addr(tbase + tc::TM_S, warp, j0), s);
             // one level per block, decay factorised through the block end
             const float lm = ((rb ^ jb) == 1) ? lam[6] : lam[7];
             const float rf = lm * fexp(Gi - sGp[jb * 32 + 31]);
-#pragma unroll
-            for (int e = 0; e < 16; e += 4) {
-                const float4 cf = *reinterpret_cast<const float4*>(sCf + j0 + e);
-                packed[e >> 1] = pack_bf16(s[e] * rf * cf.x, s[e + 1] * rf * cf.y);
-                packed[(e >> 1) + 1] = pack_bf16(s[e + 2] * rf * cf.z, s[e + 3] * rf * cf.w);
+#pragma unroll 1
+            for (int cc = 0; cc < 4; ++cc) {
+                const int j0 = jb * 32 + ch * 16 + cc * 4;
+                float s[4];
+                umma::tmem_ld4(umma::tmem_addr(tbase + tc::TM_S, warp, j0), s);
+                const float4 cf = *reinterpret_cast<const float4*>(sCf + j0);
+                *reinterpret_cast<uint2*>(sP + umma::tile_offset(row, j0, tc::PT)) =
+                    make_uint2(pack_bf16(s[0] * rf * cf.x, s[1] * rf * cf.y), pack_bf16(s[2] * rf * cf.z, s[3] * rf * cf.w));
             }
-#pragma unroll
-            for (int c = 0; c < 2; ++c)
-                *reinterpret_cast<uint4*>(sP + umma::tile_offset(row, j0 + c * 8, tc::PT)) =
-                    make_uint4(packed[c * 4], packed[c * 4 + 1], packed[c * 4 + 2], packed[c * 4 + 3]);
         }
         // diagonal block: levels 0..5, causal mask folded into the exponent
-        {
-            const int j0 = rb * 32 + ch * 16;
-            uint32_t packed[8];
-            float s[16];
-            umma::tmem_ld16(umma::tmem_addr(tbase + tc::TM_S, warp, j0), s);
-            const int li = lane;
+#pragma unroll 1
+        for (int cc = 0; cc < 4; ++cc) {
+            const int jc = ch * 16 + cc * 4;             // first of the four columns, inside the block
+            const int j0 = rb * 32 + jc;
+            float s[4];
+            umma::tmem_ld4(umma::tmem_addr(tbase + tc::TM_S, warp, j0), s);
+            const float4 gj = *reinterpret_cast<const float4*>(sGp + j0);
+            const float gjv[4] = {gj.x, gj.y, gj.z, gj.w};
 #pragma unroll
-            for (int e = 0; e < 16; e += 4) {
-                const float4 gj = *reinterpret_cast<const float4*>(sGp + j0 + e);
-                const float gjv[4] = {gj.x, gj.y, gj.z, gj.w};
-#pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    const int jj = ch * 16 + e + u;
-                    const int x = li ^ jj;
-                    float lm = lam[0];
-                    lm = (x >= 1) ? lam[1] : lm;
-                    lm = (x >= 2) ? lam[2] : lm;
-                    lm = (x >= 4) ? lam[3] : lm;
-                    lm = (x >= 8) ? lam[4] : lm;
-                    lm = (x >= 16) ? lam[5] : lm;
-                    const float d = (jj <= li) ? (Gi - gjv[u]) : -INFINITY;
-                    s[e + u] = s[e + u] * fexp(d) * lm;
-                }
-                packed[e >> 1] = pack_bf16(s[e], s[e + 1]);
-                packed[(e >> 1) + 1] = pack_bf16(s[e + 2], s[e + 3]);
+            for (int u = 0; u < 4; ++u) {
+                const int jj = jc + u;
+                const int x = lane ^ jj;
+                float lm = lam[0];
+                lm = (x >= 1) ? lam[1] : lm;
+                lm = (x >= 2) ? lam[2] : lm;
+                lm = (x >= 4) ? lam[3] : lm;
+                lm = (x >= 8) ? lam[4] : lm;
+                lm = (x >= 16) ? lam[5] : lm;
+                const float d = (jj <= lane) ? (Gi - gjv[u]) : -INFINITY;
+                s[u] = s[u] * fexp(d) * lm;
             }
-#pragma unroll
-            for (int c = 0; c < 2; ++c)
-                *reinterpret_cast<uint4*>(sP + umma::tile_offset(row, j0 + c * 8, tc::PT)) =
-                    make_uint4(packed[c * 4], packed[c * 4 + 1], packed[c * 4 + 2], packed[c * 4 + 3]);
+            *reinterpret_cast<uint2*>(sP + umma::tile_offset(row, j0, tc::PT)) = make_uint2(pack_bf16(s[0], s[1]), pack_bf16(s[2], s[3]));
         }
         STAMP();                                     // 7: P written
+        if (warp == TABLE_WARP && pl + 1 < npairs) {
+            decay_tables(pl + 1);
+            if (pl + 2 < npairs) fetch_g(pl + 2);
+        }
         umma::fence_async_smem();
         umma::fence_before_sync();
         bar_work();                                  // barrier 2
