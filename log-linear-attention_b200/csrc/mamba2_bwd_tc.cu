@@ -336,9 +336,8 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_fwdorder_tc_kernel(con
             for (int c = 0; c < 2; ++c)
                 *reinterpret_cast<uint4*>(sDS + umma::tile_offset(row, j0 + c * 8, tc::PT)) = make_uint4(0u, 0u, 0u, 0u);
         }
-        // blocks below the diagonal: one level per block, decay factorised through the block end.  A run-time loop with
-        // one copy of the body (measured 3 % faster per step than four unrolled copies; finer-grained loops with more
-        // tensor-memory loads were slower in the backward kernels).
+        // blocks below the diagonal: one level per block, decay factorised through the block end.  A run-time loop
+        // (one copy of the body): the fully unrolled form made the loop body larger than the instruction cache.
 #pragma unroll 1
         for (int jb = 0; jb < rb; ++jb) {
             const int j0 = jb * 32 + ch * 16;
@@ -681,6 +680,8 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_revorder_tc_kernel(con
     uint64_t* empty_k = bars + 5;      // ... and the compute warps have taken their k row sums
     uint64_t* dk_ready = bars + 6;     // the dk tile of the pair is staged (fp32) for the store agent
     uint64_t* stage_free = bars + 7;   // the store agent's reduce-add has read the staging area
+    uint64_t* barB1 = bars + 8;        // the part of the second batch that does not need P is complete
+    uint64_t* early_ready = bars + 9;  // every element-wise thread has written its part of dKV, Vs and the scaled do (256 arrivals)
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + SM::bar_off + 96);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + SM::bar_off + 104);
 
@@ -694,7 +695,8 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_revorder_tc_kernel(con
 
     if (tid == 0) {
 #pragma unroll
-        for (int i = 0; i < 8; ++i) umma::mbar_init(&bars[i], 1);
+        for (int i = 0; i < 9; ++i) umma::mbar_init(&bars[i], 1);
+        umma::mbar_init(early_ready, 256);
         umma::fence_mbar_init();
         *abort_flag = *p.err;
     }
@@ -760,18 +762,22 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_revorder_tc_kernel(con
                 umma::mbar_wait(full_qk, it & 1, abort_flag);
                 umma::gemm_kk<tc::PT, tc::PT, tc::KD>(tbase + tcr::TR_S, aQ, aK, ID_KK128, false);
                 umma::commit(barA);
-            }
-            __syncwarp();
-            umma::fence_before_sync();
-            bar_work();                              // barrier 2: P, Vs, dKV and scaled do are written
-            umma::fence_after_sync();
-            if (lane == 0) {
-                umma::mbar_wait(full_vd, it & 1, abort_flag);
-                umma::gemm_mm<tc::PT, tc::PT, tc::PT>(tbase + tcr::TR_DVA, aP, aDO, ID_MM64, false);          // P^T do
+                // the products that do not need P run while the element-wise warps turn S into P
+                umma::mbar_wait(early_ready, it & 1, abort_flag);
+                umma::fence_after_sync();
                 umma::gemm_km<tc::PT, tc::KD, tc::KD>(tbase + tcr::TR_DVB, aK, aDKV, ID_KM64, false);         // k dKV
                 umma::gemm_kk<tc::PT, tc::KD, tc::VD>(tbase + tcr::TR_DK, aVs, aDKV, ID_KK128, false);        // Vs dKV^T
                 umma::gemm_mm<tc::PT, tc::PT, 64>(tbase + tcr::TR_KVA, aK, aVs, ID_MM64, false);              // first chunk of the pair
                 umma::gemm_mm<tc::PT, tc::PT, 64>(tbase + tcr::TR_KVB, aK + 64 * umma::ROW_BYTES, aVs + 64 * umma::ROW_BYTES, ID_MM64, false);
+                umma::commit(barB1);
+            }
+            __syncwarp();
+            umma::fence_before_sync();
+            bar_work();                              // barrier 2: P is written
+            umma::fence_after_sync();
+            if (lane == 0) {
+                umma::mbar_wait(full_vd, it & 1, abort_flag);
+                umma::gemm_mm<tc::PT, tc::PT, tc::PT>(tbase + tcr::TR_DVA, aP, aDO, ID_MM64, false);          // P^T do
                 int slot = 0;
 #pragma unroll
                 for (int lv = 0; lv < MP; ++lv)
@@ -972,6 +978,8 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_revorder_tc_kernel(con
                 }
         }
         STAMPR();   // 3 Vs / scaled do written
+        umma::fence_async_smem();
+        asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(umma::smem_addr(early_ready)) : "memory");
         // ---- S -> P (bf16 tile)
         umma::mbar_wait(barA, it & 1, abort_flag);
         umma::fence_after_sync();
@@ -984,7 +992,7 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_revorder_tc_kernel(con
             for (int c = 0; c < 2; ++c)
                 *reinterpret_cast<uint4*>(sP + umma::tile_offset(row, j0 + c * 8, tc::PT)) = make_uint4(0u, 0u, 0u, 0u);
         }
-        // blocks below the diagonal (run-time loop: one copy of the body)
+        // blocks below the diagonal (run-time loop: one copy of the body keeps the loop inside the instruction cache)
 #pragma unroll 1
         for (int jb = 0; jb < rb; ++jb) {
             const int j0 = jb * 32 + ch * 16;
@@ -1047,50 +1055,12 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_revorder_tc_kernel(con
         bar_work();                                  // barrier 2
         umma::fence_after_sync();
 
-        umma::mbar_wait(barB, it & 1, abort_flag);
+        // ---- first the results that do not depend on P (they complete while P^T do and the reader insertions run)
+        umma::mbar_wait(barB1, it & 1, abort_flag);
         umma::fence_after_sync();
-        STAMPR();   // 6 batch B complete
-        // ---- dv = P^T do + decay_j (k dKV) : stage bf16 rows, coalesced copy-out
-        {
-            float ta[32], tb[32];
-            umma::tmem_ld32(umma::tmem_addr(tbase + tcr::TR_DVA, warp, ch * 32), ta);
-            umma::tmem_ld32(umma::tmem_addr(tbase + tcr::TR_DVB, warp, ch * 32), tb);
-            const float sc = sVf[row];
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                uint4 x;
-                uint32_t* xw = reinterpret_cast<uint32_t*>(&x);
-#pragma unroll
-                for (int e = 0; e < 4; ++e)
-                    xw[e] = pack_bf16(ta[c * 8 + e * 2] + sc * tb[c * 8 + e * 2], ta[c * 8 + e * 2 + 1] + sc * tb[c * 8 + e * 2 + 1]);
-                *reinterpret_cast<uint4*>(sVs + umma::tile_offset(row, ch * 32 + c * 8, tc::PT)) = x;   // Vs is free: second batch done
-            }
-        }
-        STAMPR();   // 7 dv staged
-        // ---- level part of dk: k_j . dk_j, fp32 staging
-        float wk_part = 0.f;
-#pragma unroll
-        for (int hb = 0; hb < 2; ++hb) {
-            float t[32];
-            umma::tmem_ld32(umma::tmem_addr(tbase + tcr::TR_DK, warp, ch * 64 + hb * 32), t);
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                const uint4 kx = *reinterpret_cast<const uint4*>(sK + umma::tile_offset(row, ch * 64 + hb * 32 + c * 8, tc::PT));
-                const uint32_t* xw = reinterpret_cast<const uint32_t*>(&kx);
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    __nv_bfloat162 v2 = *reinterpret_cast<const __nv_bfloat162*>(&xw[e]);
-                    wk_part += __bfloat162float(v2.x) * t[c * 8 + e * 2] + __bfloat162float(v2.y) * t[c * 8 + e * 2 + 1];
-                }
-            }
-            unsigned char* box = sStage + (ch * 2 + hb) * 16384;
-#pragma unroll
-            for (int c = 0; c < 8; ++c)
-                *reinterpret_cast<float4*>(box + box_offset(row, c * 4)) = make_float4(t[c * 4], t[c * 4 + 1], t[c * 4 + 2], t[c * 4 + 3]);
-        }
-        sMisc[ch * 128 + row] = wk_part;
-        STAMPR();   // 8 dk staged
-        // ---- contributor totals Y = <KV of each chunk of the pair, adjoint state> and the state update
+        STAMPR();   // 6 early part of batch B complete
+        // contributor totals Y = <KV of each chunk of the pair, adjoint state>, then the decay / reset of the adjoint states
+        const float dec = fexp(glp);
         {
             float kva[32], kvb[32];
             umma::tmem_ld32(umma::tmem_addr(tbase + tcr::TR_KVA, warp, ch * 32), kva);
@@ -1115,16 +1085,69 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_revorder_tc_kernel(con
                     sMisc[256 + warp * 8 + lv * 2 + 1] = yb;
                 }
             }
-            // move the adjoint states back across the pair: decay, reset, reader insertions
-            const float dec = fexp(glp);
-            int slot = 0;
 #pragma unroll
             for (int lv = 0; lv <= MP; ++lv) {
                 const bool reset = (lv < MP) && ((pl & ((2 << lv) - 1)) == 0);
                 const float f = reset ? 0.f : dec;
 #pragma unroll
                 for (int e = 0; e < 32; ++e) RM[lv][e] *= f;
-                if (lv < MP && ((pl >> lv) & 1)) {
+            }
+        }
+        // level part of dk: the row sums k_j . dk_j (the tile itself is staged below, once its staging area is free)
+        float wk_part = 0.f;
+#pragma unroll
+        for (int hb = 0; hb < 2; ++hb) {
+            float t[32];
+            umma::tmem_ld32(umma::tmem_addr(tbase + tcr::TR_DK, warp, ch * 64 + hb * 32), t);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const uint4 kx = *reinterpret_cast<const uint4*>(sK + umma::tile_offset(row, ch * 64 + hb * 32 + c * 8, tc::PT));
+                const uint32_t* xw = reinterpret_cast<const uint32_t*>(&kx);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    __nv_bfloat162 v2 = *reinterpret_cast<const __nv_bfloat162*>(&xw[e]);
+                    wk_part += __bfloat162float(v2.x) * t[c * 8 + e * 2] + __bfloat162float(v2.y) * t[c * 8 + e * 2 + 1];
+                }
+            }
+        }
+        sMisc[ch * 128 + row] = wk_part;
+        STAMPR();   // 7 Y, decay, k row sums
+        // ---- then what needs the whole batch: P (staging area of dk) and the scaled do are free, dv and the insertions are there
+        umma::mbar_wait(barB, it & 1, abort_flag);
+        umma::fence_after_sync();
+        // dv = P^T do + decay_j (k dKV) : stage bf16 rows, coalesced copy-out
+        {
+            float ta[32], tb[32];
+            umma::tmem_ld32(umma::tmem_addr(tbase + tcr::TR_DVA, warp, ch * 32), ta);
+            umma::tmem_ld32(umma::tmem_addr(tbase + tcr::TR_DVB, warp, ch * 32), tb);
+            const float sc = sVf[row];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                uint4 x;
+                uint32_t* xw = reinterpret_cast<uint32_t*>(&x);
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    xw[e] = pack_bf16(ta[c * 8 + e * 2] + sc * tb[c * 8 + e * 2], ta[c * 8 + e * 2 + 1] + sc * tb[c * 8 + e * 2 + 1]);
+                *reinterpret_cast<uint4*>(sVs + umma::tile_offset(row, ch * 32 + c * 8, tc::PT)) = x;   // Vs is free: second batch done
+            }
+        }
+        // dk tile -> fp32 staging (P / scaled-do space)
+#pragma unroll
+        for (int hb = 0; hb < 2; ++hb) {
+            float t[32];
+            umma::tmem_ld32(umma::tmem_addr(tbase + tcr::TR_DK, warp, ch * 64 + hb * 32), t);
+            unsigned char* box = sStage + (ch * 2 + hb) * 16384;
+#pragma unroll
+            for (int c = 0; c < 8; ++c)
+                *reinterpret_cast<float4*>(box + box_offset(row, c * 4)) = make_float4(t[c * 4], t[c * 4 + 1], t[c * 4 + 2], t[c * 4 + 3]);
+        }
+        STAMPR();   // 8 dv, dk staged
+        // reader insertions into the adjoint states
+        {
+            int slot = 0;
+#pragma unroll
+            for (int lv = 0; lv < MP; ++lv) {
+                if ((pl >> lv) & 1) {
                     float t[32];
                     umma::tmem_ld32(umma::tmem_addr(tbase + (slot == 0 ? tcr::TR_DH0 : tcr::TR_DH1), warp, ch * 32), t);
 #pragma unroll
