@@ -1,5 +1,5 @@
 // Tensor Memory Accelerator helpers: host-side tensor-map construction for (rows, heads, columns)
-// tensors and the device-side bulk tensor load (no multicast) with mbarrier transaction counting.
+// tensors and the device-side bulk tensor load (one destination CTA) with mbarrier transaction counting.
 #pragma once
 #include <cuda.h>
 #include <cuda_runtime.h>
