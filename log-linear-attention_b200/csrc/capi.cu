@@ -247,12 +247,14 @@ static size_t gdn_setup(llattn::GdnParams& p, void* ws, int parts, size_t start 
     p.NLEV = ceil_log2i(p.NT);
     Carver c(ws);
     c.off = start;
+    p.err = c.take<int>(64);      // status word first (256 bytes)
     const size_t n = (size_t)p.B * p.T * p.H;
     if (parts & GDN_WS_CHUNK) {
         p.kd = c.take<__nv_bfloat16>(n * p.K);
         p.wd = c.take<__nv_bfloat16>(n * p.K);
         p.qd = c.take<__nv_bfloat16>(n * p.K);
         p.u = c.take<__nv_bfloat16>(n * p.V);
+        p.wk = c.take<__nv_bfloat16>((size_t)p.B * p.NT * p.H * p.K * p.K);
     }
     // level states and their adjoints: one K x 32 tile per (batch, head, 32-column slice, chunk, level)
     const size_t tiles = (size_t)p.B * p.H * (p.V / llattn::GDN_VS) * p.NT * (p.NLEV > 0 ? p.NLEV : 1);
@@ -318,6 +320,8 @@ static int gdn_fwd_impl(const void* q, const void* k, const void* v, const void*
     p.beta = (const __nv_bfloat16*)beta; p.g = g; p.l = (const __nv_bfloat16*)lambda;
     p.o = (__nv_bfloat16*)o; p.g_cum = g_cum; p.Aw = (__nv_bfloat16*)Aw; p.Au = (__nv_bfloat16*)Au;
     p.final_states = final_states;
+    cudaError_t e0 = cudaMemsetAsync(p.err, 0, sizeof(int), (cudaStream_t)stream);
+    if (e0 != cudaSuccess) return (int)e0;
     return keep ? llattn::gdn_fwd_keep_dispatch(p, (cudaStream_t)stream) : llattn::gdn_fwd_dispatch(p, (cudaStream_t)stream);
 }
 
@@ -348,6 +352,8 @@ int llattn_gdn_bwd_levels(const void* q, const void* k, const void* v, const voi
     p.d_o = (const __nv_bfloat16*)d_o;
     p.d_qd = d_qd; p.d_wd = d_wd; p.d_kd = d_kd; p.d_u = (__nv_bfloat16*)d_u; p.d_gl = d_gl; p.dl = dlambda;
     cudaStream_t st = (cudaStream_t)stream;
+    cudaError_t e0 = cudaMemsetAsync(p.err, 0, sizeof(int), st);
+    if (e0 != cudaSuccess) return (int)e0;
     if ((rc = llattn::gdn_recompute_dispatch(p, st)) != 0) return rc;
     if ((rc = llattn::gdn_bwd_scan_dispatch(p, st)) != 0) return rc;
     return llattn::gdn_bwd_levels_dispatch(p, st);
@@ -403,6 +409,7 @@ static int gdn_bwd_impl(const void* q, const void* k, const void* v, const void*
     cudaStream_t st = (cudaStream_t)stream;
     cudaError_t e = cudaMemsetAsync(dlambda, 0, (size_t)B * T * H * L * sizeof(float), st);
     if (e != cudaSuccess) return (int)e;
+    if ((e = cudaMemsetAsync(p.err, 0, sizeof(int), st)) != cudaSuccess) return (int)e;
     if (!kept && (rc = llattn::gdn_recompute_dispatch(p, st)) != 0) return rc;
     if ((rc = llattn::gdn_bwd_scan_dispatch(p, st)) != 0) return rc;
     if ((rc = llattn::gdn_bwd_levels_dispatch(p, st)) != 0) return rc;

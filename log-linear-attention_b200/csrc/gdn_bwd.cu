@@ -16,6 +16,7 @@
 // the decay gradient, d lambda of the inter-chunk levels) is chunk-parallel: gdn_bwd_levels_kernel.
 #include "llattn_common.cuh"
 #include "llattn_gdn.h"
+#include "llattn_mamba2.h"
 
 namespace llattn {
 
@@ -425,10 +426,27 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_levels_kernel(const GdnParams 
         } else {
             // u E_jc^T
             warp_gemm<1, 4, false, false>(dkd, sU + vh * 64, LDV, i0, cE, LDH, ch * 64, 64, lane);
+            // d_u = kd E_jc (gradient of the chunk's own writes), 64 columns of this half of V
+            float ke[1][4][4];
+            zero_acc(ke);
+            warp_gemm<1, 2, false, true>(ke, sKd, LDK, i0, cE, LDH, ch * 32, KD, lane);
+#pragma unroll
+            for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+                for (int hh = 0; hh < 2; ++hh)
+                    *reinterpret_cast<uint32_t*>(p.d_u + (rowbase + (long)(i0 + lr + hh * 8) * p.H) * VD + vh * 64 + ch * 32 + nt * 8 + lc2) =
+                        pack_bf16(ke[0][nt][hh * 2], ke[0][nt][hh * 2 + 1]);
         }
     }
     if (nsteps == 0) {
         cp_async_wait<0>();
+    }
+    if (!trans) {
+        // the last chunk's writes reach no later chunk
+        for (int e = tid; e < CH * (VD / 8); e += 256) {
+            const int i = e / (VD / 8), c8 = (e % (VD / 8)) * 8;
+            *reinterpret_cast<uint4*>(p.d_u + (rowbase + (long)i * p.H) * VD + c8) = make_uint4(0u, 0u, 0u, 0u);
+        }
     }
     // ---- results
 #pragma unroll
@@ -462,6 +480,7 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_levels_kernel(const GdnParams 
 // ------------------------------------------------------------------------------------------
 int gdn_bwd_scan_dispatch(const GdnParams& p, cudaStream_t stream) {
     if (p.K != 128) return LLATTN_ERR_UNSUPPORTED_SHAPE;
+    if (g_use_tensor_core_path.load()) return gdn_scan_bwd_tc_dispatch(p, stream);
     auto kern = gdn_scan_bwd_kernel<128>;
     const size_t sm = ScanBwdSmem<128>::total;
     cudaError_t e;

@@ -21,6 +21,7 @@
 //       products kd^T (.), about half of the per-level formulation.  fp32 masters in registers.
 #include "llattn_common.cuh"
 #include "llattn_gdn.h"
+#include "llattn_mamba2.h"
 
 namespace llattn {
 
@@ -69,6 +70,11 @@ __global__ void __launch_bounds__(256, 1) gdn_chunk_prep_kernel(const GdnParams 
     float* sBe = reinterpret_cast<float*>(smem + SM::be_off);
     float* sLam = reinterpret_cast<float*>(smem + SM::lam_off);
     float* sX = reinterpret_cast<float*>(smem + SM::x_off);
+    // bf16 copies of wd and kd for the product kd^T wd; they take the place of A and A * Gamma once the
+    // triangular solves are done
+    static_assert(CH * LDK * 2 <= CH * LDA * 4, "the bf16 tiles fit the fp32 matrices they replace");
+    bf16* sWdS = reinterpret_cast<bf16*>(smem + SM::a_off);
+    bf16* sKdS = reinterpret_cast<bf16*>(smem + SM::ag_off);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int h = blockIdx.x % p.H;
@@ -214,8 +220,9 @@ __global__ void __launch_bounds__(256, 1) gdn_chunk_prep_kernel(const GdnParams 
                 const int cc = colk + nt * 8 + lc2;
                 const float eg = fexp(sGc[i]);
                 *reinterpret_cast<uint32_t*>(sBK + i * LDK + cc) = pack_bf16(acc[0][nt][hh * 2], acc[0][nt][hh * 2 + 1]);
-                *reinterpret_cast<uint32_t*>(p.wd + (rowbase + (long)i * p.H) * KD + cc) =
-                    pack_bf16(acc[0][nt][hh * 2] * eg, acc[0][nt][hh * 2 + 1] * eg);
+                const uint32_t wdx = pack_bf16(acc[0][nt][hh * 2] * eg, acc[0][nt][hh * 2 + 1] * eg);
+                *reinterpret_cast<uint32_t*>(p.wd + (rowbase + (long)i * p.H) * KD + cc) = wdx;
+                *reinterpret_cast<uint32_t*>(sWdS + i * LDK + cc) = wdx;
             }
     }
     {
@@ -236,8 +243,9 @@ __global__ void __launch_bounds__(256, 1) gdn_chunk_prep_kernel(const GdnParams 
         const int i = e / (KD / 2), cc = (e % (KD / 2)) * 2;
         const float sc = fexp(glast - sGc[i]);
         __nv_bfloat162 x = *reinterpret_cast<const __nv_bfloat162*>(sK + i * LDK + cc);
-        *reinterpret_cast<uint32_t*>(p.kd + (rowbase + (long)i * p.H) * KD + cc) =
-            pack_bf16(__bfloat162float(x.x) * sc, __bfloat162float(x.y) * sc);
+        const uint32_t kdx = pack_bf16(__bfloat162float(x.x) * sc, __bfloat162float(x.y) * sc);
+        *reinterpret_cast<uint32_t*>(p.kd + (rowbase + (long)i * p.H) * KD + cc) = kdx;
+        *reinterpret_cast<uint32_t*>(sKdS + i * LDK + cc) = kdx;
     }
     __syncthreads();                           // w is complete in shared memory
 
@@ -258,6 +266,23 @@ __global__ void __launch_bounds__(256, 1) gdn_chunk_prep_kernel(const GdnParams 
                 *reinterpret_cast<uint32_t*>(p.qd + (rowbase + (long)i * p.H) * KD + cc) =
                     pack_bf16((__bfloat162float(x.x) - acc[0][nt][hh * 2]) * eg, (__bfloat162float(x.y) - acc[0][nt][hh * 2 + 1]) * eg);
             }
+    }
+    // ---- -kd^T wd (K x K): with it the transition of a level state is  H' = exp(gl) H - (kd^T wd) H (+ kd^T u),
+    //      one product per level for the sequential scans instead of two dependent ones
+    if (p.wk != nullptr) {
+        float acc[1][KD / 8][4];
+        zero_acc(acc);
+        for (int m0 = warp * 16; m0 < KD; m0 += 8 * 16) {
+            zero_acc(acc);
+            warp_gemm<1, KD / 16, true, true>(acc, sKdS, LDK, m0, sWdS, LDK, 0, CH, lane);
+            bf16* dst = p.wk + ((((long)b * p.NT + c) * KD) * p.H + h) * KD;
+#pragma unroll
+            for (int nt = 0; nt < KD / 8; ++nt)
+#pragma unroll
+                for (int hh = 0; hh < 2; ++hh)
+                    *reinterpret_cast<uint32_t*>(dst + (long)(m0 + lr + hh * 8) * p.H * KD + nt * 8 + lc2) =
+                        pack_bf16(-acc[0][nt][hh * 2], -acc[0][nt][hh * 2 + 1]);
+        }
     }
     if (FROM_SAVED) return;
     // ---- P = (tril(q k^T) Aw) * Gamma * beta_j * lambda ; o = P v
@@ -580,6 +605,7 @@ static int launch_gdn_fwd(const GdnParams& p, cudaStream_t stream) {
         if ((e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm)) != cudaSuccess) return (int)e;
         kern<<<p.B * p.NT * p.H, 256, sm, stream>>>(p); LLATTN_LAUNCHED();
     }
+    if (KD == 128 && g_use_tensor_core_path.load()) return gdn_scan_tc_dispatch(p, BWD ? 2 : (KEEP ? 1 : 0), stream);
     {
         auto kern = gdn_scan_kernel<KD, BWD || KEEP, !BWD>;
         const size_t sm = ScanSmem<KD>::total;

@@ -1,5 +1,6 @@
 // Internal launch parameters of the log-linear Gated DeltaNet kernels.
 #pragma once
+#include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
@@ -29,6 +30,7 @@ struct GdnParams {
     __nv_bfloat16* wd;           // (B,T,H,K)  w exp(G)
     __nv_bfloat16* qd;           // (B,T,H,K)  exp(G) (q - tril(q k^T) w)
     __nv_bfloat16* u;            // (B,T,H,V)
+    __nv_bfloat16* wk;           // (B,NT*K,H,K)  -kd^T wd per chunk (tcgen05 scans; NULL: not produced)
     // backward
     const __nv_bfloat16* d_o;    // (B,T,H,V)
     __nv_bfloat16* hs;           // [(b,h,slice)][chunk][level][K][32]  level states read by each chunk
@@ -46,11 +48,17 @@ struct GdnParams {
     float* dl;                   // (B,T,H,L)
     int B, T, H, K, V, L;
     int NT, NLEV;
+    int* err;                    // status word (first word of the call's workspace): set by a kernel whose bounded wait ran out
+    // tensor maps of the chunk matrices (tcgen05 kernels; filled by their launchers)
+    alignas(64) CUtensorMap tm_qd, tm_wd, tm_kd, tm_wk;
 };
 
 int gdn_fwd_dispatch(const GdnParams& p, cudaStream_t stream);
 int gdn_fwd_keep_dispatch(const GdnParams& p, cudaStream_t stream);
 int gdn_recompute_dispatch(const GdnParams& p, cudaStream_t stream);
+// tcgen05 scans (K = 128).  mode 0: forward, 1: forward that keeps the level states, 2: recomputation (states only)
+int gdn_scan_tc_dispatch(const GdnParams& p, int mode, cudaStream_t stream);
+int gdn_scan_bwd_tc_dispatch(const GdnParams& p, cudaStream_t stream);     // adjoint level states (d_u comes from the level-gradient kernel)
 int gdn_bwd_scan_dispatch(const GdnParams& p, cudaStream_t stream);      // adjoint level states, d_u
 int gdn_bwd_levels_dispatch(const GdnParams& p, cudaStream_t stream);    // d_qd, d_wd, d_kd, d_gl, dl (inter-chunk levels)
 int gdn_bwd_chunk_dispatch(const GdnParams& p, cudaStream_t stream);     // dq, dk, dv, dbeta, dg, dl (intra-chunk levels)

@@ -102,6 +102,16 @@ __device__ __forceinline__ void gemm_mm(uint32_t d_tmem, uint32_t a_saddr, uint3
         mma_ss(d_tmem, da + ((kk * ROW_BYTES) >> 4), db + ((kk * ROW_BYTES) >> 4), idesc, accumulate || kk > 0);
     }
 }
+// A stored [KRED rows][M cols] (MN-major), B a K-major tile (rows = N index): D = A^T B^T
+template <int A_ROWS, int B_ROWS, int KRED>
+__device__ __forceinline__ void gemm_mk(uint32_t d_tmem, uint32_t a_saddr, uint32_t b_saddr, uint32_t idesc, bool accumulate) {
+    const uint32_t da = desc_lo_mnmajor(a_saddr, A_ROWS * ROW_BYTES), db = desc_lo_kmajor(b_saddr);
+#pragma unroll
+    for (int kk = 0; kk < KRED; kk += 16) {
+        const uint32_t kb = (kk >> 6) * B_ROWS * ROW_BYTES + (kk & 63) * 2;
+        mma_ss(d_tmem, da + ((kk * ROW_BYTES) >> 4), db + (kb >> 4), idesc, accumulate || kk > 0);
+    }
+}
 // run-time sized variants (self-test)
 __device__ __forceinline__ void gemm_kk(uint32_t d_tmem, uint32_t a_saddr, int a_rows, uint32_t b_saddr, int b_rows,
                                         int kred, uint32_t idesc, bool accumulate) {
@@ -166,6 +176,24 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32
     }
     return false;
 }
+// bounded wait for warps that have nothing else to do until the phase completes: sleeps between polls so that the
+// polling does not compete with the tensor core's operand fetch from shared memory
+__device__ __forceinline__ bool mbar_wait_backoff(uint64_t* bar, uint32_t parity, volatile int* abort, unsigned ns) {
+    const uint32_t a = smem_addr(bar);
+    for (uint32_t it = 0; it < SPIN_LIMIT; ++it) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"
+            : "=r"(done)
+            : "r"(a), "r"(parity)
+            : "memory");
+        if (done) return true;
+        if ((it & 255) == 255 && *abort) return false;
+        __nanosleep(ns);
+    }
+    *abort = 1;
+    return false;
+}
 __device__ __forceinline__ void fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
 __device__ __forceinline__ void fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
 // make generic-proxy shared memory writes (st.shared, cp.async) visible to the tensor core's async proxy
@@ -209,6 +237,42 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
 #pragma unroll
     for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+// 16 consecutive fp32 columns, issue only: the destination registers are valid after tmem_ld_wait4 has named them
+__device__ __forceinline__ void tmem_ld16_issue(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
+// one wait for four 16-column loads in flight; every destination register is an operand so that no use of them can
+// be scheduled above the wait
+__device__ __forceinline__ void tmem_ld_wait4(uint32_t (&a)[16], uint32_t (&b)[16], uint32_t (&c)[16], uint32_t (&d)[16]) {
+    asm volatile(
+        "tcgen05.wait::ld.sync.aligned;\n"
+        : "+r"(a[0]), "+r"(a[1]), "+r"(a[2]), "+r"(a[3]), "+r"(a[4]), "+r"(a[5]), "+r"(a[6]), "+r"(a[7]), "+r"(a[8]),
+          "+r"(a[9]), "+r"(a[10]), "+r"(a[11]), "+r"(a[12]), "+r"(a[13]), "+r"(a[14]), "+r"(a[15]),
+          "+r"(b[0]), "+r"(b[1]), "+r"(b[2]), "+r"(b[3]), "+r"(b[4]), "+r"(b[5]), "+r"(b[6]), "+r"(b[7]), "+r"(b[8]),
+          "+r"(b[9]), "+r"(b[10]), "+r"(b[11]), "+r"(b[12]), "+r"(b[13]), "+r"(b[14]), "+r"(b[15]),
+          "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3]), "+r"(c[4]), "+r"(c[5]), "+r"(c[6]), "+r"(c[7]), "+r"(c[8]),
+          "+r"(c[9]), "+r"(c[10]), "+r"(c[11]), "+r"(c[12]), "+r"(c[13]), "+r"(c[14]), "+r"(c[15]),
+          "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3]), "+r"(d[4]), "+r"(d[5]), "+r"(d[6]), "+r"(d[7]), "+r"(d[8]),
+          "+r"(d[9]), "+r"(d[10]), "+r"(d[11]), "+r"(d[12]), "+r"(d[13]), "+r"(d[14]), "+r"(d[15])
+        :
+        : "memory");
+}
+// compiler-level completion point for one more 16-column load (after a wait that has already covered it in hardware,
+// or on its own)
+__device__ __forceinline__ void tmem_ld_wait1(uint32_t (&a)[16]) {
+    asm volatile(
+        "tcgen05.wait::ld.sync.aligned;\n"
+        : "+r"(a[0]), "+r"(a[1]), "+r"(a[2]), "+r"(a[3]), "+r"(a[4]), "+r"(a[5]), "+r"(a[6]), "+r"(a[7]), "+r"(a[8]),
+          "+r"(a[9]), "+r"(a[10]), "+r"(a[11]), "+r"(a[12]), "+r"(a[13]), "+r"(a[14]), "+r"(a[15])
+        :
+        : "memory");
 }
 // 4 consecutive fp32 columns of this thread's lane
 __device__ __forceinline__ void tmem_ld4(uint32_t taddr, float (&v)[4]) {

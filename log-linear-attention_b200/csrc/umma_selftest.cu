@@ -84,7 +84,9 @@ __global__ void __launch_bounds__(128, 1) umma_selftest_kernel(const bf16* __res
 // Issue-to-completion time of `reps` back-to-back products of one layout combination (operands already in
 // shared memory, accumulators in tensor memory): the per-instruction cost that the kernel designs assume.
 // issuers = 2: warps 0 and 1 each issue `reps` products into their own accumulator at the same time.
-__global__ void __launch_bounds__(128, 1) umma_cycles_kernel(int N, int kred, int mode, int reps, int issuers,
+// Dynamic shared memory: 64 KB of operands (modes 0..2) or 128 KB (modes 3, 4, whose B tile has 256-row panels:
+// the chain reads up to byte 32768 + 32768 + 128 * 128 of it).
+__global__ void __launch_bounds__(128, 1) umma_cycles_kernel(int N, int kred, int mode, int reps, int issuers, int smem_bytes,
                                                              long long* __restrict__ cycles, int* __restrict__ err) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -93,7 +95,7 @@ __global__ void __launch_bounds__(128, 1) umma_cycles_kernel(int N, int kred, in
     __shared__ uint64_t bar[2];
     __shared__ uint32_t tmem_slot;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    for (int e = tid; e < 65536 / 4; e += 128) reinterpret_cast<uint32_t*>(smem)[e] = 0x3c003c00u;     // small finite bf16 pairs
+    for (int e = tid; e < smem_bytes / 4; e += 128) reinterpret_cast<uint32_t*>(smem)[e] = 0x3c003c00u;     // small finite bf16 pairs
     if (warp == 0) umma::tmem_alloc(&tmem_slot, 256);
     if (tid == 0) {
         umma::mbar_init(&bar[0], 1);
@@ -122,6 +124,12 @@ __global__ void __launch_bounds__(128, 1) umma_cycles_kernel(int N, int kred, in
                 umma::gemm_mm<128, 128, 64>(t + 64, b + 8192, a + 8192, umma::idesc_bf16(128, 64, true, true), false);
                 umma::gemm_mm<128, 128, 128>(t + 128, a, b + 16384, umma::idesc_bf16(128, 64, true, true), false);
             }
+        } else if (mode == 3) {
+            // the chains of the Gated DeltaNet scans: narrow accumulators (N = 32 per level, adjacent levels in one chain)
+            // from a 256-row K-major B tile, and the MN-major A form with a 64-token reduction
+            for (int r = 0; r < reps; ++r) umma::gemm_kk<128, 256, 128>(tbase, a, b, umma::idesc_bf16(128, N, false, false), r > 0);
+        } else if (mode == 4) {
+            for (int r = 0; r < reps; ++r) umma::gemm_mk<64, 256, 64>(tbase, a, b, umma::idesc_bf16(128, N, true, false), r > 0);
         } else if (mode == 0 && N == 128 && kred == 128) {
             for (int r = 0; r < reps; ++r) umma::gemm_kk<128, 128, 128>(tbase, a, b, umma::idesc_bf16(128, 128, false, false), r > 0);
         } else if (mode == 0 && N == 128 && kred == 64) {
@@ -173,13 +181,15 @@ __global__ void wait_timeout_kernel(uint32_t limit, int* status) {
 extern "C" int llattn_selftest_umma_cycles(int N, int kred, int mode, int reps, int issuers, long long* cycles, int* err_flag,
                                            void* stream) {
     if (!cycles || !err_flag) return LLATTN_ERR_NULL;
-    if (!(N == 64 || N == 128) || !(kred == 64 || kred == 128) || mode < 0 || mode > 2 || reps < 1 || reps > 4096 ||
+    if (!(kred == 64 || kred == 128) || mode < 0 || mode > 4 || reps < 1 || reps > 4096 ||
         !(issuers == 1 || issuers == 2 || issuers == 11 || issuers == 12))
         return LLATTN_ERR_UNSUPPORTED_SHAPE;
-    const size_t sm = 65536 + 1024;
+    if (mode <= 2 ? !(N == 64 || N == 128) : !(N >= 32 && N <= 128 && N % 32 == 0)) return LLATTN_ERR_UNSUPPORTED_SHAPE;
+    const int operand_bytes = mode >= 3 ? 131072 : 65536;
+    const size_t sm = (size_t)operand_bytes + 1024;
     cudaError_t e = cudaFuncSetAttribute(llattn::umma_cycles_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
     if (e != cudaSuccess) return (int)e;
-    llattn::umma_cycles_kernel<<<1, 128, sm, (cudaStream_t)stream>>>(N, kred, mode, reps, issuers, cycles, err_flag); LLATTN_LAUNCHED();
+    llattn::umma_cycles_kernel<<<1, 128, sm, (cudaStream_t)stream>>>(N, kred, mode, reps, issuers, operand_bytes, cycles, err_flag); LLATTN_LAUNCHED();
     return (int)cudaGetLastError();
 }
 

@@ -127,6 +127,8 @@ def chunkwise_fwd(
                                     o.data_ptr(), g_cum.data_ptr(), Aw.data_ptr(), Au.data_ptr(), ws.data_ptr(), ws.numel(),
                                     B, T, H, K, V, L, torch.cuda.current_stream().cuda_stream)
             _lib.check(rc, "llattn_gdn_fwd")
+        if _lib.CHECK_STATUS:
+            _lib.raise_on_status(ws, torch.cuda.current_stream().cuda_stream, "llattn_gdn_fwd")
     return g_cum, o, Aw, Au, ht
 
 
@@ -162,6 +164,8 @@ def chunkwise_bwd(q, k, v, b, g, l, Aw, Au, do, head_first, level_base, htype, c
         else:
             rc = lib.llattn_gdn_bwd(*head, *tail)
         _lib.check(rc, "llattn_gdn_bwd_kept" if kept else "llattn_gdn_bwd")
+        if _lib.CHECK_STATUS:
+            _lib.raise_on_status(ws, torch.cuda.current_stream().cuda_stream, "llattn_gdn_bwd")
     return dq, dk, dv, db, dg, dl
 
 

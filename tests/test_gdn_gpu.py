@@ -202,3 +202,39 @@ def test_l2norm_kernels(D):
     yr = xr * torch.rsqrt((xr * xr).sum(-1, keepdim=True) + 1e-6) * scale
     (gx,) = torch.autograd.grad(yr, xr, dy)
     torch.testing.assert_close(dx.float(), gx, rtol=1e-2, atol=1e-2 * gx.abs().max().item())
+
+
+@pytest.mark.parametrize("B,T,H,Dv,L", [(1, 1408, 2, 128, 12), (2, 1024, 1, 64, 11), (1, 8192, 1, 128, 14), (1, 192, 1, 64, 9)])
+def test_tensor_core_scans_match_warp_mma_scans(B, T, H, Dv, L):
+    """The tcgen05 scans over chunks against the warp-MMA kernels on the same inputs: both keep fp32 master
+    states and round the same operands to bf16 (level states, u - sum wd H), so outputs and gradients agree to
+    accumulation-order level.  T = 8192 reaches all seven inter-chunk levels of the largest benchmark shape."""
+    from hattention_b200 import _lib
+    from hattention_b200 import chunkwise_hgdn as hg
+    from hattention_b200.base import HType
+    dev = torch.device("cuda:0")
+    Dk = 128
+    q, k, v, b, g, l = orc.make_gdn_inputs(B, T, H, Dk, Dv, L, seed=T + 9)
+    scale = Dk ** -0.5
+    qn, kn = orc.gdn_layer_inputs(q, k, scale)
+    qn, kn, v, b, l = (x.bfloat16().to(dev) for x in (qn, kn, v, b, l / scale))
+    g = g.float().to(dev)
+    do = torch.randn(B, T, H, Dv, generator=torch.Generator().manual_seed(8)).bfloat16().to(dev)
+
+    def run():
+        g_cum, o, Aw, Au, _ = hg.chunkwise_fwd(qn, kn, v, b, g, l, False, 2, HType.WEAK, 64, False)
+        grads = hg.chunkwise_bwd(qn, kn, v, b, g_cum, l, Aw, Au, do, False, 2, HType.WEAK, 64)
+        torch.cuda.synchronize()
+        return (o,) + tuple(grads)
+
+    got = run()
+    _lib.lib().llattn_testing_use_tensor_core_path(0)
+    try:
+        want = run()
+    finally:
+        _lib.lib().llattn_testing_use_tensor_core_path(1)
+    for a, w_, key in zip(got, want, ("o", "dq", "dk", "dv", "db", "dg", "dl")):
+        assert torch.isfinite(a).all(), key
+        rel = ((a.double() - w_.double()).norm() / w_.double().norm().clamp_min(1e-30)).item()
+        assert rel <= 2e-3, f"{key}: relative Frobenius difference {rel:.2e}"
+        assert_close(a.float(), w_.float(), key, rtol=2e-2, atol=2e-3)

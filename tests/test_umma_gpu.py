@@ -35,6 +35,11 @@ def test_umma_tile_product(mode, N, kred):
     (2, 128, 128, 72.0),    # MN-major x MN-major, N = 128
     (1, 64, 128, 64.0),     # N = 64: about 54 cycles per step (32 would be the arithmetic bound)
     (2, 64, 128, 64.0),
+    (3, 32, 128, 64.0),     # Gated DeltaNet scans: one level (N = 32) from the 256-row transposed state tile
+    (3, 64, 128, 64.0),     # two and four adjacent levels in one chain
+    (3, 128, 128, 72.0),
+    (4, 32, 64, 64.0),      # MN-major A (kd^T / qd^T), 64-token reduction
+    (4, 96, 64, 64.0),
 ])
 def test_mma_issue_rate(mode, N, kred, bound):
     """Cycles per tcgen05.mma (M = 128, K = 16) of the compile-time shaped issue loops that the kernels use,
