@@ -267,22 +267,24 @@ __global__ void __launch_bounds__(256, 1) gdn_chunk_prep_kernel(const GdnParams 
                     pack_bf16((__bfloat162float(x.x) - acc[0][nt][hh * 2]) * eg, (__bfloat162float(x.y) - acc[0][nt][hh * 2 + 1]) * eg);
             }
     }
-    // ---- -kd^T wd (K x K): with it the transition of a level state is  H' = exp(gl) H - (kd^T wd) H (+ kd^T u),
-    //      one product per level for the sequential scans instead of two dependent ones
+    // ---- Wd = (exp(gl) - 1) I - kd^T wd (K x K): with it the transition of a level state is  H' = H + Wd H
+    //      (+ kd^T u), one accumulating product per level for the sequential scans instead of two dependent ones
     if (p.wk != nullptr) {
+        const float decm1 = fexp(glast) - 1.f;
         float acc[1][KD / 8][4];
         zero_acc(acc);
-        for (int m0 = warp * 16; m0 < KD; m0 += 8 * 16) {
-            zero_acc(acc);
-            warp_gemm<1, KD / 16, true, true>(acc, sKdS, LDK, m0, sWdS, LDK, 0, CH, lane);
-            bf16* dst = p.wk + ((((long)b * p.NT + c) * KD) * p.H + h) * KD;
+        const int m0 = warp * 16;              // 8 warps x 16 rows = K = 128
+        static_assert(KD == 128, "one 16-row block of Wd per warp");
+        warp_gemm<1, KD / 16, true, true>(acc, sKdS, LDK, m0, sWdS, LDK, 0, CH, lane);
+        bf16* dst = p.wk + ((((long)b * p.NT + c) * KD) * p.H + h) * KD;
 #pragma unroll
-            for (int nt = 0; nt < KD / 8; ++nt)
+        for (int nt = 0; nt < KD / 8; ++nt)
 #pragma unroll
-                for (int hh = 0; hh < 2; ++hh)
-                    *reinterpret_cast<uint32_t*>(dst + (long)(m0 + lr + hh * 8) * p.H * KD + nt * 8 + lc2) =
-                        pack_bf16(-acc[0][nt][hh * 2], -acc[0][nt][hh * 2 + 1]);
-        }
+            for (int hh = 0; hh < 2; ++hh) {
+                const int r = m0 + lr + hh * 8, cc = nt * 8 + lc2;
+                const float x0 = -acc[0][nt][hh * 2] + (r == cc ? decm1 : 0.f), x1 = -acc[0][nt][hh * 2 + 1] + (r == cc + 1 ? decm1 : 0.f);
+                *reinterpret_cast<uint32_t*>(dst + (long)r * p.H * KD + cc) = pack_bf16(x0, x1);
+            }
     }
     if (FROM_SAVED) return;
     // ---- P = (tril(q k^T) Aw) * Gamma * beta_j * lambda ; o = P v

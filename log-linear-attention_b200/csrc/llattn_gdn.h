@@ -30,7 +30,7 @@ struct GdnParams {
     __nv_bfloat16* wd;           // (B,T,H,K)  w exp(G)
     __nv_bfloat16* qd;           // (B,T,H,K)  exp(G) (q - tril(q k^T) w)
     __nv_bfloat16* u;            // (B,T,H,V)
-    __nv_bfloat16* wk;           // (B,NT*K,H,K)  -kd^T wd per chunk (tcgen05 scans; NULL: not produced)
+    __nv_bfloat16* wk;           // (B,NT*K,H,K)  (exp(gl) - 1) I - kd^T wd per chunk (tcgen05 scans; NULL: not produced)
     // backward
     const __nv_bfloat16* d_o;    // (B,T,H,V)
     __nv_bfloat16* hs;           // [(b,h,slice)][chunk][level][K][32]  level states read by each chunk
@@ -50,7 +50,7 @@ struct GdnParams {
     int NT, NLEV;
     int* err;                    // status word (first word of the call's workspace): set by a kernel whose bounded wait ran out
     // tensor maps of the chunk matrices (tcgen05 kernels; filled by their launchers)
-    alignas(64) CUtensorMap tm_qd, tm_wd, tm_kd, tm_wk;
+    alignas(64) CUtensorMap tm_qd, tm_kd, tm_wk;
 };
 
 int gdn_fwd_dispatch(const GdnParams& p, cudaStream_t stream);
