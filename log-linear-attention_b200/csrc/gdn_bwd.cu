@@ -500,6 +500,7 @@ static int launch_levels(const GdnParams& p, cudaStream_t stream) {
 }
 
 int gdn_bwd_levels_dispatch(const GdnParams& p, cudaStream_t stream) {
+    if (p.K == 128 && g_use_tensor_core_path.load()) return gdn_bwd_levels_tc_dispatch(p, stream);
     if (p.K == 128 && p.V == 128) return launch_levels<128, 128>(p, stream);
     if (p.K == 128 && p.V == 64) return launch_levels<128, 64>(p, stream);
     return LLATTN_ERR_UNSUPPORTED_SHAPE;

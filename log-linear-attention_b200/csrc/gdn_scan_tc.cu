@@ -84,8 +84,8 @@ struct ScanTcSmem {
 };
 
 // SAVE also writes, for every chunk, the bf16 level states that the chunk reads:
-// hs[((b*H + h)*nvs + vs)*NT + c][level][K][32] (the backward's recomputation, or a forward whose caller keeps
-// the workspace for the backward); OUT = false skips the output (recomputation only).
+// hs[((b*H + h)*(V/64) + vs/2)*NT + c][level][K][64] (the backward's recomputation, or a forward whose caller keeps
+// the workspace for the backward; V a multiple of 64); OUT = false skips the output (recomputation only).
 template <bool SAVE, bool OUT>
 __global__ void __launch_bounds__(gtc::NTHREADS, 1) gdn_scan_tc_kernel(const __grid_constant__ GdnParams p) {
     using SM = ScanTcSmem;
@@ -114,6 +114,8 @@ __global__ void __launch_bounds__(gtc::NTHREADS, 1) gdn_scan_tc_kernel(const __g
     const int b = blockIdx.x / (nvs * p.H);
     const int nlev = p.NLEV, NT = p.NT;
     const uint32_t lev_mask = (1u << nlev) - 1u;
+    // level-state tiles for the backward are [K][64]: one tile per pair of 32-column slices, this CTA's slice in its half
+    auto pair_tile = [&](int c, int lv) -> size_t { return ((((size_t)(blockIdx.x >> 1)) * NT + c) * nlev + lv) * (size_t)(gtc::KD * 64); };
 
     if (tid == 0) {
 #pragma unroll
@@ -330,7 +332,7 @@ __global__ void __launch_bounds__(gtc::NTHREADS, 1) gdn_scan_tc_kernel(const __g
 #pragma unroll
         for (int j = 0; j < 8; ++j) mine[j] = pack_bf16(v[2 * j], v[2 * j + 1]);
         if (SAVE) {
-            st_global_32B(p.hs + (((size_t)blockIdx.x * NT + c_next) * nlev + lv) * (size_t)(gtc::KD * gtc::VS) + (size_t)row * gtc::VS + ch * 16, mine);
+            st_global_32B(p.hs + pair_tile(c_next, lv) + (size_t)row * 64 + (vs & 1) * gtc::VS + ch * 16, mine);
         }
         ts_state.store(aSt + lv * gtc::LV_BYTES, mine);
     };
@@ -481,6 +483,7 @@ __global__ void __launch_bounds__(gtc::NTHREADS, 1) gdn_scan_bwd_tc_kernel(const
     const int b = blockIdx.x / (nvs * p.H);
     const int nlev = p.NLEV, NT = p.NT;
     const uint32_t lev_mask = (1u << nlev) - 1u;
+    auto pair_tile = [&](int c, int lv) -> size_t { return ((((size_t)(blockIdx.x >> 1)) * NT + c) * nlev + lv) * (size_t)(gtc::KD * 64); };
 
     if (tid == 0) {
 #pragma unroll
@@ -672,7 +675,7 @@ __global__ void __launch_bounds__(gtc::NTHREADS, 1) gdn_scan_bwd_tc_kernel(const
                 uint32_t mine[8];
 #pragma unroll
                 for (int j = 0; j < 8; ++j) mine[j] = pack_bf16(v[2 * j], v[2 * j + 1]);
-                st_global_32B(p.dhs + (((size_t)blockIdx.x * NT + (c - 1)) * nlev + lv) * (size_t)(gtc::KD * gtc::VS) + (size_t)row * gtc::VS + ch * 16, mine);
+                st_global_32B(p.dhs + pair_tile(c - 1, lv) + (size_t)row * 64 + (vs & 1) * gtc::VS + ch * 16, mine);
                 ts_state.store(aE + lv * gtc::LV_BYTES, mine);
             }
         }
@@ -709,7 +712,7 @@ static int launch_scan_tc(GdnParams& p, cudaStream_t stream) {
 
 // mode 0: forward (output), 1: forward that keeps the level states, 2: recomputation for the backward (states only)
 int gdn_scan_tc_dispatch(const GdnParams& p0, int mode, cudaStream_t stream) {
-    if (p0.K != gtc::KD || p0.V % gtc::VS != 0 || p0.NLEV > gtc::MAXLEV) return LLATTN_ERR_UNSUPPORTED_SHAPE;
+    if (p0.K != gtc::KD || p0.V % 64 != 0 || p0.NLEV > gtc::MAXLEV) return LLATTN_ERR_UNSUPPORTED_SHAPE;
     GdnParams p = p0;
     if (mode == 0) return launch_scan_tc<false, true>(p, stream);
     if (mode == 1) return launch_scan_tc<true, true>(p, stream);
@@ -717,7 +720,7 @@ int gdn_scan_tc_dispatch(const GdnParams& p0, int mode, cudaStream_t stream) {
 }
 
 int gdn_scan_bwd_tc_dispatch(const GdnParams& p0, cudaStream_t stream) {
-    if (p0.K != gtc::KD || p0.V % gtc::VS != 0 || p0.NLEV > gtc::MAXLEV) return LLATTN_ERR_UNSUPPORTED_SHAPE;
+    if (p0.K != gtc::KD || p0.V % 64 != 0 || p0.NLEV > gtc::MAXLEV) return LLATTN_ERR_UNSUPPORTED_SHAPE;
     GdnParams p = p0;
     int rc = gdn_tc_maps(p);
     if (rc != 0) return rc;

@@ -33,7 +33,8 @@ struct GdnParams {
     __nv_bfloat16* wk;           // (B,NT*K,H,K)  (exp(gl) - 1) I - kd^T wd per chunk (tcgen05 scans; NULL: not produced)
     // backward
     const __nv_bfloat16* d_o;    // (B,T,H,V)
-    __nv_bfloat16* hs;           // [(b,h,slice)][chunk][level][K][32]  level states read by each chunk
+    __nv_bfloat16* hs;           // level states read by each chunk: [(b,h,slice)][chunk][level][K][32] (warp-MMA kernels) or
+                                 // [(b,h,pair of slices)][chunk][level][K][64] (tcgen05 kernels); same size either way
     __nv_bfloat16* dhs;          // same layout: adjoints of the level states written by each chunk
     __nv_bfloat16* d_u;          // (B,T,H,V)
     float* d_qd;                 // (B,T,H,K)
@@ -50,7 +51,7 @@ struct GdnParams {
     int NT, NLEV;
     int* err;                    // status word (first word of the call's workspace): set by a kernel whose bounded wait ran out
     // tensor maps of the chunk matrices (tcgen05 kernels; filled by their launchers)
-    alignas(64) CUtensorMap tm_qd, tm_kd, tm_wk;
+    alignas(64) CUtensorMap tm_qd, tm_wd, tm_kd, tm_wk, tm_u, tm_do, tm_hs, tm_dhs;
 };
 
 int gdn_fwd_dispatch(const GdnParams& p, cudaStream_t stream);
@@ -60,7 +61,8 @@ int gdn_recompute_dispatch(const GdnParams& p, cudaStream_t stream);
 int gdn_scan_tc_dispatch(const GdnParams& p, int mode, cudaStream_t stream);
 int gdn_scan_bwd_tc_dispatch(const GdnParams& p, cudaStream_t stream);     // adjoint level states (d_u comes from the level-gradient kernel)
 int gdn_bwd_scan_dispatch(const GdnParams& p, cudaStream_t stream);      // adjoint level states, d_u
-int gdn_bwd_levels_dispatch(const GdnParams& p, cudaStream_t stream);    // d_qd, d_wd, d_kd, d_gl, dl (inter-chunk levels)
+int gdn_bwd_levels_dispatch(const GdnParams& p, cudaStream_t stream);    // d_qd, d_wd, d_kd, d_gl, dl (inter-chunk levels), d_u
+int gdn_bwd_levels_tc_dispatch(const GdnParams& p, cudaStream_t stream); // the same on tcgen05 (reads the [K][64] tiles of the tcgen05 scans)
 int gdn_bwd_chunk_dispatch(const GdnParams& p, cudaStream_t stream);     // dq, dk, dv, dbeta, dg, dl (intra-chunk levels)
 
 }  // namespace llattn
