@@ -44,8 +44,9 @@ struct PrepSmem {
     static constexpr size_t gc_off = au_off + 1ull * CH * LDP * 2;        // float [64] G
     static constexpr size_t be_off = gc_off + CH * 4;                     // float [64] beta
     static constexpr size_t lam_off = be_off + CH * 4;                    // float [64][8]
-    static constexpr size_t x_off = lam_off + CH * 8 * 4;                 // float [128][LDA] substitution scratch
-    static constexpr size_t total = x_off + 128ull * LDA * 4;
+    static constexpr size_t x_off = lam_off + CH * 8 * 4;                 // float [2][64][LDA] the two inverses in fp32
+    static constexpr size_t t_off = x_off + 128ull * LDA * 4;             // float [2][3][16][16] block products of the inversion
+    static constexpr size_t total = t_off + 2ull * 3 * 16 * 16 * 4;
 };
 
 // FROM_SAVED = true is the backward's recomputation: G and the two inverses are read back instead of
@@ -70,6 +71,7 @@ __global__ void __launch_bounds__(256, 1) gdn_chunk_prep_kernel(const GdnParams 
     float* sBe = reinterpret_cast<float*>(smem + SM::be_off);
     float* sLam = reinterpret_cast<float*>(smem + SM::lam_off);
     float* sX = reinterpret_cast<float*>(smem + SM::x_off);
+    float* sT = reinterpret_cast<float*>(smem + SM::t_off);
     // bf16 copies of wd and kd for the product kd^T wd; they take the place of A and A * Gamma once the
     // triangular solves are done
     static_assert(CH * LDK * 2 <= CH * LDA * 4, "the bf16 tiles fit the fp32 matrices they replace");
@@ -162,48 +164,104 @@ __global__ void __launch_bounds__(256, 1) gdn_chunk_prep_kernel(const GdnParams 
     }
     __syncthreads();
 
-    // ---- (I + A)^-1 and (I + Ag)^-1 by forward substitution: thread tid < 64 solves column tid of the
-    //      first matrix, threads 64..127 column tid-64 of the second.  x_i = [i == col] - sum_{j<i} M[i][j] x_j;
-    //      the solved part of the column lives in shared memory (one padded row per thread).
-    if (!FROM_SAVED && tid < 128) {
-        const float* M = (tid < 64) ? sA : sAg;
-        bf16* X = (tid < 64) ? sAw : sAu;
-        const int col = tid & 63;
-        // The column lives in registers: both loops are fully unrolled, so every index is static; the
-        // matrix entries are warp-wide broadcast loads.  Entries with j >= i are zero in M and x[j] is
-        // still zero there, so whole float4 groups can be used.
-        float x[CH];
+    // ---- (I + A)^-1 and (I + Ag)^-1 (unit lower triangular, fp32), blocked with 16 x 16 blocks:
+    //      diagonal blocks by forward substitution (one column per thread, 16 rows, registers), then block diagonal
+    //      by block diagonal  X_ij = -X_ii (sum_{k=j..i-1} M_ik X_kj).  The fully unrolled 64-row substitution this
+    //      replaces was 80 KB of straight-line code on a 64-step dependent chain.
+    if (!FROM_SAVED) {
+        constexpr int BS = 16, NB = CH / BS;
+        if (tid < 128) {
+            const int m = tid >> 6, col = tid & 63, bi = col / BS, cc = col % BS;
+            const float* M = (m ? sAg : sA) + (bi * BS) * LDA + bi * BS;
+            float x[BS];
 #pragma unroll
-        for (int i = 0; i < CH; ++i) x[i] = 0.f;
+            for (int i = 0; i < BS; ++i) {
+                float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
 #pragma unroll
-        for (int i = 0; i < CH; ++i) {
-            float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-            const float* Mi = M + i * LDA;
-#pragma unroll
-            for (int j4 = 0; j4 < i; j4 += 4) {
-                float4 m;      // volatile: program order is kept, so the loads of later rows are not hoisted and spilled
-                asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];\n" : "=f"(m.x), "=f"(m.y), "=f"(m.z), "=f"(m.w) : "r"(smem_u32(Mi + j4)));
-                a0 += m.x * x[j4];
-                a1 += m.y * x[j4 + 1];
-                a2 += m.z * x[j4 + 2];
-                a3 += m.w * x[j4 + 3];
+                for (int j4 = 0; j4 < i; j4 += 4) {
+                    const float4 mm = *reinterpret_cast<const float4*>(M + i * LDA + j4);   // entries with j >= i are zero
+                    a0 += mm.x * x[j4];
+                    if (j4 + 1 < i) a1 += mm.y * x[j4 + 1];
+                    if (j4 + 2 < i) a2 += mm.z * x[j4 + 2];
+                    if (j4 + 3 < i) a3 += mm.w * x[j4 + 3];
+                }
+                x[i] = ((i == cc) ? 1.f : 0.f) - ((a0 + a1) + (a2 + a3));
             }
-            const float xi = ((i == col) ? 1.f : 0.f) - ((a0 + a1) + (a2 + a3));
-            x[i] = xi;
-            const bf16 xb = __float2bfloat16(xi);
-            // volatile store: the (volatile) loads of the next row stay behind it
-            asm volatile("st.shared.b16 [%0], %1;\n" ::"r"(smem_u32(X + i * LDP + col)), "h"(*reinterpret_cast<const unsigned short*>(&xb)) : "memory");
+            float* X = sX + (m * CH + bi * BS) * LDA + col;
+#pragma unroll
+            for (int i = 0; i < BS; ++i) X[i * LDA] = x[i];
+        }
+        __syncthreads();
+#pragma unroll 1
+        for (int d = 1; d < NB; ++d) {
+            const int nb = NB - d;                 // blocks on this block diagonal, per matrix
+            // T_i = sum_{k = i-d .. i-1} M_ik X_{k, i-d}: a thread computes four adjacent columns of one row
+            for (int it = tid; it < 2 * nb * BS * 4; it += 256) {
+                const int cq = it & 3, r = (it >> 2) & 15, ib = (it >> 6) % nb, m = (it >> 6) / nb;
+                const int i = d + ib, j = i - d;
+                const float* Mrow = (m ? sAg : sA) + (i * BS + r) * LDA + j * BS;
+                const float* Xc = sX + (m * CH + j * BS) * LDA + j * BS + cq * 4;
+                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 1
+                for (int kb = 0; kb < d; ++kb) {
+#pragma unroll
+                    for (int k4 = 0; k4 < BS; k4 += 4) {
+                        const float4 mm = *reinterpret_cast<const float4*>(Mrow + kb * BS + k4);
+                        const float mv[4] = {mm.x, mm.y, mm.z, mm.w};
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const float4 xv = *reinterpret_cast<const float4*>(Xc + (kb * BS + k4 + e) * LDA);
+                            acc.x += mv[e] * xv.x;
+                            acc.y += mv[e] * xv.y;
+                            acc.z += mv[e] * xv.z;
+                            acc.w += mv[e] * xv.w;
+                        }
+                    }
+                }
+                *reinterpret_cast<float4*>(sT + ((m * 3 + ib) * BS + r) * BS + cq * 4) = acc;
+            }
+            __syncthreads();
+            // X_{i, i-d} = -X_ii T_i
+            for (int it = tid; it < 2 * nb * BS * 4; it += 256) {
+                const int cq = it & 3, r = (it >> 2) & 15, ib = (it >> 6) % nb, m = (it >> 6) / nb;
+                const int i = d + ib, j = i - d;
+                const float* Xii = sX + (m * CH + i * BS + r) * LDA + i * BS;
+                const float* T = sT + ((m * 3 + ib) * BS) * BS + cq * 4;
+                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int k4 = 0; k4 < BS; k4 += 4) {
+                    const float4 xx = *reinterpret_cast<const float4*>(Xii + k4);
+                    const float xs[4] = {xx.x, xx.y, xx.z, xx.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float4 tv = *reinterpret_cast<const float4*>(T + (k4 + e) * BS);
+                        acc.x -= xs[e] * tv.x;
+                        acc.y -= xs[e] * tv.y;
+                        acc.z -= xs[e] * tv.z;
+                        acc.w -= xs[e] * tv.w;
+                    }
+                }
+                *reinterpret_cast<float4*>(sX + (m * CH + i * BS + r) * LDA + j * BS + cq * 4) = acc;
+            }
+            __syncthreads();
+        }
+        // bf16 copies for the products below and, as whole rows (16-byte stores), for the backward
+        for (int e = tid; e < 2 * CH * (CH / 8); e += 256) {
+            const int which = e / (CH * (CH / 8)), r = (e / (CH / 8)) % CH, c8 = (e % (CH / 8)) * 8;
+            const float* X = sX + (which * CH + r) * LDA + c8;
+            uint32_t w[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                // blocks above the block diagonal were never written: they are zero
+                const bool z = (c8 / BS) > (r / BS);
+                w[q] = z ? 0u : pack_bf16(X[2 * q], X[2 * q + 1]);
+            }
+            const uint4 v4 = make_uint4(w[0], w[1], w[2], w[3]);
+            *reinterpret_cast<uint4*>((which ? sAu : sAw) + r * LDP + c8) = v4;
+            *reinterpret_cast<uint4*>((which ? p.Au : p.Aw) + (rowbase + (long)r * p.H) * CH + c8) = v4;
         }
     }
     __syncthreads();
-    if (!FROM_SAVED) {
-        // the two inverses leave for the backward as whole rows (16-byte stores)
-        for (int e = tid; e < 2 * CH * (CH / 8); e += 256) {
-            const int which = e / (CH * (CH / 8)), r = (e / (CH / 8)) % CH, c8 = (e % (CH / 8)) * 8;
-            bf16* dst = (which ? p.Au : p.Aw) + (rowbase + (long)r * p.H) * CH + c8;
-            *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>((which ? sAu : sAw) + r * LDP + c8);
-        }
-    }
 
     // ---- w = Aw (beta k) -> wd = w exp(G);  u = Au (beta v);  kd = k exp(gl - G)
     {
