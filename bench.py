@@ -302,9 +302,9 @@ def secondary_mamba2(dev, B, T, H, backward, steps, label):
             "gpu_launches": nl}
 
 
-def secondary_gdn(dev, steps):
+def secondary_gdn(dev, steps, B=4):
     from hattention_b200.gated_delta_rule_apis import chunk_h_gated_delta_rule
-    B, T, H, Dk, Dv, L = 4, 8192, 16, 128, 128, 14
+    T, H, Dk, Dv, L = 8192, 16, 128, 128, 14
     gen = torch.Generator().manual_seed(11)
     q = torch.randn(B, T, H, Dk, generator=gen).bfloat16().to(dev)
     k = torch.randn(B, T, H, Dk, generator=gen).bfloat16().to(dev)
@@ -480,6 +480,7 @@ def main():
     ap.add_argument("--timed-ms", type=float, default=1000.0,
                     help="blocks of K steps are repeated until this much device time has been measured (0: one block, "
                          "for profiler captures)")
+    ap.add_argument("--gdn-batch", type=int, default=4, help="batch of --workload gdn (4 is the benchmark configuration; profiler captures use 1)")
     ap.add_argument("--workload", default="mamba2", choices=["mamba2", "gdn", "mamba2-sp"],
                     help="mamba2 = the headline workload (other configurations ride along under `secondary`); "
                          "gdn = only the Gated DeltaNet secondary measurement (B=4 T=8192 H=16 Dk=Dv=128 L=14); mamba2-sp = Mamba-2 with one sequence split along T over the ranks (run under torchrun)")
@@ -510,7 +511,7 @@ def main():
         if not torch.cuda.is_available():
             raise SystemExit("bench.py needs a CUDA device: the hot path has no CPU fallback")
         torch.cuda.set_device(local)
-        print(json.dumps(secondary_gdn(torch.device("cuda", local), args.steps)), flush=True)
+        print(json.dumps(secondary_gdn(torch.device("cuda", local), args.steps, args.gdn_batch)), flush=True)
         return
 
     if not torch.cuda.is_available():

@@ -122,3 +122,34 @@ def test_phase_clock_stamps_of_one_pair():
             for s_, who in enumerate(("thread 0", "thread 200", "thread 96")):
                 row = d[32 * s_ + lo: 32 * s_ + lo + 16]
                 print(name, half, who, [x - d[lo] if x else None for x in row])
+
+
+def test_phase_clock_stamps_of_one_gdn_scan_chunk():
+    """Only in a library built with `make -C log-linear-attention_b200/csrc clean all EXTRA=-DLLATTN_STAMPS`: prints the
+    clock64() stamps of one chunk (chunk 37 of CTA 5) of the Gated DeltaNet forward scan: an output thread, a staging
+    thread and the MMA-issuing thread (run with -s).  Skipped for the normal build."""
+    import ctypes
+    from hattention_b200 import _lib
+    from hattention_b200 import chunkwise_hgdn as hg
+    from hattention_b200.base import HType
+    from oracle import loglinear_oracle as orc
+    lib = _lib.lib()
+    if not hasattr(lib, "llattn_debug_read_stamps_gdn"):
+        pytest.skip("library built without -DLLATTN_STAMPS")
+    dev = torch.device("cuda:0")
+    B, T, H, Dk, Dv, L = 4, 8192, 16, 128, 128, 14
+    q, k, v, b, g, l = orc.make_gdn_inputs(B, T, H, Dk, Dv, L, seed=3)
+    qn, kn = orc.gdn_layer_inputs(q, k, Dk ** -0.5)
+    qn, kn, v, b, l = (x.bfloat16().to(dev) for x in (qn, kn, v, b, l))
+    g = g.float().to(dev)
+    for _ in range(3):
+        hg.chunkwise_fwd(qn, kn, v, b, g, l, False, 2, HType.WEAK, 64, False)
+    torch.cuda.synchronize()
+    buf = (ctypes.c_longlong * 96)()
+    f = lib.llattn_debug_read_stamps_gdn
+    f.argtypes = [ctypes.c_void_p]
+    assert f(buf) == 0
+    d = list(buf)
+    t0 = min(x for x in d if x)
+    for s_, who in enumerate(("output thread 0", "staging thread 64", "MMA thread")):
+        print(who, [x - t0 if x else None for x in d[32 * s_: 32 * s_ + 16]])
