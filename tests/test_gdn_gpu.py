@@ -52,6 +52,7 @@ def test_golden_fixture_from_reference(golden_dir):
     (2, 512, 2, 128, 128, 11),      # eight chunks, three levels
     (1, 704, 1, 128, 64, 11),       # 11 chunks (not a power of two)
     (1, 1024, 2, 128, 128, 14),     # 16 chunks, spare lambda levels
+    (1, 16384, 1, 128, 64, 15),     # the longest supported sequence: 256 chunks, all eight inter-chunk levels
 ])
 def test_forward_matches_recurrence(B, T, H, Dk, Dv, L):
     q, k, v, b, g, l = orc.make_gdn_inputs(B, T, H, Dk, Dv, L, seed=T + Dv)
@@ -204,11 +205,14 @@ def test_l2norm_kernels(D):
     torch.testing.assert_close(dx.float(), gx, rtol=1e-2, atol=1e-2 * gx.abs().max().item())
 
 
-@pytest.mark.parametrize("B,T,H,Dv,L", [(1, 1408, 2, 128, 12), (2, 1024, 1, 64, 11), (1, 8192, 1, 128, 14), (1, 192, 1, 64, 9)])
+@pytest.mark.parametrize("B,T,H,Dv,L", [(1, 1408, 2, 128, 12), (2, 1024, 1, 64, 11), (1, 8192, 1, 128, 14), (1, 192, 1, 64, 9),
+                                         (1, 16384, 1, 128, 15), (1, 16320, 1, 64, 15), (1, 64, 2, 128, 7)])
 def test_tensor_core_scans_match_warp_mma_scans(B, T, H, Dv, L):
     """The tcgen05 scans over chunks against the warp-MMA kernels on the same inputs: both keep fp32 master
     states and round the same operands to bf16 (level states, u - sum wd H), so outputs and gradients agree to
-    accumulation-order level.  T = 8192 reaches all seven inter-chunk levels of the largest benchmark shape."""
+    accumulation-order level.  T = 8192 reaches all seven inter-chunk levels of the largest benchmark shape, T = 16384 the
+    eighth (the longest supported sequence: every tensor-memory slot of the scans in use), 16320 = 255 chunks ends on the
+    chunk with all eight levels live, T = 64 is a single chunk (no scan step at all)."""
     from hattention_b200 import _lib
     from hattention_b200 import chunkwise_hgdn as hg
     from hattention_b200.base import HType
@@ -237,4 +241,4 @@ def test_tensor_core_scans_match_warp_mma_scans(B, T, H, Dv, L):
         assert torch.isfinite(a).all(), key
         rel = ((a.double() - w_.double()).norm() / w_.double().norm().clamp_min(1e-30)).item()
         assert rel <= 2e-3, f"{key}: relative Frobenius difference {rel:.2e}"
-        assert_close(a.float(), w_.float(), key, rtol=2e-2, atol=2e-3)
+        assert_close(a.float(), w_.float(), key)       # single elements: this path's tolerance against the oracle
