@@ -659,7 +659,10 @@ __global__ void __launch_bounds__(256, 1) gdn_scan_kernel(const GdnParams p) {
 template <int KD, int VD, bool BWD, bool KEEP = false>
 static int launch_gdn_fwd(const GdnParams& p, cudaStream_t stream) {
     cudaError_t e;
-    {
+    if (!BWD && KD == 128 && g_use_tensor_core_path.load()) {
+        int rc = gdn_prep_tc_dispatch(p, stream);
+        if (rc != 0) return rc;
+    } else {
         auto kern = gdn_chunk_prep_kernel<KD, VD, BWD>;
         const size_t sm = PrepSmem<KD, VD>::total;
         if ((e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm)) != cudaSuccess) return (int)e;

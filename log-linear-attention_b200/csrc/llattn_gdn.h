@@ -51,12 +51,13 @@ struct GdnParams {
     int NT, NLEV;
     int* err;                    // status word (first word of the call's workspace): set by a kernel whose bounded wait ran out
     // tensor maps of the chunk matrices (tcgen05 kernels; filled by their launchers)
-    alignas(64) CUtensorMap tm_qd, tm_wd, tm_kd, tm_wk, tm_u, tm_do, tm_hs, tm_dhs;
+    alignas(64) CUtensorMap tm_q, tm_k, tm_v, tm_qd, tm_wd, tm_kd, tm_wk, tm_u, tm_do, tm_hs, tm_dhs;
 };
 
 int gdn_fwd_dispatch(const GdnParams& p, cudaStream_t stream);
 int gdn_fwd_keep_dispatch(const GdnParams& p, cudaStream_t stream);
 int gdn_recompute_dispatch(const GdnParams& p, cudaStream_t stream);
+int gdn_prep_tc_dispatch(const GdnParams& p, cudaStream_t stream);        // chunk preparation of the forward on tcgen05 (K = 128)
 // tcgen05 scans (K = 128).  mode 0: forward, 1: forward that keeps the level states, 2: recomputation (states only)
 int gdn_scan_tc_dispatch(const GdnParams& p, int mode, cudaStream_t stream);
 int gdn_scan_bwd_tc_dispatch(const GdnParams& p, cudaStream_t stream);     // adjoint level states (d_u comes from the level-gradient kernel)
