@@ -225,13 +225,24 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_hi_bwd_tc_kernel(const __g
     const uint32_t tbase = *tmem_slot;
     uint32_t phT[2] = {0, 0};
 
+    // this row's lambda of the levels read: requested one pair ahead, so that the loads' latency is not part of a pair
+    bf16 lam_next[tcs::MAXLH];
+    auto fetch_lambda = [&](int pl) {
+        const long t0 = (long)(r * SEG) * CH + (long)pl * tc::PT;
+        const bf16* lrow = p.l + (((long)b * p.T + t0 + row) * p.H + h) * p.L + INTRA_LEVELS + MLOW;
+#pragma unroll
+        for (int i = 0; i < tcs::MAXLH; ++i)
+            if (i < nl) lam_next[i] = lrow[lev[i]];
+    };
+    fetch_lambda(0);
+
     for (int pl = 0; pl < npairs; ++pl) {
         const long t0 = (long)(r * SEG) * CH + (long)pl * tc::PT;
         const float sc = fexp(sGs[pl * tc::PT + row]);          // exp(G_i) from the segment start
-        const bf16* lrow = p.l + (((long)b * p.T + t0 + row) * p.H + h) * p.L + INTRA_LEVELS + MLOW;
         float lamv[tcs::MAXLH];
 #pragma unroll
-        for (int i = 0; i < tcs::MAXLH; ++i) lamv[i] = (i < nl) ? __bfloat162float(lrow[lev[i]]) : 0.f;
+        for (int i = 0; i < tcs::MAXLH; ++i) lamv[i] = (i < nl) ? __bfloat162float(lam_next[i]) : 0.f;
+        if (pl + 1 < npairs) fetch_lambda(pl + 1);
         umma::mbar_wait(full_do, pl & 1, abort_flag);
         uint4 dox[4];
 #pragma unroll
@@ -284,19 +295,20 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_hi_bwd_tc_kernel(const __g
         bar_work();                                  // scaled copies written; second batch may start
         umma::fence_after_sync();
         // ---- dlambda out, reader totals Z per chunk, q.dq contribution
-        if (ch == 0) {
+        {
+            // the two warps of a lane quarter take alternate levels
             float* gdl = p.dl + (((long)b * p.T + t0 + row) * p.H + h) * p.L + INTRA_LEVELS + MLOW;
             float wsum = 0.f;
-            for (int i = 0; i < nl; ++i) {
+            for (int i = ch; i < nl; i += 2) {
                 const float dlv = sDL[row * NDLH + i] + sDL[(128 + row) * NDLH + i];
                 gdl[lev[i]] = dlv;
                 float z = lamv[i] * dlv;
                 wsum += z;
 #pragma unroll
                 for (int d = 16; d > 0; d >>= 1) z += __shfl_xor_sync(0xffffffffu, z, d);
-                if (lane == 0) sTot[SEG + 1 + warp * tcs::MAXLH + i] = z;      // per 32-row block
+                if (lane == 0) sTot[SEG + 1 + rb * tcs::MAXLH + i] = z;        // per 32-row block
             }
-            red_add_f32(p.wq + ((long)b * p.T + t0 + row) * p.H + h, wsum);
+            if (ch < nl) red_add_f32(p.wq + ((long)b * p.T + t0 + row) * p.H + h, wsum);
         }
         umma::mbar_wait(barB, pl & 1, abort_flag);
         umma::fence_after_sync();

@@ -153,3 +153,12 @@ def test_phase_clock_stamps_of_one_gdn_scan_chunk():
     t0 = min(x for x in d if x)
     for s_, who in enumerate(("output thread 0", "staging thread 64", "MMA thread")):
         print(who, [x - t0 if x else None for x in d[32 * s_: 32 * s_ + 16]])
+    # the chunk preparation kernel of the same forward: item 3 of CTA 5, threads 0 (lanes 0..63) and 64 (lanes 64..127);
+    # the second half of each row holds the stamps inside the triangular inverses
+    f = lib.llattn_debug_read_stamps_gdn_prep
+    f.argtypes = [ctypes.c_void_p]
+    assert f(buf) == 0
+    d = list(buf)
+    t0 = min(x for x in d if x)
+    for s_, who in enumerate(("preparation, thread 0", "preparation, thread 64")):
+        print(who, [x - t0 if x else None for x in d[32 * s_: 32 * s_ + 32]])
