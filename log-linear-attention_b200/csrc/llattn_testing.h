@@ -17,6 +17,15 @@ void llattn_testing_use_tensor_core_path(int enabled);
  * kernel returns.  Lets a test see the give-up path without a hung GPU.  spin_limit is clamped to [1, 2^20]. */
 int llattn_selftest_wait_timeout(int spin_limit, int* status_dev, void* stream);
 
+/* Cycles of `reps` executions of one element-wise phase of the kernels (the fp32 32 x 32 x 32 block product of the
+ * triangular inverses, 256 threads, operands in shared memory, a 256-thread barrier after each).  `copies` (1 or 64) separate
+ * copies of the phase's code (about 2.3 KB each) are executed per repetition, which sets the instruction footprint of the loop
+ * body; `spin_warps` (0..4) further warps of the CTA poll meanwhile; `env` adds features of the production kernels' environment:
+ * bit 0 operands inside a 160 KB dynamic shared-memory allocation, bit 1 all 512 tensor-memory columns held, bit 2 the polling
+ * thread of warp 8 uses mbarrier.try_wait (needs spin_warps >= 1).  cycles[0] receives clock64() ticks for reps x copies
+ * phases; sink takes 384 floats. */
+int llattn_selftest_ew_cycles(int reps, int spin_warps, int copies, int env, long long* cycles, float* sink, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -22,6 +22,11 @@ __device__ __forceinline__ uint32_t smem_addr(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
 
+// First 1024-byte boundary inside a dynamic shared-memory array, formed by pointer arithmetic on the array itself.
+__device__ __forceinline__ unsigned char* align_1024(unsigned char* shared_array) {
+    return shared_array + ((1024u - (smem_addr(shared_array) & 1023u)) & 1023u);
+}
+
 // byte offset of element (row, col) inside a tile of `rows` rows stored as 64-column panels
 __device__ __forceinline__ uint32_t tile_offset(int row, int col, int rows) {
     const int panel = col >> 6, c = col & 63;

@@ -212,3 +212,119 @@ extern "C" int llattn_selftest_wait_timeout(int spin_limit, int* status_dev, voi
     llattn::wait_timeout_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(limit, status_dev); LLATTN_LAUNCHED();
     return (int)cudaGetLastError();
 }
+
+// ---- element-wise phase micro-benchmark: the fp32 block product of the triangular inverses (256 threads, each one row x
+// eight columns of a 32 x 32 x 32 product from shared memory), timed with clock64() around `reps` executions of COPIES copies
+// of its code.  (The operand pointers are chosen at run time between a static and a dynamic allocation, so the compiler cannot
+// drop the stores of the results as dead, which it does when they go to a static array nothing reads.)  `env` adds features of the production kernels' environment one at a time:
+//   bit 0: the operands sit in a 160 KB dynamic shared-memory allocation (200 KB with the static arrays)
+//   bit 1: the CTA holds all 512 tensor-memory columns meanwhile
+//   bit 2: one thread of warp 8 polls an mbarrier with try_wait (as the MMA-issuing thread does) instead of a plain flag
+//   `spin_warps` (0..4) warps beyond the eight working ones poll while the loop runs.
+namespace llattn {
+template <int COPIES>
+__global__ void __launch_bounds__(384, 1) ew_product_cycles_kernel(int reps, int spin_warps, int env, long long* __restrict__ cycles,
+                                                                   float* __restrict__ sink) {
+    constexpr int LDA = 68, BS = 32;
+    extern __shared__ unsigned char dyn_raw[];
+    __shared__ float stA[64 * LDA], stX[64 * LDA], stT[32 * 32];
+    __shared__ volatile int flag;
+    __shared__ uint64_t bar;
+    __shared__ uint32_t tmem_slot;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    float *sA = stA, *sX = stX, *sT = stT;
+    if (env & 1) {
+        unsigned char* dyn = umma::align_1024(dyn_raw);
+        sA = reinterpret_cast<float*>(dyn + 65536);
+        sX = reinterpret_cast<float*>(dyn + 102400);
+        sT = reinterpret_cast<float*>(dyn + 102400 + 128 * LDA * 4);
+    }
+    for (int e = tid; e < 64 * LDA; e += 384) {
+        sA[e] = 0.001f * (e % 97);
+        sX[e] = 0.002f * (e % 89);
+    }
+    if (tid == 0) {
+        flag = 0;
+        umma::mbar_init(&bar, 1);
+        umma::fence_mbar_init();
+    }
+    if ((env & 2) && warp == 8) umma::tmem_alloc(&tmem_slot, 512);
+    __syncthreads();
+    if (warp >= 8) {
+        if (warp - 8 < spin_warps) {
+            if ((env & 4) && warp == 8) {
+                if (lane == 0) umma::mbar_wait(&bar, 0);                     // bounded; completed when the timed loop ends
+            } else {
+                for (unsigned it = 0; it < (1u << 24) && flag == 0; ++it) {  // bounded: the flag is set when the timed loop ends
+                }
+            }
+        }
+        if ((env & 2) && warp == 8) {
+            for (unsigned it = 0; it < (1u << 24) && flag == 0; ++it) {
+            }
+            __syncwarp();
+            umma::tmem_dealloc(tmem_slot, 512);
+        }
+        return;
+    }
+    float total = 0.f;
+    asm volatile("bar.sync 2, 256;\n" ::: "memory");
+    const long long t0 = clock64();
+    for (int rep = 0; rep < reps; ++rep) {
+#pragma unroll
+        for (int copy = 0; copy < COPIES; ++copy) {
+            const int cq = (tid + copy) & 3, r = (tid >> 2) & 31, m = tid >> 7;
+            const float* Mrow = sA + (m * BS + r) * LDA;
+            const float* Xc = sX + cq * 8;
+            float acc[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+#pragma unroll
+            for (int k4 = 0; k4 < BS; k4 += 4) {
+                const float4 mm = *reinterpret_cast<const float4*>(Mrow + k4);
+                const float mv[4] = {mm.x, mm.y, mm.z, mm.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float4 x0 = *reinterpret_cast<const float4*>(Xc + (k4 + e) * LDA);
+                    const float4 x1 = *reinterpret_cast<const float4*>(Xc + (k4 + e) * LDA + 4);
+                    acc[0] += mv[e] * x0.x; acc[1] += mv[e] * x0.y; acc[2] += mv[e] * x0.z; acc[3] += mv[e] * x0.w;
+                    acc[4] += mv[e] * x1.x; acc[5] += mv[e] * x1.y; acc[6] += mv[e] * x1.z; acc[7] += mv[e] * x1.w;
+                }
+            }
+            float* T = sT + (r * BS + cq * 8) % (32 * 32 - 8);
+            *reinterpret_cast<float4*>(T) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+            *reinterpret_cast<float4*>(T + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
+            total += acc[0] + acc[7];
+            asm volatile("bar.sync 2, 256;\n" ::: "memory");
+        }
+    }
+    const long long t1 = clock64();
+    if (tid == 0) {
+        cycles[0] = t1 - t0;
+        flag = 1;
+        asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(umma::smem_addr(&bar)) : "memory");
+    }
+    sink[tid] = total;
+}
+}  // namespace llattn
+
+extern "C" int llattn_selftest_ew_cycles(int reps, int spin_warps, int copies, int env, long long* cycles, float* sink, void* stream) {
+    if (!cycles || !sink || reps < 1 || reps > 4096 || spin_warps < 0 || spin_warps > 4 || env < 0 || env > 7) return LLATTN_ERR_UNSUPPORTED_SHAPE;
+    if ((env & 4) && spin_warps < 1) return LLATTN_ERR_UNSUPPORTED_SHAPE;
+    cudaStream_t st = (cudaStream_t)stream;
+    const size_t sm = (env & 1) ? 160 * 1024 + 1024 : 0;
+    cudaError_t e;
+#define LLATTN_EW_CASE(C)                                                                                                     \
+    if (copies == C) {                                                                                                        \
+        if ((e = cudaFuncSetAttribute(llattn::ew_product_cycles_kernel<C>, cudaFuncAttributeMaxDynamicSharedMemorySize,      \
+                                      160 * 1024 + 1024)) != cudaSuccess)                                                     \
+            return (int)e;                                                                                                    \
+        llattn::ew_product_cycles_kernel<C><<<1, 384, sm, st>>>(reps, spin_warps, env, cycles, sink);                         \
+        LLATTN_LAUNCHED();                                                                                                    \
+        return (int)cudaGetLastError();                                                                                       \
+    }
+    LLATTN_EW_CASE(1)
+    LLATTN_EW_CASE(64)
+#undef LLATTN_EW_CASE
+    return LLATTN_ERR_UNSUPPORTED_SHAPE;
+}

@@ -162,3 +162,34 @@ def test_phase_clock_stamps_of_one_gdn_scan_chunk():
     t0 = min(x for x in d if x)
     for s_, who in enumerate(("preparation, thread 0", "preparation, thread 64")):
         print(who, [x - t0 if x else None for x in d[32 * s_: 32 * s_ + 32]])
+
+
+def test_elementwise_phase_cycles():
+    """Cycles of one element-wise phase in isolation (the fp32 block product of the triangular inverses: 256 threads, 72
+    16-byte shared-memory loads and 256 FMAs per thread, one 256-thread barrier) as a function of the instruction footprint of
+    the loop body around it (1 or 64 separate copies of the phase's code: 4 KB to 150 KB) and of features of the production
+    kernels' environment (large dynamic shared memory, tensor memory held, a thread polling an mbarrier).  Prints the figures
+    (run with -s).  Measured: 2.31 k cycles in every variant, the same as inside the preparation kernel: the phase is bound by
+    shared-memory transactions (a 16-byte load costs four cycles per warp whatever the address pattern: 8 warps x 72 loads x
+    4 = 2304), not by instruction fetch, polling warps or the allocation sizes."""
+    import ctypes
+    from hattention_b200 import _lib
+    lib = _lib.lib()
+    lib.llattn_selftest_ew_cycles.restype = ctypes.c_int
+    lib.llattn_selftest_ew_cycles.argtypes = [ctypes.c_int] * 4 + [ctypes.c_void_p] * 3
+    dev = torch.device("cuda:0")
+    cyc = torch.zeros(1, dtype=torch.int64, device=dev)
+    sink = torch.zeros(384, dtype=torch.float32, device=dev)
+    for spin, copies, env in ((0, 1, 0), (4, 1, 0), (0, 64, 0), (0, 1, 1), (0, 1, 2), (1, 1, 4), (2, 64, 7)):
+        res = {}
+        for reps in (4, 36):
+            best = None
+            for _ in range(3):
+                assert lib.llattn_selftest_ew_cycles(reps, spin, copies, env, cyc.data_ptr(), sink.data_ptr(),
+                                                     torch.cuda.current_stream().cuda_stream) == 0
+                torch.cuda.synchronize()
+                best = cyc.item() if best is None else min(best, cyc.item())
+            res[reps] = best
+        per = (res[36] - res[4]) / (32 * copies)
+        print(f"polling warps {spin}, {copies:2d} copies of the code, environment bits {env}: {per:.0f} cycles per phase")
+        assert 0 < per < 4000
