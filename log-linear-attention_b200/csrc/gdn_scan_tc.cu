@@ -10,8 +10,8 @@
 // state lives in TENSOR MEMORY and the transition is one accumulating tcgen05.mma chain onto it, so the dependent
 // chain of a chunk is: bf16 copies (shared memory) --MMA--> masters --element-wise warps--> new bf16 copies.  The
 // element-wise step only converts (and, where a carry merges levels, adds a few slots); its loops over levels
-// are run-time loops over tensor-memory addresses, which keeps the kernel's code small enough to stay in the
-// instruction cache (a version with register masters and fully unrolled level loops spent its time fetching code).
+// are run-time loops over tensor-memory addresses (a version with the masters in registers, every level loop
+// unrolled and one chain of products per level took twice as long per chunk).
 // The reader products qd H_lv (output) use the same bf16 copies; they are issued behind the transition products
 // and consumed one chunk later.  The bf16 copies are kept transposed ([V column][K]) so that they are K-major B
 // operands whose rows continue from level to level: a range of levels is read by ONE chain with N = 32 x (number

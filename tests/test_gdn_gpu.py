@@ -242,3 +242,34 @@ def test_tensor_core_scans_match_warp_mma_scans(B, T, H, Dv, L):
         rel = ((a.double() - w_.double()).norm() / w_.double().norm().clamp_min(1e-30)).item()
         assert rel <= 2e-3, f"{key}: relative Frobenius difference {rel:.2e}"
         assert_close(a.float(), w_.float(), key)       # single elements: this path's tolerance against the oracle
+
+
+def test_repeated_calls_are_bit_identical():
+    """Twenty forward + backward calls on the same inputs at 128 chunks (all seven inter-chunk levels): the output and every
+    gradient that is not accumulated with atomics must come out bit for bit the same.  The tcgen05 kernels hand tiles
+    between a TMA producer, one MMA-issuing thread and eight element-wise warps through mbarriers; an ordering mistake there
+    shows up as an occasional difference between repetitions rather than as a wrong result every time."""
+    from hattention_b200 import chunkwise_hgdn as hg
+    from hattention_b200.base import HType
+    dev = torch.device("cuda:0")
+    B, T, H, Dk, Dv, L = 1, 8192, 4, 128, 128, 14
+    q, k, v, b, g, l = orc.make_gdn_inputs(B, T, H, Dk, Dv, L, seed=21)
+    scale = Dk ** -0.5
+    qn, kn = orc.gdn_layer_inputs(q, k, scale)
+    qn, kn, v, b, l = (x.bfloat16().to(dev) for x in (qn, kn, v, b, l / scale))
+    g = g.float().to(dev)
+    do = torch.randn(B, T, H, Dv, generator=torch.Generator().manual_seed(9)).bfloat16().to(dev)
+    first = None
+    for rep in range(20):
+        kept = []
+        g_cum, o, Aw, Au, _ = hg.chunkwise_fwd(qn, kn, v, b, g, l, False, 2, HType.WEAK, 64, False, keep_workspace=kept)
+        dq, dk, dv, db, dg, dl = hg.chunkwise_bwd(qn, kn, v, b, g_cum, l, Aw, Au, do, False, 2, HType.WEAK, 64, fwd_workspace=kept[0])
+        torch.cuda.synchronize()
+        cur = dict(o=o, Aw=Aw, Au=Au, dq=dq, dk=dk, dv=dv)      # d beta, dg, d lambda are accumulated with atomics in the chunk-local kernel
+        if first is None:
+            first = {k_: x.clone() for k_, x in cur.items()}
+            for k_, x in cur.items():
+                assert torch.isfinite(x.float()).all(), k_
+        else:
+            for k_, x in cur.items():
+                assert torch.equal(x, first[k_]), f"{k_} differs in repetition {rep}"
