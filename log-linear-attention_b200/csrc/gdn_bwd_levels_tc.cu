@@ -186,7 +186,6 @@ __global__ void __launch_bounds__(glt::NTHREADS, 1) gdn_bwd_levels_tc_kernel(con
             if (nsteps == 0) continue;
             if (lane == 0) {
                 ok = umma::mbar_wait(fullC, nchunk & 1, abort_flag);
-                if (ok && nchunk > 0) ok = umma::mbar_wait(accFree, (nchunk - 1) & 1, abort_flag);
                 bool first_qw = true, first_k = true;
                 // first batch of a step: [qd; wd] H and kd E into the step's result slots
                 auto issue_first = [&](int s, uint32_t gs) -> bool {
@@ -200,12 +199,21 @@ __global__ void __launch_bounds__(glt::NTHREADS, 1) gdn_bwd_levels_tc_kernel(con
                     umma::commit(&barA[tb]);
                     return true;
                 };
+#ifdef LLATTN_STAMPS
+                int nstamp = 0;
+                const int stamp_slot = (blockIdx.x == 5 && nchunk == 8) ? 2 : -1;
+#endif
                 if (ok) ok = issue_first(0, g);
                 for (int s = 0; s < nsteps && ok; ++s, ++g) {
                     const int st = g % NSTAGE, tb = g & 1;
+                    STAMP();                                 // m0 top of the step
                     if (s + 1 < nsteps) ok = issue_first(s + 1, g + 1);
+                    STAMP();                                 // m1 first batch of the next step issued
                     if (ok) ok = umma::mbar_wait(&barOp[tb], (g >> 1) & 1, abort_flag);
                     if (!ok) break;
+                    STAMP();                                 // m2 operands of this step ready
+                    // the first second batch of an item overwrites the previous item's results
+                    if (s == 0 && nchunk > 0 && !umma::mbar_wait(accFree, (nchunk - 1) & 1, abort_flag)) { ok = false; break; }
                     umma::fence_after_sync();
                     const LevStep ls = lev_step(s, c, per_half, trans, live);
                     const uint32_t aH = umma::smem_addr(sHE + st * 2 * glt::HE_BYTES), aE = aH + glt::HE_BYTES;
@@ -224,6 +232,7 @@ __global__ void __launch_bounds__(glt::NTHREADS, 1) gdn_bwd_levels_tc_kernel(con
                     }
                     umma::commit(&barB[tb]);
                     umma::commit(&empty[st]);
+                    STAMP();                                 // m3 second batch issued
                 }
             }
             ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
@@ -249,6 +258,22 @@ __global__ void __launch_bounds__(glt::NTHREADS, 1) gdn_bwd_levels_tc_kernel(con
     const uint32_t tbase = *tmem_slot;
     uint32_t g = 0, nchunk = 0;
     bool alive = true;
+
+    // lambda of an item's inter-chunk levels is requested one item ahead (a few values per thread) so that the loads'
+    // latency is covered by the previous item's steps
+    constexpr int LAMQ = (CH * glt::LSTRIDE + 255) / 256;
+    __nv_bfloat16 lam_next[LAMQ];
+    auto fetch_lambda = [&](int item) {
+        const int h = item % p.H, c = (item / p.H) % NT, b = item / (p.H * NT);
+        const long rowbase = ((long)b * p.T + (long)c * CH) * p.H + h;
+#pragma unroll
+        for (int q = 0; q < LAMQ; ++q) {
+            const int e = tid + q * 256;
+            const int r = e / glt::LSTRIDE, lv = e - r * glt::LSTRIDE;
+            lam_next[q] = (e < CH * glt::LSTRIDE && lv < nlev) ? p.l[(rowbase + (long)r * p.H) * p.L + INTRA_LEVELS + lv] : __float2bfloat16(0.f);
+        }
+    };
+    if ((int)blockIdx.x < nitems) fetch_lambda(blockIdx.x);
 
     for (int item = blockIdx.x; item < nitems && alive; item += gridDim.x) {
         const int h = item % p.H, c = (item / p.H) % NT, b = item / (p.H * NT);
@@ -278,13 +303,23 @@ __global__ void __launch_bounds__(glt::NTHREADS, 1) gdn_bwd_levels_tc_kernel(con
             if (tid == 0) p.d_gl[((long)b * NT + c) * p.H + h] = 0.f;
             continue;
         }
+#ifdef LLATTN_STAMPS
+        int nstamp = 0;
+        const int stamp_slot = (blockIdx.x == 5 && nchunk == 8) ? (tid == 0 ? 0 : (tid == 64 ? 1 : -1)) : -1;
+#endif
+        STAMP();                                             // item top
         // lambda of the inter-chunk levels and the d lambda accumulators of this item
-        for (int e = tid; e < CH * glt::LSTRIDE; e += 256) {
-            const int r = e / glt::LSTRIDE, lv = e - r * glt::LSTRIDE;
-            sLam[e] = (lv < nlev) ? __bfloat162float(p.l[(rowbase + (long)r * p.H) * p.L + INTRA_LEVELS + lv]) : 0.f;
-            sDl[e] = 0.f;
-            sDl[CH * glt::LSTRIDE + e] = 0.f;
+#pragma unroll
+        for (int q = 0; q < LAMQ; ++q) {
+            const int e = tid + q * 256;
+            if (e < CH * glt::LSTRIDE) {
+                sLam[e] = __bfloat162float(lam_next[q]);
+                sDl[e] = 0.f;
+                sDl[CH * glt::LSTRIDE + e] = 0.f;
+            }
         }
+        if (item + (int)gridDim.x < nitems) fetch_lambda(item + gridDim.x);
+        if (tid == 0) tma::wait_group_read0();           // the previous item's staged results have been read
         bar_compute();
         float ddec = 0.f;
         bool any_level = false;
@@ -294,11 +329,13 @@ __global__ void __launch_bounds__(glt::NTHREADS, 1) gdn_bwd_levels_tc_kernel(con
             const unsigned char* stage = sHE + (g % NSTAGE) * 2 * glt::HE_BYTES;
             const LevStep ls = lev_step(s, c, per_half, trans, live);
             const int lv = ls.level, vh = ls.vh;
+            STAMP();                                         // e0 top of the step
             bool ok = umma::mbar_wait(&barA[st], (g >> 1) & 1, abort_flag);
             // the operand tiles of this parity were last read by the second batch of step g - 2
             if (ok && g >= 2) ok = umma::mbar_wait(&barB[st], ((g >> 1) - 1) & 1, abort_flag);
             if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
             umma::fence_after_sync();
+            STAMP();                                         // e1 first batch complete
             unsigned char* op = sOP + st * glt::OP_BYTES;
             if (lv >= 0) {
                 any_level = true;
@@ -377,6 +414,7 @@ __global__ void __launch_bounds__(glt::NTHREADS, 1) gdn_bwd_levels_tc_kernel(con
             umma::fence_async_smem();
             umma::fence_before_sync();
             asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(umma::smem_addr(&barOp[st])) : "memory");
+            STAMP();                                         // e2 operands written
         }
         if (!alive) break;
         // ---- results of the item
@@ -387,34 +425,60 @@ __global__ void __launch_bounds__(glt::NTHREADS, 1) gdn_bwd_levels_tc_kernel(con
             umma::fence_after_sync();
         }
         asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(umma::smem_addr(emptyC)) : "memory");
+        // d_qd, -d_wd, d_kd leave through shared memory: each thread writes its row's 32 floats of a 64 x 32 box (128-byte
+        // swizzled), one thread stores the six boxes of a half with bulk tensor stores.  Both halves are staged in the
+        // operand tiles of the steps, idle until the next item's first step.
+        {
+            const int row0 = b * p.T + c * CH;
 #pragma unroll
-        for (int hb = 0; hb < 2; ++hb) {
-            float t[32];
-            if (any_level) {
-                umma::tmem_ld32(umma::tmem_addr(tbase + glt::TM_QW, warp, ch * 64 + hb * 32), t);
-            } else {
-#pragma unroll
-                for (int e = 0; e < 32; ++e) t[e] = 0.f;
-            }
-            float* dst = (qrow ? gq : gw) + hb * 32;
-            const float sg = qrow ? 1.f : -1.f;
-            const bool zero_w = !qrow && !trans;     // without a transition wd has no gradient and its rows were never computed
-#pragma unroll
-            for (int e = 0; e < 32; e += 4)
-                *reinterpret_cast<float4*>(dst + e) = zero_w ? make_float4(0.f, 0.f, 0.f, 0.f) : make_float4(sg * t[e], sg * t[e + 1], sg * t[e + 2], sg * t[e + 3]);
-            if (qrow) {
-                if (trans) {
-                    umma::tmem_ld32(umma::tmem_addr(tbase + glt::TM_K, warp, ch * 64 + hb * 32), t);
+            for (int hb = 0; hb < 2; ++hb) {
+                unsigned char* stg = sNZ;
+                if (hb == 1) {
+                    if (tid == 0) tma::wait_group_read0();
+                    bar_compute();
+                }
+                float t[32];
+                const bool zero_qw = !any_level || (!qrow && !trans);   // without a transition wd has no gradient and its rows were never computed
+                if (!zero_qw) {
+                    umma::tmem_ld32(umma::tmem_addr(tbase + glt::TM_QW, warp, ch * 64 + hb * 32), t);
                 } else {
 #pragma unroll
                     for (int e = 0; e < 32; ++e) t[e] = 0.f;
                 }
+                const float sg = qrow ? 1.f : -1.f;
+                unsigned char* box = stg + ((qrow ? 0 : 2) + ch) * 8192 + i * 128;
 #pragma unroll
-                for (int e = 0; e < 32; e += 4) *reinterpret_cast<float4*>(gk + hb * 32 + e) = make_float4(t[e], t[e + 1], t[e + 2], t[e + 3]);
+                for (int j = 0; j < 8; ++j)
+                    *reinterpret_cast<float4*>(box + ((j ^ (i & 7)) << 4)) = make_float4(sg * t[4 * j], sg * t[4 * j + 1], sg * t[4 * j + 2], sg * t[4 * j + 3]);
+                if (qrow) {
+                    if (trans) {
+                        umma::tmem_ld32(umma::tmem_addr(tbase + glt::TM_K, warp, ch * 64 + hb * 32), t);
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) t[e] = 0.f;
+                    }
+                    box = stg + (4 + ch) * 8192 + i * 128;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        *reinterpret_cast<float4*>(box + ((j ^ (i & 7)) << 4)) = make_float4(t[4 * j], t[4 * j + 1], t[4 * j + 2], t[4 * j + 3]);
+                }
+                umma::fence_async_smem();
+                if (hb == 1) {
+                    umma::fence_before_sync();
+                    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(umma::smem_addr(accFree)) : "memory");
+                }
+                bar_compute();
+                if (tid == 0) {
+#pragma unroll
+                    for (int c2 = 0; c2 < 2; ++c2) {
+                        tma::store_box(&p.tm_dqd, c2 * 64 + hb * 32, h, row0, stg + c2 * 8192);
+                        tma::store_box(&p.tm_dwd, c2 * 64 + hb * 32, h, row0, stg + (2 + c2) * 8192);
+                        tma::store_box(&p.tm_dkd, c2 * 64 + hb * 32, h, row0, stg + (4 + c2) * 8192);
+                    }
+                    tma::commit_group();
+                }
             }
         }
-        umma::fence_before_sync();
-        asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(umma::smem_addr(accFree)) : "memory");
         if (!trans) {
             // the last chunk's writes reach no later chunk
             for (int e = tid; e < CH * (p.V / 8); e += 256) {
@@ -436,8 +500,10 @@ __global__ void __launch_bounds__(glt::NTHREADS, 1) gdn_bwd_levels_tc_kernel(con
             if (lv < nlev) p.dl[(rowbase + (long)r * p.H) * p.L + INTRA_LEVELS + lv] = sDl[e] + sDl[CH * glt::LSTRIDE + e];
         }
         bar_compute();                               // the tables are rewritten for the next item
+        STAMP();                                             // item end
         ++nchunk;
     }
+    if (tid == 0) tma::wait_group0();
     umma::fence_before_sync();
     bar_work();
 }
@@ -452,6 +518,9 @@ int gdn_bwd_levels_tc_dispatch(const GdnParams& p0, cudaStream_t stream) {
     if ((rc = tma::make_panel_map(&p.tm_kd, p.kd, BT, p.H, p.K, CH)) != 0) return rc;
     if ((rc = tma::make_panel_map(&p.tm_u, p.u, BT, p.H, p.V, CH)) != 0) return rc;
     if ((rc = tma::make_panel_map(&p.tm_do, p.d_o, BT, p.H, p.V, CH)) != 0) return rc;
+    if ((rc = tma::make_f32_box_map(&p.tm_dqd, p.d_qd, BT, p.H, p.K, CH)) != 0) return rc;
+    if ((rc = tma::make_f32_box_map(&p.tm_dwd, p.d_wd, BT, p.H, p.K, CH)) != 0) return rc;
+    if ((rc = tma::make_f32_box_map(&p.tm_dkd, p.d_kd, BT, p.H, p.K, CH)) != 0) return rc;
     const long tiles = (long)p.B * p.H * (p.V / 64) * p.NT * (p.NLEV > 0 ? p.NLEV : 1);
     if ((rc = tma::make_panel_map(&p.tm_hs, p.hs, tiles * glt::KD, 1, 64, glt::KD)) != 0) return rc;
     if ((rc = tma::make_panel_map(&p.tm_dhs, p.dhs, tiles * glt::KD, 1, 64, glt::KD)) != 0) return rc;
@@ -468,3 +537,9 @@ int gdn_bwd_levels_tc_dispatch(const GdnParams& p0, cudaStream_t stream) {
 }
 
 }  // namespace llattn
+
+#ifdef LLATTN_STAMPS
+extern "C" int llattn_debug_read_stamps_gdn_levels(long long* host_dst) {
+    return (int)cudaMemcpyFromSymbol(host_dst, llattn::g_stamps, sizeof(llattn::g_stamps));
+}
+#endif

@@ -51,7 +51,7 @@ struct GdnParams {
     int NT, NLEV;
     int* err;                    // status word (first word of the call's workspace): set by a kernel whose bounded wait ran out
     // tensor maps of the chunk matrices (tcgen05 kernels; filled by their launchers)
-    alignas(64) CUtensorMap tm_q, tm_k, tm_v, tm_qd, tm_wd, tm_kd, tm_wk, tm_u, tm_do, tm_hs, tm_dhs;
+    alignas(64) CUtensorMap tm_q, tm_k, tm_v, tm_qd, tm_wd, tm_kd, tm_wk, tm_u, tm_do, tm_hs, tm_dhs, tm_dqd, tm_dwd, tm_dkd;
 };
 
 int gdn_fwd_dispatch(const GdnParams& p, cudaStream_t stream);

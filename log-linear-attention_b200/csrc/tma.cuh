@@ -77,9 +77,18 @@ __device__ __forceinline__ void reduce_add_box(const CUtensorMap* map, int col0,
         ::"l"(map), "r"(col0), "r"(head), "r"(row0), "r"((uint32_t)__cvta_generic_to_shared(smem_src))
         : "memory");
 }
+// global[box] = shared[box] for one box of a map; col0 * element size must be a multiple of 16 bytes and no coordinate negative
+__device__ __forceinline__ void store_box(const CUtensorMap* map, int col0, int head, int row0, const void* smem_src) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%1, %2, %3}], [%4];\n"
+        ::"l"(map), "r"(col0), "r"(head), "r"(row0), "r"((uint32_t)__cvta_generic_to_shared(smem_src))
+        : "memory");
+}
 __device__ __forceinline__ void commit_group() { asm volatile("cp.async.bulk.commit_group;\n" ::: "memory"); }
 // the sources of every committed bulk operation of this thread have been read
 __device__ __forceinline__ void wait_group_read0() { asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory"); }
+// the sources of every committed bulk operation of this thread but the latest group have been read
+__device__ __forceinline__ void wait_group_read1() { asm volatile("cp.async.bulk.wait_group.read 1;\n" ::: "memory"); }
 // every committed bulk operation of this thread has completed
 __device__ __forceinline__ void wait_group0() { asm volatile("cp.async.bulk.wait_group 0;\n" ::: "memory"); }
 #endif
