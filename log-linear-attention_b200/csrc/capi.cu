@@ -370,6 +370,8 @@ static size_t gdn_bwd_setup(llattn::GdnParams& p, void* ws, bool kept = false) {
     p.d_kd = c.take<float>(n * p.K);
     p.d_u = c.take<__nv_bfloat16>(n * p.V);
     p.d_gl = c.take<float>((size_t)p.B * p.NT * p.H);
+    p.dqd_neg = c.take<__nv_bfloat16>(n * p.K);
+    p.d_grow = c.take<float>(n);
     return c.off;
 }
 
@@ -412,6 +414,10 @@ static int gdn_bwd_impl(const void* q, const void* k, const void* v, const void*
     if ((e = cudaMemsetAsync(p.err, 0, sizeof(int), st)) != cudaSuccess) return (int)e;
     if (!kept && (rc = llattn::gdn_recompute_dispatch(p, st)) != 0) return rc;
     if ((rc = llattn::gdn_bwd_scan_dispatch(p, st)) != 0) return rc;
+    if (!llattn::gdn_bwd_levels_writes_row_terms(p)) {
+        p.dqd_neg = nullptr;
+        p.d_grow = nullptr;
+    }
     if ((rc = llattn::gdn_bwd_levels_dispatch(p, st)) != 0) return rc;
     return llattn::gdn_bwd_chunk_dispatch(p, st);
 }

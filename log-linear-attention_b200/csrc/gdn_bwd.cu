@@ -499,6 +499,11 @@ static int launch_levels(const GdnParams& p, cudaStream_t stream) {
     return (int)cudaGetLastError();
 }
 
+// true when the kernel gdn_bwd_levels_dispatch selects also writes dqd_neg / d_grow and folds sum d_kd.kd into d_gl
+bool gdn_bwd_levels_writes_row_terms(const GdnParams& p) {
+    return p.K == 128 && g_use_tensor_core_path.load() && p.V % 64 == 0 && p.V <= 128;
+}
+
 int gdn_bwd_levels_dispatch(const GdnParams& p, cudaStream_t stream) {
     if (p.K == 128 && g_use_tensor_core_path.load()) return gdn_bwd_levels_tc_dispatch(p, stream);
     if (p.K == 128 && p.V == 128) return launch_levels<128, 128>(p, stream);

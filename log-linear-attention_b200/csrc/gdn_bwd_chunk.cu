@@ -13,6 +13,7 @@
 // Aw and Au come from the forward; d(M^-1) = -M^-T dM^-1 M^-T turns their gradients into dA.
 #include "llattn_common.cuh"
 #include "llattn_gdn.h"
+#include "tc_common.cuh"
 
 namespace llattn {
 
@@ -39,7 +40,9 @@ struct ChunkBwdSmem {
     static constexpr size_t total = f_off + (6 * CH + 2 * CH * 8 + 8) * 4;
 };
 
-template <int KD, int VD>
+// FUSED: the level-gradient kernel has already written -(d_qd exp(G)) in bf16, the per-token sums d_qd.qd + d_wd.wd - d_kd.kd and
+// the chunk total of d_kd.kd (inside d_gl); otherwise a row pass over the K-wide gradients derives them here.
+template <int KD, int VD, bool FUSED>
 __global__ void __launch_bounds__(256, 1) gdn_bwd_chunk_kernel(const GdnParams p) {
     using SM = ChunkBwdSmem<KD, VD>;
     constexpr int LDK = SM::LDK, LDV = SM::LDV, LDP = SM::LDP;
@@ -72,6 +75,11 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_chunk_kernel(const GdnParams p
     float* sMisc = sDL + CH * 8;      // [0] = sum d_kd . kd
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+#ifdef LLATTN_STAMPS
+    int nstamp = 0;
+    const int stamp_slot = (blockIdx.x == 3000 && tid == 0) ? 0 : -1;
+#endif
+    STAMP();
     const int h = blockIdx.x % p.H;
     const int c = (blockIdx.x / p.H) % p.NT;
     const int b = blockIdx.x / (p.H * p.NT);
@@ -86,64 +94,94 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_chunk_kernel(const GdnParams p
     load_tile_async<CH, VD, 256>(sDU, p.d_u + rowbase * VD, (long)p.H * VD, tid);
     load_tile_async<CH, CH, 256>(sAw, p.Aw + rowbase * CH, (long)p.H * CH, tid);
     load_tile_async<CH, CH, 256>(sAu, p.Au + rowbase * CH, (long)p.H * CH, tid);
+    if (FUSED) load_tile_async<CH, KD, 256>(sDqd, p.dqd_neg + rowbase * KD, (long)p.H * KD, tid);
     cp_async_commit();
-    if (tid < CH) {
-        sG[tid] = p.g_cum[rowbase + (long)tid * p.H];
-        sBe[tid] = __bfloat162float(p.beta[rowbase + (long)tid * p.H]);
-        sDG[tid] = 0.f;
-        sDB[tid] = 0.f;
-    }
-    for (int e = tid; e < CH * 8; e += 256) {
-        const int i = e >> 3, lv = e & 7;
-        sLam[e] = (lv < INTRA_LEVELS) ? __bfloat162float(p.l[(rowbase + (long)i * p.H) * p.L + lv]) : 0.f;
-        sDL[e] = 0.f;
+    {
+        // every small load is issued before the first shared-memory store, so their latencies overlap
+        float gv = 0.f;
+        __nv_bfloat16 bv = __float2bfloat16(0.f), lv2[2];
+        if (tid < CH) {
+            gv = __ldg(p.g_cum + rowbase + (long)tid * p.H);
+            bv = __ldg(p.beta + rowbase + (long)tid * p.H);
+        }
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const int e = tid + u * 256, i = e >> 3, lv = e & 7;
+            lv2[u] = (lv < INTRA_LEVELS) ? __ldg(p.l + (rowbase + (long)i * p.H) * p.L + lv) : __float2bfloat16(0.f);
+        }
+        float grow = 0.f;
+        if (FUSED && tid < CH) grow = __ldg(p.d_grow + rowbase + (long)tid * p.H);
+        if (tid < CH) {
+            sG[tid] = gv;
+            sBe[tid] = __bfloat162float(bv);
+            sDG[tid] = grow;
+            sDB[tid] = 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            sLam[tid + u * 256] = __bfloat162float(lv2[u]);
+            sDL[tid + u * 256] = 0.f;
+        }
     }
     if (tid == 0) sMisc[0] = 0.f;
     __syncthreads();
+    STAMP();
     if (tid < CH) {
         sEG[tid] = fexp(sG[tid]);
         sEGk[tid] = fexp(sG[CH - 1] - sG[tid]);
     }
     __syncthreads();
+    STAMP();
 
     // ---- row pass over the K-wide gradients: -(d_qd exp(G)) as a bf16 operand; the decay terms
     //      dG_i += d_qd.qd + d_wd.wd - d_kd.kd and the chunk total of d_kd.kd
-    {
+    if (!FUSED) {
         float kdsum = 0.f;
-#pragma unroll 4
-        for (int it = 0; it < CH / 8; ++it) {
-            const int i = it * 8 + warp;
-            const long off = (rowbase + (long)i * p.H) * KD + lane * 4;
-            const float4 a = *reinterpret_cast<const float4*>(p.d_qd + off);
-            const float4 bw = *reinterpret_cast<const float4*>(p.d_wd + off);
-            const float4 ck = *reinterpret_cast<const float4*>(p.d_kd + off);
-            const uint2 xq = *reinterpret_cast<const uint2*>(p.qd + off);
-            const uint2 xw = *reinterpret_cast<const uint2*>(p.wd + off);
-            const uint2 xk = *reinterpret_cast<const uint2*>(p.kd + off);
-            const __nv_bfloat162 q0 = *reinterpret_cast<const __nv_bfloat162*>(&xq.x), q1 = *reinterpret_cast<const __nv_bfloat162*>(&xq.y);
-            const __nv_bfloat162 w0 = *reinterpret_cast<const __nv_bfloat162*>(&xw.x), w1 = *reinterpret_cast<const __nv_bfloat162*>(&xw.y);
-            const __nv_bfloat162 k0 = *reinterpret_cast<const __nv_bfloat162*>(&xk.x), k1 = *reinterpret_cast<const __nv_bfloat162*>(&xk.y);
-            float dq_ = a.x * __bfloat162float(q0.x) + a.y * __bfloat162float(q0.y) + a.z * __bfloat162float(q1.x) + a.w * __bfloat162float(q1.y);
-            float dw_ = bw.x * __bfloat162float(w0.x) + bw.y * __bfloat162float(w0.y) + bw.z * __bfloat162float(w1.x) + bw.w * __bfloat162float(w1.y);
-            float dk_ = ck.x * __bfloat162float(k0.x) + ck.y * __bfloat162float(k0.y) + ck.z * __bfloat162float(k1.x) + ck.w * __bfloat162float(k1.y);
-            float r = dq_ + dw_ - dk_;
+        // four rows per batch: every load of a batch is issued before the first use, so a batch pays the load latency once
 #pragma unroll
-            for (int d = 16; d > 0; d >>= 1) {
-                r += __shfl_xor_sync(0xffffffffu, r, d);
-                dk_ += __shfl_xor_sync(0xffffffffu, dk_, d);
+        for (int bt = 0; bt < CH / 32; ++bt) {
+            float4 a[4], bw[4], ck[4];
+            uint2 xq[4], xw[4], xk[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int i = (bt * 4 + u) * 8 + warp;
+                const long off = (rowbase + (long)i * p.H) * KD + lane * 4;
+                a[u] = __ldg(reinterpret_cast<const float4*>(p.d_qd + off));
+                bw[u] = __ldg(reinterpret_cast<const float4*>(p.d_wd + off));
+                ck[u] = __ldg(reinterpret_cast<const float4*>(p.d_kd + off));
+                xq[u] = __ldg(reinterpret_cast<const uint2*>(p.qd + off));
+                xw[u] = __ldg(reinterpret_cast<const uint2*>(p.wd + off));
+                xk[u] = __ldg(reinterpret_cast<const uint2*>(p.kd + off));
             }
-            if (lane == 0) sDG[i] += r;          // one warp per row: no other writer at this point
-            kdsum += dk_;
-            const float eg = -sEG[i];
-            uint2 o;
-            o.x = pack_bf16(a.x * eg, a.y * eg);
-            o.y = pack_bf16(a.z * eg, a.w * eg);
-            *reinterpret_cast<uint2*>(sDqd + i * LDK + lane * 4) = o;
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int i = (bt * 4 + u) * 8 + warp;
+                const __nv_bfloat162 q0 = *reinterpret_cast<const __nv_bfloat162*>(&xq[u].x), q1 = *reinterpret_cast<const __nv_bfloat162*>(&xq[u].y);
+                const __nv_bfloat162 w0 = *reinterpret_cast<const __nv_bfloat162*>(&xw[u].x), w1 = *reinterpret_cast<const __nv_bfloat162*>(&xw[u].y);
+                const __nv_bfloat162 k0 = *reinterpret_cast<const __nv_bfloat162*>(&xk[u].x), k1 = *reinterpret_cast<const __nv_bfloat162*>(&xk[u].y);
+                float dq_ = a[u].x * __bfloat162float(q0.x) + a[u].y * __bfloat162float(q0.y) + a[u].z * __bfloat162float(q1.x) + a[u].w * __bfloat162float(q1.y);
+                float dw_ = bw[u].x * __bfloat162float(w0.x) + bw[u].y * __bfloat162float(w0.y) + bw[u].z * __bfloat162float(w1.x) + bw[u].w * __bfloat162float(w1.y);
+                float dk_ = ck[u].x * __bfloat162float(k0.x) + ck[u].y * __bfloat162float(k0.y) + ck[u].z * __bfloat162float(k1.x) + ck[u].w * __bfloat162float(k1.y);
+                float r = dq_ + dw_ - dk_;
+#pragma unroll
+                for (int d = 16; d > 0; d >>= 1) {
+                    r += __shfl_xor_sync(0xffffffffu, r, d);
+                    dk_ += __shfl_xor_sync(0xffffffffu, dk_, d);
+                }
+                if (lane == 0) sDG[i] += r;          // one warp per row: no other writer at this point
+                kdsum += dk_;
+                const float eg = -sEG[i];
+                uint2 o;
+                o.x = pack_bf16(a[u].x * eg, a[u].y * eg);
+                o.y = pack_bf16(a[u].z * eg, a[u].w * eg);
+                *reinterpret_cast<uint2*>(sDqd + i * LDK + lane * 4) = o;
+            }
         }
         if (lane == 0) atomicAdd(&sMisc[0], kdsum);
     }
     cp_async_wait<0>();
     __syncthreads();
+    STAMP();
 
     // ---- KK = k k^T, QK = tril(q k^T), Aw * beta_j
     {
@@ -168,6 +206,7 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_chunk_kernel(const GdnParams p
         }
     }
     __syncthreads();
+    STAMP();
 
     // ---- w = (Aw * beta_j) k ;  X = QK Aw ;  dP = do v^T
     float accX[1][4][4], accP[1][4][4];
@@ -187,6 +226,7 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_chunk_kernel(const GdnParams p
         warp_gemm<1, 2, false, false>(accP, sDo, LDV, r0, sV, LDV, cw * 32, VD, lane);
     }
     __syncthreads();                           // Aw * beta_j has been consumed: its tile becomes P
+    STAMP();
     {
         float rs[2] = {0.f, 0.f};
 #pragma unroll
@@ -242,6 +282,7 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_chunk_kernel(const GdnParams p
         }
     }
     __syncthreads();
+    STAMP();
 
     // ---- dv = P^T do + beta * (Au^T d_u) ;  dbeta_i += (Au^T d_u)_i . v_i
     {
@@ -251,6 +292,7 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_chunk_kernel(const GdnParams p
         const int c0 = cw * (VD / 2);
         warp_gemm<1, NPV, true, true>(acc, sTa, LDP, r0, sDo, LDV, c0, CH, lane);
         warp_gemm<1, NPV, true, true>(acc2, sAu, LDP, r0, sDU, LDV, c0, CH, lane);
+        STAMP();
         float rb[2] = {0.f, 0.f};
 #pragma unroll
         for (int nt = 0; nt < 2 * NPV; ++nt)
@@ -270,6 +312,7 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_chunk_kernel(const GdnParams p
             if ((lane & 3) == 0) atomicAdd(&sDB[r0 + lr + hh * 8], rb[hh]);
         }
     }
+    STAMP();
     // ---- dQK = tril(dX Aw^T - (d_qd exp(G)) w^T)
     {
         float acc[1][4][4];
@@ -285,6 +328,7 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_chunk_kernel(const GdnParams p
                     pack_bf16(j <= i ? acc[0][nt][hh * 2] : 0.f, j + 1 <= i ? acc[0][nt][hh * 2 + 1] : 0.f);
             }
     }
+    STAMP();
     // ---- dw = d_wd exp(G) - QK^T (d_qd exp(G))
     {
         float acc[1][2 * NPK][4];
@@ -309,6 +353,7 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_chunk_kernel(const GdnParams p
             }
     }
     __syncthreads();                           // dw and dQK complete; P has been consumed
+    STAMP();
     // ---- dAw = QK^T dX + (dw k^T) * beta_j   -> tile
     {
         float acc[1][4][4], acc2[1][4][4];
@@ -326,6 +371,7 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_chunk_kernel(const GdnParams p
             }
     }
     __syncthreads();                           // dAw complete; dX and QK have been consumed
+    STAMP();
     // ---- dAw Aw^T -> tile
     {
         float acc[1][4][4];
@@ -338,6 +384,7 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_chunk_kernel(const GdnParams p
                 *reinterpret_cast<uint32_t*>(sTb + (r0 + lr + hh * 8) * LDP + cw * 32 + nt * 8 + lc2) = pack_bf16(acc[0][nt][hh * 2], acc[0][nt][hh * 2 + 1]);
     }
     __syncthreads();
+    STAMP();
     // ---- dA (from Aw) = -Aw^T (dAw Aw^T) ;  d(beta k) = Aw^T dw starts the dk accumulator
     float dA1[1][4][4];
     float dk_acc[1][2 * NPK][4];
@@ -374,6 +421,7 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_chunk_kernel(const GdnParams p
             if ((lane & 3) == 0) atomicAdd(&sDB[r0 + lr + hh * 8], rb[hh]);
         }
     }
+    STAMP();
     // ---- dAu = (d_u v^T) * beta_j -> tile (the dAw tile has been consumed before the last barrier)
     {
         float acc[1][4][4];
@@ -388,6 +436,7 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_chunk_kernel(const GdnParams p
             }
     }
     __syncthreads();                           // dAu complete; (dAw Aw^T) consumed
+    STAMP();
     {
         float acc[1][4][4];
         zero_acc(acc);
@@ -399,6 +448,7 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_chunk_kernel(const GdnParams p
                 *reinterpret_cast<uint32_t*>(sTb + (r0 + lr + hh * 8) * LDP + cw * 32 + nt * 8 + lc2) = pack_bf16(acc[0][nt][hh * 2], acc[0][nt][hh * 2 + 1]);
     }
     __syncthreads();
+    STAMP();
     // ---- dAg = -Au^T (dAu Au^T);  dA = dA1 + dAg * Gamma;  decay and beta terms;  dKK = beta_i dA
     {
         float dAg[1][4][4];
@@ -451,6 +501,7 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_chunk_kernel(const GdnParams p
         }
     }
     __syncthreads();                           // dKK complete (in the QK tile)
+    STAMP();
     // ---- dq = d_qd exp(G) + dQK k ;  dk += dQK^T q + (dKK + dKK^T) k
     {
         const int c0 = cw * (KD / 2);
@@ -463,6 +514,7 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_chunk_kernel(const GdnParams p
             for (int hh = 0; hh < 2; ++hh)
                 pre[nt][hh] = *reinterpret_cast<const float2*>(p.d_qd + (rowbase + (long)(r0 + lr + hh * 8) * p.H) * KD + c0 + nt * 8 + lc2);
         warp_gemm<1, NPK, false, true>(acc, sDQK, LDP, r0, sK, LDK, c0, CH, lane);
+        STAMP();
 #pragma unroll
         for (int nt = 0; nt < 2 * NPK; ++nt)
 #pragma unroll
@@ -473,9 +525,11 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_chunk_kernel(const GdnParams p
                 const float eg = sEG[i];
                 *reinterpret_cast<float2*>(p.dq + off) = make_float2(acc[0][nt][hh * 2] + d.x * eg, acc[0][nt][hh * 2 + 1] + d.y * eg);
             }
+        STAMP();
         warp_gemm<1, NPK, true, true>(dk_acc, sDQK, LDP, r0, sQ, LDK, c0, CH, lane);
         warp_gemm<1, NPK, false, true>(dk_acc, sQK, LDP, r0, sK, LDK, c0, CH, lane);
         warp_gemm<1, NPK, true, true>(dk_acc, sQK, LDP, r0, sK, LDK, c0, CH, lane);
+        STAMP();
 #pragma unroll
         for (int nt = 0; nt < 2 * NPK; ++nt)
 #pragma unroll
@@ -484,6 +538,7 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_chunk_kernel(const GdnParams p
                 *reinterpret_cast<float2*>(p.dk + (rowbase + (long)i * p.H) * KD + j) = make_float2(dk_acc[0][nt][hh * 2], dk_acc[0][nt][hh * 2 + 1]);
             }
     }
+    STAMP();
     // ---- dg = reverse cumulative sum of dG (the chunk total also collects the state-decay part and
     //      the total of d_kd . kd) ;  dbeta ;  d lambda of the intra-chunk levels
     if (warp == 0) {
@@ -498,11 +553,12 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_chunk_kernel(const GdnParams p
         const int i = e >> 3, lv = e & 7;
         if (lv < INTRA_LEVELS) p.dl[(rowbase + (long)i * p.H) * p.L + lv] = sDL[e];
     }
+    STAMP();
 }
 
-template <int KD, int VD>
+template <int KD, int VD, bool FUSED>
 static int launch_chunk(const GdnParams& p, cudaStream_t stream) {
-    auto kern = gdn_bwd_chunk_kernel<KD, VD>;
+    auto kern = gdn_bwd_chunk_kernel<KD, VD, FUSED>;
     const size_t sm = ChunkBwdSmem<KD, VD>::total;
     cudaError_t e;
     if ((e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm)) != cudaSuccess) return (int)e;
@@ -511,9 +567,16 @@ static int launch_chunk(const GdnParams& p, cudaStream_t stream) {
 }
 
 int gdn_bwd_chunk_dispatch(const GdnParams& p, cudaStream_t stream) {
-    if (p.K == 128 && p.V == 128) return launch_chunk<128, 128>(p, stream);
-    if (p.K == 128 && p.V == 64) return launch_chunk<128, 64>(p, stream);
+    const bool fused = p.dqd_neg != nullptr && p.d_grow != nullptr;
+    if (p.K == 128 && p.V == 128) return fused ? launch_chunk<128, 128, true>(p, stream) : launch_chunk<128, 128, false>(p, stream);
+    if (p.K == 128 && p.V == 64) return fused ? launch_chunk<128, 64, true>(p, stream) : launch_chunk<128, 64, false>(p, stream);
     return LLATTN_ERR_UNSUPPORTED_SHAPE;
 }
 
 }  // namespace llattn
+
+#ifdef LLATTN_STAMPS
+extern "C" int llattn_debug_read_stamps_gdn_chunk(long long* host_dst) {
+    return (int)cudaMemcpyFromSymbol(host_dst, llattn::g_stamps, sizeof(llattn::g_stamps));
+}
+#endif

@@ -42,8 +42,9 @@ struct LevTcSmem {
     static constexpr uint32_t op_off = nz_off + 2 * glt::NZ_BYTES;              // [2]
     static constexpr uint32_t lam_off = op_off + 2 * glt::OP_BYTES;             // float [64][LSTRIDE]
     static constexpr uint32_t dl_off = lam_off + CH * glt::LSTRIDE * 4;         // float [2][64][LSTRIDE]
-    static constexpr uint32_t red_off = dl_off + 2 * CH * glt::LSTRIDE * 4;     // float [8]
-    static constexpr uint32_t bar_off = (red_off + 64 + 7) & ~7u;
+    static constexpr uint32_t red_off = dl_off + 2 * CH * glt::LSTRIDE * 4;     // float [16]
+    static constexpr uint32_t rowt_off = red_off + 64;                          // float [4][64]: row terms of the decay gradient
+    static constexpr uint32_t bar_off = (rowt_off + 4 * CH * 4 + 7) & ~7u;
     static constexpr uint32_t total = bar_off + 256 + 1024;
 };
 static_assert(LevTcSmem::total <= 232448, "shared memory of one CTA");
@@ -81,6 +82,7 @@ __global__ void __launch_bounds__(glt::NTHREADS, 1) gdn_bwd_levels_tc_kernel(con
     float* sLam = reinterpret_cast<float*>(smem + SM::lam_off);
     float* sDl = reinterpret_cast<float*>(smem + SM::dl_off);
     float* sRed = reinterpret_cast<float*>(smem + SM::red_off);
+    float* sRowT = reinterpret_cast<float*>(smem + SM::rowt_off);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SM::bar_off);
     uint64_t* fullC = bars + 0;      // chunk tiles (qd, wd, kd, u, do) landed
     uint64_t* emptyC = bars + 1;     // every product of the item is complete and the element-wise warps are done with do (256 arrivals)
@@ -258,6 +260,7 @@ __global__ void __launch_bounds__(glt::NTHREADS, 1) gdn_bwd_levels_tc_kernel(con
     const uint32_t tbase = *tmem_slot;
     uint32_t g = 0, nchunk = 0;
     bool alive = true;
+    const bool fuse_rows = p.dqd_neg != nullptr && p.d_grow != nullptr;
 
     // lambda of an item's inter-chunk levels is requested one item ahead (a few values per thread) so that the loads'
     // latency is covered by the previous item's steps
@@ -301,6 +304,14 @@ __global__ void __launch_bounds__(glt::NTHREADS, 1) gdn_bwd_levels_tc_kernel(con
                 *reinterpret_cast<uint4*>(p.d_u + (rowbase + (long)r * p.H) * p.V + c8) = make_uint4(0u, 0u, 0u, 0u);
             }
             if (tid == 0) p.d_gl[((long)b * NT + c) * p.H + h] = 0.f;
+            if (fuse_rows) {
+                if (tid < CH) p.d_grow[rowbase + (long)tid * p.H] = 0.f;
+                if (qrow) {
+#pragma unroll
+                    for (int e = 0; e < 64; e += 8)
+                        *reinterpret_cast<uint4*>(p.dqd_neg + (rowbase + (long)i * p.H) * glt::KD + ch * 64 + e) = make_uint4(0u, 0u, 0u, 0u);
+                }
+            }
             continue;
         }
 #ifdef LLATTN_STAMPS
@@ -319,6 +330,10 @@ __global__ void __launch_bounds__(glt::NTHREADS, 1) gdn_bwd_levels_tc_kernel(con
             }
         }
         if (item + (int)gridDim.x < nitems) fetch_lambda(item + gridDim.x);
+        // cumulative gates used by the item's results: requested now, used after the last step
+        float g_row = 0.f, g_last = 0.f;
+        if (fuse_rows && qrow) g_row = __ldg(p.g_cum + rowbase + (long)i * p.H);
+        if (tid == 0) g_last = __ldg(p.g_cum + rowbase + (long)(CH - 1) * p.H);
         if (tid == 0) tma::wait_group_read0();           // the previous item's staged results have been read
         bar_compute();
         float ddec = 0.f;
@@ -424,27 +439,32 @@ __global__ void __launch_bounds__(glt::NTHREADS, 1) gdn_bwd_levels_tc_kernel(con
             if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
             umma::fence_after_sync();
         }
-        asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(umma::smem_addr(emptyC)) : "memory");
+        // row terms for the chunk-local gradients (when requested), while the chunk's own qd / wd / kd tiles are still in shared
+        // memory: d_qd . qd + d_wd . wd - d_kd . kd per token, the chunk total of d_kd . kd, and -(d_qd exp(G)) in bf16
+        float rterm = 0.f, kdot = 0.f;
+        const bool zero_qw = !any_level || (!qrow && !trans);   // without a transition wd has no gradient and its rows were never computed
         // d_qd, -d_wd, d_kd leave through shared memory: each thread writes its row's 32 floats of a 64 x 32 box (128-byte
         // swizzled), one thread stores the six boxes of a half with bulk tensor stores.  Both halves are staged in the
-        // operand tiles of the steps, idle until the next item's first step.
+        // operand tiles of the steps, idle until the next item's first step.  The chunk's own tiles are released (emptyC)
+        // once the row terms have been taken from them.
         {
             const int row0 = b * p.T + c * CH;
-#pragma unroll
-            for (int hb = 0; hb < 2; ++hb) {
+            auto stage_half = [&](const int hb) {
                 unsigned char* stg = sNZ;
-                if (hb == 1) {
-                    if (tid == 0) tma::wait_group_read0();
-                    bar_compute();
-                }
+                STAMP();                                     // r0 / r3 half begins
                 float t[32];
-                const bool zero_qw = !any_level || (!qrow && !trans);   // without a transition wd has no gradient and its rows were never computed
                 if (!zero_qw) {
                     umma::tmem_ld32(umma::tmem_addr(tbase + glt::TM_QW, warp, ch * 64 + hb * 32), t);
                 } else {
 #pragma unroll
                     for (int e = 0; e < 32; ++e) t[e] = 0.f;
                 }
+                if (hb == 1) {
+                    // the first half's boxes must have been read before the staging area is rewritten
+                    if (tid == 0) tma::wait_group_read0();
+                    bar_compute();
+                }
+                STAMP();                                     // r1 / r4 staging free
                 const float sg = qrow ? 1.f : -1.f;
                 unsigned char* box = stg + ((qrow ? 0 : 2) + ch) * 8192 + i * 128;
 #pragma unroll
@@ -462,6 +482,7 @@ __global__ void __launch_bounds__(glt::NTHREADS, 1) gdn_bwd_levels_tc_kernel(con
                     for (int j = 0; j < 8; ++j)
                         *reinterpret_cast<float4*>(box + ((j ^ (i & 7)) << 4)) = make_float4(t[4 * j], t[4 * j + 1], t[4 * j + 2], t[4 * j + 3]);
                 }
+                STAMP();                                     // r2 / r5 rows staged
                 umma::fence_async_smem();
                 if (hb == 1) {
                     umma::fence_before_sync();
@@ -477,8 +498,64 @@ __global__ void __launch_bounds__(glt::NTHREADS, 1) gdn_bwd_levels_tc_kernel(con
                     }
                     tma::commit_group();
                 }
+            };
+            // the row terms are computed while the first half's boxes are being read
+            stage_half(0);
+            if (fuse_rows) {
+                const float sg = qrow ? 1.f : -1.f;
+                const float eg = -fexp(g_row);
+    #pragma unroll
+                for (int hb = 0; hb < 2; ++hb) {
+                    float t[32];
+                    if (!zero_qw) {
+                        umma::tmem_ld32(umma::tmem_addr(tbase + glt::TM_QW, warp, ch * 64 + hb * 32), t);
+                    } else {
+    #pragma unroll
+                        for (int e = 0; e < 32; ++e) t[e] = 0.f;
+                    }
+                    const unsigned char* orow = sQW + ch * (128 * 128) + row * 128;
+    #pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const uint4 x = *reinterpret_cast<const uint4*>(orow + (((hb * 4 + j) ^ (row & 7)) << 4));
+                        const uint32_t xs[4] = {x.x, x.y, x.z, x.w};
+    #pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xs[e]));
+                            rterm += sg * (t[8 * j + 2 * e] * f.x + t[8 * j + 2 * e + 1] * f.y);
+                        }
+                    }
+                    if (qrow) {
+                        __nv_bfloat16* dst = p.dqd_neg + (rowbase + (long)i * p.H) * glt::KD + ch * 64 + hb * 32;
+    #pragma unroll
+                        for (int j = 0; j < 2; ++j) {
+                            uint32_t w[8];
+    #pragma unroll
+                            for (int e = 0; e < 8; ++e) w[e] = pack_bf16(t[16 * j + 2 * e] * eg, t[16 * j + 2 * e + 1] * eg);
+                            asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};\n"
+                                         ::"l"(dst + 16 * j), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]) : "memory");
+                        }
+                        if (trans) {
+                            umma::tmem_ld32(umma::tmem_addr(tbase + glt::TM_K, warp, ch * 64 + hb * 32), t);
+                            const unsigned char* krow = sKd + ch * (CH * 128) + i * 128;
+    #pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                const uint4 x = *reinterpret_cast<const uint4*>(krow + (((hb * 4 + j) ^ (i & 7)) << 4));
+                                const uint32_t xs[4] = {x.x, x.y, x.z, x.w};
+    #pragma unroll
+                                for (int e = 0; e < 4; ++e) {
+                                    const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xs[e]));
+                                    kdot += t[8 * j + 2 * e] * f.x + t[8 * j + 2 * e + 1] * f.y;
+                                }
+                            }
+                        }
+                    }
+                }
+                sRowT[((rb >> 1) * 2 + ch) * CH + i] = rterm - kdot;   // four partial sums per token: (q | w rows) x column half
             }
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(umma::smem_addr(emptyC)) : "memory");
+            stage_half(1);
         }
+        STAMP();                                             // r6 stores issued
         if (!trans) {
             // the last chunk's writes reach no later chunk
             for (int e = tid; e < CH * (p.V / 8); e += 256) {
@@ -487,14 +564,25 @@ __global__ void __launch_bounds__(glt::NTHREADS, 1) gdn_bwd_levels_tc_kernel(con
             }
         }
 #pragma unroll
-        for (int d = 16; d > 0; d >>= 1) ddec += __shfl_xor_sync(0xffffffffu, ddec, d);
-        if (lane == 0) sRed[warp] = ddec;
+        for (int d = 16; d > 0; d >>= 1) {
+            ddec += __shfl_xor_sync(0xffffffffu, ddec, d);
+            kdot += __shfl_xor_sync(0xffffffffu, kdot, d);
+        }
+        if (lane == 0) {
+            sRed[warp] = ddec;
+            sRed[8 + warp] = kdot;
+        }
         bar_compute();
         if (tid == 0) {
-            float t = 0.f;
-            for (int w = 0; w < 8; ++w) t += sRed[w];
-            p.d_gl[((long)b * NT + c) * p.H + h] = t * fexp(p.g_cum[rowbase + (long)(CH - 1) * p.H]);
+            float t = 0.f, tk = 0.f;
+            for (int w = 0; w < 8; ++w) {
+                t += sRed[w];
+                tk += sRed[8 + w];
+            }
+            p.d_gl[((long)b * NT + c) * p.H + h] = t * fexp(g_last) + tk;
         }
+        if (fuse_rows && tid < CH)
+            p.d_grow[rowbase + (long)tid * p.H] = (sRowT[tid] + sRowT[CH + tid]) + (sRowT[2 * CH + tid] + sRowT[3 * CH + tid]);
         for (int e = tid; e < CH * glt::LSTRIDE; e += 256) {
             const int r = e / glt::LSTRIDE, lv = e - r * glt::LSTRIDE;
             if (lv < nlev) p.dl[(rowbase + (long)r * p.H) * p.L + INTRA_LEVELS + lv] = sDl[e] + sDl[CH * glt::LSTRIDE + e];

@@ -37,6 +37,9 @@ struct GdnParams {
                                  // [(b,h,pair of slices)][chunk][level][K][64] (tcgen05 kernels); same size either way
     __nv_bfloat16* dhs;          // same layout: adjoints of the level states written by each chunk
     __nv_bfloat16* d_u;          // (B,T,H,V)
+    __nv_bfloat16* dqd_neg;      // (B,T,H,K)  -(d_qd exp(G)) and
+    float* d_grow;               // (B,T,H)    d_qd . qd + d_wd . wd - d_kd . kd, written by the tcgen05 level-gradient kernel for the
+                                 //            chunk-local kernel (both null: that kernel derives them itself); d_gl then includes sum d_kd . kd
     float* d_qd;                 // (B,T,H,K)
     float* d_wd;                 // (B,T,H,K)
     float* d_kd;                 // (B,T,H,K)
@@ -54,6 +57,7 @@ struct GdnParams {
     alignas(64) CUtensorMap tm_q, tm_k, tm_v, tm_qd, tm_wd, tm_kd, tm_wk, tm_u, tm_do, tm_hs, tm_dhs, tm_dqd, tm_dwd, tm_dkd;
 };
 
+bool gdn_bwd_levels_writes_row_terms(const GdnParams& p);
 int gdn_fwd_dispatch(const GdnParams& p, cudaStream_t stream);
 int gdn_fwd_keep_dispatch(const GdnParams& p, cudaStream_t stream);
 int gdn_recompute_dispatch(const GdnParams& p, cudaStream_t stream);
