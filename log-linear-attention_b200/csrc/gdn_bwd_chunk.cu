@@ -36,8 +36,8 @@ struct ChunkBwdSmem {
     static constexpr size_t tb_off = ta_off + 1ull * CH * LDP * 2;        // dX, dAw Aw^T, dAu Au^T
     static constexpr size_t dqk_off = tb_off + 1ull * CH * LDP * 2;       // dQK
     static constexpr size_t f_off = dqk_off + 1ull * CH * LDP * 2;        // floats
-    // floats: G[64] beta[64] eG[64] eGk[64] dG[64] dB[64] lam[64][8] dL[64][8] misc[8]
-    static constexpr size_t total = f_off + (6 * CH + 2 * CH * 8 + 8) * 4;
+    // floats: G[64] beta[64] eG[64] eGk[64] dG[64] dB[64] lam[64][8] dL[64][8] misc[8] part[22][64]
+    static constexpr size_t total = f_off + (6 * CH + 2 * CH * 8 + 8 + 22 * CH) * 4;
 };
 
 // FUSED: the level-gradient kernel has already written -(d_qd exp(G)) in bf16, the per-token sums d_qd.qd + d_wd.wd - d_kd.kd and
@@ -70,14 +70,26 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_chunk_kernel(const GdnParams p
     float* sEGk = sEG + CH;
     float* sDG = sEGk + CH;
     float* sDB = sDG + CH;
-    float* sLam = sDB + CH;           // [64][8]
+    float* sLam = sDB + CH;           // [64][8]   (the dB slot itself is unused: beta gradients are summed from the partial slots)
     float* sDL = sLam + CH * 8;       // [64][8]
     float* sMisc = sDL + CH * 8;      // [0] = sum d_kd . kd
+    // partial sums of the decay (G) and beta gradients, one slot per producing warp group so that no stage needs shared-memory
+    // atomics: column sums are split over the four row blocks of warps, row sums over the two column halves
+    float* sPart = sMisc + 8;
+    float* pColG_P = sPart;                 // [4][64]  P stage
+    float* pColG_A = sPart + 4 * CH;        // [4][64]  dA stage
+    float* pColB_P = sPart + 8 * CH;        // [4][64]
+    float* pRowG_P = sPart + 12 * CH;       // [2][64]
+    float* pRowG_A = sPart + 14 * CH;       // [2][64]
+    float* pRowB_V = sPart + 16 * CH;       // [2][64]  dv stage
+    float* pRowB_K = sPart + 18 * CH;       // [2][64]  d(beta k) stage
+    float* pRowB_A = sPart + 20 * CH;       // [2][64]
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int rbw = warp & 3;               // row block of the warp
 #ifdef LLATTN_STAMPS
     int nstamp = 0;
-    const int stamp_slot = (blockIdx.x == 3000 && tid == 0) ? 0 : -1;
+    const int stamp_slot = (blockIdx.x == 3000 && (tid & 31) == 0 && (warp == 0 || warp == 7 || warp == 2)) ? (warp == 0 ? 0 : (warp == 7 ? 1 : 2)) : -1;
 #endif
     STAMP();
     const int h = blockIdx.x % p.H;
@@ -96,6 +108,13 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_chunk_kernel(const GdnParams p
     load_tile_async<CH, CH, 256>(sAu, p.Au + rowbase * CH, (long)p.H * CH, tid);
     if (FUSED) load_tile_async<CH, KD, 256>(sDqd, p.dqd_neg + rowbase * KD, (long)p.H * KD, tid);
     cp_async_commit();
+    if (FUSED) {
+        // the fp32 level gradients are read as accumulator fragments in later stages: bring their 3 x 64 rows x 512 bytes into L2 now
+        const long off = (rowbase + (long)(tid >> 2) * p.H) * KD + (tid & 3) * 32;
+        asm volatile("prefetch.global.L2 [%0];\n" ::"l"(p.d_wd + off));
+        asm volatile("prefetch.global.L2 [%0];\n" ::"l"(p.d_kd + off));
+        asm volatile("prefetch.global.L2 [%0];\n" ::"l"(p.d_qd + off));
+    }
     {
         // every small load is issued before the first shared-memory store, so their latencies overlap
         float gv = 0.f;
@@ -115,7 +134,6 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_chunk_kernel(const GdnParams p
             sG[tid] = gv;
             sBe[tid] = __bfloat162float(bv);
             sDG[tid] = grow;
-            sDB[tid] = 0.f;
         }
 #pragma unroll
         for (int u = 0; u < 2; ++u) {
@@ -236,24 +254,47 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_chunk_kernel(const GdnParams p
             for (int hh = 0; hh < 2; ++hh) {
                 const int i = r0 + lr + hh * 8;
                 const float gi = sG[i];
-                float pv[2], dx[2];
+                float pv[2] = {0.f, 0.f}, dx[2] = {0.f, 0.f};
+                // 8 x 8 block of the fragment (the same for the whole warp): above the diagonal nothing; below it every
+                // element is causal and lies in one Fenwick level, whose d lambda sum goes through the four lanes of a row
+                // to a single shared-memory atomic; the diagonal blocks keep one atomic per element.
+                const int ib = (r0 >> 3) + hh, jb = cw * 4 + nt;
+                if (jb <= ib) {
+                    const bool below = jb < ib;
+                    const int levb = 35 - __clz(ib ^ jb);
+                    float dls = 0.f, dlv[2] = {0.f, 0.f};
+                    int dll[2] = {-1, -1};
 #pragma unroll
-                for (int e = 0; e < 2; ++e) {
-                    const int j = cw * 32 + nt * 8 + lc2 + e;
-                    pv[e] = 0.f;
-                    dx[e] = 0.f;
-                    if (j <= i) {
-                        const int lev = level_of(i, j);
-                        const float gam = fexp(gi - sG[j]), bj = sBe[j], lm = sLam[i * 8 + lev];
-                        const float x = accX[0][nt][hh * 2 + e], dp = accP[0][nt][hh * 2 + e];
-                        const float xg = dp * x * gam;
-                        pv[e] = x * gam * bj * lm;
-                        dx[e] = dp * gam * bj * lm;
-                        atomicAdd(&sDL[i * 8 + lev], xg * bj);
-                        cb[e] += xg * lm;
-                        const float s = xg * bj * lm;
-                        rs[hh] += s;
-                        cs[e] += s;
+                    for (int e = 0; e < 2; ++e) {
+                        const int j = cw * 32 + nt * 8 + lc2 + e;
+                        if (below || j <= i) {
+                            const int lev = below ? levb : level_of(i, j);
+                            const float gam = fexp(gi - sG[j]), bj = sBe[j], lm = sLam[i * 8 + lev];
+                            const float x = accX[0][nt][hh * 2 + e], dp = accP[0][nt][hh * 2 + e];
+                            const float xg = dp * x * gam;
+                            pv[e] = x * gam * bj * lm;
+                            dx[e] = dp * gam * bj * lm;
+                            if (below) dls += xg * bj;
+                            else { dlv[e] = xg * bj; dll[e] = lev; }
+                            cb[e] += xg * lm;
+                            const float s = xg * bj * lm;
+                            rs[hh] += s;
+                            cs[e] += s;
+                        }
+                    }
+                    // each (row, level) sum has a single writer: the level's columns lie in one column half, and a row belongs to one warp
+                    if (below) {
+                        dls += __shfl_xor_sync(0xffffffffu, dls, 1);
+                        dls += __shfl_xor_sync(0xffffffffu, dls, 2);
+                        if ((lane & 3) == 0) sDL[i * 8 + levb] += dls;
+                    } else {
+#pragma unroll
+                        for (int lv = 0; lv < 4; ++lv) {     // the levels inside a diagonal 8 x 8 block
+                            float v = (dll[0] == lv ? dlv[0] : 0.f) + (dll[1] == lv ? dlv[1] : 0.f);
+                            v += __shfl_xor_sync(0xffffffffu, v, 1);
+                            v += __shfl_xor_sync(0xffffffffu, v, 2);
+                            if ((lane & 3) == 0) sDL[i * 8 + lv] += v;
+                        }
                     }
                 }
                 const int j0 = cw * 32 + nt * 8 + lc2;
@@ -269,8 +310,8 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_chunk_kernel(const GdnParams p
                 }
                 if (lr == 0) {
                     const int j = cw * 32 + nt * 8 + lc2 + e;
-                    atomicAdd(&sDG[j], -cs[e]);
-                    atomicAdd(&sDB[j], cb[e]);
+                    pColG_P[rbw * CH + j] = -cs[e];
+                    pColB_P[rbw * CH + j] = cb[e];
                 }
             }
         }
@@ -278,7 +319,7 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_chunk_kernel(const GdnParams p
         for (int hh = 0; hh < 2; ++hh) {
             rs[hh] += __shfl_xor_sync(0xffffffffu, rs[hh], 1);
             rs[hh] += __shfl_xor_sync(0xffffffffu, rs[hh], 2);
-            if ((lane & 3) == 0) atomicAdd(&sDG[r0 + lr + hh * 8], rs[hh]);
+            if ((lane & 3) == 0) pRowG_P[cw * CH + r0 + lr + hh * 8] = rs[hh];
         }
     }
     __syncthreads();
@@ -291,6 +332,7 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_chunk_kernel(const GdnParams p
         zero_acc(acc2);
         const int c0 = cw * (VD / 2);
         warp_gemm<1, NPV, true, true>(acc, sTa, LDP, r0, sDo, LDV, c0, CH, lane);
+        STAMP();
         warp_gemm<1, NPV, true, true>(acc2, sAu, LDP, r0, sDU, LDV, c0, CH, lane);
         STAMP();
         float rb[2] = {0.f, 0.f};
@@ -309,7 +351,7 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_chunk_kernel(const GdnParams p
         for (int hh = 0; hh < 2; ++hh) {
             rb[hh] += __shfl_xor_sync(0xffffffffu, rb[hh], 1);
             rb[hh] += __shfl_xor_sync(0xffffffffu, rb[hh], 2);
-            if ((lane & 3) == 0) atomicAdd(&sDB[r0 + lr + hh * 8], rb[hh]);
+            if ((lane & 3) == 0) pRowB_V[cw * CH + r0 + lr + hh * 8] = rb[hh];
         }
     }
     STAMP();
@@ -418,7 +460,7 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_chunk_kernel(const GdnParams p
         for (int hh = 0; hh < 2; ++hh) {
             rb[hh] += __shfl_xor_sync(0xffffffffu, rb[hh], 1);
             rb[hh] += __shfl_xor_sync(0xffffffffu, rb[hh], 2);
-            if ((lane & 3) == 0) atomicAdd(&sDB[r0 + lr + hh * 8], rb[hh]);
+            if ((lane & 3) == 0) pRowB_K[cw * CH + r0 + lr + hh * 8] = rb[hh];
         }
     }
     STAMP();
@@ -462,11 +504,11 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_chunk_kernel(const GdnParams p
             for (int hh = 0; hh < 2; ++hh) {
                 const int i = r0 + lr + hh * 8;
                 const float gi = sG[i], bi = sBe[i];
-                float dkk[2];
+                float dkk[2] = {0.f, 0.f};
+                if (cw * 4 + nt <= (r0 >> 3) + hh)       // 8 x 8 blocks above the diagonal hold no causal pair (the same for the whole warp)
 #pragma unroll
                 for (int e = 0; e < 2; ++e) {
                     const int j = cw * 32 + nt * 8 + lc2 + e;
-                    dkk[e] = 0.f;
                     if (j < i) {
                         const float gam = fexp(gi - sG[j]);
                         const float kk = __bfloat162float(sKK[i * LDP + j]);
@@ -485,7 +527,7 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_chunk_kernel(const GdnParams p
             for (int e = 0; e < 2; ++e) {
 #pragma unroll
                 for (int d = 4; d < 32; d <<= 1) cs[e] += __shfl_xor_sync(0xffffffffu, cs[e], d);
-                if (lr == 0) atomicAdd(&sDG[cw * 32 + nt * 8 + lc2 + e], -cs[e]);
+                if (lr == 0) pColG_A[rbw * CH + cw * 32 + nt * 8 + lc2 + e] = -cs[e];
             }
         }
 #pragma unroll
@@ -495,8 +537,8 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_chunk_kernel(const GdnParams p
             rb[hh] += __shfl_xor_sync(0xffffffffu, rb[hh], 1);
             rb[hh] += __shfl_xor_sync(0xffffffffu, rb[hh], 2);
             if ((lane & 3) == 0) {
-                atomicAdd(&sDG[r0 + lr + hh * 8], rs[hh]);
-                atomicAdd(&sDB[r0 + lr + hh * 8], rb[hh]);
+                pRowG_A[cw * CH + r0 + lr + hh * 8] = rs[hh];
+                pRowB_A[cw * CH + r0 + lr + hh * 8] = rb[hh];
             }
         }
     }
@@ -542,13 +584,30 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_chunk_kernel(const GdnParams p
     // ---- dg = reverse cumulative sum of dG (the chunk total also collects the state-decay part and
     //      the total of d_kd . kd) ;  dbeta ;  d lambda of the intra-chunk levels
     if (warp == 0) {
-        float x0 = sDG[CH - 1 - 2 * lane], x1 = sDG[CH - 2 - 2 * lane];   // reversed order
+        // dG of a token: the row terms plus every stage's partial sums
+        auto dg_total = [&](int i) {
+            float t = sDG[i];
+#pragma unroll
+            for (int r = 0; r < 4; ++r) t += pColG_P[r * CH + i] + pColG_A[r * CH + i];
+#pragma unroll
+            for (int r = 0; r < 2; ++r) t += pRowG_P[r * CH + i] + pRowG_A[r * CH + i];
+            return t;
+        };
+        float x0 = dg_total(CH - 1 - 2 * lane), x1 = dg_total(CH - 2 - 2 * lane);   // reversed order
         if (lane == 0) x0 += sMisc[0] + p.d_gl[((long)b * p.NT + c) * p.H + h];
         warp_cumsum64(x0, x1, lane);
         p.dg[rowbase + (long)(CH - 1 - 2 * lane) * p.H] = x0;
         p.dg[rowbase + (long)(CH - 2 - 2 * lane) * p.H] = x1;
     }
-    if (tid >= 64 && tid < 128) p.dbeta[rowbase + (long)(tid - 64) * p.H] = sDB[tid - 64];
+    if (tid >= 64 && tid < 128) {
+        const int i = tid - 64;
+        float t = 0.f;
+#pragma unroll
+        for (int r = 0; r < 4; ++r) t += pColB_P[r * CH + i];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) t += pRowB_V[r * CH + i] + pRowB_K[r * CH + i] + pRowB_A[r * CH + i];
+        p.dbeta[rowbase + (long)i * p.H] = t;
+    }
     for (int e = tid; e < CH * 8; e += 256) {
         const int i = e >> 3, lv = e & 7;
         if (lv < INTRA_LEVELS) p.dl[(rowbase + (long)i * p.H) * p.L + lv] = sDL[e];
