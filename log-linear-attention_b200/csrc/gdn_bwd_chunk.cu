@@ -99,12 +99,28 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_chunk_kernel(const GdnParams p
     const int r0 = (warp & 3) * 16, cw = warp >> 2;
     const int lr = lane >> 2, lc2 = (lane & 3) * 2;
 
+    // the small loads go first: their latency passes while the tile copies are being issued
+    float gv = 0.f;
+    __nv_bfloat16 bv = __float2bfloat16(0.f), lv2[2];
+    if (tid < CH) {
+        gv = __ldg(p.g_cum + rowbase + (long)tid * p.H);
+        bv = __ldg(p.beta + rowbase + (long)tid * p.H);
+    }
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+        const int e = tid + u * 256, i = e >> 3, lv = e & 7;
+        lv2[u] = (lv < INTRA_LEVELS) ? __ldg(p.l + (rowbase + (long)i * p.H) * p.L + lv) : __float2bfloat16(0.f);
+    }
+    float grow = 0.f;
+    if (FUSED && tid < CH) grow = __ldg(p.d_grow + rowbase + (long)tid * p.H);
+    // two groups: the first products (k k^T, q k^T, Aw * beta_j) wait for q, k, Aw only
     load_tile_async<CH, KD, 256>(sQ, p.q + rowbase * KD, (long)p.H * KD, tid);
     load_tile_async<CH, KD, 256>(sK, p.k + rowbase * KD, (long)p.H * KD, tid);
+    load_tile_async<CH, CH, 256>(sAw, p.Aw + rowbase * CH, (long)p.H * CH, tid);
+    cp_async_commit();
     load_tile_async<CH, VD, 256>(sV, p.v + rowbase * VD, (long)p.H * VD, tid);
     load_tile_async<CH, VD, 256>(sDo, p.d_o + rowbase * VD, (long)p.H * VD, tid);
     load_tile_async<CH, VD, 256>(sDU, p.d_u + rowbase * VD, (long)p.H * VD, tid);
-    load_tile_async<CH, CH, 256>(sAw, p.Aw + rowbase * CH, (long)p.H * CH, tid);
     load_tile_async<CH, CH, 256>(sAu, p.Au + rowbase * CH, (long)p.H * CH, tid);
     if (FUSED) load_tile_async<CH, KD, 256>(sDqd, p.dqd_neg + rowbase * KD, (long)p.H * KD, tid);
     cp_async_commit();
@@ -115,31 +131,15 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_chunk_kernel(const GdnParams p
         asm volatile("prefetch.global.L2 [%0];\n" ::"l"(p.d_kd + off));
         asm volatile("prefetch.global.L2 [%0];\n" ::"l"(p.d_qd + off));
     }
-    {
-        // every small load is issued before the first shared-memory store, so their latencies overlap
-        float gv = 0.f;
-        __nv_bfloat16 bv = __float2bfloat16(0.f), lv2[2];
-        if (tid < CH) {
-            gv = __ldg(p.g_cum + rowbase + (long)tid * p.H);
-            bv = __ldg(p.beta + rowbase + (long)tid * p.H);
-        }
+    if (tid < CH) {
+        sG[tid] = gv;
+        sBe[tid] = __bfloat162float(bv);
+        sDG[tid] = grow;
+    }
 #pragma unroll
-        for (int u = 0; u < 2; ++u) {
-            const int e = tid + u * 256, i = e >> 3, lv = e & 7;
-            lv2[u] = (lv < INTRA_LEVELS) ? __ldg(p.l + (rowbase + (long)i * p.H) * p.L + lv) : __float2bfloat16(0.f);
-        }
-        float grow = 0.f;
-        if (FUSED && tid < CH) grow = __ldg(p.d_grow + rowbase + (long)tid * p.H);
-        if (tid < CH) {
-            sG[tid] = gv;
-            sBe[tid] = __bfloat162float(bv);
-            sDG[tid] = grow;
-        }
-#pragma unroll
-        for (int u = 0; u < 2; ++u) {
-            sLam[tid + u * 256] = __bfloat162float(lv2[u]);
-            sDL[tid + u * 256] = 0.f;
-        }
+    for (int u = 0; u < 2; ++u) {
+        sLam[tid + u * 256] = __bfloat162float(lv2[u]);
+        sDL[tid + u * 256] = 0.f;
     }
     if (tid == 0) sMisc[0] = 0.f;
     __syncthreads();
@@ -197,7 +197,7 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_chunk_kernel(const GdnParams p
         }
         if (lane == 0) atomicAdd(&sMisc[0], kdsum);
     }
-    cp_async_wait<0>();
+    cp_async_wait<1>();
     __syncthreads();
     STAMP();
 
@@ -223,6 +223,7 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_chunk_kernel(const GdnParams p
             *reinterpret_cast<uint32_t*>(sTa + i * LDP + j) = pack_bf16(__bfloat162float(x.x) * sBe[j], __bfloat162float(x.y) * sBe[j + 1]);
         }
     }
+    cp_async_wait<0>();                        // v, do, d_u, Au (and the bf16 d_qd term) have landed
     __syncthreads();
     STAMP();
 
