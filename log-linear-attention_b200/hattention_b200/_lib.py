@@ -3,7 +3,8 @@ import ctypes
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-_LIB_PATH = os.path.join(_HERE, "libllattn.so")
+# LLATTN_LIB names another build of the same library (for instance one compiled with -DLLATTN_STAMPS for the clock-stamp tests)
+_LIB_PATH = os.environ.get("LLATTN_LIB") or os.path.join(_HERE, "libllattn.so")
 _lib = None
 
 ERRORS = {

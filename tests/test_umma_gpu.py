@@ -164,6 +164,45 @@ def test_phase_clock_stamps_of_one_gdn_scan_chunk():
         print(who, [x - t0 if x else None for x in d[32 * s_: 32 * s_ + 32]])
 
 
+def test_phase_clock_stamps_of_the_gdn_backward_kernels():
+    """Only in a library built with -DLLATTN_STAMPS (see above; LLATTN_LIB can name such a build): prints the clock64() stamps
+    of one item of the level-gradient kernel (item 8 of CTA 5: per step, top / first batch complete / operands written for
+    the element-wise threads 0 and 64, top / next first batch issued / operands ready / second batch issued for the MMA
+    thread, then the stages of the result write-out) and of one CTA of the chunk-local gradient kernel (lane 0 of warps 0,
+    7 and 2 after each barrier and between the products of the longer stages).  Run with -s."""
+    import ctypes
+    from hattention_b200 import _lib
+    from hattention_b200.gated_delta_rule_apis import chunk_h_gated_delta_rule
+    lib = _lib.lib()
+    if not hasattr(lib, "llattn_debug_read_stamps_gdn_levels"):
+        pytest.skip("library built without -DLLATTN_STAMPS")
+    dev = torch.device("cuda:0")
+    B, T, H, Dk, Dv, L = 4, 8192, 16, 128, 128, 14
+    gen = torch.Generator().manual_seed(11)
+    q = torch.randn(B, T, H, Dk, generator=gen).bfloat16().to(dev)
+    k = torch.randn(B, T, H, Dk, generator=gen).bfloat16().to(dev)
+    v = torch.randn(B, T, H, Dv, generator=gen).bfloat16().to(dev)
+    beta = torch.sigmoid(torch.randn(B, T, H, generator=gen)).bfloat16().to(dev)
+    g = torch.nn.functional.logsigmoid(torch.randn(B, T, H, generator=gen) + 3.0).float().to(dev)
+    lam = torch.nn.functional.softplus(torch.randn(B, T, H, L, generator=gen)).bfloat16().to(dev)
+    do = torch.randn(B, T, H, Dv, generator=gen).bfloat16().to(dev)
+    ins = [x.clone().requires_grad_(True) for x in (q, k, v, g, lam, beta)]
+    for _ in range(3):
+        o = chunk_h_gated_delta_rule(*ins, use_qk_l2norm_in_kernel=True)[0]
+        torch.autograd.grad(o, ins, do)
+    torch.cuda.synchronize()
+    for fn, names in (("llattn_debug_read_stamps_gdn_levels", ("levels, thread 0 (q rows)", "levels, thread 64 (w rows)", "levels, MMA thread")),
+                      ("llattn_debug_read_stamps_gdn_chunk", ("chunk-local, warp 0", "chunk-local, warp 7", "chunk-local, warp 2"))):
+        buf = (ctypes.c_longlong * 96)()
+        f = getattr(lib, fn)
+        f.argtypes = [ctypes.c_void_p]
+        assert f(buf) == 0
+        d = list(buf)
+        t0 = min(x for x in d if x)
+        for s_, who in enumerate(names):
+            print(who, [x - t0 if x else None for x in d[32 * s_: 32 * s_ + 32]])
+
+
 def test_elementwise_phase_cycles():
     """Cycles of one element-wise phase in isolation (the fp32 block product of the triangular inverses: 256 threads, 72
     16-byte shared-memory loads and 256 FMAs per thread, one 256-thread barrier) as a function of the instruction footprint of
