@@ -504,21 +504,21 @@ __global__ void __launch_bounds__(glt::NTHREADS, 1) gdn_bwd_levels_tc_kernel(con
             if (fuse_rows) {
                 const float sg = qrow ? 1.f : -1.f;
                 const float eg = -fexp(g_row);
-    #pragma unroll
+#pragma unroll
                 for (int hb = 0; hb < 2; ++hb) {
                     float t[32];
                     if (!zero_qw) {
                         umma::tmem_ld32(umma::tmem_addr(tbase + glt::TM_QW, warp, ch * 64 + hb * 32), t);
                     } else {
-    #pragma unroll
+#pragma unroll
                         for (int e = 0; e < 32; ++e) t[e] = 0.f;
                     }
                     const unsigned char* orow = sQW + ch * (128 * 128) + row * 128;
-    #pragma unroll
+#pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         const uint4 x = *reinterpret_cast<const uint4*>(orow + (((hb * 4 + j) ^ (row & 7)) << 4));
                         const uint32_t xs[4] = {x.x, x.y, x.z, x.w};
-    #pragma unroll
+#pragma unroll
                         for (int e = 0; e < 4; ++e) {
                             const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xs[e]));
                             rterm += sg * (t[8 * j + 2 * e] * f.x + t[8 * j + 2 * e + 1] * f.y);
@@ -526,22 +526,21 @@ __global__ void __launch_bounds__(glt::NTHREADS, 1) gdn_bwd_levels_tc_kernel(con
                     }
                     if (qrow) {
                         __nv_bfloat16* dst = p.dqd_neg + (rowbase + (long)i * p.H) * glt::KD + ch * 64 + hb * 32;
-    #pragma unroll
+#pragma unroll
                         for (int j = 0; j < 2; ++j) {
                             uint32_t w[8];
-    #pragma unroll
+#pragma unroll
                             for (int e = 0; e < 8; ++e) w[e] = pack_bf16(t[16 * j + 2 * e] * eg, t[16 * j + 2 * e + 1] * eg);
-                            asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};\n"
-                                         ::"l"(dst + 16 * j), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]) : "memory");
+                            st_global_32B(dst + 16 * j, w);
                         }
                         if (trans) {
                             umma::tmem_ld32(umma::tmem_addr(tbase + glt::TM_K, warp, ch * 64 + hb * 32), t);
                             const unsigned char* krow = sKd + ch * (CH * 128) + i * 128;
-    #pragma unroll
+#pragma unroll
                             for (int j = 0; j < 4; ++j) {
                                 const uint4 x = *reinterpret_cast<const uint4*>(krow + (((hb * 4 + j) ^ (i & 7)) << 4));
                                 const uint32_t xs[4] = {x.x, x.y, x.z, x.w};
-    #pragma unroll
+#pragma unroll
                                 for (int e = 0; e < 4; ++e) {
                                     const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xs[e]));
                                     kdot += t[8 * j + 2 * e] * f.x + t[8 * j + 2 * e + 1] * f.y;

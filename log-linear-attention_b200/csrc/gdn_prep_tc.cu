@@ -426,20 +426,24 @@ __global__ void __launch_bounds__(gpt::NTHREADS, 1) gdn_chunk_prep_tc_kernel(con
                 float t[32];
                 umma::tmem_ld32(umma::tmem_addr(tbase + gpt::TM_W, warp, ch * 64 + hb * 32), t);
 #pragma unroll
-                for (int cc = 0; cc < 4; ++cc) {
-                    const int col = ch * 64 + hb * 32 + cc * 8;
-                    uint32_t w[4], wd[4];
+                for (int c2 = 0; c2 < 2; ++c2) {
+                    uint32_t wd8[8];
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        w[e] = pack_bf16(t[cc * 8 + e * 2], t[cc * 8 + e * 2 + 1]);
-                        wd[e] = pack_bf16(t[cc * 8 + e * 2] * eg, t[cc * 8 + e * 2 + 1] * eg);
+                    for (int cq = 0; cq < 2; ++cq) {
+                        const int cc = c2 * 2 + cq;
+                        const int col = ch * 64 + hb * 32 + cc * 8;
+                        uint32_t w[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            w[e] = pack_bf16(t[cc * 8 + e * 2], t[cc * 8 + e * 2 + 1]);
+                            wd8[cq * 4 + e] = pack_bf16(t[cc * 8 + e * 2] * eg, t[cc * 8 + e * 2 + 1] * eg);
+                        }
+                        const uint32_t off = umma::tile_offset(i, col, CH);
+                        // beta k is consumed (batch 2 is complete): w takes its place, wd the place of beta v
+                        *reinterpret_cast<uint4*>(sR1 + off) = make_uint4(w[0], w[1], w[2], w[3]);
+                        *reinterpret_cast<uint4*>(sR1 + gpt::T64_BYTES + off) = make_uint4(wd8[cq * 4], wd8[cq * 4 + 1], wd8[cq * 4 + 2], wd8[cq * 4 + 3]);
                     }
-                    const uint32_t off = umma::tile_offset(i, col, CH);
-                    // beta k is consumed (batch 2 is complete): w takes its place, wd the place of beta v
-                    *reinterpret_cast<uint4*>(sR1 + off) = make_uint4(w[0], w[1], w[2], w[3]);
-                    const uint4 wd4 = make_uint4(wd[0], wd[1], wd[2], wd[3]);
-                    *reinterpret_cast<uint4*>(sR1 + gpt::T64_BYTES + off) = wd4;
-                    *reinterpret_cast<uint4*>(p.wd + (rowbase + (long)i * p.H) * gpt::KD + col) = wd4;
+                    st_global_32B(p.wd + (rowbase + (long)i * p.H) * gpt::KD + ch * 64 + hb * 32 + c2 * 16, wd8);
                 }
             }
         } else {
@@ -448,10 +452,12 @@ __global__ void __launch_bounds__(gpt::NTHREADS, 1) gdn_chunk_prep_tc_kernel(con
                 float t[32];
                 umma::tmem_ld32(umma::tmem_addr(tbase + gpt::TM_U, warp, ch * (VD / 2) + hb * 32), t);
 #pragma unroll
-                for (int cc = 0; cc < 4; ++cc)
-                    *reinterpret_cast<uint4*>(p.u + (rowbase + (long)i * p.H) * VD + ch * (VD / 2) + hb * 32 + cc * 8) =
-                        make_uint4(pack_bf16(t[cc * 8], t[cc * 8 + 1]), pack_bf16(t[cc * 8 + 2], t[cc * 8 + 3]),
-                                   pack_bf16(t[cc * 8 + 4], t[cc * 8 + 5]), pack_bf16(t[cc * 8 + 6], t[cc * 8 + 7]));
+                for (int c2 = 0; c2 < 2; ++c2) {
+                    uint32_t w[8];
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) w[e] = pack_bf16(t[c2 * 16 + e * 2], t[c2 * 16 + e * 2 + 1]);
+                    st_global_32B(p.u + (rowbase + (long)i * p.H) * VD + ch * (VD / 2) + hb * 32 + c2 * 16, w);
+                }
             }
         }
         umma::fence_async_smem();
@@ -472,17 +478,20 @@ __global__ void __launch_bounds__(gpt::NTHREADS, 1) gdn_chunk_prep_tc_kernel(con
                 const int col0 = ch * 64 + half * 32;
                 umma::tmem_ld32(umma::tmem_addr(tbase + gpt::TM_QW, warp, col0), t);
 #pragma unroll
-                for (int cc = 0; cc < 4; ++cc) {
-                    const int col = col0 + cc * 8;
-                    const uint4 qx = *reinterpret_cast<const uint4*>(qk + umma::tile_offset(i, col, 128));
-                    const uint32_t* xw = reinterpret_cast<const uint32_t*>(&qx);
-                    uint32_t w[4];
+                for (int c2 = 0; c2 < 2; ++c2) {
+                    uint32_t w[8];
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const __nv_bfloat162 v2 = *reinterpret_cast<const __nv_bfloat162*>(&xw[e]);
-                        w[e] = pack_bf16((__bfloat162float(v2.x) - t[cc * 8 + e * 2]) * eg, (__bfloat162float(v2.y) - t[cc * 8 + e * 2 + 1]) * eg);
+                    for (int cq = 0; cq < 2; ++cq) {
+                        const int cc = c2 * 2 + cq;
+                        const uint4 qx = *reinterpret_cast<const uint4*>(qk + umma::tile_offset(i, col0 + cc * 8, 128));
+                        const uint32_t* xw = reinterpret_cast<const uint32_t*>(&qx);
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const __nv_bfloat162 v2 = *reinterpret_cast<const __nv_bfloat162*>(&xw[e]);
+                            w[cq * 4 + e] = pack_bf16((__bfloat162float(v2.x) - t[cc * 8 + e * 2]) * eg, (__bfloat162float(v2.y) - t[cc * 8 + e * 2 + 1]) * eg);
+                        }
                     }
-                    *reinterpret_cast<uint4*>(p.qd + (rowbase + (long)i * p.H) * gpt::KD + col) = make_uint4(w[0], w[1], w[2], w[3]);
+                    st_global_32B(p.qd + (rowbase + (long)i * p.H) * gpt::KD + col0 + c2 * 16, w);
                 }
             }
             float x[16];
@@ -521,14 +530,14 @@ __global__ void __launch_bounds__(gpt::NTHREADS, 1) gdn_chunk_prep_tc_kernel(con
                 float t[32];
                 umma::tmem_ld32(umma::tmem_addr(tbase + gpt::TM_WD, warp, ch * 64 + hb * 32), t);
 #pragma unroll
-                for (int cc = 0; cc < 4; ++cc) {
-                    uint32_t w[4];
+                for (int c2 = 0; c2 < 2; ++c2) {
+                    uint32_t w[8];
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const int col = ch * 64 + hb * 32 + cc * 8 + e * 2;
-                        w[e] = pack_bf16(-t[cc * 8 + e * 2] + (col == row ? decm1 : 0.f), -t[cc * 8 + e * 2 + 1] + (col + 1 == row ? decm1 : 0.f));
+                    for (int e = 0; e < 8; ++e) {
+                        const int col = ch * 64 + hb * 32 + c2 * 16 + e * 2;
+                        w[e] = pack_bf16(-t[c2 * 16 + e * 2] + (col == row ? decm1 : 0.f), -t[c2 * 16 + e * 2 + 1] + (col + 1 == row ? decm1 : 0.f));
                     }
-                    *reinterpret_cast<uint4*>(dst + hb * 32 + cc * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+                    st_global_32B(dst + hb * 32 + c2 * 16, w);
                 }
             }
         }
@@ -546,10 +555,12 @@ __global__ void __launch_bounds__(gpt::NTHREADS, 1) gdn_chunk_prep_tc_kernel(con
             if (NC == 32) umma::tmem_ld32(umma::tmem_addr(tbase + gpt::TM_O, warp, col0), reinterpret_cast<float(&)[32]>(t));
             else umma::tmem_ld16(umma::tmem_addr(tbase + gpt::TM_O, warp, col0), reinterpret_cast<float(&)[16]>(t));
 #pragma unroll
-            for (int cc = 0; cc < NC / 8; ++cc)
-                *reinterpret_cast<uint4*>(p.o + (rowbase + (long)i * p.H) * VD + col0 + cc * 8) =
-                    make_uint4(pack_bf16(t[cc * 8], t[cc * 8 + 1]), pack_bf16(t[cc * 8 + 2], t[cc * 8 + 3]),
-                               pack_bf16(t[cc * 8 + 4], t[cc * 8 + 5]), pack_bf16(t[cc * 8 + 6], t[cc * 8 + 7]));
+            for (int c2 = 0; c2 < NC / 16; ++c2) {
+                uint32_t w[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) w[e] = pack_bf16(t[c2 * 16 + e * 2], t[c2 * 16 + e * 2 + 1]);
+                st_global_32B(p.o + (rowbase + (long)i * p.H) * VD + col0 + c2 * 16, w);
+            }
         }
         umma::fence_before_sync();
         bar_compute();                                   // the small tables are rewritten for the next item

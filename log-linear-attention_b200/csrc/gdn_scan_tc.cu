@@ -63,12 +63,6 @@ struct TransposedStore {
     }
 };
 
-// one 32-byte store (a full sector per lane; two 16-byte stores would touch every sector twice)
-__device__ __forceinline__ void st_global_32B(void* dst, const uint32_t (&w)[8]) {
-    asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};\n"
-                 ::"l"(dst), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]) : "memory");
-}
-
 __device__ __forceinline__ float lambda_of_level(uint64_t l0123, uint64_t l4567, int lv) {
     const uint64_t w = (lv < 4) ? l0123 : l4567;
     return __uint_as_float((uint32_t)((w >> ((lv & 3) * 16)) & 0xFFFFull) << 16);

@@ -70,6 +70,12 @@ __device__ __forceinline__ void release_tile_after_loads(uint64_t* bar, uint32_t
 
 __device__ __forceinline__ void bar_work() { asm volatile("bar.sync 1, 288;\n" ::: "memory"); }
 
+// one 32-byte global store (a full sector per lane; two 16-byte stores of a thread that owns a row would touch every sector twice)
+__device__ __forceinline__ void st_global_32B(void* dst, const uint32_t (&w)[8]) {
+    asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};\n"
+                 ::"l"(dst), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]) : "memory");
+}
+
 // barrier over the 8 element-wise warps only
 __device__ __forceinline__ void bar_compute() { asm volatile("bar.sync 2, 256;\n" ::: "memory"); }
 
