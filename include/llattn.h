@@ -233,6 +233,13 @@ int llattn_gdn_bwd_kept(const void* q, const void* k, const void* v, const void*
                         const void* Aw, const void* Au, const void* d_o, float* dq, float* dk, float* dv, float* dbeta,
                         float* dg, float* dlambda, const void* fwd_workspace, size_t fwd_workspace_bytes, void* workspace,
                         size_t workspace_bytes, int B, int T, int H, int K, int V, int L, void* stream);
+/* llattn_gdn_bwd_kept with dv written in bf16 (B,T,H,V), the dtype the reference's autograd function returns for bf16 v
+ * (hattention/kernel.py:226: dv.to(v)): saves the caller a conversion pass over dv.  Same workspace size. */
+int llattn_gdn_bwd_kept_bf16dv(const void* q, const void* k, const void* v, const void* beta, const float* g_cum,
+                               const void* lambda, const void* Aw, const void* Au, const void* d_o, float* dq, float* dk,
+                               void* dv_bf16, float* dbeta, float* dg, float* dlambda, const void* fwd_workspace,
+                               size_t fwd_workspace_bytes, void* workspace, size_t workspace_bytes,
+                               int B, int T, int H, int K, int V, int L, void* stream);
 
 /* Row-wise L2 normalisation of q / k and its backward, as applied around the Gated DeltaNet drivers
  * when use_qk_l2norm_in_kernel is set.  Replace fla.modules.l2norm.l2norm_fwd / l2norm_bwd with the

@@ -385,10 +385,10 @@ size_t llattn_gdn_bwd_workspace_bytes(int B, int T, int H, int K, int V, int L) 
 static int gdn_bwd_impl(const void* q, const void* k, const void* v, const void* beta, const float* g_cum, const void* lambda,
                         const void* Aw, const void* Au, const void* d_o, float* dq, float* dk, float* dv, float* dbeta, float* dg,
                         float* dlambda, const void* fwd_workspace, size_t fwd_workspace_bytes, void* workspace,
-                        size_t workspace_bytes, int B, int T, int H, int K, int V, int L, void* stream) {
+                        size_t workspace_bytes, int B, int T, int H, int K, int V, int L, void* stream, void* dv_bf16 = nullptr) {
     int rc = gdn_check(B, T, H, K, V, L);
     if (rc != 0) return rc;
-    if (!q || !k || !v || !beta || !g_cum || !lambda || !Aw || !Au || !d_o || !dq || !dk || !dv || !dbeta || !dg || !dlambda)
+    if (!q || !k || !v || !beta || !g_cum || !lambda || !Aw || !Au || !d_o || !dq || !dk || (!dv && !dv_bf16) || !dbeta || !dg || !dlambda)
         return LLATTN_ERR_NULL;
     llattn::GdnParams p = {};
     p.B = B; p.T = T; p.H = H; p.K = K; p.V = V; p.L = L;
@@ -407,7 +407,7 @@ static int gdn_bwd_impl(const void* q, const void* k, const void* v, const void*
     p.g_cum = const_cast<float*>(g_cum);
     p.Aw = (__nv_bfloat16*)const_cast<void*>(Aw); p.Au = (__nv_bfloat16*)const_cast<void*>(Au);
     p.d_o = (const __nv_bfloat16*)d_o;
-    p.dq = dq; p.dk = dk; p.dv = dv; p.dbeta = dbeta; p.dg = dg; p.dl = dlambda;
+    p.dq = dq; p.dk = dk; p.dv = dv; p.dv_bf16 = (__nv_bfloat16*)dv_bf16; p.dbeta = dbeta; p.dg = dg; p.dl = dlambda;
     cudaStream_t st = (cudaStream_t)stream;
     cudaError_t e = cudaMemsetAsync(dlambda, 0, (size_t)B * T * H * L * sizeof(float), st);
     if (e != cudaSuccess) return (int)e;
@@ -428,6 +428,15 @@ int llattn_gdn_bwd(const void* q, const void* k, const void* v, const void* beta
                    int B, int T, int H, int K, int V, int L, void* stream) {
     return gdn_bwd_impl(q, k, v, beta, g_cum, lambda, Aw, Au, d_o, dq, dk, dv, dbeta, dg, dlambda, nullptr, 0, workspace,
                         workspace_bytes, B, T, H, K, V, L, stream);
+}
+
+int llattn_gdn_bwd_kept_bf16dv(const void* q, const void* k, const void* v, const void* beta, const float* g_cum, const void* lambda,
+                               const void* Aw, const void* Au, const void* d_o, float* dq, float* dk, void* dv_bf16, float* dbeta,
+                               float* dg, float* dlambda, const void* fwd_workspace, size_t fwd_workspace_bytes, void* workspace,
+                               size_t workspace_bytes, int B, int T, int H, int K, int V, int L, void* stream) {
+    if (!fwd_workspace || !dv_bf16) return LLATTN_ERR_NULL;
+    return gdn_bwd_impl(q, k, v, beta, g_cum, lambda, Aw, Au, d_o, dq, dk, nullptr, dbeta, dg, dlambda, fwd_workspace,
+                        fwd_workspace_bytes, workspace, workspace_bytes, B, T, H, K, V, L, stream, dv_bf16);
 }
 
 size_t llattn_gdn_bwd_kept_workspace_bytes(int B, int T, int H, int K, int V, int L) {

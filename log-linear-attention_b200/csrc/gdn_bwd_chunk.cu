@@ -345,8 +345,9 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_chunk_kernel(const GdnParams p
                 const float bi = sBe[i];
                 const __nv_bfloat162 x = *reinterpret_cast<const __nv_bfloat162*>(sV + i * LDV + j);
                 rb[hh] += acc2[0][nt][hh * 2] * __bfloat162float(x.x) + acc2[0][nt][hh * 2 + 1] * __bfloat162float(x.y);
-                *reinterpret_cast<float2*>(p.dv + (rowbase + (long)i * p.H) * VD + j) =
-                    make_float2(acc[0][nt][hh * 2] + bi * acc2[0][nt][hh * 2], acc[0][nt][hh * 2 + 1] + bi * acc2[0][nt][hh * 2 + 1]);
+                const float d0 = acc[0][nt][hh * 2] + bi * acc2[0][nt][hh * 2], d1 = acc[0][nt][hh * 2 + 1] + bi * acc2[0][nt][hh * 2 + 1];
+                if (p.dv_bf16) *reinterpret_cast<uint32_t*>(p.dv_bf16 + (rowbase + (long)i * p.H) * VD + j) = pack_bf16(d0, d1);
+                else *reinterpret_cast<float2*>(p.dv + (rowbase + (long)i * p.H) * VD + j) = make_float2(d0, d1);
             }
 #pragma unroll
         for (int hh = 0; hh < 2; ++hh) {

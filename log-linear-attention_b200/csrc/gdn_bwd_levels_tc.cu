@@ -400,10 +400,12 @@ __global__ void __launch_bounds__(glt::NTHREADS, 1) gdn_bwd_levels_tc_kernel(con
                         // d_u = kd E_jc, 32 columns of this half of V
                         bf16* du = p.d_u + (rowbase + (long)i * p.H) * p.V + vh * 64 + ch * 32;
 #pragma unroll
-                        for (int cc = 0; cc < 4; ++cc)
-                            *reinterpret_cast<uint4*>(du + cc * 8) =
-                                make_uint4(pack_bf16(ke[cc * 8], ke[cc * 8 + 1]), pack_bf16(ke[cc * 8 + 2], ke[cc * 8 + 3]),
-                                           pack_bf16(ke[cc * 8 + 4], ke[cc * 8 + 5]), pack_bf16(ke[cc * 8 + 6], ke[cc * 8 + 7]));
+                        for (int c2 = 0; c2 < 2; ++c2) {
+                            uint32_t w[8];
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) w[e] = pack_bf16(ke[c2 * 16 + 2 * e], ke[c2 * 16 + 2 * e + 1]);
+                            st_global_32B(du + c2 * 16, w);
+                        }
                     }
                 } else if (lv >= 0) {
                     // <E, H>: the two tiles have the same layout, so equal offsets are equal elements

@@ -47,6 +47,7 @@ struct GdnParams {
     float* dq;                   // (B,T,H,K) fp32 results
     float* dk;
     float* dv;                   // (B,T,H,V)
+    __nv_bfloat16* dv_bf16;      // (B,T,H,V)  written instead of dv when not null
     float* dbeta;                // (B,T,H)
     float* dg;                   // (B,T,H)
     float* dl;                   // (B,T,H,L)

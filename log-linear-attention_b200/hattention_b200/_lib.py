@@ -85,6 +85,8 @@ def lib():
     L.llattn_gdn_bwd_kept_workspace_bytes.argtypes = [ctypes.c_int] * 6
     L.llattn_gdn_bwd_kept.restype = ctypes.c_int
     L.llattn_gdn_bwd_kept.argtypes = [_P] * 15 + [_P, ctypes.c_size_t, _P, ctypes.c_size_t] + [ctypes.c_int] * 6 + [_P]
+    L.llattn_gdn_bwd_kept_bf16dv.restype = ctypes.c_int
+    L.llattn_gdn_bwd_kept_bf16dv.argtypes = L.llattn_gdn_bwd_kept.argtypes
     L.llattn_selftest_umma_cycles.restype = ctypes.c_int
     L.llattn_selftest_umma_cycles.argtypes = [ctypes.c_int] * 5 + [_P, _P, _P]
     L.llattn_testing_use_tensor_core_path.restype = None        # test-only symbol (csrc/llattn_testing.h)

@@ -132,9 +132,11 @@ def chunkwise_fwd(
     return g_cum, o, Aw, Au, ht
 
 
-def chunkwise_bwd(q, k, v, b, g, l, Aw, Au, do, head_first, level_base, htype, chunk_size, fwd_workspace=None, **unused):
+def chunkwise_bwd(q, k, v, b, g, l, Aw, Au, do, head_first, level_base, htype, chunk_size, fwd_workspace=None,
+                  dv_bf16=False, **unused):
     """Gradients (dq, dk, dv, db, dg, dl), fp32, of the driver for normalised q, k (signature of
-    chunkwise_hgdn.py:799-817; `g` is the in-chunk cumulative sum returned by chunkwise_fwd).
+    chunkwise_hgdn.py:799-817; `g` is the in-chunk cumulative sum returned by chunkwise_fwd).  With `dv_bf16` and a kept
+    forward workspace dv comes back in bf16 (what the autograd function hands on for bf16 v), written by the kernel itself.
     One C-ABI call: recomputation of the chunk matrices and level states (skipped when `fwd_workspace`
     is the workspace a `chunkwise_fwd(..., keep_workspace=[])` call on the same inputs left), reverse scan
     of the adjoint states, state-dependent gradients, chunk-local gradients."""
@@ -147,10 +149,10 @@ def chunkwise_bwd(q, k, v, b, g, l, Aw, Au, do, head_first, level_base, htype, c
         gc_ = g.to(torch.float32).contiguous()
         f32 = dict(dtype=torch.float32, device=q.device)
         dq, dk = torch.empty(B, T, H, K, **f32), torch.empty(B, T, H, K, **f32)
-        dv = torch.empty(B, T, H, V, **f32)
+        kept = fwd_workspace is not None
+        dv = torch.empty(B, T, H, V, dtype=torch.bfloat16 if (dv_bf16 and kept) else torch.float32, device=q.device)
         db, dg = torch.empty(B, T, H, **f32), torch.empty(B, T, H, **f32)
         dl = torch.empty(B, T, H, L, **f32)
-        kept = fwd_workspace is not None
         n = (lib.llattn_gdn_bwd_kept_workspace_bytes if kept else lib.llattn_gdn_bwd_workspace_bytes)(B, T, H, K, V, L)
         if n == 0:
             raise ValueError("unsupported GDN shape (K must be 128, V 64 or 128, T <= 16384)")
@@ -160,7 +162,8 @@ def chunkwise_bwd(q, k, v, b, g, l, Aw, Au, do, head_first, level_base, htype, c
                 db.data_ptr(), dg.data_ptr(), dl.data_ptr())
         tail = (ws.data_ptr(), ws.numel(), B, T, H, K, V, L, torch.cuda.current_stream().cuda_stream)
         if kept:
-            rc = lib.llattn_gdn_bwd_kept(*head, fwd_workspace.data_ptr(), fwd_workspace.numel(), *tail)
+            fn = lib.llattn_gdn_bwd_kept_bf16dv if dv.dtype == torch.bfloat16 else lib.llattn_gdn_bwd_kept
+            rc = fn(*head, fwd_workspace.data_ptr(), fwd_workspace.numel(), *tail)
         else:
             rc = lib.llattn_gdn_bwd(*head, *tail)
         _lib.check(rc, "llattn_gdn_bwd_kept" if kept else "llattn_gdn_bwd")
@@ -206,7 +209,7 @@ def gdn_backward(q, k, v, b, g_cum, l, Aw, Au, do, scale, head_first, level_base
     if G != H:
         raise NotImplementedError("GDN backward expects one q/k per head")
     dq, dk, dv, db, dg, dl = chunkwise_bwd(qn, kn, v, b, g_cum, l, Aw, Au, do, head_first, level_base, htype, chunk_size,
-                                           fwd_workspace=fwd_ws)
+                                           fwd_workspace=fwd_ws, dv_bf16=(v.dtype == torch.bfloat16))
     dq = l2norm_bwd(q, dq, scale)
     dk = l2norm_bwd(k, dk)
     return dq, dk, dv, db, dg, dl

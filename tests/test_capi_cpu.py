@@ -143,6 +143,7 @@ def test_gdn_entry_points_reject_bad_arguments(lib):
     assert lib.llattn_gdn_fwd_keep_workspace_bytes(1, 1024, 2, 96, 64, 12) == 0
     assert lib.llattn_gdn_fwd_keep(*([null] * 10), null, 0, 1, 1024, 2, 128, 64, 11, null) == -6
     assert lib.llattn_gdn_bwd_kept(*([null] * 15), null, 0, null, 0, 1, 1024, 2, 128, 64, 11, null) == -6
+    assert lib.llattn_gdn_bwd_kept_bf16dv(*([null] * 15), null, 0, null, 0, 1, 1024, 2, 128, 64, 11, null) == -6
 
 
 def test_elementwise_entry_points_reject_bad_arguments(lib):

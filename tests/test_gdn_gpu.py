@@ -246,7 +246,7 @@ def test_tensor_core_scans_match_warp_mma_scans(B, T, H, Dv, L):
 
 def test_repeated_calls_are_bit_identical():
     """Twenty forward + backward calls on the same inputs at 128 chunks (all seven inter-chunk levels): the output and every
-    gradient that is not accumulated with atomics must come out bit for bit the same.  The tcgen05 kernels hand tiles
+    gradient must come out bit for bit the same (no kernel of this path accumulates with atomics).  The tcgen05 kernels hand tiles
     between a TMA producer, one MMA-issuing thread and eight element-wise warps through mbarriers; an ordering mistake there
     shows up as an occasional difference between repetitions rather than as a wrong result every time."""
     from hattention_b200 import chunkwise_hgdn as hg
@@ -265,7 +265,7 @@ def test_repeated_calls_are_bit_identical():
         g_cum, o, Aw, Au, _ = hg.chunkwise_fwd(qn, kn, v, b, g, l, False, 2, HType.WEAK, 64, False, keep_workspace=kept)
         dq, dk, dv, db, dg, dl = hg.chunkwise_bwd(qn, kn, v, b, g_cum, l, Aw, Au, do, False, 2, HType.WEAK, 64, fwd_workspace=kept[0])
         torch.cuda.synchronize()
-        cur = dict(o=o, Aw=Aw, Au=Au, dq=dq, dk=dk, dv=dv)      # d beta, dg, d lambda are accumulated with atomics in the chunk-local kernel
+        cur = dict(o=o, Aw=Aw, Au=Au, dq=dq, dk=dk, dv=dv, db=db, dg=dg, dl=dl)
         if first is None:
             first = {k_: x.clone() for k_, x in cur.items()}
             for k_, x in cur.items():
@@ -273,3 +273,26 @@ def test_repeated_calls_are_bit_identical():
         else:
             for k_, x in cur.items():
                 assert torch.equal(x, first[k_]), f"{k_} differs in repetition {rep}"
+
+
+def test_kept_backward_writes_dv_in_bf16():
+    """llattn_gdn_bwd_kept_bf16dv: dv written by the kernel in bf16 equals the fp32 dv of llattn_gdn_bwd_kept rounded to bf16,
+    element for element, and the other gradients are bit-identical."""
+    from hattention_b200 import chunkwise_hgdn as hg
+    from hattention_b200.base import HType
+    dev = torch.device("cuda:0")
+    B, T, H, Dk, Dv, L = 2, 1024, 3, 128, 128, 11
+    q, k, v, b, g, l = orc.make_gdn_inputs(B, T, H, Dk, Dv, L, seed=5)
+    scale = Dk ** -0.5
+    qn, kn = orc.gdn_layer_inputs(q, k, scale)
+    qn, kn, v, b, l = (x.bfloat16().to(dev) for x in (qn, kn, v, b, l / scale))
+    g = g.float().to(dev)
+    do = torch.randn(B, T, H, Dv, generator=torch.Generator().manual_seed(2)).bfloat16().to(dev)
+    kept = []
+    g_cum, o, Aw, Au, _ = hg.chunkwise_fwd(qn, kn, v, b, g, l, False, 2, HType.WEAK, 64, False, keep_workspace=kept)
+    ref = hg.chunkwise_bwd(qn, kn, v, b, g_cum, l, Aw, Au, do, False, 2, HType.WEAK, 64, fwd_workspace=kept[0])
+    got = hg.chunkwise_bwd(qn, kn, v, b, g_cum, l, Aw, Au, do, False, 2, HType.WEAK, 64, fwd_workspace=kept[0], dv_bf16=True)
+    assert got[2].dtype == torch.bfloat16 and ref[2].dtype == torch.float32
+    assert torch.equal(got[2], ref[2].to(torch.bfloat16))
+    for i_ in (0, 1, 3, 4, 5):
+        assert torch.equal(got[i_], ref[i_])
