@@ -887,26 +887,25 @@ __global__ void __launch_bounds__(256) m2_seg_dscan_kernel(const Mamba2Params p,
     float st[MAXLH][4];
 #pragma unroll
     for (int j = 0; j < MAXLH; ++j) st[j][0] = st[j][1] = st[j][2] = st[j][3] = 0.f;
-    // the loads of segment r - 1 are issued before the arithmetic of segment r (the recurrence itself is
-    // only in registers), so that a thread always has one segment's worth of loads in flight
-    float4 nF = make_float4(0.f, 0.f, 0.f, 0.f);
-    float4 ndF[MAXLH];
-    auto fetch = [&](int r) {
-        nF = (r >= 0 && r < p.NS - 1) ? *reinterpret_cast<const float4*>(F + (long)r * KV) : make_float4(0.f, 0.f, 0.f, 0.f);
+    // the recurrence itself is only in registers; the loads of segment r - 2 are issued right after the arithmetic of segment r
+    // (two register sets used alternately), so that a thread has up to two segments' worth of loads in flight
+    struct Loads {
+        float4 f;
+        float4 dF[MAXLH];
+        float d;
+    };
+    auto fetch = [&](Loads& L, int r) {
+        L.f = (r >= 0 && r < p.NS - 1) ? __ldg(reinterpret_cast<const float4*>(F + (long)r * KV)) : make_float4(0.f, 0.f, 0.f, 0.f);
+        L.d = (r >= 0 && r < p.NS - 1) ? __ldg(D + r) : 0.f;
 #pragma unroll
         for (int j = 0; j < MAXLH; ++j)
-            ndF[j] = (r >= 0 && j < p.LH && ((r >> j) & 1)) ? *reinterpret_cast<const float4*>(dF + ((long)r * p.LH + j) * KV)
-                                                            : make_float4(0.f, 0.f, 0.f, 0.f);
+            L.dF[j] = (r >= 0 && j < p.LH && ((r >> j) & 1)) ? __ldg(reinterpret_cast<const float4*>(dF + ((long)r * p.LH + j) * KV))
+                                                             : make_float4(0.f, 0.f, 0.f, 0.f);
     };
-    fetch(p.NS - 1);
-    for (int r = p.NS - 1; r >= 0; --r) {
+    auto process = [&](const Loads& L, int r) {
         float4 out = make_float4(0.f, 0.f, 0.f, 0.f);
-        const float4 f = nF;
-        float4 cdF[MAXLH];
-#pragma unroll
-        for (int j = 0; j < MAXLH; ++j) cdF[j] = ndF[j];
-        const float d = (r < p.NS - 1) ? __expf(D[r]) : 0.f;
-        fetch(r - 1);
+        const float4 f = L.f;
+        const float d = (r < p.NS - 1) ? __expf(L.d) : 0.f;
 #pragma unroll
         for (int j = 0; j < MAXLH; ++j) {
             if (j < p.LH) {
@@ -928,11 +927,22 @@ __global__ void __launch_bounds__(256) m2_seg_dscan_kernel(const Mamba2Params p,
                     st[j][0] *= d; st[j][1] *= d; st[j][2] *= d; st[j][3] *= d;
                 }
                 if (bit) {
-                    st[j][0] += cdF[j].x; st[j][1] += cdF[j].y; st[j][2] += cdF[j].z; st[j][3] += cdF[j].w;
+                    st[j][0] += L.dF[j].x; st[j][1] += L.dF[j].y; st[j][2] += L.dF[j].z; st[j][3] += L.dF[j].w;
                 }
             }
         }
         if (r < p.NS - 1) *reinterpret_cast<float4*>(dH + (long)r * KV) = out;
+    };
+    Loads A, B;
+    fetch(A, p.NS - 1);
+    fetch(B, p.NS - 2);
+    for (int r = p.NS - 1; r >= 0; r -= 2) {
+        process(A, r);
+        fetch(A, r - 2);
+        if (r - 1 >= 0) {
+            process(B, r - 1);
+            fetch(B, r - 3);
+        }
     }
 }
 
@@ -979,31 +989,68 @@ __global__ void __launch_bounds__(256) m2_dg_kernel(const Mamba2Params p, float*
     float* sY = sZ + p.NT * p.LZ;                       // [NT][MLOW+1]
     float* sYs = sY + p.NT * (MLOW + 1);                // [NS][LH]
     for (int i = tid; i < p.NT + p.NS; i += 256) sx[i] = 0.f;
-    for (int i = tid; i < p.NT * p.LZ; i += 256) {
-        const int c = i / p.LZ, lvz = i - c * p.LZ;
-        sZ[i] = ((c >> lvz) & 1) ? Zc[i] : 0.f;          // only reader entries were written
+    // eight loads per thread are in flight before the first of them is stored
+    for (int i0 = 0; i0 < p.NT * p.LZ; i0 += 8 * 256) {
+        float tmp[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int i = i0 + u * 256 + tid, c = i / p.LZ, lvz = i - c * p.LZ;
+            tmp[u] = (i < p.NT * p.LZ && ((c >> lvz) & 1)) ? __ldg(Zc + i) : 0.f;          // only reader entries were written
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int i = i0 + u * 256 + tid;
+            if (i < p.NT * p.LZ) sZ[i] = tmp[u];
+        }
     }
-    for (int i = tid; i < p.NT * (MLOW + 1); i += 256) sY[i] = Yc[i];
-    for (int i = tid; i < p.NS * p.LH; i += 256) sYs[i] = Yseg[i];
+    for (int i0 = 0; i0 < p.NT * (MLOW + 1); i0 += 4 * 256) {
+        float tmp[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int i = i0 + u * 256 + tid;
+            tmp[u] = (i < p.NT * (MLOW + 1)) ? __ldg(Yc + i) : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int i = i0 + u * 256 + tid;
+            if (i < p.NT * (MLOW + 1)) sY[i] = tmp[u];
+        }
+    }
+    for (int i = tid; i < p.NS * p.LH; i += 256) sYs[i] = __ldg(Yseg + i);
     __syncthreads();
     int nlev = 0;
     while ((1 << nlev) < p.NT) ++nlev;          // inter-chunk levels in use
     // every level writes its own row XL[lv][c] (no shared-memory atomics); rows are summed per chunk below
     float* XL = sYs + p.NS * (p.LH > 0 ? p.LH : 1);     // [nlev][NT]
-    if (tid < nlev) {
-        const int lv = tid, period = 2 << lv;
+    // One level per warp and round.  Within a block pair of 2^(lv+1) chunks the contributor sweep runs forwards over the first
+    // half (inclusive running sum of Y) and the reader sweep backwards over the second half (running sum of Z, exclusive): the
+    // half-blocks are independent, so each lane takes one (block, sweep) with the same branch-free loop and the longest chain is
+    // 2^lv steps instead of two passes over all chunks.
+    for (int lv = warp; lv < nlev; lv += 8) {
+        const int hl = 1 << lv, period = 2 << lv;
         float* xl = XL + lv * p.NT;
-        for (int c = 0; c < p.NT; ++c) xl[c] = 0.f;
-        if (lv < MLOW) {
+        for (int c = lane; c < p.NT; c += 32) xl[c] = 0.f;
+        __syncwarp();
+        const int nblk = (p.NT + period - 1) / period;
+        for (int t = lane; t < 2 * nblk; t += 32) {
+            const int base = (t >> 1) * period;
+            const bool rev = t & 1;
+            const bool active = rev || lv < MLOW;
+            const float* src = rev ? sZ + lv : sY + lv;
+            const int stride = rev ? p.LZ : (MLOW + 1);
+            const int c0 = rev ? base + period - 1 : base, dir = rev ? -1 : 1;
             float run = 0.f;
-            for (int c = 0; c < p.NT; ++c) {
-                if ((c & (period - 1)) == 0) run = 0.f;
-                if (!((c >> lv) & 1)) {
-                    run += sY[c * (MLOW + 1) + lv];
-                    xl[c] = run;
+            for (int k = 0; k < hl; ++k) {
+                const int c = c0 + dir * k;
+                if (active && c < p.NT) {
+                    const float v = src[c * stride];
+                    xl[c] = rev ? run : run + v;
+                    run += v;
                 }
             }
-        } else {
+        }
+        if (lv >= MLOW && lane == 31) {
+            // contributor totals of the high levels live per segment
             const int j = lv - MLOW, pj = 2 << j;
             float run = 0.f;
             for (int r = 0; r < p.NS; ++r) {
@@ -1014,28 +1061,33 @@ __global__ void __launch_bounds__(256) m2_dg_kernel(const Mamba2Params p, float*
                 }
             }
         }
-        float run = 0.f;
-        for (int c = p.NT - 1; c >= 0; --c) {
-            if ((c >> lv) & 1) {
-                xl[c] = run;
-                run += sZ[c * p.LZ + lv];
+    }
+    if (warp == (nlev & 7)) {
+        // combined high levels: running sum inside each segment, one segment per lane (on the warp with the fewest levels)
+        for (int c0 = lane * SEG; c0 < p.NT; c0 += 32 * SEG) {
+            float run = 0.f;
+            for (int c = c0; c < c0 + SEG && c < p.NT; ++c) {
+                run += sY[c * (MLOW + 1) + MLOW];
+                X[c] = run;
             }
-            if ((c & (period - 1)) == 0) run = 0.f;
-        }
-    } else if (tid == 32) {
-        // combined high levels inside a segment
-        float run = 0.f;
-        for (int c = 0; c < p.NT; ++c) {
-            if ((c & (SEG - 1)) == 0) run = 0.f;
-            run += sY[c * (MLOW + 1) + MLOW];
-            X[c] = run;
         }
     }
     __syncthreads();
-    for (int c = c_begin + warp; c < c_end; c += 8) {
+    // a warp's (up to eight) chunks: all loads first
+    float w0[8], w1[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+        const int c = c_begin + warp + u * 8;
         const long base = ((long)b * p.T + (long)c * CH) * p.H + h;
-        float x0 = p.wq[base + (long)(63 - 2 * lane) * p.H];
-        float x1 = p.wq[base + (long)(62 - 2 * lane) * p.H];
+        w0[u] = (c < c_end) ? __ldg(p.wq + base + (long)(63 - 2 * lane) * p.H) : 0.f;
+        w1[u] = (c < c_end) ? __ldg(p.wq + base + (long)(62 - 2 * lane) * p.H) : 0.f;
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+        const int c = c_begin + warp + u * 8;
+        if (c >= c_end) break;
+        const long base = ((long)b * p.T + (long)c * CH) * p.H + h;
+        float x0 = w0[u], x1 = w1[u];
         warp_cumsum64(x0, x1, lane);
         float add = X[c] + XS[c / SEG];
         for (int lv = 0; lv < nlev; ++lv) add += XL[lv * p.NT + c];

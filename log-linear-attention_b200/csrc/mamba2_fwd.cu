@@ -395,13 +395,28 @@ __global__ void __launch_bounds__(256) m2_seg_scan_kernel(const Mamba2Params p, 
     float st[MAX_LH][4];
 #pragma unroll
     for (int j = 0; j < MAX_LH; ++j) st[j][0] = st[j][1] = st[j][2] = st[j][3] = 0.f;
-    for (int r = 0; r < p.NS; ++r) {
-        float4 f = make_float4(0.f, 0.f, 0.f, 0.f);
-        float d = 0.f;
-        if (r < p.NS - 1) {
-            f = *reinterpret_cast<const float4*>(F + (long)r * KV);
-            d = __expf(D[r]);
-        }
+    // the recurrence is in registers; the summaries of eight segments are requested together so that a thread pays the load
+    // latency once per eight segments
+    constexpr int RB = 8;
+    for (int r0 = 0; r0 < p.NS; r0 += RB) {
+      float4 fb[RB];
+      float db[RB];
+#pragma unroll
+      for (int u = 0; u < RB; ++u) {
+          const int r = r0 + u;
+          fb[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+          db[u] = 0.f;
+          if (r < p.NS - 1) {
+              fb[u] = __ldg(reinterpret_cast<const float4*>(F + (long)r * KV));
+              db[u] = __ldg(D + r);
+          }
+      }
+#pragma unroll
+      for (int u = 0; u < RB; ++u) {
+        const int r = r0 + u;
+        if (r >= p.NS) break;
+        const float4 f = fb[u];
+        const float d = (r < p.NS - 1) ? __expf(db[u]) : 0.f;
 #pragma unroll
         for (int j = 0; j < MAX_LH; ++j) {
             if (j < p.LH) {
@@ -423,6 +438,7 @@ __global__ void __launch_bounds__(256) m2_seg_scan_kernel(const Mamba2Params p, 
                 }
             }
         }
+      }
     }
 }
 
