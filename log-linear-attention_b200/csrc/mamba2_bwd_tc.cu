@@ -370,42 +370,72 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_fwdorder_tc_kernel(con
                     make_uint4(packed[c * 4], packed[c * 4 + 1], packed[c * 4 + 2], packed[c * 4 + 3]);
         }
         // diagonal block: levels 0..5, causal mask folded into the exponent
+        STAMP();   // 2a blocks off the diagonal done
         {
             const int j0 = rb * 32 + ch * 16;
             uint32_t packed[8];
             float s[16], dp[16];
             umma::tmem_ld16x2(umma::tmem_addr(tbase + tcb::TB_S, warp, j0), s, umma::tmem_addr(tbase + tcb::TB_DP, warp, j0), dp);
+            STAMP();   // 2b diagonal block loaded
+            // The level of (row li, column jj) is the position of the highest bit in which they differ.  With the column's
+            // low four bits a compile-time constant, "bit k differs" is one of the thread's own bits or its complement, so
+            // lambda is picked with four selects on precomputed predicates; and the d lambda sum of level k is the sum over
+            // the sibling block of size 2^(k-1) of the row's own position, taken from a binary tree of partial sums (15
+            // additions and 30 selects per thread instead of six predicated additions per element).  A thread whose
+            // sixteen columns lie in the other half of the 32-block (bit 4 differs) has level 5 throughout.
             const int li = lane;
+            const bool B0 = li & 1, B1 = li & 2, B2 = li & 4, B3 = li & 8;
+            const bool hi = (((li >> 4) & 1) != ch);
+            // per half of eight columns: what the levels 0..3 would get if the row's own position lay in this half, and the half's sum
+            float c_own[2], c_sib1[2], c_sib2[2], c_sib4[2], c_sum[2];
 #pragma unroll
-            for (int e = 0; e < 16; e += 4) {
-                const float4 gj = *reinterpret_cast<const float4*>(sGp + j0 + e);
-                const float gjv[4] = {gj.x, gj.y, gj.z, gj.w};
+            for (int hf = 0; hf < 2; ++hf) {
+                float es[8];
 #pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    const int jj = ch * 16 + e + u;
-                    const int x = li ^ jj;
-                    const float d = (jj <= li) ? (Gi - gjv[u]) : -INFINITY;
-                    const float ed = dp[e + u] * fexp(d);
-                    const float es = ed * s[e + u];
-                    float lm = lam[0];
-                    lm = (x >= 1) ? lam[1] : lm;
-                    lm = (x >= 2) ? lam[2] : lm;
-                    lm = (x >= 4) ? lam[3] : lm;
-                    lm = (x >= 8) ? lam[4] : lm;
-                    lm = (x >= 16) ? lam[5] : lm;
-                    bins[0] += (x == 0) ? es : 0.f;
-                    bins[1] += (x == 1) ? es : 0.f;
-                    bins[2] += (x >= 2 && x < 4) ? es : 0.f;
-                    bins[3] += (x >= 4 && x < 8) ? es : 0.f;
-                    bins[4] += (x >= 8 && x < 16) ? es : 0.f;
-                    bins[5] += (x >= 16) ? es : 0.f;
-                    const float dsv = ed * lm;
-                    wq_tile += __bfloat162float(__float2bfloat16(dsv)) * s[e + u];
-                    s[e + u] = dsv;
+                for (int e = 0; e < 8; e += 4) {
+                    const float4 gj = *reinterpret_cast<const float4*>(sGp + j0 + hf * 8 + e);
+                    const float gjv[4] = {gj.x, gj.y, gj.z, gj.w};
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const int ee = hf * 8 + e + u;                     // low four bits of the column
+                        const int jj = ch * 16 + ee;
+                        const float d = (jj <= li) ? (Gi - gjv[u]) : -INFINITY;
+                        const float ed = dp[ee] * fexp(d);
+                        es[e + u] = ed * s[ee];
+                        const bool q3 = hf ? !B3 : B3, q2 = ((ee >> 2) & 1) ? !B2 : B2;
+                        const bool q1 = ((ee >> 1) & 1) ? !B1 : B1, q0 = (ee & 1) ? !B0 : B0;
+                        float lm = q0 ? lam[1] : lam[0];
+                        lm = q1 ? lam[2] : lm;
+                        lm = q2 ? lam[3] : lm;
+                        lm = q3 ? lam[4] : lm;
+                        lm = hi ? lam[5] : lm;
+                        const float dsv = ed * lm;
+                        wq_tile += __bfloat162float(__float2bfloat16(dsv)) * s[ee];
+                        s[ee] = dsv;
+                    }
+                    packed[(hf * 8 + e) >> 1] = pack_bf16(s[hf * 8 + e], s[hf * 8 + e + 1]);
+                    packed[((hf * 8 + e) >> 1) + 1] = pack_bf16(s[hf * 8 + e + 2], s[hf * 8 + e + 3]);
                 }
-                packed[e >> 1] = pack_bf16(s[e], s[e + 1]);
-                packed[(e >> 1) + 1] = pack_bf16(s[e + 2], s[e + 3]);
+                // walk down the half's tree of partial sums along the row's own bits 2, 1, 0
+                const float p0 = es[0] + es[1], p1 = es[2] + es[3], p2 = es[4] + es[5], p3 = es[6] + es[7];
+                const float q0s = p0 + p1, q1s = p2 + p3;
+                c_sum[hf] = q0s + q1s;
+                c_sib4[hf] = B2 ? q0s : q1s;
+                const float e0 = B2 ? p2 : p0, e1 = B2 ? p3 : p1;
+                c_sib2[hf] = B1 ? e0 : e1;
+                float f4[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) f4[i] = B2 ? es[4 + i] : es[i];
+                const float g0 = B1 ? f4[2] : f4[0], g1 = B1 ? f4[3] : f4[1];
+                c_sib1[hf] = B0 ? g0 : g1;
+                c_own[hf] = B0 ? g1 : g0;
             }
+            bins[0] += hi ? 0.f : (B3 ? c_own[1] : c_own[0]);
+            bins[1] += hi ? 0.f : (B3 ? c_sib1[1] : c_sib1[0]);
+            bins[2] += hi ? 0.f : (B3 ? c_sib2[1] : c_sib2[0]);
+            bins[3] += hi ? 0.f : (B3 ? c_sib4[1] : c_sib4[0]);
+            bins[4] += hi ? 0.f : (B3 ? c_sum[0] : c_sum[1]);
+            bins[5] += hi ? (c_sum[0] + c_sum[1]) : 0.f;
 #pragma unroll
             for (int c = 0; c < 2; ++c)
                 *reinterpret_cast<uint4*>(sDS + umma::tile_offset(row, j0 + c * 8, tc::PT)) =
