@@ -332,7 +332,11 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_chunk_fwd_tc_kernel(const 
                     make_uint2(pack_bf16(s[0] * rf * cf.x, s[1] * rf * cf.y), pack_bf16(s[2] * rf * cf.z, s[3] * rf * cf.w));
             }
         }
-        // diagonal block: levels 0..5, causal mask folded into the exponent
+        // diagonal block: levels 0..5, causal mask folded into the exponent.  The level of (row, column) is the position of the
+        // highest bit in which they differ: per bit, "differs" is the row's own bit or its complement, so lambda is picked by
+        // selects on predicates instead of comparisons per element.
+        const bool B0 = lane & 1, B1 = lane & 2, B2 = lane & 4, B3 = lane & 8;
+        const bool hi = (((lane >> 4) & 1) != ch);
 #pragma unroll 1
         for (int cc = 0; cc < 4; ++cc) {
             const int jc = ch * 16 + cc * 4;             // first of the four columns, inside the block
@@ -341,16 +345,16 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_chunk_fwd_tc_kernel(const 
             umma::tmem_ld4(umma::tmem_addr(tbase + tc::TM_S, warp, j0), s);
             const float4 gj = *reinterpret_cast<const float4*>(sGp + j0);
             const float gjv[4] = {gj.x, gj.y, gj.z, gj.w};
+            const bool q2 = B2 != bool(cc & 1), q3 = B3 != bool(cc & 2);
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
                 const int jj = jc + u;
-                const int x = lane ^ jj;
-                float lm = lam[0];
-                lm = (x >= 1) ? lam[1] : lm;
-                lm = (x >= 2) ? lam[2] : lm;
-                lm = (x >= 4) ? lam[3] : lm;
-                lm = (x >= 8) ? lam[4] : lm;
-                lm = (x >= 16) ? lam[5] : lm;
+                const bool q1 = (u & 2) ? !B1 : B1, q0 = (u & 1) ? !B0 : B0;
+                float lm = q0 ? lam[1] : lam[0];
+                lm = q1 ? lam[2] : lm;
+                lm = q2 ? lam[3] : lm;
+                lm = q3 ? lam[4] : lm;
+                lm = hi ? lam[5] : lm;
                 const float d = (jj <= lane) ? (Gi - gjv[u]) : -INFINITY;
                 s[u] = s[u] * fexp(d) * lm;
             }
