@@ -78,8 +78,10 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_fwdorder_tc_kernel(con
     uint64_t* empty_qk = bars + 4;  // q / k tiles may be refilled
     uint64_t* empty_vd = bars + 5;  // v / do tiles may be refilled
     uint64_t* dq_ready = bars + 6;  // the dq tile of the pair is staged (fp32) for the store agent
-    uint64_t* dk_ready = bars + 7;  // ... the dk tile
+    uint64_t* dk_ready = bars + 7;  // ... columns 0..63 of the dk tile (128 arrivals: the warps of column half 0)
     uint64_t* stage_free = bars + 8;   // the store agent's reduce-adds have read both staging areas
+    uint64_t* barDK = bars + 9;     // the dk product (first of the second batch) is complete: the q tile is free
+    uint64_t* dk_ready1 = bars + 10;   // columns 64..127 of the dk tile are staged (128 arrivals: column half 1)
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + SM::bar_off + 96);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + SM::bar_off + 104);
 
@@ -93,7 +95,8 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_fwdorder_tc_kernel(con
 
     if (tid == 0) {
 #pragma unroll
-        for (int i = 0; i < 9; ++i) umma::mbar_init(&bars[i], 1);
+        for (int i = 0; i < 10; ++i) umma::mbar_init(&bars[i], i == 7 ? 128 : 1);
+        umma::mbar_init(dk_ready1, 128);
         umma::fence_mbar_init();
         *abort_flag = *p.err;
     }
@@ -136,9 +139,15 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_fwdorder_tc_kernel(con
                 for (int pl = 0; pl < npairs; ++pl) {
                     const int grow = b * p.T + (r * SEGP + pl) * tc::PT;
                     // dk first: its staging area is the q / k tile space, which the next pair's loads wait for
+                    // (in two halves: columns 0..63 are staged in the q tile as soon as the dk product is complete, columns
+                    // 64..127 in the k tile once the whole batch is, so that half of the reduce-add is over by then)
                     if (!umma::mbar_wait(dk_ready, pl & 1, abort_flag)) break;
 #pragma unroll
-                    for (int bx = 0; bx < 4; ++bx) tma::reduce_add_box(&p.tm_dk, bx * 32, grp, grow, sStage2 + bx * 16384);
+                    for (int bx = 0; bx < 2; ++bx) tma::reduce_add_box(&p.tm_dk, bx * 32, grp, grow, sStage2 + bx * 16384);
+                    tma::commit_group();
+                    if (!umma::mbar_wait(dk_ready1, pl & 1, abort_flag)) break;
+#pragma unroll
+                    for (int bx = 2; bx < 4; ++bx) tma::reduce_add_box(&p.tm_dk, bx * 32, grp, grow, sStage2 + bx * 16384);
                     tma::commit_group();
                     tma::wait_group_read0();
                     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(umma::smem_addr(empty_qk)) : "memory");
@@ -184,7 +193,9 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_fwdorder_tc_kernel(con
             bar_work();                              // barrier 2: dS, scaled do and Vs are written
             umma::fence_after_sync();
             if (lane == 0) {
-                // dq = dS k (+ level parts), dk = dS^T q, KV = k^T Vs
+                // dk = dS^T q first (the q tile becomes staging space when it is complete), dq = dS k (+ level parts), KV = k^T Vs
+                umma::gemm_mm<tc::PT, tc::PT, tc::PT>(tbase + tcb::TB_DK, aDS, aQ, ID_MM128, false);
+                umma::commit(barDK);
                 umma::gemm_km<tc::PT, tc::PT, tc::PT>(tbase + tcb::TB_DQ, aDS, aK, ID_KM128, false);
                 int slot = 0;
 #pragma unroll
@@ -194,7 +205,6 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_fwdorder_tc_kernel(con
                                                               umma::smem_addr(sH + lv * tc::H_BYTES), ID_KK128, true);
                         ++slot;
                     }
-                umma::gemm_mm<tc::PT, tc::PT, tc::PT>(tbase + tcb::TB_DK, aDS, aQ, ID_MM128, false);
                 umma::gemm_mm<tc::PT, tc::PT, tc::PT>(tbase + tcb::TB_KV, aK, aVs, ID_MM64, false);
                 umma::commit(barB);
                 // v and do were last read (generic loads and the first batch) before barrier 2
@@ -509,6 +519,45 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_fwdorder_tc_kernel(con
         // every read of this pair's decay tables is behind barrier 2 (what follows uses Gi / glp from registers):
         // one warp rebuilds them for the next pair while the second batch runs
         if (warp == TABLE_WARP && pl + 1 < npairs) decay_tables(sGp);
+        // ---- dk tile: k_j . dk_j row sums, then fp32 staging for the TMA reduce-add.  The staging area is the q / k tile space,
+        //      which the next pair's loads wait for, so it is filled as early as its halves become free: columns 0..63 (the
+        //      warps of column half 0) go into the q tile as soon as the dk product - issued first in the batch - is complete,
+        //      columns 64..127 into the k tile once dq and KV are complete and every thread is done with its k row sums.
+        auto dk_half = [&]() {
+            float wk_part = 0.f;
+            float dkv[2][32];
+#pragma unroll
+            for (int hb = 0; hb < 2; ++hb) {
+                umma::tmem_ld32(umma::tmem_addr(tbase + tcb::TB_DK, warp, ch * 64 + hb * 32), dkv[hb]);
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const uint4 kx = *reinterpret_cast<const uint4*>(sK + umma::tile_offset(row, ch * 64 + hb * 32 + c * 8, tc::PT));
+                    const uint32_t* xw = reinterpret_cast<const uint32_t*>(&kx);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        __nv_bfloat162 v2 = *reinterpret_cast<const __nv_bfloat162*>(&xw[e]);
+                        wk_part += __bfloat162float(v2.x) * dkv[hb][c * 8 + e * 2] + __bfloat162float(v2.y) * dkv[hb][c * 8 + e * 2 + 1];
+                    }
+                }
+            }
+            sWk[ch * 128 + row] = wk_part;
+            if (ch == 1) asm volatile("bar.sync 3, 128;\n" ::: "memory");   // the warps of this half are done with the k tile they overwrite
+#pragma unroll
+            for (int hb = 0; hb < 2; ++hb) {
+                unsigned char* box = sStage2 + (ch * 2 + hb) * 16384;
+#pragma unroll
+                for (int c = 0; c < 8; ++c)
+                    *reinterpret_cast<float4*>(box + box_offset(row, c * 4)) =
+                        make_float4(dkv[hb][c * 4], dkv[hb][c * 4 + 1], dkv[hb][c * 4 + 2], dkv[hb][c * 4 + 3]);
+            }
+            umma::fence_async_smem();
+            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(umma::smem_addr(ch == 0 ? dk_ready : dk_ready1)) : "memory");
+        };
+        if (ch == 0) {
+            umma::mbar_wait(barDK, pl & 1, abort_flag);
+            umma::fence_after_sync();
+            dk_half();
+        }
         // ---- while the second batch runs: dlambda out (coalesced), q.dq row sums, reader totals Z per chunk
         {
             float* gdl = p.dl + (((long)b * p.T + t0) * p.H + h) * L;
@@ -518,8 +567,8 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_fwdorder_tc_kernel(con
                 if (i < L) gdl[(long)rr * p.H * L + i] = sDL[rr * tcb::NDL + i] + sDL[(128 + rr) * tcb::NDL + i];
             }
         }
-        float wq_row = 0.f;                          // valid for ch == 0 threads: q_i . dq_i
-        if (ch == 0) {
+        float wq_row = 0.f;                          // valid for ch == 1 threads: q_i . dq_i  (column half 0 stages its dk half meanwhile)
+        if (ch == 1) {
             float zl[NLAM];
 #pragma unroll
             for (int i = 0; i < NLAM; ++i) {
@@ -532,7 +581,7 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_fwdorder_tc_kernel(con
                 float z = zl[i];
 #pragma unroll
                 for (int d = 16; d > 0; d >>= 1) z += __shfl_xor_sync(0xffffffffu, z, d);
-                if (lane == 0) sWk[256 + warp * 16 + i] = z;
+                if (lane == 0) sWk[256 + rb * 16 + i] = z;
             }
         }
         bar_compute();
@@ -555,39 +604,8 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_fwdorder_tc_kernel(con
         umma::mbar_wait(barB, pl & 1, abort_flag);
         umma::fence_after_sync();
         STAMP();   // 8 batch B complete
-        // ---- dk tile first: k_j . dk_j row sums need the k tile, which then becomes staging space
-        float wk_part = 0.f;
-        float dkv[2][32];
-#pragma unroll
-        for (int hb = 0; hb < 2; ++hb) {
-            umma::tmem_ld32(umma::tmem_addr(tbase + tcb::TB_DK, warp, ch * 64 + hb * 32), dkv[hb]);
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                const uint4 kx = *reinterpret_cast<const uint4*>(sK + umma::tile_offset(row, ch * 64 + hb * 32 + c * 8, tc::PT));
-                const uint32_t* xw = reinterpret_cast<const uint32_t*>(&kx);
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    __nv_bfloat162 v2 = *reinterpret_cast<const __nv_bfloat162*>(&xw[e]);
-                    wk_part += __bfloat162float(v2.x) * dkv[hb][c * 8 + e * 2] + __bfloat162float(v2.y) * dkv[hb][c * 8 + e * 2 + 1];
-                }
-            }
-        }
-        sWk[ch * 128 + row] = wk_part;
-        bar_compute();                               // every thread is done with the k tile
-        // ---- dk tile -> fp32 staging in the q / k tile space -> TMA reduce-add (first, so that the tile space is
-        //      handed back to the producer as early as possible)
-#pragma unroll
-        for (int hb = 0; hb < 2; ++hb) {
-            unsigned char* box = sStage2 + (ch * 2 + hb) * 16384;
-#pragma unroll
-            for (int c = 0; c < 8; ++c)
-                *reinterpret_cast<float4*>(box + box_offset(row, c * 4)) =
-                    make_float4(dkv[hb][c * 4], dkv[hb][c * 4 + 1], dkv[hb][c * 4 + 2], dkv[hb][c * 4 + 3]);
-        }
+        if (ch == 1) dk_half();
         STAMP();   // 9 dk staged
-        umma::fence_async_smem();
-        bar_compute();
-        if (tid == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(umma::smem_addr(dk_ready)) : "memory");
         // ---- dq tile -> fp32 staging (dS + scaled do space) -> TMA reduce-add
 #pragma unroll
         for (int hb = 0; hb < 2; ++hb) {
@@ -602,7 +620,7 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_fwdorder_tc_kernel(con
         umma::fence_async_smem();
         bar_compute();
         if (tid == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(umma::smem_addr(dq_ready)) : "memory");
-        if (ch == 0) {
+        if (ch == 1) {
             const float w = wq_row - (sWk[row] + sWk[128 + row]);
             red_add_f32(p.wq + ((long)b * p.T + t0 + row) * p.H + h, w);
         }
