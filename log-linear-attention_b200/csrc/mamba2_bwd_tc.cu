@@ -86,12 +86,21 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_fwdorder_tc_kernel(con
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + SM::bar_off + 104);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int h = blockIdx.x % p.H;
-    const int r = (blockIdx.x / p.H) % p.NS;
-    const int b = blockIdx.x / (p.H * p.NS);
-    const int grp = h / (p.H / p.G);
+    // Persistent CTAs: one per SM walks the (batch, segment, head) items blockIdx.x, blockIdx.x + gridDim.x, ...  Every role
+    // runs the same item / pair sequence; mbarrier parities follow the running pair count `gs` of the CTA, and what a pair
+    // prepares for the next one (lambda, decay tables, TMA loads) carries over from an item's last pair to the next item's
+    // first, so that neither the tail of an item (its last reduce-adds) nor the launch of a CTA is paid per item.
+    const int nitems = p.B * p.H * p.NS;
+    int h, r, b, grp, npairs;
+    auto decode = [&](int item) {
+        h = item % p.H;
+        r = (item / p.H) % p.NS;
+        b = item / (p.H * p.NS);
+        grp = h / (p.H / p.G);
+        npairs = min(SEGP, p.NT / 2 - r * SEGP);
+    };
+    decode(blockIdx.x);
     const int L = p.L;
-    const int npairs = min(SEGP, p.NT / 2 - r * SEGP);
 
     if (tid == 0) {
 #pragma unroll
@@ -114,19 +123,24 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_fwdorder_tc_kernel(con
         if (warp == tc::MMA_WARP + 1) {
             // ---- TMA producer
             if (lane == 0) {
-                const int brow = b * p.T + r * SEGP * tc::PT;
-                for (int pl = 0; pl < npairs; ++pl) {
-                    const int row0 = brow + pl * tc::PT;
-                    if (pl >= 1 && !umma::mbar_wait(empty_vd, (pl - 1) & 1, abort_flag)) break;
-                    tma::expect_tx(full_vd, 2 * tc::V_BYTES);
-                    tma::load_panel(sV, &p.tm_v, 0, h, row0, full_vd);
-                    tma::load_panel(sDO, &p.tm_do, 0, h, row0, full_vd);
-                    if (pl >= 1 && !umma::mbar_wait(empty_qk, (pl - 1) & 1, abort_flag)) break;
-                    tma::expect_tx(full_qk, 2 * tc::Q_BYTES);
-                    tma::load_panel(sQ, &p.tm_q, 0, grp, row0, full_qk);
-                    tma::load_panel(sQ + tc::Q_BYTES / 2, &p.tm_q, 64, grp, row0, full_qk);
-                    tma::load_panel(sK, &p.tm_k, 0, grp, row0, full_qk);
-                    tma::load_panel(sK + tc::Q_BYTES / 2, &p.tm_k, 64, grp, row0, full_qk);
+                uint32_t gs = 0;
+                bool ok = true;
+                for (int item = blockIdx.x; item < nitems && ok; item += gridDim.x) {
+                    decode(item);
+                    const int brow = b * p.T + r * SEGP * tc::PT;
+                    for (int pl = 0; pl < npairs; ++pl, ++gs) {
+                        const int row0 = brow + pl * tc::PT;
+                        if (gs >= 1 && !umma::mbar_wait(empty_vd, (gs - 1) & 1, abort_flag)) { ok = false; break; }
+                        tma::expect_tx(full_vd, 2 * tc::V_BYTES);
+                        tma::load_panel(sV, &p.tm_v, 0, h, row0, full_vd);
+                        tma::load_panel(sDO, &p.tm_do, 0, h, row0, full_vd);
+                        if (gs >= 1 && !umma::mbar_wait(empty_qk, (gs - 1) & 1, abort_flag)) { ok = false; break; }
+                        tma::expect_tx(full_qk, 2 * tc::Q_BYTES);
+                        tma::load_panel(sQ, &p.tm_q, 0, grp, row0, full_qk);
+                        tma::load_panel(sQ + tc::Q_BYTES / 2, &p.tm_q, 64, grp, row0, full_qk);
+                        tma::load_panel(sK, &p.tm_k, 0, grp, row0, full_qk);
+                        tma::load_panel(sK + tc::Q_BYTES / 2, &p.tm_k, 64, grp, row0, full_qk);
+                    }
                 }
             }
             return;
@@ -136,27 +150,32 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_fwdorder_tc_kernel(con
             //      waits for them, so that no element-wise thread stalls on a bulk-group wait; the q / k tile space
             //      (which doubles as the dk staging area) is freed as soon as the dk reduce-add has read it
             if (lane == 0) {
-                for (int pl = 0; pl < npairs; ++pl) {
+                uint32_t gs = 0;
+                bool ok = true;
+                for (int item = blockIdx.x; item < nitems && ok; item += gridDim.x) {
+                  decode(item);
+                  for (int pl = 0; pl < npairs; ++pl, ++gs) {
                     const int grow = b * p.T + (r * SEGP + pl) * tc::PT;
                     // dk first: its staging area is the q / k tile space, which the next pair's loads wait for
                     // (in two halves: columns 0..63 are staged in the q tile as soon as the dk product is complete, columns
                     // 64..127 in the k tile once the whole batch is, so that half of the reduce-add is over by then)
-                    if (!umma::mbar_wait(dk_ready, pl & 1, abort_flag)) break;
+                    if (!umma::mbar_wait(dk_ready, gs & 1, abort_flag)) { ok = false; break; }
 #pragma unroll
                     for (int bx = 0; bx < 2; ++bx) tma::reduce_add_box(&p.tm_dk, bx * 32, grp, grow, sStage2 + bx * 16384);
                     tma::commit_group();
-                    if (!umma::mbar_wait(dk_ready1, pl & 1, abort_flag)) break;
+                    if (!umma::mbar_wait(dk_ready1, gs & 1, abort_flag)) { ok = false; break; }
 #pragma unroll
                     for (int bx = 2; bx < 4; ++bx) tma::reduce_add_box(&p.tm_dk, bx * 32, grp, grow, sStage2 + bx * 16384);
                     tma::commit_group();
                     tma::wait_group_read0();
                     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(umma::smem_addr(empty_qk)) : "memory");
-                    if (!umma::mbar_wait(dq_ready, pl & 1, abort_flag)) break;
+                    if (!umma::mbar_wait(dq_ready, gs & 1, abort_flag)) { ok = false; break; }
 #pragma unroll
                     for (int bx = 0; bx < 4; ++bx) tma::reduce_add_box(&p.tm_dq, bx * 32, grp, grow, sStage + bx * 16384);
                     tma::commit_group();
                     tma::wait_group_read0();
                     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(umma::smem_addr(stage_free)) : "memory");
+                  }
                 }
                 tma::wait_group0();                  // every reduce-add has been performed before the CTA retires
             }
@@ -171,11 +190,14 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_fwdorder_tc_kernel(con
         const uint32_t tbase = *tmem_slot;
         const uint32_t aQ = umma::smem_addr(sQ), aK = umma::smem_addr(sK), aV = umma::smem_addr(sV), aDO = umma::smem_addr(sDO);
         const uint32_t aDS = umma::smem_addr(sDS), aDOs = umma::smem_addr(sDOs), aVs = umma::smem_addr(sVs);
-        for (int pl = 0; pl < npairs; ++pl) {
+        uint32_t gs = 0;
+        for (int item = blockIdx.x; item < nitems && !*abort_flag; item += gridDim.x) {
+          decode(item);
+          for (int pl = 0; pl < npairs; ++pl, ++gs) {
             // (no barrier here: the end-of-pair barrier of the previous pair is all the tensor core needs)
             if (lane == 0) {
-                umma::mbar_wait(full_qk, pl & 1, abort_flag);
-                umma::mbar_wait(full_vd, pl & 1, abort_flag);
+                umma::mbar_wait(full_qk, gs & 1, abort_flag);
+                umma::mbar_wait(full_vd, gs & 1, abort_flag);
                 umma::gemm_kk<tc::PT, tc::PT, tc::KD>(tbase + tcb::TB_S, aQ, aK, ID_KK128, false);
                 umma::gemm_kk<tc::PT, tc::PT, tc::VD>(tbase + tcb::TB_DP, aDO, aV, ID_KK128, false);
                 int slot = 0;
@@ -215,6 +237,7 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_fwdorder_tc_kernel(con
             bar_work();                              // barrier 3: end of the pair
             umma::fence_after_sync();
             if (*abort_flag) break;
+          }
         }
         if (*abort_flag && lane == 0) atomicExch(p.err, 1);
         umma::fence_before_sync();
@@ -239,17 +262,16 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_fwdorder_tc_kernel(con
         const int rr = e / L, cc = e - rr * L;
         lam_rc[i] = (rr < tc::PT) ? (uint32_t)((rr << 8) | cc) : 0xffffffffu;
     }
-    auto fetch_small = [&](int pl) {
-        const long t0 = (long)(r * SEGP + pl) * tc::PT;
-        const unsigned short* lp = reinterpret_cast<const unsigned short*>(p.l) + (((long)b * p.T + t0) * p.H + h) * L;
+    // (tok0: first token of the pair counted over the whole batch, b * T + t0; hh: its head)
+    auto fetch_small = [&](long tok0, int hh) {
+        const unsigned short* lp = reinterpret_cast<const unsigned short*>(p.l) + (tok0 * p.H + hh) * L;
 #pragma unroll
         for (int i = 0; i < LAMR; ++i)
             if (lam_rc[i] != 0xffffffffu) lam_r[i] = lp[(long)(lam_rc[i] >> 8) * p.H * L + (lam_rc[i] & 255)];
     };
     // raw g of a pair: one warp (the one that builds the decay tables), four consecutive tokens per lane
-    auto fetch_g = [&](int pl) {
-        const long t0 = (long)(r * SEGP + pl) * tc::PT;
-        const float* gp = p.g + ((long)b * p.T + t0 + 4 * lane) * p.H + h;
+    auto fetch_g = [&](long tok0, int hh) {
+        const float* gp = p.g + (tok0 + 4 * lane) * p.H + hh;
 #pragma unroll
         for (int i = 0; i < 4; ++i) g_n[i] = gp[(long)i * p.H];
     };
@@ -289,11 +311,14 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_fwdorder_tc_kernel(con
             if (lam_rc[i] != 0xffffffffu)
                 if ((lam_rc[i] & 255) < tcb::LAMC) sLam[(lam_rc[i] >> 8) * tcb::LAMC + (lam_rc[i] & 255)] = __ushort_as_bfloat16((unsigned short)lam_r[i]);
     };
-    fetch_small(0);
-    store_lam();
-    if (warp == TABLE_WARP) {
-        fetch_g(0);
-        decay_tables(sGp);
+    {
+        const long tok0 = (long)b * p.T + (long)r * SEGP * tc::PT;       // first pair of the CTA's first item
+        fetch_small(tok0, h);
+        store_lam();
+        if (warp == TABLE_WARP) {
+            fetch_g(tok0, h);
+            decay_tables(sGp);
+        }
     }
     umma::fence_before_sync();
     bar_work();
@@ -302,19 +327,32 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_fwdorder_tc_kernel(con
 
     float M[MP > 0 ? MP : 1][32];
     float dsum[MP > 0 ? MP : 1];
-#pragma unroll
-    for (int i = 0; i < (MP > 0 ? MP : 1); ++i) dsum[i] = 0.f;
+    uint32_t gs = 0;                                  // pairs this CTA has started: mbarrier parities
+    bool alive = true;
 
-    for (int pl = 0; pl < npairs; ++pl) {
+    for (int item = blockIdx.x; item < nitems && alive; item += gridDim.x) {
+      decode(item);
+#pragma unroll
+      for (int i = 0; i < (MP > 0 ? MP : 1); ++i) dsum[i] = 0.f;
+      for (int pl = 0; pl < npairs; ++pl, ++gs) {
 #ifdef LLATTN_STAMPS
         int nstamp = 0;
-        const int stamp_slot = (blockIdx.x == 300 && pl == 2) ? (tid == 0 ? 0 : (tid == 200 ? 1 : (tid == 96 ? 2 : -1))) : -1;
+        const int stamp_slot = (blockIdx.x == 5 && gs == 6) ? (tid == 0 ? 0 : (tid == 200 ? 1 : (tid == 96 ? 2 : -1))) : -1;
 #endif
         STAMP();   // 0 top
         const long t0 = (long)(r * SEGP + pl) * tc::PT;
-        if (pl + 1 < npairs) {
-            fetch_small(pl + 1);
-            if (warp == TABLE_WARP) fetch_g(pl + 1);
+        // the pair after this one: the next of the segment, or the first pair of the CTA's next item
+        const int nitem = item + gridDim.x;
+        const bool have_next = (pl + 1 < npairs) || (nitem < nitems);
+        long ntok = (long)b * p.T + t0 + tc::PT;
+        int nh = h;
+        if (pl + 1 >= npairs && nitem < nitems) {
+            nh = nitem % p.H;
+            ntok = (long)(nitem / (p.H * p.NS)) * p.T + (long)((nitem / p.H) % p.NS) * SEGP * tc::PT;
+        }
+        if (have_next) {
+            fetch_small(ntok, nh);
+            if (warp == TABLE_WARP) fetch_g(ntok, nh);
         }
         STAMP();   // 1 small fetches issued
         int nread = 0;
@@ -326,10 +364,10 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_fwdorder_tc_kernel(con
 #pragma unroll
         for (int i = 0; i < NLAM; ++i) lam[i] = (i < L) ? __bfloat162float(sLam[row * tcb::LAMC + i]) : 0.f;
 
-        umma::mbar_wait(full_vd, pl & 1, abort_flag);
-        umma::mbar_wait(full_qk, pl & 1, abort_flag);
-        umma::mbar_wait(barA, pl & 1, abort_flag);
-        if (pl >= 1) umma::mbar_wait(stage_free, (pl - 1) & 1, abort_flag);   // dS / scaled-do space was the dq staging area
+        umma::mbar_wait(full_vd, gs & 1, abort_flag);
+        umma::mbar_wait(full_qk, gs & 1, abort_flag);
+        umma::mbar_wait(barA, gs & 1, abort_flag);
+        if (gs >= 1) umma::mbar_wait(stage_free, (gs - 1) & 1, abort_flag);   // dS / scaled-do space was the dq staging area
         umma::fence_after_sync();
 
         STAMP();   // 2 batch A complete
@@ -518,7 +556,7 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_fwdorder_tc_kernel(con
         STAMP();   // 6 after barrier 2
         // every read of this pair's decay tables is behind barrier 2 (what follows uses Gi / glp from registers):
         // one warp rebuilds them for the next pair while the second batch runs
-        if (warp == TABLE_WARP && pl + 1 < npairs) decay_tables(sGp);
+        if (warp == TABLE_WARP && have_next) decay_tables(sGp);
         // ---- dk tile: k_j . dk_j row sums, then fp32 staging for the TMA reduce-add.  The staging area is the q / k tile space,
         //      which the next pair's loads wait for, so it is filled as early as its halves become free: columns 0..63 (the
         //      warps of column half 0) go into the q tile as soon as the dk product - issued first in the batch - is complete,
@@ -554,7 +592,7 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_fwdorder_tc_kernel(con
             asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(umma::smem_addr(ch == 0 ? dk_ready : dk_ready1)) : "memory");
         };
         if (ch == 0) {
-            umma::mbar_wait(barDK, pl & 1, abort_flag);
+            umma::mbar_wait(barDK, gs & 1, abort_flag);
             umma::fence_after_sync();
             dk_half();
         }
@@ -601,7 +639,7 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_fwdorder_tc_kernel(con
         }
         STAMP();   // 7 dl / Z out
 
-        umma::mbar_wait(barB, pl & 1, abort_flag);
+        umma::mbar_wait(barB, gs & 1, abort_flag);
         umma::fence_after_sync();
         STAMP();   // 8 batch B complete
         if (ch == 1) dk_half();
@@ -660,13 +698,14 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_fwdorder_tc_kernel(con
             }
         }
         STAMP();   // 12 states merged
-        if (pl + 1 < npairs) store_lam();
+        if (have_next) store_lam();
         umma::fence_async_smem();
         umma::fence_before_sync();
         bar_work();                                  // barrier 3
         STAMP();   // 13 after barrier 3
         umma::fence_after_sync();
-        if (*abort_flag) break;
+        if (*abort_flag) { alive = false; break; }
+      }
     }
     umma::fence_before_sync();
     bar_work();
@@ -1275,7 +1314,11 @@ int mamba2_bwd1_tc_launch(const Mamba2Params& p_in, cudaStream_t stream) {
     const size_t sm = Bwd1TcSmem<M2_MLOW>::total;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
     if (e != cudaSuccess) return (int)e;
-    kern<<<p.B * p.H * p.NS, tc::NTHREADS, sm, stream>>>(p); LLATTN_LAUNCHED();
+    int dev = 0, sms = 0;
+    if ((e = cudaGetDevice(&dev)) != cudaSuccess) return (int)e;
+    if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return (int)e;
+    const int nitems = p.B * p.H * p.NS;
+    kern<<<nitems < sms ? nitems : sms, tc::NTHREADS, sm, stream>>>(p); LLATTN_LAUNCHED();      // persistent: one CTA per SM
     return (int)cudaGetLastError();
 }
 
