@@ -267,9 +267,16 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_hi_bwd_tc_kernel(const __g
                 umma::fence_before_sync();
                 bar_work();                          // the three slots may be reused
             }
-            if (i == 0) {
-                // the staging area of the previous pair (same memory as the scaled copies) has been read
-                if (tid == 0) tma::wait_group_read0();
+            if (i < 4) {
+                // The staging area of the previous pair's dq tile is the memory of the first four scaled copies: box i of
+                // the reduce-add (its own bulk group) must have been read before copy i is written.  Waiting box by box
+                // lets the first copy start after a quarter of the read.
+                if (tid == 0) {
+                    if (i == 0) tma::wait_group_read<3>();
+                    else if (i == 1) tma::wait_group_read<2>();
+                    else if (i == 2) tma::wait_group_read<1>();
+                    else tma::wait_group_read<0>();
+                }
                 bar_compute();
             }
             const float rs = lamv[i] * sc;
@@ -312,6 +319,11 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_hi_bwd_tc_kernel(const __g
         }
         umma::mbar_wait(barB, pl & 1, abort_flag);
         umma::fence_after_sync();
+        if (nl < 4) {
+            // boxes nl..3 of the previous pair's reduce-add were not waited for above
+            if (tid == 0) tma::wait_group_read<0>();
+            bar_compute();
+        }
         // ---- dq tile -> fp32 staging (the scaled copies are no longer needed) -> TMA reduce-add
 #pragma unroll
         for (int hb = 0; hb < 2; ++hb) {
@@ -328,8 +340,10 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_hi_bwd_tc_kernel(const __g
         if (tid == 0) {
             const int grow = b * p.T + (int)t0;
 #pragma unroll
-            for (int bx = 0; bx < 4; ++bx) tma::reduce_add_box(&p.tm_dq, bx * 32, grp, grow, sStage + bx * 16384);
-            tma::commit_group();
+            for (int bx = 0; bx < 4; ++bx) {
+                tma::reduce_add_box(&p.tm_dq, bx * 32, grp, grow, sStage + bx * 16384);
+                tma::commit_group();                 // one group per box: the next pair waits for them one by one
+            }
         }
         if (tid < 2 * nl) {
             const int i = tid >> 1, cpart = tid & 1;
@@ -348,7 +362,12 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_hi_bwd_tc_kernel(const __g
         umma::tmem_ld32(umma::tmem_addr(tbase + TM_DF + i * 64, warp, ch * 32), t);
         float* dF = p.seg_dF + ((((long)b * p.H + h) * p.NS + r) * p.LH + lev[i]) * tc::KD * tc::VD + row * tc::VD + ch * 32;
 #pragma unroll
-        for (int c = 0; c < 8; ++c) *reinterpret_cast<float4*>(dF + c * 4) = make_float4(t[c * 4], t[c * 4 + 1], t[c * 4 + 2], t[c * 4 + 3]);
+        for (int c = 0; c < 4; ++c) {
+            uint32_t w[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) w[e] = __float_as_uint(t[c * 8 + e]);
+            st_global_32B(dF + c * 8, w);            // a thread owns its row: 32-byte stores fill whole sectors
+        }
     }
     if (tid == 0) tma::wait_group0();
     umma::fence_before_sync();

@@ -89,6 +89,9 @@ __device__ __forceinline__ void commit_group() { asm volatile("cp.async.bulk.com
 __device__ __forceinline__ void wait_group_read0() { asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory"); }
 // the sources of every committed bulk operation of this thread but the latest group have been read
 __device__ __forceinline__ void wait_group_read1() { asm volatile("cp.async.bulk.wait_group.read 1;\n" ::: "memory"); }
+// ... but the latest N groups
+template <int N>
+__device__ __forceinline__ void wait_group_read() { asm volatile("cp.async.bulk.wait_group.read %0;\n" ::"n"(N) : "memory"); }
 // every committed bulk operation of this thread has completed
 __device__ __forceinline__ void wait_group0() { asm volatile("cp.async.bulk.wait_group 0;\n" ::: "memory"); }
 #endif
