@@ -655,7 +655,12 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_seg_state_tc_kernel(const 
         umma::tmem_ld32(umma::tmem_addr(tbase, warp, ch * 32), t);
         float* F = p.seg_F + (((long)b * p.H + h) * p.NS + r) * tc::KD * tc::VD + row * tc::VD + ch * 32;
 #pragma unroll
-        for (int c = 0; c < 8; ++c) *reinterpret_cast<float4*>(F + c * 4) = make_float4(t[c * 4], t[c * 4 + 1], t[c * 4 + 2], t[c * 4 + 3]);
+        for (int c = 0; c < 4; ++c) {
+            uint32_t w[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) w[e] = __float_as_uint(t[c * 8 + e]);
+            st_global_32B(F + c * 8, w);
+        }
     }
     if (tid == 0) p.seg_D[((long)b * p.H + h) * p.NS + r] = gend;
     umma::fence_before_sync();
