@@ -258,7 +258,7 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_chunk_kernel(const GdnParams p
                 float pv[2] = {0.f, 0.f}, dx[2] = {0.f, 0.f};
                 // 8 x 8 block of the fragment (the same for the whole warp): above the diagonal nothing; below it every
                 // element is causal and lies in one Fenwick level, whose d lambda sum goes through the four lanes of a row
-                // to a single shared-memory atomic; the diagonal blocks keep one atomic per element.
+                // to that row's single writer; the diagonal blocks sum their four levels the same way.
                 const int ib = (r0 >> 3) + hh, jb = cw * 4 + nt;
                 if (jb <= ib) {
                     const bool below = jb < ib;
