@@ -308,55 +308,70 @@ __global__ void __launch_bounds__(gpt::NTHREADS, 1) gdn_chunk_prep_tc_kernel(con
             }
             bar_compute();
             STAMPR();                                    // r0 diagonal blocks
-            {
-                // T = A_10 X_00: a thread computes eight adjacent columns of one row
-                const int cq = tid & 3, r = (tid >> 2) & 31, m = tid >> 7;
-                const float* Mrow = (m ? sAg : sA) + (BS + r) * LDA;
-                const float* Xc = sX + (m * CH) * LDA + cq * 8;
-                float acc[8];
+            // The two products run on 128 threads with a 4 x 4 register tile each (eight 16-byte loads per 64 FMAs): these
+            // phases are bound by shared-memory transactions, and one row x eight columns per thread on all 256 threads
+            // needed nine loads per 32 FMAs.  The order of summation over k is unchanged.
+            if (tid < 128) {
+                // T = A_10 X_00
+                const int m = tid >> 6, tr = (tid >> 3) & 7, tcq = tid & 7;
+                const float* Mrow = (m ? sAg : sA) + (BS + 4 * tr) * LDA;
+                const float* Xc = sX + (m * CH) * LDA + 4 * tcq;
+                float acc[4][4];
 #pragma unroll
-                for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+                for (int i = 0; i < 4; ++i)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
 #pragma unroll
                 for (int k4 = 0; k4 < BS; k4 += 4) {
-                    const float4 mm = *reinterpret_cast<const float4*>(Mrow + k4);
-                    const float mv[4] = {mm.x, mm.y, mm.z, mm.w};
+                    float4 av[4], bv[4];
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const float4 x0 = *reinterpret_cast<const float4*>(Xc + (k4 + e) * LDA);
-                        const float4 x1 = *reinterpret_cast<const float4*>(Xc + (k4 + e) * LDA + 4);
-                        acc[0] += mv[e] * x0.x; acc[1] += mv[e] * x0.y; acc[2] += mv[e] * x0.z; acc[3] += mv[e] * x0.w;
-                        acc[4] += mv[e] * x1.x; acc[5] += mv[e] * x1.y; acc[6] += mv[e] * x1.z; acc[7] += mv[e] * x1.w;
+                    for (int i = 0; i < 4; ++i) av[i] = *reinterpret_cast<const float4*>(Mrow + i * LDA + k4);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) bv[e] = *reinterpret_cast<const float4*>(Xc + (k4 + e) * LDA);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const float ae[4] = {av[i].x, av[i].y, av[i].z, av[i].w};
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            acc[i][0] += ae[e] * bv[e].x; acc[i][1] += ae[e] * bv[e].y; acc[i][2] += ae[e] * bv[e].z; acc[i][3] += ae[e] * bv[e].w;
+                        }
                     }
                 }
-                float* T = sT + (m * BS + r) * BS + cq * 8;
-                *reinterpret_cast<float4*>(T) = make_float4(acc[0], acc[1], acc[2], acc[3]);
-                *reinterpret_cast<float4*>(T + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    *reinterpret_cast<float4*>(sT + (m * BS + 4 * tr + i) * BS + 4 * tcq) = make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
             }
             bar_compute();
             STAMPR();                                    // r1 first product
-            {
+            if (tid < 128) {
                 // X_10 = -X_11 T
-                const int cq = tid & 3, r = (tid >> 2) & 31, m = tid >> 7;
-                const float* Xii = sX + (m * CH + BS + r) * LDA + BS;
-                const float* T = sT + (m * BS) * BS + cq * 8;
-                float acc[8];
+                const int m = tid >> 6, tr = (tid >> 3) & 7, tcq = tid & 7;
+                const float* Xii = sX + (m * CH + BS + 4 * tr) * LDA + BS;
+                const float* T = sT + (m * BS) * BS + 4 * tcq;
+                float acc[4][4];
 #pragma unroll
-                for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+                for (int i = 0; i < 4; ++i)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
 #pragma unroll
                 for (int k4 = 0; k4 < BS; k4 += 4) {
-                    const float4 xx = *reinterpret_cast<const float4*>(Xii + k4);
-                    const float xs[4] = {xx.x, xx.y, xx.z, xx.w};
+                    float4 av[4], bv[4];
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const float4 t0 = *reinterpret_cast<const float4*>(T + (k4 + e) * BS);
-                        const float4 t1 = *reinterpret_cast<const float4*>(T + (k4 + e) * BS + 4);
-                        acc[0] -= xs[e] * t0.x; acc[1] -= xs[e] * t0.y; acc[2] -= xs[e] * t0.z; acc[3] -= xs[e] * t0.w;
-                        acc[4] -= xs[e] * t1.x; acc[5] -= xs[e] * t1.y; acc[6] -= xs[e] * t1.z; acc[7] -= xs[e] * t1.w;
+                    for (int i = 0; i < 4; ++i) av[i] = *reinterpret_cast<const float4*>(Xii + i * LDA + k4);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) bv[e] = *reinterpret_cast<const float4*>(T + (k4 + e) * BS);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const float ae[4] = {av[i].x, av[i].y, av[i].z, av[i].w};
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            acc[i][0] -= ae[e] * bv[e].x; acc[i][1] -= ae[e] * bv[e].y; acc[i][2] -= ae[e] * bv[e].z; acc[i][3] -= ae[e] * bv[e].w;
+                        }
                     }
                 }
-                float* X = sX + (m * CH + BS + r) * LDA + cq * 8;
-                *reinterpret_cast<float4*>(X) = make_float4(acc[0], acc[1], acc[2], acc[3]);
-                *reinterpret_cast<float4*>(X + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    *reinterpret_cast<float4*>(sX + (m * CH + BS + 4 * tr + i) * LDA + 4 * tcq) = make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
             }
             bar_compute();
             STAMPR();                                    // r2 second product
