@@ -512,6 +512,24 @@ __global__ void __launch_bounds__(gpt::NTHREADS, 1) gdn_chunk_prep_tc_kernel(con
             float x[16];
             const int j0 = ch * 32 + half * 16;
             umma::tmem_ld16(umma::tmem_addr(tbase + gpt::TM_X, warp, j0), x);
+            // The Fenwick level of (i, j) is the position of the highest bit in which they differ.  The low four bits of j are
+            // compile-time constants here and its upper two are the same for the whole warp, so "bit k differs" is one of the
+            // row's own bits or its complement: lambda is picked from registers with six selects, and the decay and beta of
+            // the sixteen columns come in eight 16-byte loads.
+            float lamr[8];
+            {
+                const float4 l0 = *reinterpret_cast<const float4*>(sLam + i * 8), l1 = *reinterpret_cast<const float4*>(sLam + i * 8 + 4);
+                lamr[0] = l0.x; lamr[1] = l0.y; lamr[2] = l0.z; lamr[3] = l0.w; lamr[4] = l1.x; lamr[5] = l1.y; lamr[6] = l1.z; lamr[7] = l1.w;
+            }
+            const bool B0 = i & 1, B1 = i & 2, B2 = i & 4, B3 = i & 8;
+            const bool q4 = bool(i & 16) != bool(j0 & 16), q5 = bool(i & 32) != bool(j0 & 32);
+            float gcv[16], bev[16];
+#pragma unroll
+            for (int c4 = 0; c4 < 4; ++c4) {
+                const float4 g4 = *reinterpret_cast<const float4*>(sGc + j0 + c4 * 4), b4 = *reinterpret_cast<const float4*>(sBe + j0 + c4 * 4);
+                gcv[c4 * 4] = g4.x; gcv[c4 * 4 + 1] = g4.y; gcv[c4 * 4 + 2] = g4.z; gcv[c4 * 4 + 3] = g4.w;
+                bev[c4 * 4] = b4.x; bev[c4 * 4 + 1] = b4.y; bev[c4 * 4 + 2] = b4.z; bev[c4 * 4 + 3] = b4.w;
+            }
 #pragma unroll
             for (int cc = 0; cc < 2; ++cc) {
                 uint32_t w[4];
@@ -520,8 +538,16 @@ __global__ void __launch_bounds__(gpt::NTHREADS, 1) gdn_chunk_prep_tc_kernel(con
                     float pv[2];
 #pragma unroll
                     for (int u = 0; u < 2; ++u) {
-                        const int j = j0 + cc * 8 + e * 2 + u;
-                        pv[u] = (j <= i) ? x[cc * 8 + e * 2 + u] * fexp(gi - sGc[j]) * sBe[j] * sLam[i * 8 + level_of(i, j)] : 0.f;
+                        const int jl = cc * 8 + e * 2 + u;           // low four bits of the column
+                        const int j = j0 + jl;
+                        const bool q0 = (jl & 1) ? !B0 : B0, q1 = (jl & 2) ? !B1 : B1, q2 = (jl & 4) ? !B2 : B2, q3 = (jl & 8) ? !B3 : B3;
+                        float lm = q0 ? lamr[1] : lamr[0];
+                        lm = q1 ? lamr[2] : lm;
+                        lm = q2 ? lamr[3] : lm;
+                        lm = q3 ? lamr[4] : lm;
+                        lm = q4 ? lamr[5] : lm;
+                        lm = q5 ? lamr[6] : lm;
+                        pv[u] = (j <= i) ? x[jl] * fexp(gi - gcv[jl]) * bev[jl] * lm : 0.f;
                     }
                     w[e] = pack_bf16(pv[0], pv[1]);
                 }
@@ -544,14 +570,17 @@ __global__ void __launch_bounds__(gpt::NTHREADS, 1) gdn_chunk_prep_tc_kernel(con
             for (int hb = 0; hb < 2; ++hb) {
                 float t[32];
                 umma::tmem_ld32(umma::tmem_addr(tbase + gpt::TM_WD, warp, ch * 64 + hb * 32), t);
+                // the diagonal of the 128 x 128 matrix crosses this warp's rows in one 32-column block only (the same for the
+                // whole warp), at column `lane` of it; everything else is a negation, done on the packed words
+                if (ch * 2 + hb == (row >> 5)) {
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) t[e] = (e == lane) ? t[e] - decm1 : t[e];
+                }
 #pragma unroll
                 for (int c2 = 0; c2 < 2; ++c2) {
                     uint32_t w[8];
 #pragma unroll
-                    for (int e = 0; e < 8; ++e) {
-                        const int col = ch * 64 + hb * 32 + c2 * 16 + e * 2;
-                        w[e] = pack_bf16(-t[c2 * 16 + e * 2] + (col == row ? decm1 : 0.f), -t[c2 * 16 + e * 2 + 1] + (col + 1 == row ? decm1 : 0.f));
-                    }
+                    for (int e = 0; e < 8; ++e) w[e] = pack_bf16(t[c2 * 16 + e * 2], t[c2 * 16 + e * 2 + 1]) ^ 0x80008000u;
                     st_global_32B(dst + hb * 32 + c2 * 16, w);
                 }
             }
