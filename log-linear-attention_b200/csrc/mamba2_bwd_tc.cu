@@ -253,13 +253,14 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_fwdorder_tc_kernel(con
     const int ch = warp >> 2;
 
     float g_n[4];
-    constexpr int LAMR = (tc::PT * tc::MAX_L_TC) / 256;
+    constexpr int LAMR = (tc::PT * NLAM + 255) / 256;   // only the NLAM columns these kernels read are fetched
     uint32_t lam_r[LAMR];
     uint32_t lam_rc[LAMR];
+    const int NC = L < NLAM ? L : NLAM;             // columns of a lambda row that are fetched
 #pragma unroll
     for (int i = 0; i < LAMR; ++i) {
         const int e = tid + i * 256;
-        const int rr = e / L, cc = e - rr * L;
+        const int rr = e / NC, cc = e - rr * NC;
         lam_rc[i] = (rr < tc::PT) ? (uint32_t)((rr << 8) | cc) : 0xffffffffu;
     }
     // (tok0: first token of the pair counted over the whole batch, b * T + t0; hh: its head)
@@ -897,13 +898,14 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_revorder_tc_kernel(con
     const int ch = warp >> 2;
 
     float g_n[4];
-    constexpr int LAMR = (tc::PT * tc::MAX_L_TC) / 256;
+    constexpr int LAMR = (tc::PT * tc::MAX_L_TC) / 256;   // (every column: fetching only the NLAM columns read here made this kernel spill)
     uint32_t lam_r[LAMR];
     uint32_t lam_rc[LAMR];
+    const int NC = L;
 #pragma unroll
     for (int i = 0; i < LAMR; ++i) {
         const int e = tid + i * 256;
-        const int rr = e / L, cc = e - rr * L;
+        const int rr = e / NC, cc = e - rr * NC;
         lam_rc[i] = (rr < tc::PT) ? (uint32_t)((rr << 8) | cc) : 0xffffffffu;
     }
     auto fetch_small = [&](int pl) {

@@ -160,13 +160,14 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_chunk_fwd_tc_kernel(const 
     // lambda rows of the pair (two threads per row, staged through shared memory) and raw g of the
     // pair (warps 0 and 1), fetched one pair ahead
     float g_n[4];
-    constexpr int LAMR = (tc::PT * tc::MAX_L_TC) / 256;   // elements per thread, consecutive threads on consecutive elements
+    constexpr int LAMR = (tc::PT * NLAM + 255) / 256;   // only the NLAM columns these kernels read are fetched
     uint32_t lam_r[LAMR];                            // one 32-bit register per 16-bit element
     uint32_t lam_rc[LAMR];                           // (row << 8) | column of each element, 0xffffffff = none
+    const int NC = L < NLAM ? L : NLAM;             // columns of a lambda row that are fetched
 #pragma unroll
     for (int i = 0; i < LAMR; ++i) {
         const int e = tid + i * 256;
-        const int rr = e / L, cc = e - rr * L;
+        const int rr = e / NC, cc = e - rr * NC;
         lam_rc[i] = (rr < tc::PT) ? (uint32_t)((rr << 8) | cc) : 0xffffffffu;
     }
     auto fetch_small = [&](int pl) {
