@@ -251,6 +251,10 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_chunk_kernel(const GdnParams p
 #pragma unroll
         for (int nt = 0; nt < 4; ++nt) {
             float cs[2] = {0.f, 0.f}, cb[2] = {0.f, 0.f};
+            // G and beta of this thread's two columns: one 8-byte load each per 8-column tile
+            const float2 gj2 = *reinterpret_cast<const float2*>(sG + cw * 32 + nt * 8 + lc2);
+            const float2 bj2 = *reinterpret_cast<const float2*>(sBe + cw * 32 + nt * 8 + lc2);
+            const float gjv[2] = {gj2.x, gj2.y}, bjv[2] = {bj2.x, bj2.y};
 #pragma unroll
             for (int hh = 0; hh < 2; ++hh) {
                 const int i = r0 + lr + hh * 8;
@@ -270,7 +274,7 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_chunk_kernel(const GdnParams p
                         const int j = cw * 32 + nt * 8 + lc2 + e;
                         if (below || j <= i) {
                             const int lev = below ? levb : level_of(i, j);
-                            const float gam = fexp(gi - sG[j]), bj = sBe[j], lm = sLam[i * 8 + lev];
+                            const float gam = fexp(gi - gjv[e]), bj = bjv[e], lm = sLam[i * 8 + lev];
                             const float x = accX[0][nt][hh * 2 + e], dp = accP[0][nt][hh * 2 + e];
                             const float xg = dp * x * gam;
                             pv[e] = x * gam * bj * lm;
@@ -502,18 +506,21 @@ __global__ void __launch_bounds__(256, 1) gdn_bwd_chunk_kernel(const GdnParams p
 #pragma unroll
         for (int nt = 0; nt < 4; ++nt) {
             float cs[2] = {0.f, 0.f};
+            const float2 gjA2 = *reinterpret_cast<const float2*>(sG + cw * 32 + nt * 8 + lc2);
+            const float gjA[2] = {gjA2.x, gjA2.y};
 #pragma unroll
             for (int hh = 0; hh < 2; ++hh) {
                 const int i = r0 + lr + hh * 8;
                 const float gi = sG[i], bi = sBe[i];
                 float dkk[2] = {0.f, 0.f};
+                const float2 kkv = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(sKK + i * LDP + cw * 32 + nt * 8 + lc2));
                 if (cw * 4 + nt <= (r0 >> 3) + hh)       // 8 x 8 blocks above the diagonal hold no causal pair (the same for the whole warp)
 #pragma unroll
                 for (int e = 0; e < 2; ++e) {
                     const int j = cw * 32 + nt * 8 + lc2 + e;
                     if (j < i) {
-                        const float gam = fexp(gi - sG[j]);
-                        const float kk = __bfloat162float(sKK[i * LDP + j]);
+                        const float gam = fexp(gi - gjA[e]);
+                        const float kk = e ? kkv.y : kkv.x;
                         const float dag = -dAg[0][nt][hh * 2 + e];
                         const float s = dag * bi * kk * gam;
                         rs[hh] += s;
