@@ -98,6 +98,13 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_hi_bwd_tc_kernel(const __g
     uint32_t* sink = reinterpret_cast<uint32_t*>(smem + SM::sink_off);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+#ifdef LLATTN_STAMPS
+    // one CTA's life: entry, before / after the segment's cumulative decay, top of each pair, end of the pairs, reader summaries
+    // written, reduce-adds complete, exit (thread 0)
+    int nstamp = 0;
+    const int stamp_slot = (blockIdx.x == 700 && tid == 0) ? 0 : -1;
+#endif
+    STAMP();
     const int h = blockIdx.x % p.H;
     const int r = 1 + (blockIdx.x / p.H) % (p.NS - 1);
     const int b = blockIdx.x / (p.H * (p.NS - 1));
@@ -218,7 +225,9 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_hi_bwd_tc_kernel(const __g
     const int rb = warp & 3;
     const int row = rb * 32 + lane;
     const int ch = warp >> 2;
+    STAMP();
     segment_cumsum<SEG>(p, b, h, r, nchunks, sGs, sTot, warp, lane, tid);
+    STAMP();
     umma::fence_before_sync();
     bar_work();
     umma::fence_after_sync();
@@ -237,6 +246,7 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_hi_bwd_tc_kernel(const __g
     fetch_lambda(0);
 
     for (int pl = 0; pl < npairs; ++pl) {
+        STAMP();
         const long t0 = (long)(r * SEG) * CH + (long)pl * tc::PT;
         const float sc = fexp(sGs[pl * tc::PT + row]);          // exp(G_i) from the segment start
         float lamv[tcs::MAXLH];
@@ -356,6 +366,7 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_hi_bwd_tc_kernel(const __g
         umma::fence_after_sync();
         if (*abort_flag) break;
     }
+    STAMP();
     // ---- dF[r][j] out
     for (int i = 0; i < nl; ++i) {
         float t[32];
@@ -369,9 +380,12 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_hi_bwd_tc_kernel(const __g
             st_global_32B(dF + c * 8, w);            // a thread owns its row: 32-byte stores fill whole sectors
         }
     }
+    STAMP();
     if (tid == 0) tma::wait_group0();
+    STAMP();
     umma::fence_before_sync();
     bar_work();
+    STAMP();
 }
 
 // ------------------------------------------------------------------------------------------
@@ -726,3 +740,9 @@ int mamba2_hi_bwd_tc_launch(const Mamba2Params& p_in, cudaStream_t stream) {
 }
 
 }  // namespace llattn
+
+#ifdef LLATTN_STAMPS
+extern "C" int llattn_debug_read_stamps_seg(long long* host_dst) {
+    return (int)cudaMemcpyFromSymbol(host_dst, llattn::g_stamps, sizeof(llattn::g_stamps));
+}
+#endif

@@ -110,6 +110,15 @@ def test_phase_clock_stamps_of_one_pair():
         o, gc, _ = chunkwise_fwd(q, k, v, g, l, False, 2, HType.WEAK, 64, False, keep_workspace=kept)
         chunkwise_bwd(q, k, v, gc, l, do, False, 2, HType.WEAK, 64, fwd_workspace=kept[0])
     torch.cuda.synchronize()
+    if hasattr(lib, "llattn_debug_read_stamps_seg"):
+        # one CTA of the high-level backward kernel: entry, before / after the segment's cumulative decay, top of each pair,
+        # end of the pairs, reader summaries written, reduce-adds complete, exit
+        buf = (ctypes.c_longlong * 96)()
+        f = lib.llattn_debug_read_stamps_seg
+        f.argtypes = [ctypes.c_void_p]
+        assert f(buf) == 0
+        d = list(buf)[:16]
+        print("high-level backward, one CTA", [x - d[0] if x else None for x in d])
     for name, fn in (("forward", "llattn_debug_read_stamps"), ("backward", "llattn_debug_read_stamps_bwd")):
         buf = (ctypes.c_longlong * 96)()
         f = getattr(lib, fn)
