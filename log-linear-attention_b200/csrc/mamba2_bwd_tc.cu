@@ -73,17 +73,19 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_fwdorder_tc_kernel(con
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SM::bar_off);
     uint64_t* barA = bars + 0;      // first MMA batch complete
     uint64_t* barB = bars + 1;      // second MMA batch complete
-    uint64_t* full_qk = bars + 2;   // TMA: q and k tiles
+    uint64_t* full_qk = bars + 2;   // TMA: q tile
     uint64_t* full_vd = bars + 3;   // TMA: v and do tiles
-    uint64_t* empty_qk = bars + 4;  // q / k tiles may be refilled
+    uint64_t* empty_qk = bars + 4;  // the q tile may be refilled (the first half of the dk reduce-add has read it)
     uint64_t* empty_vd = bars + 5;  // v / do tiles may be refilled
     uint64_t* dq_ready = bars + 6;  // the dq tile of the pair is staged (fp32) for the store agent
     uint64_t* dk_ready = bars + 7;  // ... columns 0..63 of the dk tile (128 arrivals: the warps of column half 0)
     uint64_t* stage_free = bars + 8;   // the store agent's reduce-adds have read both staging areas
     uint64_t* barDK = bars + 9;     // the dk product (first of the second batch) is complete: the q tile is free
     uint64_t* dk_ready1 = bars + 10;   // columns 64..127 of the dk tile are staged (128 arrivals: column half 1)
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + SM::bar_off + 96);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + SM::bar_off + 104);
+    uint64_t* full_k = bars + 11;   // TMA: k tile (loaded separately: its space is released later than the q tile's)
+    uint64_t* empty_k = bars + 12;  // the k tile may be refilled (the second half of the dk reduce-add has read it)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + SM::bar_off + 112);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + SM::bar_off + 120);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     // Persistent CTAs: one per SM walks the (batch, segment, head) items blockIdx.x, blockIdx.x + gridDim.x, ...  Every role
@@ -106,6 +108,8 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_fwdorder_tc_kernel(con
 #pragma unroll
         for (int i = 0; i < 10; ++i) umma::mbar_init(&bars[i], i == 7 ? 128 : 1);
         umma::mbar_init(dk_ready1, 128);
+        umma::mbar_init(full_k, 1);
+        umma::mbar_init(empty_k, 1);
         umma::fence_mbar_init();
         *abort_flag = *p.err;
     }
@@ -135,11 +139,13 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_fwdorder_tc_kernel(con
                         tma::load_panel(sV, &p.tm_v, 0, h, row0, full_vd);
                         tma::load_panel(sDO, &p.tm_do, 0, h, row0, full_vd);
                         if (gs >= 1 && !umma::mbar_wait(empty_qk, (gs - 1) & 1, abort_flag)) { ok = false; break; }
-                        tma::expect_tx(full_qk, 2 * tc::Q_BYTES);
+                        tma::expect_tx(full_qk, tc::Q_BYTES);
                         tma::load_panel(sQ, &p.tm_q, 0, grp, row0, full_qk);
                         tma::load_panel(sQ + tc::Q_BYTES / 2, &p.tm_q, 64, grp, row0, full_qk);
-                        tma::load_panel(sK, &p.tm_k, 0, grp, row0, full_qk);
-                        tma::load_panel(sK + tc::Q_BYTES / 2, &p.tm_k, 64, grp, row0, full_qk);
+                        if (gs >= 1 && !umma::mbar_wait(empty_k, (gs - 1) & 1, abort_flag)) { ok = false; break; }
+                        tma::expect_tx(full_k, tc::Q_BYTES);
+                        tma::load_panel(sK, &p.tm_k, 0, grp, row0, full_k);
+                        tma::load_panel(sK + tc::Q_BYTES / 2, &p.tm_k, 64, grp, row0, full_k);
                     }
                 }
             }
@@ -163,12 +169,14 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_fwdorder_tc_kernel(con
 #pragma unroll
                     for (int bx = 0; bx < 2; ++bx) tma::reduce_add_box(&p.tm_dk, bx * 32, grp, grow, sStage2 + bx * 16384);
                     tma::commit_group();
+                    tma::wait_group_read0();             // the q tile's space has been read: the next q may be loaded
+                    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(umma::smem_addr(empty_qk)) : "memory");
                     if (!umma::mbar_wait(dk_ready1, gs & 1, abort_flag)) { ok = false; break; }
 #pragma unroll
                     for (int bx = 2; bx < 4; ++bx) tma::reduce_add_box(&p.tm_dk, bx * 32, grp, grow, sStage2 + bx * 16384);
                     tma::commit_group();
                     tma::wait_group_read0();
-                    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(umma::smem_addr(empty_qk)) : "memory");
+                    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(umma::smem_addr(empty_k)) : "memory");
                     if (!umma::mbar_wait(dq_ready, gs & 1, abort_flag)) { ok = false; break; }
 #pragma unroll
                     for (int bx = 0; bx < 4; ++bx) tma::reduce_add_box(&p.tm_dq, bx * 32, grp, grow, sStage + bx * 16384);
@@ -196,10 +204,12 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_fwdorder_tc_kernel(con
           for (int pl = 0; pl < npairs; ++pl, ++gs) {
             // (no barrier here: the end-of-pair barrier of the previous pair is all the tensor core needs)
             if (lane == 0) {
-                umma::mbar_wait(full_qk, gs & 1, abort_flag);
+                // dP needs only v and do, which land long before q and k (their space doubles as the dk staging area)
                 umma::mbar_wait(full_vd, gs & 1, abort_flag);
-                umma::gemm_kk<tc::PT, tc::PT, tc::KD>(tbase + tcb::TB_S, aQ, aK, ID_KK128, false);
                 umma::gemm_kk<tc::PT, tc::PT, tc::VD>(tbase + tcb::TB_DP, aDO, aV, ID_KK128, false);
+                umma::mbar_wait(full_qk, gs & 1, abort_flag);
+                umma::mbar_wait(full_k, gs & 1, abort_flag);
+                umma::gemm_kk<tc::PT, tc::PT, tc::KD>(tbase + tcb::TB_S, aQ, aK, ID_KK128, false);
                 int slot = 0;
 #pragma unroll
                 for (int lv = 0; lv < MP; ++lv)
@@ -367,6 +377,7 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_fwdorder_tc_kernel(con
 
         umma::mbar_wait(full_vd, gs & 1, abort_flag);
         umma::mbar_wait(full_qk, gs & 1, abort_flag);
+        umma::mbar_wait(full_k, gs & 1, abort_flag);
         umma::mbar_wait(barA, gs & 1, abort_flag);
         if (gs >= 1) umma::mbar_wait(stage_free, (gs - 1) & 1, abort_flag);   // dS / scaled-do space was the dq staging area
         umma::fence_after_sync();
