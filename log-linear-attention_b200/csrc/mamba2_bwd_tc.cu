@@ -64,7 +64,7 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_fwdorder_tc_kernel(con
     unsigned char* sStage2 = smem + SM::q_off;          // 64 KB fp32 staging for dk = q + k tiles (free once the second batch and the k row sums are done)
     unsigned char* sVs = smem + SM::vs_off;
     float* sDL = reinterpret_cast<float*>(smem + SM::dl_off);            // [2][128][NDL]
-    float* sWk = reinterpret_cast<float*>(smem + SM::misc_off);          // [2][128] partial k.dk, then [4][16] Z partials
+    float* sWk = reinterpret_cast<float*>(smem + SM::misc_off);          // [4][128] partial k.dk per 32-column box; [4][16] Z partials at +256 (consumed before boxes 2, 3 write there)
     unsigned char* sH = smem + SM::h_off;
     float* sGp = reinterpret_cast<float*>(smem + SM::gp_off);
     float* sCf = sGp + 128;
@@ -107,7 +107,7 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_fwdorder_tc_kernel(con
     if (tid == 0) {
 #pragma unroll
         for (int i = 0; i < 10; ++i) umma::mbar_init(&bars[i], i == 7 ? 128 : 1);
-        umma::mbar_init(dk_ready1, 128);
+        umma::mbar_init(dk_ready1, 256);
         umma::mbar_init(full_k, 1);
         umma::mbar_init(empty_k, 1);
         umma::fence_mbar_init();
@@ -573,40 +573,36 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_fwdorder_tc_kernel(con
         //      which the next pair's loads wait for, so it is filled as early as its halves become free: columns 0..63 (the
         //      warps of column half 0) go into the q tile as soon as the dk product - issued first in the batch - is complete,
         //      columns 64..127 into the k tile once dq and KV are complete and every thread is done with its k row sums.
-        auto dk_half = [&]() {
+        // One 32-column box of the dk tile: k . dk partial row sum (slot `slot` of sWk), fp32 staging of the box
+        auto dk_box = [&](int bx, int slot, bool k_tile_barrier) {
+            float dkv[32];
+            umma::tmem_ld32(umma::tmem_addr(tbase + tcb::TB_DK, warp, bx * 32), dkv);
             float wk_part = 0.f;
-            float dkv[2][32];
 #pragma unroll
-            for (int hb = 0; hb < 2; ++hb) {
-                umma::tmem_ld32(umma::tmem_addr(tbase + tcb::TB_DK, warp, ch * 64 + hb * 32), dkv[hb]);
+            for (int c = 0; c < 4; ++c) {
+                const uint4 kx = *reinterpret_cast<const uint4*>(sK + umma::tile_offset(row, bx * 32 + c * 8, tc::PT));
+                const uint32_t* xw = reinterpret_cast<const uint32_t*>(&kx);
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    const uint4 kx = *reinterpret_cast<const uint4*>(sK + umma::tile_offset(row, ch * 64 + hb * 32 + c * 8, tc::PT));
-                    const uint32_t* xw = reinterpret_cast<const uint32_t*>(&kx);
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        __nv_bfloat162 v2 = *reinterpret_cast<const __nv_bfloat162*>(&xw[e]);
-                        wk_part += __bfloat162float(v2.x) * dkv[hb][c * 8 + e * 2] + __bfloat162float(v2.y) * dkv[hb][c * 8 + e * 2 + 1];
-                    }
+                for (int e = 0; e < 4; ++e) {
+                    __nv_bfloat162 v2 = *reinterpret_cast<const __nv_bfloat162*>(&xw[e]);
+                    wk_part += __bfloat162float(v2.x) * dkv[c * 8 + e * 2] + __bfloat162float(v2.y) * dkv[c * 8 + e * 2 + 1];
                 }
             }
-            sWk[ch * 128 + row] = wk_part;
-            if (ch == 1) asm volatile("bar.sync 3, 128;\n" ::: "memory");   // the warps of this half are done with the k tile they overwrite
+            sWk[slot * 128 + row] = wk_part;
+            if (k_tile_barrier) bar_compute();       // every thread is done with the k tile that the boxes 2 and 3 overwrite
+            unsigned char* box = sStage2 + bx * 16384;
 #pragma unroll
-            for (int hb = 0; hb < 2; ++hb) {
-                unsigned char* box = sStage2 + (ch * 2 + hb) * 16384;
-#pragma unroll
-                for (int c = 0; c < 8; ++c)
-                    *reinterpret_cast<float4*>(box + box_offset(row, c * 4)) =
-                        make_float4(dkv[hb][c * 4], dkv[hb][c * 4 + 1], dkv[hb][c * 4 + 2], dkv[hb][c * 4 + 3]);
-            }
-            umma::fence_async_smem();
-            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(umma::smem_addr(ch == 0 ? dk_ready : dk_ready1)) : "memory");
+            for (int c = 0; c < 8; ++c)
+                *reinterpret_cast<float4*>(box + box_offset(row, c * 4)) = make_float4(dkv[c * 4], dkv[c * 4 + 1], dkv[c * 4 + 2], dkv[c * 4 + 3]);
         };
         if (ch == 0) {
+            // columns 0..63 (boxes 0, 1) by the warps of column half 0, into the q tile
             umma::mbar_wait(barDK, gs & 1, abort_flag);
             umma::fence_after_sync();
-            dk_half();
+            dk_box(0, 0, false);
+            dk_box(1, 1, false);
+            umma::fence_async_smem();
+            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(umma::smem_addr(dk_ready)) : "memory");
         }
         // ---- while the second batch runs: dlambda out (coalesced), q.dq row sums, reader totals Z per chunk
         {
@@ -654,7 +650,11 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_fwdorder_tc_kernel(con
         umma::mbar_wait(barB, gs & 1, abort_flag);
         umma::fence_after_sync();
         STAMP();   // 8 batch B complete
-        if (ch == 1) dk_half();
+        // columns 64..127 (boxes 2, 3) into the k tile: one box per warp of a lane quarter, so that this step on the critical
+        // path (the k tile's reload waits for the reduce-add of these boxes) takes half as long
+        dk_box(2 + ch, 2 + ch, true);
+        umma::fence_async_smem();
+        asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(umma::smem_addr(dk_ready1)) : "memory");
         STAMP();   // 9 dk staged
         // ---- dq tile -> fp32 staging (dS + scaled do space) -> TMA reduce-add
 #pragma unroll
@@ -671,7 +671,7 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_fwdorder_tc_kernel(con
         bar_compute();
         if (tid == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(umma::smem_addr(dq_ready)) : "memory");
         if (ch == 1) {
-            const float w = wq_row - (sWk[row] + sWk[128 + row]);
+            const float w = wq_row - ((sWk[row] + sWk[128 + row]) + (sWk[256 + row] + sWk[384 + row]));
             red_add_f32(p.wq + ((long)b * p.T + t0 + row) * p.H + h, w);
         }
         STAMP();   // 11 reduces issued
