@@ -207,9 +207,8 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_fwdorder_tc_kernel(con
                 // dP needs only v and do, which land long before q and k (their space doubles as the dk staging area)
                 umma::mbar_wait(full_vd, gs & 1, abort_flag);
                 umma::gemm_kk<tc::PT, tc::PT, tc::VD>(tbase + tcb::TB_DP, aDO, aV, ID_KK128, false);
+                // the level reads need q only; S = q k^T goes last, when the k tile (released last) has landed
                 umma::mbar_wait(full_qk, gs & 1, abort_flag);
-                umma::mbar_wait(full_k, gs & 1, abort_flag);
-                umma::gemm_kk<tc::PT, tc::PT, tc::KD>(tbase + tcb::TB_S, aQ, aK, ID_KK128, false);
                 int slot = 0;
 #pragma unroll
                 for (int lv = 0; lv < MP; ++lv)
@@ -218,6 +217,8 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_fwdorder_tc_kernel(con
                                                               umma::smem_addr(sH + lv * tc::H_BYTES), ID_KM64, false);
                         ++slot;
                     }
+                umma::mbar_wait(full_k, gs & 1, abort_flag);
+                umma::gemm_kk<tc::PT, tc::PT, tc::KD>(tbase + tcb::TB_S, aQ, aK, ID_KK128, false);
                 umma::commit(barA);
             }
             __syncwarp();
