@@ -795,7 +795,7 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_revorder_tc_kernel(con
 
     if (tid == 0) {
 #pragma unroll
-        for (int i = 0; i < 9; ++i) umma::mbar_init(&bars[i], 1);
+        for (int i = 0; i < 9; ++i) umma::mbar_init(&bars[i], i == 5 ? 256 : 1);   // empty_k: one arrival per element-wise thread
         umma::mbar_init(early_ready, 256);
         umma::fence_mbar_init();
         *abort_flag = *p.err;
@@ -814,18 +814,19 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_revorder_tc_kernel(con
                 const int brow = b * p.T + r * SEGP * tc::PT;
                 for (int it = 0; it < npairs; ++it) {
                     const int row0 = brow + (npairs - 1 - it) * tc::PT;
-                    // q, v, do are free as soon as the previous pair's second batch is done; k a little later,
-                    // after its row sums: the loads then overlap the read-out of that pair's results
-                    if (it >= 1 && !umma::mbar_wait(empty_qvd, (it - 1) & 1, abort_flag)) break;
+                    // k is free once the element-wise threads have taken its row sums (its products belong to the early part of
+                    // the second batch); q, v, do once the whole second batch is done: the loads overlap the read-out of that
+                    // pair's results
+                    if (it >= 1 && !umma::mbar_wait(empty_k, (it - 1) & 1, abort_flag)) break;
                     tma::expect_tx(full_qk, 2 * tc::Q_BYTES);
+                    tma::load_panel(sK, &p.tm_k, 0, grp, row0, full_qk);
+                    tma::load_panel(sK + tc::Q_BYTES / 2, &p.tm_k, 64, grp, row0, full_qk);
+                    if (it >= 1 && !umma::mbar_wait(empty_qvd, (it - 1) & 1, abort_flag)) break;
                     tma::load_panel(sQ, &p.tm_q, 0, grp, row0, full_qk);
                     tma::load_panel(sQ + tc::Q_BYTES / 2, &p.tm_q, 64, grp, row0, full_qk);
                     tma::expect_tx(full_vd, 2 * tc::V_BYTES);
                     tma::load_panel(sV, &p.tm_v, 0, h, row0, full_vd);
                     tma::load_panel(sDO, &p.tm_do, 0, h, row0, full_vd);
-                    if (it >= 1 && !umma::mbar_wait(empty_k, (it - 1) & 1, abort_flag)) break;
-                    tma::load_panel(sK, &p.tm_k, 0, grp, row0, full_qk);
-                    tma::load_panel(sK + tc::Q_BYTES / 2, &p.tm_k, 64, grp, row0, full_qk);
                 }
             }
             return;
@@ -1212,6 +1213,9 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_revorder_tc_kernel(con
             }
         }
         sMisc[ch * 128 + row] = wk_part;
+        // the k tile has no reader left (its products completed with barB1): released here, not at the end of the pair, so that
+        // the next pair's k is in flight while dv, the dk staging and the state updates run
+        asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(umma::smem_addr(empty_k)) : "memory");
         STAMPR();   // 7 Y, decay, k row sums
         // ---- then what needs the whole batch: P (staging area of dk) and the scaled do are free, dv and the insertions are there
         umma::mbar_wait(barB, it & 1, abort_flag);
@@ -1261,8 +1265,7 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_revorder_tc_kernel(con
         umma::fence_async_smem();
         bar_compute();
         if (tid == 0) {
-            // every compute thread has read its part of the k tile and staged its part of dk
-            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(umma::smem_addr(empty_k)) : "memory");
+            // every compute thread has staged its part of dk
             asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(umma::smem_addr(dk_ready)) : "memory");
         }
         {
