@@ -64,6 +64,7 @@ def test_golden_fixture_from_reference(golden_dir):
     (1, 2048, 2, 64, 64, 2, 15),      # K = 64, spare lambda levels
     (1, 1024, 4, 64, 128, 2, 11),     # two q/k groups with an even chunk count: group indexing of the TMA loads / reduce-adds
     (1, 16384, 2, 64, 128, 1, 15),    # 32 segments: five high levels
+    (1, 2048, 8, 64, 128, 2, 13),     # four heads per q/k group, four segments
 ])
 def test_forward_and_backward_match_oracle(B, T, H, P, N, G, L):
     q, k, v, g, l, do = rounded_inputs(B, T, H, P, N, G, L, seed=T + H)
