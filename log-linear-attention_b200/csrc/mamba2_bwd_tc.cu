@@ -1214,7 +1214,8 @@ __global__ void __launch_bounds__(tc::NTHREADS, 1) m2_bwd_revorder_tc_kernel(con
         }
         sMisc[ch * 128 + row] = wk_part;
         // the k tile has no reader left (its products completed with barB1): released here, not at the end of the pair, so that
-        // the next pair's k is in flight while dv, the dk staging and the state updates run
+        // the next pair's k is in flight while dv, the dk staging and the state updates run.  The store of wk_part above needs
+        // every k word this thread loaded, so the loads have returned before the arrive is issued.
         asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(umma::smem_addr(empty_k)) : "memory");
         STAMPR();   // 7 Y, decay, k row sums
         // ---- then what needs the whole batch: P (staging area of dk) and the scaled do are free, dv and the insertions are there
