@@ -1,7 +1,7 @@
 """Recipe for the reference-Triton arm of the benchmark: put an importable copy of the reference's
 `hattention` package under baseline/_ref/ (git-ignored; it is not part of this repository's source).
 
-    python baseline/make_ref.py /path/to/log-linear-attention      # default: /root/reference
+    python baseline/make_ref.py /path/to/log-linear-attention      # default: $LLATTN_REFERENCE_CHECKOUT
 
 What it does
   * copies the reference's `hattention/` directory verbatim into baseline/_ref/hattention/;
@@ -35,4 +35,4 @@ def main(src_root: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    main(sys.argv[1] if len(sys.argv) > 1 else os.environ.get("LLATTN_REFERENCE_CHECKOUT", "/root/reference"))

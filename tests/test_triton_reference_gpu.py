@@ -5,7 +5,7 @@ oracle on a head subset.  Skipped where the copy of the reference or its Triton 
 What is asserted: this repository's outputs and gradients are within the tolerance of the oracle, and at least
 as close to it as the Triton path is.  The Triton path's own distance to the oracle is recorded (one JSON line
 per tensor when LLATTN_PARITY_REPORT names a file), not asserted: on the library versions of this image it is
-far outside the tolerance in a pattern of eight rows out of every sixteen (see DESIGN.md), so "matches the
+far outside the tolerance in a pattern of eight rows out of every sixteen, so "matches the
 Triton path" cannot be a pass criterion here while "matches the reference's PyTorch definition" can."""
 import json
 import os
