@@ -73,6 +73,20 @@ def _check(q, k, v, b, g, l, head_first, level_base, htype, chunk_size):
     return B, T, H, G, K, V, L
 
 
+# Widest value head one kernel call takes.  The delta rule acts on every value column independently (the transition
+# I - beta k k^T and the decay involve q, k, beta, g only), so a wider head (the reference's own model has Dv = 384,
+# configs/flame/h_gated_deltanet_mid.json) is processed as slices of at most this many columns: outputs and dv are
+# concatenated, the gradients of the shared inputs are summed.
+V_SLICE = 128
+V_MAX = 384
+
+
+def _v_slices(V: int):
+    if V % 64 != 0 or V > V_MAX:
+        raise ValueError(f"unsupported GDN shape (V must be a multiple of 64 up to {V_MAX}, got {V})")
+    return [(s, min(s + V_SLICE, V)) for s in range(0, V, V_SLICE)]
+
+
 def chunkwise_fwd(
     q: torch.Tensor,
     k: torch.Tensor,
@@ -97,6 +111,14 @@ def chunkwise_fwd(
     B, T, H, G, K, V, L = _check(q, k, v, b, g, l, head_first, level_base, htype, chunk_size)
     if output_final_state and keep_workspace is not None:
         raise NotImplementedError("final states and a kept workspace in the same call")
+    if V > V_SLICE:
+        # slice by slice; nothing is kept for the backward (it recomputes, as the reference does)
+        parts = [chunkwise_fwd(q, k, v[..., s:e], b, g, l, head_first, level_base, htype, chunk_size, output_final_state)
+                 for s, e in _v_slices(V)]
+        g_cum, _, Aw, Au, _ = parts[0]
+        o = torch.cat([p_[1] for p_ in parts], dim=-1)
+        ht = torch.cat([p_[4] for p_ in parts], dim=3) if output_final_state else None
+        return g_cum, o, Aw, Au, ht
     lib = _lib.lib()
     with torch.cuda.device(q.device):
         if G != H:   # one q/k per head, as the reference expands them (chunkwise_hgdn.py:613-620)
@@ -111,7 +133,7 @@ def chunkwise_fwd(
         keep = keep_workspace is not None
         n = (lib.llattn_gdn_fwd_keep_workspace_bytes if keep else lib.llattn_gdn_fwd_workspace_bytes)(B, T, H, K, V, L)
         if n == 0:
-            raise ValueError("unsupported GDN shape (K must be 128, V 64 or 128, T <= 16384)")
+            raise ValueError("unsupported GDN shape (K must be 128, V a multiple of 64, T <= 16384)")
         ws = torch.empty(n, dtype=torch.uint8, device=q.device)
         if keep:
             keep_workspace.append(ws)
@@ -143,6 +165,20 @@ def chunkwise_bwd(q, k, v, b, g, l, Aw, Au, do, head_first, level_base, htype, c
     B, T, H, G_, K, V, L = _check(q, k, v, b, g, l, head_first, level_base, htype, chunk_size)
     if G_ != H:
         raise NotImplementedError("GDN backward expects one q/k per head")
+    if V > V_SLICE:
+        if fwd_workspace is not None:
+            raise ValueError("a kept forward workspace covers one value slice only")
+        dq = dk = db = dg = dl = None
+        dvs = []
+        for s, e in _v_slices(V):
+            pq, pk, pv, pb, pg, pl = chunkwise_bwd(q, k, v[..., s:e], b, g, l, Aw, Au, do[..., s:e], head_first, level_base,
+                                                   htype, chunk_size)
+            dvs.append(pv)
+            if dq is None:
+                dq, dk, db, dg, dl = pq, pk, pb, pg, pl
+            else:
+                dq += pq; dk += pk; db += pb; dg += pg; dl += pl
+        return dq, dk, torch.cat(dvs, dim=-1), db, dg, dl
     lib = _lib.lib()
     with torch.cuda.device(q.device):
         q_, k_, v_, b_, l_, do_, Aw_, Au_ = (x.to(torch.bfloat16).contiguous() for x in (q, k, v, b, l, do, Aw, Au))
@@ -155,7 +191,7 @@ def chunkwise_bwd(q, k, v, b, g, l, Aw, Au, do, head_first, level_base, htype, c
         dl = torch.empty(B, T, H, L, **f32)
         n = (lib.llattn_gdn_bwd_kept_workspace_bytes if kept else lib.llattn_gdn_bwd_workspace_bytes)(B, T, H, K, V, L)
         if n == 0:
-            raise ValueError("unsupported GDN shape (K must be 128, V 64 or 128, T <= 16384)")
+            raise ValueError("unsupported GDN shape (K must be 128, V a multiple of 64, T <= 16384)")
         ws = torch.empty(n, dtype=torch.uint8, device=q.device)
         head = (q_.data_ptr(), k_.data_ptr(), v_.data_ptr(), b_.data_ptr(), gc_.data_ptr(), l_.data_ptr(),
                 Aw_.data_ptr(), Au_.data_ptr(), do_.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),

@@ -104,3 +104,15 @@ def test_hstate_bookkeeping():
     assert float(a.states.abs().sum()) == 0.0 and sum(a.counts) == 0
     with pytest.raises(ValueError):
         a.replace(HState(2, HType.WEAK, HStruct.MAMBA2, (1, 2, 4, 4, 8), torch.float32, torch.device("cpu")))
+
+
+def test_gdn_value_heads_wider_than_one_kernel_call_are_sliced():
+    """chunkwise_hgdn processes a value head wider than 128 columns as slices of at most 128: the slices tile the
+    head exactly; widths that are not multiples of 64 or exceed 384 are refused."""
+    from hattention_b200 import chunkwise_hgdn as m
+    assert m._v_slices(192) == [(0, 128), (128, 192)]
+    assert m._v_slices(256) == [(0, 128), (128, 256)]
+    assert m._v_slices(384) == [(0, 128), (128, 256), (256, 384)]
+    for bad in (96, 200, 448):
+        with pytest.raises(ValueError):
+            m._v_slices(bad)

@@ -102,6 +102,24 @@ def test_gradients_match_oracle_multi_level():
         assert_close(got, w_, key)
 
 
+def test_wide_value_head_matches_oracle():
+    """Dv = 192 (the host side runs a 128-column and a 64-column slice; the delta rule treats value columns
+    independently): output and every gradient against the fp64 recurrence."""
+    B, T, H, Dk, Dv, L = 1, 256, 2, 128, 192, 9
+    q, k, v, b, g, l = orc.make_gdn_inputs(B, T, H, Dk, Dv, L, seed=192)
+    q, k, v, b, l = (x.bfloat16().float() for x in (q, k, v, b, l))
+    do = torch.randn(B, T, H, Dv, generator=torch.Generator().manual_seed(6)).bfloat16().float()
+    scale = Dk ** -0.5
+    o, grads = run_cuda_grads(q, k, v, b, g, l, do)
+    ins = [x.double().requires_grad_(True) for x in (q, k, v, b, g, l)]
+    qn, kn = orc.gdn_layer_inputs(ins[0], ins[1], scale)
+    want, _ = orc.recurrent(qn, kn, ins[2], ins[4], ins[5] / scale, b=ins[3])
+    wg = torch.autograd.grad((want * do.double()).sum(), ins)
+    assert_close(o, want, "o")
+    for got, w_, key in zip(grads, wg, ("dq", "dk", "dv", "db", "dg", "dl")):
+        assert_close(got, w_, key)
+
+
 @pytest.mark.parametrize("B,T,H,Dv,L", [(1, 1408, 2, 128, 12), (2, 1024, 1, 64, 11)])
 def test_backward_stages_match_whole_path_autograd(B, T, H, Dv, L):
     """Driver-level gradients (normalised q, k) from the CUDA backward, and from its level stage
