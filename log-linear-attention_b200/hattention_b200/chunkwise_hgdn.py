@@ -81,6 +81,15 @@ V_SLICE = 128
 V_MAX = 384
 
 
+# Key width of the kernels.  Narrower q / k are padded with zero features: the products q k^T, k k^T, the transition and the
+# level states' live rows are unchanged, the padded state rows stay zero, and the gradients of the padding are dropped.
+K_CALL = 128
+
+
+def _pad_k(x: torch.Tensor) -> torch.Tensor:
+    return torch.nn.functional.pad(x, (0, K_CALL - x.shape[-1]))
+
+
 def _v_slices(V: int):
     if V % 64 != 0 or V > V_MAX:
         raise ValueError(f"unsupported GDN shape (V must be a multiple of 64 up to {V_MAX}, got {V})")
@@ -119,6 +128,10 @@ def chunkwise_fwd(
         o = torch.cat([p_[1] for p_ in parts], dim=-1)
         ht = torch.cat([p_[4] for p_ in parts], dim=3) if output_final_state else None
         return g_cum, o, Aw, Au, ht
+    if K < K_CALL:
+        g_cum, o, Aw, Au, ht = chunkwise_fwd(_pad_k(q), _pad_k(k), v, b, g, l, head_first, level_base, htype, chunk_size,
+                                             output_final_state, keep_workspace=keep_workspace)
+        return g_cum, o, Aw, Au, (ht[:, :, :K].contiguous() if ht is not None else None)
     lib = _lib.lib()
     with torch.cuda.device(q.device):
         if G != H:   # one q/k per head, as the reference expands them (chunkwise_hgdn.py:613-620)
@@ -133,7 +146,7 @@ def chunkwise_fwd(
         keep = keep_workspace is not None
         n = (lib.llattn_gdn_fwd_keep_workspace_bytes if keep else lib.llattn_gdn_fwd_workspace_bytes)(B, T, H, K, V, L)
         if n == 0:
-            raise ValueError("unsupported GDN shape (K must be 128, V a multiple of 64, T <= 16384)")
+            raise ValueError("unsupported GDN shape (K at most 128, V a multiple of 64, T <= 16384)")
         ws = torch.empty(n, dtype=torch.uint8, device=q.device)
         if keep:
             keep_workspace.append(ws)
@@ -179,6 +192,10 @@ def chunkwise_bwd(q, k, v, b, g, l, Aw, Au, do, head_first, level_base, htype, c
             else:
                 dq += pq; dk += pk; db += pb; dg += pg; dl += pl
         return dq, dk, torch.cat(dvs, dim=-1), db, dg, dl
+    if K < K_CALL:
+        dq, dk, dv, db, dg, dl = chunkwise_bwd(_pad_k(q), _pad_k(k), v, b, g, l, Aw, Au, do, head_first, level_base, htype,
+                                               chunk_size, fwd_workspace=fwd_workspace, dv_bf16=dv_bf16)
+        return dq[..., :K].contiguous(), dk[..., :K].contiguous(), dv, db, dg, dl
     lib = _lib.lib()
     with torch.cuda.device(q.device):
         q_, k_, v_, b_, l_, do_, Aw_, Au_ = (x.to(torch.bfloat16).contiguous() for x in (q, k, v, b, l, do, Aw, Au))
@@ -191,7 +208,7 @@ def chunkwise_bwd(q, k, v, b, g, l, Aw, Au, do, head_first, level_base, htype, c
         dl = torch.empty(B, T, H, L, **f32)
         n = (lib.llattn_gdn_bwd_kept_workspace_bytes if kept else lib.llattn_gdn_bwd_workspace_bytes)(B, T, H, K, V, L)
         if n == 0:
-            raise ValueError("unsupported GDN shape (K must be 128, V a multiple of 64, T <= 16384)")
+            raise ValueError("unsupported GDN shape (K at most 128, V a multiple of 64, T <= 16384)")
         ws = torch.empty(n, dtype=torch.uint8, device=q.device)
         head = (q_.data_ptr(), k_.data_ptr(), v_.data_ptr(), b_.data_ptr(), gc_.data_ptr(), l_.data_ptr(),
                 Aw_.data_ptr(), Au_.data_ptr(), do_.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),

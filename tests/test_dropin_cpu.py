@@ -116,3 +116,7 @@ def test_gdn_value_heads_wider_than_one_kernel_call_are_sliced():
     for bad in (96, 200, 448):
         with pytest.raises(ValueError):
             m._v_slices(bad)
+    import torch
+    x = torch.ones(1, 2, 1, 64)
+    padded = m._pad_k(x)
+    assert padded.shape == (1, 2, 1, m.K_CALL) and padded[..., 64:].abs().sum() == 0 and torch.equal(padded[..., :64], x)

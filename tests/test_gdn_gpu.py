@@ -102,11 +102,13 @@ def test_gradients_match_oracle_multi_level():
         assert_close(got, w_, key)
 
 
-def test_wide_value_head_matches_oracle():
-    """Dv = 192 (the host side runs a 128-column and a 64-column slice; the delta rule treats value columns
-    independently): output and every gradient against the fp64 recurrence."""
-    B, T, H, Dk, Dv, L = 1, 256, 2, 128, 192, 9
-    q, k, v, b, g, l = orc.make_gdn_inputs(B, T, H, Dk, Dv, L, seed=192)
+@pytest.mark.parametrize("Dk,Dv", [(128, 192), (64, 128)])
+def test_wide_value_head_and_narrow_key_head_match_oracle(Dk, Dv):
+    """Dv = 192: the host side runs a 128-column and a 64-column slice (the delta rule treats value columns
+    independently).  Dk = 64: q and k are padded with zero features to the kernels' key width.  Output and every
+    gradient against the fp64 recurrence."""
+    B, T, H, L = 1, 256, 2, 9
+    q, k, v, b, g, l = orc.make_gdn_inputs(B, T, H, Dk, Dv, L, seed=Dv)
     q, k, v, b, l = (x.bfloat16().float() for x in (q, k, v, b, l))
     do = torch.randn(B, T, H, Dv, generator=torch.Generator().manual_seed(6)).bfloat16().float()
     scale = Dk ** -0.5
